@@ -1,0 +1,129 @@
+/* quadbit_b200 — C-ABI of the B200 (sm_100a) two-level NVFP4 library.
+ *
+ * Plain pointers and sizes only. Every pointer is a DEVICE pointer unless stated; the
+ * caller allocates every input, output and workspace. `stream` is a cudaStream_t passed
+ * as void* (0 = legacy default stream). Functions returning int return 0 on success, a
+ * cudaError_t (< 1000) or one of the QB_ERR_* codes below.
+ *
+ * Two groups of entry points:
+ *   1. the reference library's own symbols (vitali87/quadbit, cuda/sparse_fp4_lib.cu and
+ *      cuda/dense_nvfp4_fast_lib.cu), same names, argument order and tensor layouts, so
+ *      the reference's ctypes callers bind unchanged;
+ *   2. native `qb_*` entry points that take the tensor-core friendly layouts directly
+ *      (no per-call re-layout) and expose the packers that the reference runs in torch.
+ *
+ * Two shared objects are built from the same sources, as in the reference:
+ *   libquadbit_sparse_fp4.so   (reference: sparse_fp4.so)    quantize_act_nvfp4_2lvl is per-32
+ *   libquadbit_dense_nvfp4.so  (reference: dense_nvfp4.so)   quantize_act_nvfp4_2lvl is per-16
+ *
+ * Tensor layouts
+ *   reference ("ref") layouts, K = reduction length, ks = K/128:
+ *     Ac     [out][K/4]  u8   kept pairs of the 2:4 weight, low nibble = even k
+ *     Ab/Bb  [rows][K/2] u8   dense E2M1, low nibble = even k
+ *     meta   [ks][out][2] i32 group g of a 128-K step: word g/8, bits 4*(g%8): i0 | i1<<2
+ *     scale  [ks][rows][P] u8 UE4M3 codes, P = 4 (one per 32 logical K, sparse path) or
+ *                             P = 8 (one per 16 K, dense path)
+ *     gA/gB  [rows] f32       per-row global scale
+ *   native layouts (Kp = K rounded up to 256; a K tail must be zero filled):
+ *     scale atoms [ceil(rows/128)][Kp*P/512][512] u8, byte (r%32)*16 + ((r%128)/32)*4 + c
+ *                 for scale column 4*atom + c of row r  (the block-scaled MMA's "128x4" atom)
+ *     metadata    [out/128][Kp/256][128][16] u8: per row, the two 8-byte ref words of
+ *                 steps 2j and 2j+1
+ */
+#ifndef QUADBIT_B200_H
+#define QUADBIT_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QB_OK 0
+#define QB_ERR_ARG 1001          /* bad shape, null or misaligned pointer: nothing was launched */
+#define QB_ERR_TIMEOUT 1002      /* a bounded device-side wait expired (status = 100200 + site) */
+#define QB_ERR_UNSUPPORTED 1003
+#define QB_ERR_DRIVER 1004
+
+/* ------------------------------------------------------------------ reference symbols */
+
+/* cuda/sparse_fp4_lib.cu:1042 — single-level 2:4-sparse GEMM, C[out][tok] bf16; synchronises. */
+int sparse_fp4_mm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
+                  int out, int tok, int K);
+/* cuda/sparse_fp4_lib.cu:1110 — two-level: C[out][tok] = gA[out]*gB[tok]*sum; synchronises. */
+int sparse_fp4_mm_2lvl(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
+                       int out, int tok, int K, const void* gA, const void* gB);
+/* cuda/sparse_fp4_lib.cu:1117 — same, token-major output C[tok][out]; synchronises. */
+int sparse_fp4_mm_2lvl_t(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
+                         int out, int tok, int K, const void* gA, const void* gB);
+/* cuda/sparse_fp4_lib.cu:733 (sparse lib: per-32) / cuda/dense_nvfp4_fast_lib.cu:203 (`...b`, per-16):
+ * single-level activation quantiser, bf16 x[tok][K] -> Bbytes, scaleB (ref layout). */
+void quantize_act_nvfp4(const void* x, void* Bbytes, void* scaleB, int tok, int K);
+void quantize_act_nvfp4b(const void* x, void* Bbytes, void* scaleB, int tok, int K);
+/* cuda/sparse_fp4_lib.cu:774 (per-32) and cuda/dense_nvfp4_fast_lib.cu:338 (per-16, same name in the
+ * dense library): two-level activation quantiser, also writes gB[tok]. */
+void quantize_act_nvfp4_2lvl(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K);
+/* cuda/sparse_fp4_lib.cu:781 — stream variant. */
+void quantize_act_nvfp4_2lvl_s(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K, void* stream);
+/* cuda/sparse_fp4_lib.cu:1347 — split-K 2:4-sparse GEMM for decode; Cf = fp32 workspace [tok][out];
+ * output token-major C[tok][out]; synchronises. */
+int sparse_down_sk_2lvl(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta,
+                        void* Cout, void* Cf, int out, int tok, int K, const void* gA, const void* gB, int splits);
+/* cuda/sparse_fp4_lib.cu:1640 — segmented MoE GEMM over routed rows sorted by expert; eblk[rows/128]
+ * is the expert of each 128-row block; outT 0: C[Mpe][rows], 1: C[rows][Mpe]. Synchronises iff stream==0. */
+int sparse_moe_mm_2lvl(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
+                       int Mtot, int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk, int outT,
+                       void* stream);
+/* cuda/sparse_fp4_lib.cu:1661 — same with epilogue C[rows][Mpe] = (acc + bias[expert][f]) * sc_w[row]
+ * (bias bf16 [E][Hout], may be null). */
+int sparse_moe_mm_2lvl_bw(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
+                          int Mtot, int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk,
+                          const void* sc_w, const void* bias, int Hout, void* stream);
+/* cuda/sparse_fp4_lib.cu:1606 — counting-sort routing: src[poff[e]+slot] = i (poff int64, src pre-filled -1). */
+int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream);
+/* cuda/sparse_fp4_lib.cu:1615 — y[t][f] = sum_k dbuf[inverse[t][k]][f], bf16. */
+int moe_combine_topk(const void* dbuf, const void* inverse, void* y, int t, int H, int topk, int Mpe, void* stream);
+/* cuda/sparse_fp4_lib.cu:1028,1325,1570,1871 — one-time kernel attribute set-up (call before graph capture). */
+void qb_init_func_attrs(void);
+void qb_init_sk_attrs(void);
+void qb_init_moe_attrs(void);
+void qb_init_gusw_attrs(void);
+/* cuda/dense_nvfp4_fast_lib.cu:289 — dense two-level GEMM, per-16 scales SFA/SFB [K/128][rows][8]; synchronises. */
+int dense_nvfp4_mm(const void* A, const void* B, const void* SFA, const void* SFB, void* C, int out, int tok, int K,
+                   const void* gA, const void* gB);
+
+/* ------------------------------------------------------------------ native entry points */
+
+/* Activation quantiser. block = 32 (sparse path) or 16 (dense path). g == NULL selects the
+ * single-level recipe. sf_ref and/or sf_atoms receive the scales (either may be NULL). */
+int qb_quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
+                    void* stream);
+/* Offline 2:4 compressor (torch packer of harness/verify_sparse_2lvl.py:108-122 as one kernel).
+ * w_dtype 0 = fp32, 1 = bf16. Any output may be NULL. */
+int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_native, void* sf_ref,
+                     void* sf_atoms, void* gA, int out, int K, void* stream);
+/* Dense two-level packer (harness/dense_e2e.py:79-88 as one kernel). */
+int qb_pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out, int K,
+                  void* stream);
+/* ref -> native re-layouts. */
+int qb_relayout_sf(const void* sf_ref, void* sf_atoms, int rows, int K, int block, void* stream);
+int qb_relayout_meta(const void* meta_ref, void* meta_native, int out, int K, void* stream);
+/* Sizes in bytes of the native arrays. */
+long long qb_sf_atoms_bytes(int rows, int K, int block);
+long long qb_meta_native_bytes(int out, int K);
+/* The GEMM on native layouts. a_rows = rows of A (out, or experts*out for grouped mode with
+ * eblk != NULL); out_mode 0: bf16 C[out][tok], 1: bf16 C[tok][out], 2: fp32 raw accumulators
+ * C[out][tok] (globals ignored), 3: bf16 C[tok][out] = (acc*gA*gB + bias[expert][f]) * row_w[t].
+ * splits > 1 splits K across CTAs through the fp32 workspace Cf[tok][out]. bn = token tile
+ * (16..256, 0 = auto). Asynchronous on `stream`; qb_status() reports device-side errors. */
+int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
+            const void* gB, void* C, void* Cf, const void* eblk, const void* bias, const void* row_w, int a_rows, int out,
+            int tok, int K, int sparse, int out_mode, int splits, int bn, void* stream);
+/* Synchronise `stream`, return and clear the device status word (0 = no error). */
+int qb_status(void* stream);
+/* Error code of the last void-returning entry point on this thread. */
+int qb_last_error(void);
+const char* qb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

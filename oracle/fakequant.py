@@ -257,23 +257,29 @@ def linear_dense(x: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
 def sf_to_atoms(scale_ref: torch.Tensor) -> torch.Tensor:
     """Reference step-major scales [K/128, rows, P] (P = 4 per-32 or 8 per-16) ->
     the 128x4 scale-factor atoms the block-scaled tensor-core instruction reads:
-    [ceil(rows/128), K*P/512, 512] u8 with byte (r%32)*16 + (r//32)*4 + c inside an atom,
-    atom j covering 4 consecutive scale columns. Rows are zero padded to 128."""
+    [ceil(rows/128), Kp*P/512, 512] u8 with byte (r%32)*16 + (r//32)*4 + c inside an atom,
+    atom j covering 4 consecutive scale columns. Rows are zero padded to 128 and K to a
+    multiple of 256 (Kp)."""
     ks, rows, P = scale_ref.shape
     rp = (rows + 127) // 128 * 128
-    s = torch.zeros(ks, rp, P, dtype=torch.uint8)
-    s[:, :rows] = scale_ref
-    s = s.permute(1, 0, 2).reshape(rp, ks * P)                       # [rows, ncol]
-    s = s.view(rp // 128, 4, 32, ks * P // 4, 4)                     # [rb, r1, r0, atom, c]
-    return s.permute(0, 3, 2, 1, 4).contiguous().view(rp // 128, ks * P // 4, 512)
+    kp = (ks + 1) // 2 * 2
+    s = torch.zeros(kp, rp, P, dtype=torch.uint8)
+    s[:ks, :rows] = scale_ref
+    s = s.permute(1, 0, 2).reshape(rp, kp * P)                       # [rows, ncol]
+    s = s.view(rp // 128, 4, 32, kp * P // 4, 4)                     # [rb, r1, r0, atom, c]
+    return s.permute(0, 3, 2, 1, 4).contiguous().view(rp // 128, kp * P // 4, 512)
 
 
 def meta_to_native(meta_ref: torch.Tensor) -> torch.Tensor:
-    """Reference metadata [K/128, out, 2] i32 -> [out/128, K/256, 128, 16] u8: per 128-row
-    block and 256 logical K, 16 bytes per row (group g of a 128-K step at bits 4g)."""
+    """Reference metadata [K/128, out, 2] i32 -> [out/128, Kp/256, 128, 16] u8: per 128-row
+    block and 256 logical K, 16 bytes per row (group g of a 128-K step at bits 4g); K is
+    zero padded to a multiple of 256."""
     ks, out_f, _ = meta_ref.shape
-    m = meta_ref.permute(1, 0, 2).contiguous().view(torch.uint8).view(out_f, ks // 2, 16)
-    return m.view(out_f // 128, 128, ks // 2, 16).permute(0, 2, 1, 3).contiguous()
+    kp = (ks + 1) // 2 * 2
+    mp = torch.zeros(kp, out_f, 2, dtype=torch.int32)
+    mp[:ks] = meta_ref
+    m = mp.permute(1, 0, 2).contiguous().view(torch.uint8).view(out_f, kp // 2, 16)
+    return m.view(out_f // 128, 128, kp // 2, 16).permute(0, 2, 1, 3).contiguous()
 
 
 # ---------------------------------------------------------------- MoE

@@ -1,0 +1,74 @@
+"""ctypes binding of the two shared objects (the reference binds its .so the same way:
+harness/quadbit_linear.py:51-63, harness/qb_vllm_plugin/qb_sm120_plugin.py:1124-1153).
+
+There is no fallback: if the library cannot be built or loaded, import-time users get an
+exception; nothing in this package computes on the CPU."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from functools import lru_cache
+
+from . import build_so
+
+P, I = c_void_p, c_int
+
+_SIGS = {
+    # reference symbols
+    "sparse_fp4_mm": ([P] * 6 + [I] * 3, I),
+    "sparse_fp4_mm_2lvl": ([P] * 6 + [I] * 3 + [P] * 2, I),
+    "sparse_fp4_mm_2lvl_t": ([P] * 6 + [I] * 3 + [P] * 2, I),
+    "quantize_act_nvfp4": ([P] * 3 + [I] * 2, None),
+    "quantize_act_nvfp4b": ([P] * 3 + [I] * 2, None),
+    "quantize_act_nvfp4_2lvl": ([P] * 4 + [I] * 2, None),
+    "quantize_act_nvfp4_2lvl_s": ([P] * 4 + [I] * 2 + [P], None),
+    "sparse_down_sk_2lvl": ([P] * 7 + [I] * 3 + [P] * 2 + [I], I),
+    "sparse_moe_mm_2lvl": ([P] * 6 + [I] * 4 + [P] * 3 + [I, P], I),
+    "sparse_moe_mm_2lvl_bw": ([P] * 6 + [I] * 4 + [P] * 5 + [I, P], I),
+    "moe_route": ([P] * 4 + [I] * 2 + [P], I),
+    "moe_combine_topk": ([P] * 3 + [I] * 4 + [P], I),
+    "qb_init_func_attrs": ([], None),
+    "qb_init_sk_attrs": ([], None),
+    "qb_init_moe_attrs": ([], None),
+    "qb_init_gusw_attrs": ([], None),
+    "dense_nvfp4_mm": ([P] * 5 + [I] * 3 + [P] * 2, I),
+    # native
+    "qb_quantize_act": ([P] * 5 + [I] * 3 + [P], I),
+    "qb_compress_2to4": ([P, I] + [P] * 6 + [I] * 2 + [P], I),
+    "qb_pack_dense": ([P, I] + [P] * 4 + [I] * 2 + [P], I),
+    "qb_relayout_sf": ([P] * 2 + [I] * 3 + [P], I),
+    "qb_relayout_meta": ([P] * 2 + [I] * 2 + [P], I),
+    "qb_sf_atoms_bytes": ([I] * 3, c_longlong),
+    "qb_meta_native_bytes": ([I] * 2, c_longlong),
+    "qb_gemm": ([P] * 12 + [I] * 8 + [P], I),
+    "qb_status": ([P], I),
+    "qb_last_error": ([], I),
+    "qb_version": ([], ctypes.c_char_p),
+}
+
+EXPORTED = tuple(_SIGS)
+
+
+@lru_cache(maxsize=None)
+def load(flavour: str = "sparse_fp4") -> ctypes.CDLL:
+    """Build (if stale or missing) and load libquadbit_<flavour>.so with argtypes set."""
+    if flavour not in build_so.FLAVOURS:
+        raise ValueError(f"unknown library flavour {flavour!r}")
+    path = build_so.so_path(flavour)
+    if not path.exists():
+        build_so.build()
+    lib = ctypes.CDLL(str(path))
+    for name, (argtypes, restype) in _SIGS.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is missing
+        fn.argtypes = argtypes
+        fn.restype = restype
+    return lib
+
+
+class QuadbitError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise QuadbitError(f"{what} failed with code {rc}")

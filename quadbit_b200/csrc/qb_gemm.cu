@@ -1,0 +1,500 @@
+// Two-level NVFP4 GEMM for sm_100a, dense and 2:4-sparse, on the 5th-generation tensor
+// cores:  C[out,tok] = gA[out] * gB[tok] * sum_k (a * sfa) * (b * sfb)
+//
+// Replaces matmul_sp / run_sp_mm (cuda/sparse_fp4_lib.cu:30-221,1029-1041), dmatmul_nvf
+// (cuda/dense_nvfp4_fast_lib.cu:23-151), the split-K decode pair matmul_sp_sk + cvt_sp_2lvl_t
+// (cuda/sparse_fp4_lib.cu:1160-1344) and the segmented MoE GEMM matmul_sp_moe
+// (cuda/sparse_fp4_lib.cu:1362-1566), which are warp-level mma.sync / mma.sp kernels that
+// do not exist on this architecture.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      producer: TMA tiles of A (weights, 128 rows) and B (tokens, BN rows) with
+//               hardware swizzle, plus bulk copies of the scale-factor atoms and the 2:4
+//               metadata, into a multi-stage shared-memory ring (mbarrier full/empty).
+//   warp 1      MMA issuer: one lane copies scale factors / metadata smem -> TMEM
+//               (tcgen05.cp) and issues tcgen05.mma[.sp] kind::mxf4nvf4 block_scale with
+//               the accumulator in TMEM; tcgen05.commit releases smem stages and hands
+//               finished accumulators to the epilogue. Allocates / frees TMEM.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quadrant),
+//               multiply by the fp32 globals, convert to bf16 and store; with two
+//               accumulator stages (BN <= 128) this overlaps the next tile's main loop.
+// The weight is always the tensor-core A operand (M = 128 rows per CTA; the only operand
+// that can be 2:4-sparse), tokens are the N dimension (16..256), so thin-M decode is the
+// same kernel with a small token tile and K split across CTAs.
+//
+// A pipeline stage covers 256 logical K: dense A 128x128 B (SWIZZLE_128B, 4 MMAs of K=64),
+// sparse A 128x64 B of kept values (SWIZZLE_64B, 2 MMAs of K=128 logical), B BNx128 B
+// (SWIZZLE_128B). Scale factors: 4 per row per MMA (dense: one per 16 K, sparse: one per
+// 32 logical K), stored as 512-byte "128x4" atoms. Metadata: 16 B per row per stage.
+// Every wait is bounded (see mbar_wait); on expiry the CTA records QB_ERR_TIMEOUT, drains
+// and frees its TMEM.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "qb_common.cuh"
+#include "qb_internal.h"
+
+namespace qb {
+
+__device__ int g_status = 0;
+
+struct KParams {
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    const uint8_t* meta;
+    const float* gA;
+    const float* gB;
+    void* C;
+    float* Cf;
+    const int* eblk;
+    const __nv_bfloat16* bias;
+    const float* row_w;
+    int out_f, tok, K;
+    int num_m, num_n, splits, kblocks;   // kblocks = ceil(K/256)
+    int sfb_rowblocks;                   // ceil(tok/128)
+    int b_box_bytes;                     // bytes one B TMA box delivers (box rows * 128)
+    int out_mode;
+};
+
+template <bool SPARSE, int BN>
+struct Cfg {
+    static constexpr int BM = 128;
+    static constexpr int A_ROW = SPARSE ? 64 : 128;
+    static constexpr int A_BYTES = BM * A_ROW;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int B_ALLOC = B_BYTES < 1024 ? 1024 : B_BYTES;
+    static constexpr int MMAS = SPARSE ? 2 : 4;
+    static constexpr int B_KSTEP = SPARSE ? 64 : 32;   // bytes of a B row consumed per MMA
+    static constexpr int NB128 = (BN + 127) / 128;
+    static constexpr int SFA_BYTES = MMAS * 512;
+    static constexpr int SFB_BYTES = NB128 * MMAS * 512;
+    static constexpr int META_BYTES = SPARSE ? 2048 : 0;
+    static constexpr int STAGE_BYTES = A_BYTES + B_ALLOC + SFA_BYTES + SFB_BYTES + META_BYTES;
+    static constexpr int ACC_STAGES = BN <= 128 ? 2 : 1;
+    static constexpr int EPI_BYTES = 4 * 32 * 80;   // per-warp 32x32 bf16 transpose tile, 80-byte pitch
+    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 256;
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
+    // TMEM columns
+    static constexpr int SFA_COLS = MMAS * 4;
+    static constexpr int SFB_COLS = MMAS * 4 * NB128;
+    static constexpr int E_COLS = SPARSE ? 4 : 0;
+    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;
+    static constexpr int TM_SF0 = ((ACC_STAGES * BN + 3) / 4) * 4;
+    static constexpr int TM_USED = TM_SF0 + 2 * SF_SET;
+    static constexpr int TM_COLS = TM_USED <= 32 ? 32 : TM_USED <= 64 ? 64 : TM_USED <= 128 ? 128 : TM_USED <= 256 ? 256 : 512;
+    static_assert(TM_USED <= 512, "TMEM budget");
+    static_assert(STAGES >= 2, "smem budget");
+    static constexpr int CH = (BN % 32 == 0) ? 32 : 8;   // epilogue column chunk
+};
+
+enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4 };
+
+template <bool SPARSE, int BN>
+__global__ void __launch_bounds__(192, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
+    using C = Cfg<SPARSE, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ volatile int abort_flag;
+    __shared__ uint32_t tmem_base_slot;
+
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
+    const uint32_t bars = smem0 + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto accf_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
+    auto acce_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+    auto stageA = [&](int s) { return smem0 + (uint32_t)s * C::STAGE_BYTES; };
+    auto stageB = [&](int s) { return stageA(s) + C::A_BYTES; };
+    auto stageSFA = [&](int s) { return stageB(s) + C::B_ALLOC; };
+    auto stageSFB = [&](int s) { return stageSFA(s) + C::SFA_BYTES; };
+    auto stageMETA = [&](int s) { return stageSFB(s) + C::SFB_BYTES; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 4); }
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::TM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int tiles_mn = p.num_m * p.num_n;
+    const int total_tiles = tiles_mn * p.splits;
+    const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
+    const int atoms_per_rb = p.kblocks * C::MMAS;   // scale atoms per 128-row block along K
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
+            const int m = mn % p.num_m, n = mn / p.num_m;
+            const int n0 = n * BN;
+            const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m * 128;
+            const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
+            const int rb0 = n0 >> 7;
+            const int nsfb = min(C::NB128, p.sfb_rowblocks - rb0);
+            const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
+            for (int kb = kb0; kb < kb1; kb++) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
+                if (lane == 0) {
+                    mbar_expect_tx(full_bar(stage), tx);
+                    tma_load_2d(stageA(stage), &tmA, full_bar(stage), kb * C::A_ROW, a_row0);
+                    tma_load_2d(stageB(stage), &tmB, full_bar(stage), kb * 128, n0);
+                    bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
+                              C::SFA_BYTES, full_bar(stage));
+                    for (int i = 0; i < nsfb; i++)
+                        bulk_load(stageSFB(stage) + i * C::MMAS * 512,
+                                  p.sfb + ((size_t)(rb0 + i) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::MMAS * 512,
+                                  full_bar(stage));
+                    if (SPARSE)
+                        bulk_load(stageMETA(stage), p.meta + ((size_t)(a_row0 >> 7) * p.kblocks + kb) * 2048, 2048,
+                                  full_bar(stage));
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        const uint32_t idesc = make_idesc_nvf4(BN, SPARSE);
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        uint32_t kiter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
+            const int n = mn / p.num_m;
+            const int n0 = n * BN;
+            const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
+            const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
+            if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; kb++, kiter++) {
+                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sfset = tmem_base + C::TM_SF0 + (kiter & 1) * C::SF_SET;
+                    const uint32_t t_sfa = sfset, t_sfb = sfset + C::SFA_COLS, t_e = sfset + C::SFA_COLS + C::SFB_COLS;
+#pragma unroll
+                    for (int i = 0; i < C::MMAS; i++)
+                        tc_cp_32x128b_warpx4(t_sfa + 4 * i, make_smem_desc(stageSFA(stage) + i * 512, 128, 0, 0));
+#pragma unroll
+                    for (int nb = 0; nb < C::NB128; nb++)
+#pragma unroll
+                        for (int i = 0; i < C::MMAS; i++)
+                            tc_cp_32x128b_warpx4(t_sfb + i * (4 * C::NB128) + 4 * nb,
+                                                 make_smem_desc(stageSFB(stage) + (nb * C::MMAS + i) * 512, 128, 0, 0));
+                    if (SPARSE) tc_cp_128x128b(t_e, make_smem_desc(stageMETA(stage), 128, 0, 0));
+#pragma unroll
+                    for (int i = 0; i < C::MMAS; i++) {
+                        const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                        const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
+                        const uint32_t accum = (kb > kb0 || i > 0) ? 1u : 0u;
+                        if (SPARSE)
+                            tc_mma_nvf4_sp(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff,
+                                           t_e + 2 * i, accum);
+                        else
+                            tc_mma_nvf4(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff, accum);
+                    }
+                    tc_commit(empty_bar(stage));
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+            if (lane == 0) tc_commit(accf_bar(acc));
+            __syncwarp();
+            if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                     // TMEM lane quadrant this warp may read
+        const int r_in_tile = q * 32 + lane;        // accumulator row = output feature in tile
+        uint8_t* stg = smem_gen + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
+            const int m = mn % p.num_m, n = mn / p.num_m;
+            const int n0 = n * BN;
+            const int expert = p.eblk ? p.eblk[n] : 0;
+            const int o = m * 128 + r_in_tile;                    // output feature index
+            const int a_row = expert * p.out_f + o;               // row of A / gA
+            (void)z;
+            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            tc_fence_after();
+            const float ga = p.gA ? __ldg(p.gA + a_row) : 1.f;
+            const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += C::CH) {
+                uint32_t r[C::CH];
+                if constexpr (C::CH == 32) tc_ld_32x32(t_acc + c0, r); else tc_ld_32x8(t_acc + c0, r);
+                tc_wait_ld();
+                const int col_l = n0 + c0 + (lane % C::CH);
+                float gbl = 1.f;
+                if (p.gB && col_l < p.tok) gbl = __ldg(p.gB + col_l);
+                if (p.splits > 1) {
+                    // split-K: raw partial sums into the fp32 workspace Cf[tok][out]
+#pragma unroll
+                    for (int j = 0; j < C::CH; j++) {
+                        const int col = n0 + c0 + j;
+                        if (col < p.tok) atomicAdd(p.Cf + (size_t)col * p.out_f + o, __uint_as_float(r[j]));
+                    }
+                } else if (p.out_mode == 2) {
+                    float* Cp = reinterpret_cast<float*>(p.C) + (size_t)o * p.tok;
+#pragma unroll
+                    for (int j = 0; j < C::CH; j++) {
+                        const int col = n0 + c0 + j;
+                        if (col < p.tok) Cp[col] = __uint_as_float(r[j]);
+                    }
+                } else if (p.out_mode == 0) {
+                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)o * p.tok;
+                    uint32_t pk[C::CH / 2];
+#pragma unroll
+                    for (int j = 0; j < C::CH; j += 2) {
+                        float g0 = __shfl_sync(0xffffffffu, gbl, j), g1 = __shfl_sync(0xffffffffu, gbl, j + 1);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]) * (ga * g0), __uint_as_float(r[j + 1]) * (ga * g1));
+                        pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    const int col0 = n0 + c0;
+                    if (col0 + C::CH <= p.tok && (p.tok & 7) == 0) {
+#pragma unroll
+                        for (int v = 0; v < C::CH / 8; v++)
+                            *reinterpret_cast<uint4*>(Cp + col0 + 8 * v) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < C::CH; j++)
+                            if (col0 + j < p.tok) {
+                                uint32_t w = pk[j / 2];
+                                uint16_t hv = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffff);
+                                reinterpret_cast<uint16_t*>(Cp)[col0 + j] = hv;
+                            }
+                    }
+                } else {
+                    // token-major output C[tok][out]: transpose a 32(out) x CH(tok) block through
+                    // shared memory so that global stores are 16-byte vectors
+                    float bias_v = 0.f;
+                    if (p.out_mode == 3 && p.bias) bias_v = __bfloat162float(p.bias[(size_t)expert * p.out_f + o]);
+                    float rw = 1.f;
+                    if (p.out_mode == 3 && p.row_w && col_l < p.tok) rw = __ldg(p.row_w + col_l);
+#pragma unroll
+                    for (int j = 0; j < C::CH; j++) {
+                        float g0 = __shfl_sync(0xffffffffu, gbl, j);
+                        float v = __uint_as_float(r[j]) * (ga * g0);
+                        if (p.out_mode == 3) v = (v + bias_v) * __shfl_sync(0xffffffffu, rw, j);
+                        *reinterpret_cast<__nv_bfloat16*>(stg + j * 80 + lane * 2) = __float2bfloat16_rn(v);
+                    }
+                    __syncwarp();
+                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C);
+#pragma unroll
+                    for (int it = 0; it < C::CH / 8; it++) {
+                        const int idx = it * 32 + lane;
+                        const int trow = idx >> 2, chunk = idx & 3;
+                        const int col = n0 + c0 + trow;
+                        if (col < p.tok) {
+                            uint4 val = *reinterpret_cast<const uint4*>(stg + trow * 80 + chunk * 16);
+                            *reinterpret_cast<uint4*>(Cp + (size_t)col * p.out_f + m * 128 + q * 32 + chunk * 8) = val;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(acc));
+            if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // teardown: every role has left its loop (all waits are bounded)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TM_COLS);
+    }
+}
+
+// split-K finish: C = bf16(Cf[tok][out] * gA[out] * gB[tok]) in either output layout
+__global__ void splitk_finish_kernel(const float* __restrict__ Cf, const float* __restrict__ gA, const float* __restrict__ gB,
+                                     __nv_bfloat16* __restrict__ C, int out_f, int tok, int out_mode) {
+    size_t n = (size_t)out_f * tok;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        int o = (int)(i % out_f);
+        int t = (int)(i / out_f);
+        float v = Cf[i] * ((gA ? gA[o] : 1.f) * (gB ? gB[t] : 1.f));
+        if (out_mode == 0) C[(size_t)o * tok + t] = __float2bfloat16_rn(v);
+        else C[i] = __float2bfloat16_rn(v);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+static int make_map_u8(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
+                       uint32_t box_rows, CUtensorMapSwizzle sw) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return QB_ERR_DRIVER;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {box_bytes, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QB_OK : QB_ERR_DRIVER;
+}
+
+template <bool SPARSE, int BN>
+static int set_attr() {
+    return (int)cudaFuncSetAttribute(nvfp4_gemm_kernel<SPARSE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<SPARSE, BN>::SMEM_BYTES);
+}
+
+int gemm_init_attrs() {
+    static int rc = -1;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        int r = 0;
+#define QB_SA(BN) if (!r) r = set_attr<false, BN>(); if (!r) r = set_attr<true, BN>();
+        QB_SA(16) QB_SA(32) QB_SA(64) QB_SA(128) QB_SA(256)
+#undef QB_SA
+        rc = r;
+    });
+    return rc;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <bool SPARSE, int BN>
+static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
+    using C = Cfg<SPARSE, BN>;
+    CUtensorMap tmA, tmB;
+    int rc = make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
+                         SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint32_t b_rows = a.tok < BN ? (uint32_t)a.tok : (uint32_t)BN;   // box never taller than the tensor
+    kp.b_box_bytes = (int)(b_rows * 128);
+    rc = make_map_u8(&tmB, a.B, (uint64_t)a.K / 2, (uint64_t)a.tok, 128, b_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    int total = kp.num_m * kp.num_n * kp.splits;
+    int grid = total < sm_count() ? total : sm_count();
+    nvfp4_gemm_kernel<SPARSE, BN><<<grid, 192, C::SMEM_BYTES, st>>>(tmA, tmB, kp);
+    return (int)cudaGetLastError();
+}
+
+int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
+    if (a.out_f <= 0 || a.tok < 0 || a.K <= 0 || a.a_rows <= 0) return QB_ERR_ARG;
+    if (a.tok == 0) return QB_OK;
+    if (a.out_f % 128 || a.K % 128 || a.a_rows % 128) return QB_ERR_ARG;
+    if (!a.A || !a.B || !a.sfa || !a.sfb || !a.C || (a.sparse && !a.meta)) return QB_ERR_ARG;
+    if (((uintptr_t)a.A & 15) || ((uintptr_t)a.B & 15) || ((uintptr_t)a.sfa & 15) || ((uintptr_t)a.sfb & 15) ||
+        ((uintptr_t)a.meta & 15) || ((uintptr_t)a.C & 15))
+        return QB_ERR_ARG;
+    if (a.out_mode < 0 || a.out_mode > 3) return QB_ERR_ARG;
+    int splits = a.splits < 1 ? 1 : a.splits;
+    if (splits > 1 && (!a.Cf || a.eblk || a.out_mode > 1)) return QB_ERR_ARG;
+    if (a.eblk && a.a_rows % a.out_f) return QB_ERR_ARG;
+    int rc = gemm_init_attrs();
+    if (rc) return rc;
+
+    int bn = a.bn;
+    if (a.eblk) bn = 128;
+    if (bn == 0) bn = a.tok <= 16 ? 16 : a.tok <= 32 ? 32 : a.tok <= 64 ? 64 : 128;
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return QB_ERR_ARG;
+    if (bn < 32 && a.tok > bn) return QB_ERR_ARG;   // sub-32 token tiles cannot be offset inside a scale atom
+
+    KParams kp;
+    kp.sfa = (const uint8_t*)a.sfa; kp.sfb = (const uint8_t*)a.sfb; kp.meta = (const uint8_t*)a.meta;
+    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.Cf = a.Cf; kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
+    kp.out_f = a.out_f; kp.tok = a.tok; kp.K = a.K;
+    kp.num_m = a.out_f / 128;
+    kp.num_n = (a.tok + bn - 1) / bn;
+    kp.kblocks = (a.K + 255) / 256;
+    if (splits > kp.kblocks) splits = kp.kblocks;
+    // every split must own at least one K block
+    while (splits > 1 && ((kp.kblocks + splits - 1) / splits) * (splits - 1) >= kp.kblocks) splits--;
+    kp.splits = splits;
+    kp.sfb_rowblocks = (a.tok + 127) / 128;
+    kp.out_mode = a.out_mode;
+    if (splits > 1) {
+        rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
+        if (rc) return rc;
+    }
+#define QB_GO(BN) (a.sparse ? launch<true, BN>(a, kp, st) : launch<false, BN>(a, kp, st))
+    switch (bn) {
+        case 16: rc = QB_GO(16); break;
+        case 32: rc = QB_GO(32); break;
+        case 64: rc = QB_GO(64); break;
+        case 128: rc = QB_GO(128); break;
+        default: rc = QB_GO(256); break;
+    }
+#undef QB_GO
+    if (rc) return rc;
+    if (splits > 1) {
+        size_t n = (size_t)a.out_f * a.tok;
+        int blocks = (int)((n + 255) / 256);
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+        splitk_finish_kernel<<<blocks, 256, 0, st>>>(a.Cf, a.gA, a.gB, (__nv_bfloat16*)a.C, a.out_f, a.tok, a.out_mode);
+        rc = (int)cudaGetLastError();
+    }
+    return rc;
+}
+
+int read_status(cudaStream_t st) {
+    int rc = (int)cudaStreamSynchronize(st);
+    if (rc) return rc;
+    int h = 0;
+    rc = (int)cudaMemcpyFromSymbol(&h, g_status, sizeof(int));
+    if (rc) return rc;
+    if (h) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    }
+    return h;
+}
+
+}  // namespace qb

@@ -1,0 +1,54 @@
+// Internal (C++) interfaces between the translation units of the library. The public
+// C-ABI is declared in include/quadbit_b200.h and defined in qb_abi.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qb {
+
+// ---- qb_quant.cu
+int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
+                 cudaStream_t st);
+int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st);
+int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st);
+
+// ---- qb_compress.cu
+// w_dtype: 0 = fp32, 1 = bf16. Any output pointer may be null.
+int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_nat, void* sf_ref, void* sf_atoms,
+                  void* gA, int out_f, int K, cudaStream_t st);
+int pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out_f, int K,
+               cudaStream_t st);
+
+// ---- qb_gemm.cu
+struct GemmArgs {
+    const void* A;         // packed weights: dense [out][K/2], sparse [out][K/4]
+    const void* B;         // packed activations [tok][K/2]
+    const void* sfa;       // weight scale atoms
+    const void* sfb;       // activation scale atoms
+    const void* meta;      // native 2:4 metadata (sparse only)
+    const float* gA;       // per-row global scale of A (null = 1)
+    const float* gB;       // per-row global scale of B (null = 1)
+    void* C;               // output
+    float* Cf;             // fp32 split-K workspace [tok][out] (splits > 1)
+    const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
+    const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
+    const float* row_w;    // epilogue 3: fp32 per-routed-row weight [tok] (may be null)
+    int a_rows;            // rows of A (plain: out; grouped: experts * out_per_expert)
+    int out_f;             // output features per GEMM (plain: out; grouped: out_per_expert)
+    int tok;               // rows of B
+    int K;                 // logical reduction length
+    int sparse;            // 1 = 2:4-sparse A
+    int out_mode;          // 0: bf16 C[out][tok]  1: bf16 C[tok][out]  2: fp32 raw accumulators C[out][tok]
+                           // 3: bf16 C[tok][out] = (acc*gA*gB + bias)*row_w
+    int splits;            // K splits (>1 uses Cf + a convert pass)
+    int bn;                // token tile (0 = choose)
+};
+int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);
+int gemm_init_attrs();
+int read_status(cudaStream_t st);   // synchronises st and returns + clears the device status word
+
+// ---- qb_moe.cu
+int moe_route(const void* assign, void* poff, void* counter, void* src, int n, int e, cudaStream_t st);
+int moe_combine_topk(const void* dbuf, const void* inverse, void* y, int t, int H, int topk, int Mpe, cudaStream_t st);
+
+}  // namespace qb

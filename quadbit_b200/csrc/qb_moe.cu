@@ -1,0 +1,77 @@
+// MoE routing helpers around the grouped GEMM: counting-sort route and top-k combine.
+// Replace moe_route_scatter / moe_combine (cuda/sparse_fp4_lib.cu:1576-1620); same
+// argument meaning. Both are HBM-bound index/copy kernels.
+#include "qb_common.cuh"
+#include "qb_internal.h"
+
+namespace qb {
+
+// src[poff[e] + slot] = i for every routed slot i with expert e = assign[i] >= 0; the order
+// inside an expert segment is arbitrary. Padding entries of src keep the caller's -1.
+__global__ void moe_route_kernel(const int* __restrict__ assign, const long long* __restrict__ poff, int* counter,
+                                 int* __restrict__ src, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int e = assign[i];
+    if (e < 0) return;
+    int slot = atomicAdd(&counter[e], 1);
+    src[poff[e] + slot] = i;
+}
+
+// y[t, f] = sum_k dbuf[inverse[t, k], f] over the rows with inverse >= 0; 8 bf16 per thread.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ dbuf, const int* __restrict__ inverse,
+                                   __nv_bfloat16* __restrict__ y, int H, int topk, int Mpe) {
+    extern __shared__ int rows[];
+    const int token = blockIdx.x;
+    if ((int)threadIdx.x < topk) rows[threadIdx.x] = inverse[(size_t)token * topk + threadIdx.x];
+    __syncthreads();
+    const bool vec = (H % 8 == 0) && (Mpe % 8 == 0);
+    if (vec) {
+        for (int f = threadIdx.x * 8; f < H; f += blockDim.x * 8) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int k = 0; k < topk; k++) {
+                int r = rows[k];
+                if (r < 0) continue;
+                uint4 u = __ldg(reinterpret_cast<const uint4*>(dbuf + (size_t)r * Mpe + f));
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                for (int i = 0; i < 4; i++) { float2 v = __bfloat1622float2(h[i]); acc[2 * i] += v.x; acc[2 * i + 1] += v.y; }
+            }
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; i++) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            *reinterpret_cast<uint4*>(y + (size_t)token * H + f) = o;
+        }
+    } else {
+        for (int f = threadIdx.x; f < H; f += blockDim.x) {
+            float acc = 0.f;
+            for (int k = 0; k < topk; k++) {
+                int r = rows[k];
+                if (r >= 0) acc += __bfloat162float(dbuf[(size_t)r * Mpe + f]);
+            }
+            y[(size_t)token * H + f] = __float2bfloat16_rn(acc);
+        }
+    }
+}
+
+int moe_route(const void* assign, void* poff, void* counter, void* src, int n, int e, cudaStream_t st) {
+    if (n < 0 || e <= 0 || !poff || !counter) return QB_ERR_ARG;
+    int rc = (int)cudaMemsetAsync(counter, 0, (size_t)e * sizeof(int), st);
+    if (rc || n == 0) return rc;
+    if (!assign || !src) return QB_ERR_ARG;
+    moe_route_kernel<<<(n + 255) / 256, 256, 0, st>>>((const int*)assign, (const long long*)poff, (int*)counter, (int*)src, n);
+    return (int)cudaGetLastError();
+}
+
+int moe_combine_topk(const void* dbuf, const void* inverse, void* y, int t, int H, int topk, int Mpe, cudaStream_t st) {
+    if (t < 0 || H <= 0 || topk <= 0 || topk > 256 || Mpe < H) return QB_ERR_ARG;
+    if (t == 0) return QB_OK;
+    if (!dbuf || !inverse || !y) return QB_ERR_ARG;
+    if ((((uintptr_t)dbuf | (uintptr_t)y) & 15) != 0) return QB_ERR_ARG;
+    moe_combine_kernel<<<t, 256, (size_t)topk * sizeof(int), st>>>((const __nv_bfloat16*)dbuf, (const int*)inverse,
+                                                                  (__nv_bfloat16*)y, H, topk, Mpe);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace qb

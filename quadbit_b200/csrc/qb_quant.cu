@@ -1,0 +1,177 @@
+// Fused bf16 -> NVFP4 activation quantiser (two-level and single-level, per-32 for the
+// 2:4-sparse GEMM, per-16 for the dense GEMM) and the scale / metadata re-layout kernels.
+//
+// Replaces quant_act / quant_act_2lvl_k (cuda/sparse_fp4_lib.cu:704-786) and quant_act_nv /
+// quant_act_nv2_k (cuda/dense_nvfp4_fast_lib.cu:175-206,305-342). Arithmetic follows the
+// reference's torch fake-quant (act_2lvl_deq_p32, harness/verify_sparse_2lvl.py:100-106;
+// act_fp4_dequant, harness/recovery_worth.py:78-84) bit for bit: IEEE divisions, boundary
+// values to the lower E2M1 code, divisor clamped to 1e-30 for all-zero blocks.
+//
+// HBM-bound: one CTA per token row; every lane moves 16 bytes (8 bf16) per load so a warp
+// reads 512 contiguous bytes, the row stays in registers between the amax pass and the
+// quantise pass (each input byte is read once), the block amax is a 2- or 4-lane shuffle
+// reduction, each lane writes one packed 32-bit word (a warp writes 128 contiguous bytes)
+// and four scale bytes are merged into one 32-bit store.
+#include "qb_common.cuh"
+#include "qb_internal.h"
+
+namespace qb {
+
+template <int BLOCK, int NJ, bool TWO_LEVEL>
+__global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
+                                                          uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
+                                                          float* __restrict__ g_out, int tok, int K) {
+    constexpr int LPB = BLOCK / 8;   // lanes per scale block
+    constexpr int G = 4 * LPB;       // lanes per 4-scale word
+    constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
+    const int row = blockIdx.x;
+    const int nchunks = K >> 3;
+    const int lane = threadIdx.x & 31;
+    const uint4* xr = x + (size_t)row * nchunks;
+
+    uint4 v[NJ];
+    float cmax[NJ];
+    float tmax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (c < nchunks) v[j] = __ldg(xr + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __bfloat1622float2(h[i]);
+            m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+        cmax[j] = m;
+        tmax = fmaxf(tmax, m);
+    }
+
+    float gl = 1.f;
+    if (TWO_LEVEL) {
+        __shared__ float red[32];
+        tmax = warp_max(tmax);
+        if (lane == 0) red[threadIdx.x >> 5] = tmax;
+        __syncthreads();
+        float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+        r = warp_max(r);
+        gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
+        if (threadIdx.x == 0) g_out[row] = gl;
+    }
+
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        float bmax = cmax[j];
+#pragma unroll
+        for (int o = 1; o < LPB; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+        uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax, 6.f));
+        float sdeq = TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code);
+        float sg = fmaxf(sdeq, 1e-30f);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __bfloat1622float2(h[i]);
+            w |= (q_fp4_div(f.x, sg) | (q_fp4_div(f.y, sg) << 4)) << (8 * i);
+        }
+        // merge the 4 scale codes of 4 consecutive blocks into one word (all lanes shuffle)
+        uint32_t sw = 0;
+        int base = lane & ~(G - 1);
+#pragma unroll
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * LPB) << (8 * i);
+        if (c < nchunks) {
+            Bwords[(size_t)row * nchunks + c] = w;
+            if ((lane & (G - 1)) == 0) {
+                int jcol = c / LPB;   // scale column, multiple of 4 here
+                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
+                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(K) / BLOCK / 4)) = sw;
+            }
+        }
+    }
+}
+
+template <int BLOCK, bool TWO_LEVEL>
+static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
+                        cudaStream_t st) {
+    int nchunks = K / 8;
+    int threads = nchunks <= 2048 ? 256 : (nchunks <= 4096 ? 512 : 1024);
+    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
+    int nj = (nchunks + threads - 1) / threads;
+#define QB_LQ(NJ)                                                                                                 \
+    quant_act_kernel<BLOCK, NJ, TWO_LEVEL><<<tok, threads, 0, st>>>((const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
+                                                                    (uint8_t*)sf_atoms, g, tok, K)
+    if (nj <= 1) QB_LQ(1);
+    else if (nj <= 2) QB_LQ(2);
+    else if (nj <= 4) QB_LQ(4);
+    else if (nj <= 8) QB_LQ(8);
+    else return QB_ERR_UNSUPPORTED;
+#undef QB_LQ
+    return (int)cudaGetLastError();
+}
+
+int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
+                 cudaStream_t st) {
+    if (tok < 0 || K <= 0 || K % 128 != 0 || (block != 16 && block != 32)) return QB_ERR_ARG;
+    if (tok == 0) return QB_OK;
+    if (!x || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
+    if (((uintptr_t)x & 15) || ((uintptr_t)Bbytes & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3)) return QB_ERR_ARG;
+    if (K > 65536) return QB_ERR_UNSUPPORTED;
+    if (block == 32)
+        return g ? launch_quant<32, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st)
+                 : launch_quant<32, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st);
+    return g ? launch_quant<16, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st)
+             : launch_quant<16, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st);
+}
+
+// ---- re-layout: reference step-major scales [K/128][rows][P] -> 128x4 atoms
+__global__ void sf_ref_to_atoms_kernel(const uint32_t* __restrict__ ref, uint8_t* __restrict__ atoms, int rows, int ksteps,
+                                       int P, int atoms_per_rowblock) {
+    // one thread per 4-scale word: word index = (step*rows + r)*(P/4) + q
+    size_t n = (size_t)ksteps * rows * (P / 4);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        int q = (int)(i % (P / 4));
+        size_t t = i / (P / 4);
+        int r = (int)(t % rows);
+        int s = (int)(t / rows);
+        int jcol = s * P + q * 4;
+        *reinterpret_cast<uint32_t*>(atoms + sf_atom_offset(r, jcol, atoms_per_rowblock)) = ref[i];
+    }
+}
+
+int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st) {
+    if (rows < 0 || K <= 0 || K % 128 || (block != 16 && block != 32)) return QB_ERR_ARG;
+    if (rows == 0) return QB_OK;
+    if (!ref || !atoms || ((uintptr_t)ref & 3) || ((uintptr_t)atoms & 3)) return QB_ERR_ARG;
+    int P = 128 / block;
+    size_t n = (size_t)(K / 128) * rows * (P / 4);
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sf_ref_to_atoms_kernel<<<blocks, 256, 0, st>>>((const uint32_t*)ref, (uint8_t*)atoms, rows, K / 128, P, kpad256(K) / 128 * P / 4);
+    return (int)cudaGetLastError();
+}
+
+// ---- re-layout: reference metadata [K/128][out][2] i32 -> [out/128][K/256][128][16 B]
+__global__ void meta_ref_to_native_kernel(const uint2* __restrict__ ref, uint2* __restrict__ nat, int out_f, int ksteps,
+                                          int kblocks) {
+    size_t n = (size_t)ksteps * out_f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        int r = (int)(i % out_f);
+        int s = (int)(i / out_f);
+        size_t dst = (((size_t)(r >> 7) * kblocks + (s >> 1)) * 128 + (r & 127)) * 2 + (s & 1);
+        nat[dst] = ref[i];
+    }
+}
+
+int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st) {
+    if (out_f <= 0 || K <= 0 || K % 128 || out_f % 128) return QB_ERR_ARG;
+    if (!ref || !nat || ((uintptr_t)ref & 7) || ((uintptr_t)nat & 7)) return QB_ERR_ARG;
+    size_t n = (size_t)(K / 128) * out_f;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    meta_ref_to_native_kernel<<<blocks, 256, 0, st>>>((const uint2*)ref, (uint2*)nat, out_f, K / 128, kpad256(K) / 256);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace qb
