@@ -445,7 +445,9 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     if (a.eblk) bn = 128;
     if (bn == 0) bn = a.tok <= 16 ? 16 : a.tok <= 32 ? 32 : a.tok <= 64 ? 64 : 128;
     if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return QB_ERR_ARG;
-    if (bn < 32 && a.tok > bn) return QB_ERR_ARG;   // sub-32 token tiles cannot be offset inside a scale atom
+    // a token tile starts at scale-atom column (n0 % 128) / 32 and the MMA only accepts even
+    // scale-factor columns, so tiles narrower than 64 tokens must be the only tile
+    if (bn < 64 && a.tok > bn) return QB_ERR_ARG;
 
     KParams kp;
     kp.sfa = (const uint8_t*)a.sfa; kp.sfb = (const uint8_t*)a.sfb; kp.meta = (const uint8_t*)a.meta;

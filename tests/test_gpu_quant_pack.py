@@ -170,13 +170,15 @@ def test_relayout_kernels(lib):
         P = 128 // block
         sc = torch.randint(0, 127, (K // 128, rows, P), dtype=torch.uint8)
         atoms = torch.zeros(lib.qb_sf_atoms_bytes(rows, K, block), dtype=torch.uint8, device="cuda")
-        assert lib.qb_relayout_sf(sc.cuda().data_ptr(), atoms.data_ptr(), rows, K, block, S()) == 0
+        sc_d = sc.cuda()
+        assert lib.qb_relayout_sf(sc_d.data_ptr(), atoms.data_ptr(), rows, K, block, S()) == 0
         torch.cuda.synchronize()
         mask = fq.sf_to_atoms(torch.ones_like(sc)).view(-1).bool()
         assert torch.equal(atoms.cpu()[mask], fq.sf_to_atoms(sc).view(-1)[mask])
     meta = torch.randint(-2**31, 2**31 - 1, (8, 256, 2), dtype=torch.int32)
     nat = torch.zeros(lib.qb_meta_native_bytes(256, 1024), dtype=torch.uint8, device="cuda")
-    assert lib.qb_relayout_meta(meta.cuda().data_ptr(), nat.data_ptr(), 256, 1024, S()) == 0
+    meta_d = meta.cuda()
+    assert lib.qb_relayout_meta(meta_d.data_ptr(), nat.data_ptr(), 256, 1024, S()) == 0
     torch.cuda.synchronize()
     assert torch.equal(nat.cpu(), fq.meta_to_native(meta).view(-1))
 
