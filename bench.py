@@ -1,0 +1,397 @@
+"""Benchmark of the two-level NVFP4 GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" = the 2:4-sparse NVFP4 GEMM set at Llama-3-8B prefill shapes for M = 4096 tokens
+(fused QKV 6144x4096, o_proj 4096x4096, gate 14336x4096, up 14336x4096, down 4096x14336),
+operands already packed / quantised and resident in HBM. Metric: effective TFLOP/s
+(2*M*N*K per GEMM, pruned zeros count) over the whole set.
+
+N > 1 (one process per GPU under torchrun, NCCL): the set is sharded tensor-parallel, strong
+scaling: QKV / gate / up split the output features (no communication), o_proj / down split
+K and all-reduce their bf16 [tok,out] output over NCCL.
+
+Extra keys: "shapes" (per-shape sparse and dense figures, 8192^3, the activation quantiser
+and thin-M decode in GB/s), "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks".
+`--impl reference` times the CPU restatement of the reference's torch fake-quant path
+(oracle/) with all host threads on a bounded token sample of the same set.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOK = 4096
+SHAPES = [("qkv", 6144, 4096, "col"), ("o_proj", 4096, 4096, "row"), ("gate", 14336, 4096, "col"),
+          ("up", 14336, 4096, "col"), ("down", 4096, 14336, "row")]
+METRIC = "sparse NVFP4 GEMM effective TFLOP/s, Llama-3-8B prefill shapes (M=4096 tokens)"
+WORKLOAD = "configs[1]: 2:4-sparse two-level NVFP4 GEMM set qkv/o/gate/up/down at M=4096 tokens"
+
+
+def set_flops(tok: int) -> float:
+    return sum(2.0 * tok * n * k for _, n, k, _ in SHAPES)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_port_time(tok: int, shapes, reps: int):
+    """Reference torch CPU path restated in oracle/: per-token activation fake-quant + fp32
+    F.linear against the (offline) dequantised 2:4 weight. Returns best seconds of `reps`."""
+    import torch
+    import torch.nn.functional as F
+
+    from oracle import fakequant as fq
+    torch.set_num_threads(os.cpu_count())
+    ws = []
+    for i, (_, n, k, _) in enumerate(shapes):
+        g = torch.Generator().manual_seed(100 + i)
+        ws.append(fq.sparse_fp4_dequant_2lvl(torch.randn(n, k, generator=g) * 0.02))
+    xs = [torch.randn(tok, k, generator=torch.Generator().manual_seed(200 + i)) for i, (_, _, k, _) in enumerate(shapes)]
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for w, x in zip(ws, xs):
+            F.linear(fq.act_dequant_2lvl(x, 32), w)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cores = os.cpu_count()
+    # calibrate on one small step, then size the token sample so the run stays near 90 s
+    t_cal = cpu_port_time(64, SHAPES, 1)
+    per_tok = t_cal / 64
+    n_it = args.steps + args.warmup
+    tok = int(max(16, min(TOK, 90.0 / max(per_tok * n_it, 1e-9))))
+    tok = max(16, tok // 16 * 16)
+    import torch.nn.functional as F
+
+    from oracle import fakequant as fq
+    torch.set_num_threads(cores)
+    ws = [fq.sparse_fp4_dequant_2lvl(torch.randn(n, k, generator=torch.Generator().manual_seed(100 + i)) * 0.02)
+          for i, (_, n, k, _) in enumerate(SHAPES)]
+    xs = [torch.randn(tok, k, generator=torch.Generator().manual_seed(200 + i)) for i, (_, _, k, _) in enumerate(SHAPES)]
+
+    def step():
+        for w, x in zip(ws, xs):
+            F.linear(fq.act_dequant_2lvl(x, 32), w)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = set_flops(tok) * args.steps / dt / 1e12
+    sample = f"{tok} of {TOK} tokens per step (act fake-quant + fp32 GEMM, weights dequantised offline), {cores} torch threads"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp32 (CPU fake-quant of nvfp4)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import torch
+
+    import quadbit_b200 as qb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = qb.load("sparse_fp4")
+    hbm_gbs, bf16_burst, bf16_sust, peak_src = load_peaks()
+
+    def ev_time(fn, iters, warm=0):
+        for _ in range(warm):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    # ---- operands of the sharded set
+    layers = []
+    for i, (name, n, k, par) in enumerate(SHAPES):
+        if args.only and name != args.only:
+            continue
+        n_l, k_l = n, k
+        if world > 1:
+            if par == "col":
+                n_l = n // world
+            else:
+                k_l = k // world
+        g = torch.Generator(device="cpu").manual_seed(100 + i)
+        W = (torch.randn(n_l, k_l, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        dense = bool(args.only and args.dense)
+        lin = qb.DenseNVLinear(W, keep_ref_layout=False) if dense else qb.QuadbitLinear(W, keep_ref_layout=False)
+        x = torch.randn(TOK, k_l, generator=torch.Generator(device="cpu").manual_seed(200 + i)).to(torch.bfloat16).to(dev)
+        Bb, sB, gB = qb.quantize_act(lin.lib, x, lin.block, True)
+        out = torch.empty((TOK, n_l), dtype=torch.bfloat16, device=dev)
+        layers.append(dict(name=name, lin=lin, x=x, Bb=Bb, sB=sB, gB=gB, out=out, par=par, n=n, k=k))
+        del W
+    launches = [0]
+
+    def gemm_into(L, bn=256):
+        lin = L["lin"]
+        if isinstance(lin, qb.DenseNVLinear):
+            rc = lib.qb_gemm(lin.Ab.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(), 0, lin.gA.data_ptr(),
+                             L["gB"].data_ptr(), L["out"].data_ptr(), 0, 0, 0, 0, lin.out, lin.out, TOK, lin.inn, 0, 1, 1, bn,
+                             torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = lib.qb_gemm(lin.Ac.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(),
+                             lin.meta_native.data_ptr(), lin.gA.data_ptr(), L["gB"].data_ptr(), L["out"].data_ptr(), 0, 0, 0, 0,
+                             lin.out_f, lin.out_f, TOK, lin.in_f, 1, 1, 1, bn, torch.cuda.current_stream().cuda_stream)
+        if rc:
+            raise RuntimeError(f"qb_gemm rc {rc}")
+        launches[0] += 1
+
+    def step():
+        for L in layers:
+            gemm_into(L)
+            if world > 1 and L["par"] == "row":
+                dist.all_reduce(L["out"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches[0] = 0
+    with ClockSampler(local) as cs:
+        torch.cuda.synchronize()
+        t = ev_time(step, args.steps)
+    if world > 1:
+        tt = torch.tensor([t], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t = float(tt.item())
+        dist.barrier()
+    status = lib.qb_status(0)
+    if status:
+        raise RuntimeError(f"device status {status}")
+    value = sum(2.0 * TOK * L["n"] * L["k"] for L in layers) / t / 1e12
+    n_launch = launches[0]
+
+    line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens": TOK, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": "no explicit flush: one step touches ~0.45 GB of distinct operands and outputs (> 126 MB L2) "
+                             "before any buffer is reused",
+                       "token_tile": 256},
+            "gpu_launches": n_launch, "clocks": cs.summary()}
+
+    if args.only:
+        line["config"]["only"] = args.only + (" dense" if args.dense else " sparse")
+    if rank == 0 and world == 1 and not args.only:
+        # ---- per-shape detail (sparse and dense GEMM only), quantiser, decode
+        shapes = {}
+        for L in layers + [None]:
+            if L is None:
+                n, k, tokL, name = 8192, 8192, 8192, "sq8192"
+                Wd = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+                xd = torch.randn(tokL, k, device=dev).to(torch.bfloat16)
+                sp = qb.QuadbitLinear(Wd, keep_ref_layout=False)
+            else:
+                n, k, tokL, name = L["n"], L["k"], TOK, L["name"]
+                Wd = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+                xd = L["x"]
+                sp = L["lin"]
+            dn = qb.DenseNVLinear(Wd, keep_ref_layout=False)
+            del Wd
+            Bs, sBs, gBs = sp.pack_act(xd)
+            Bd, sBd, gBd = qb.quantize_act(dn.lib, xd, 16, True)
+            ts = ev_time(lambda: sp.run(Bs, sBs, tokL, gBs, out_t=True, bn=256), 10, 3)
+            td = ev_time(lambda: dn.run(Bd, sBd, tokL, gBd, out_t=True, bn=256), 10, 3)
+            tq = ev_time(lambda: sp.pack_act(xd), 10, 3)
+            fl = 2.0 * tokL * n * k
+            shapes[name] = {"sparse_tflops": fl / ts / 1e12, "dense_tflops": fl / td / 1e12, "sparse_us": ts * 1e6,
+                            "dense_us": td * 1e6, "act_quant_us": tq * 1e6,
+                            "act_quant_gbs": (tokL * k * 2 + tokL * k * (0.5 + 1 / 32) + 4 * tokL) / tq / 1e9}
+            del dn, Bs, sBs, gBs, Bd, sBd, gBd
+        line["shapes"] = shapes
+
+        # ---- thin-M decode: dense NVFP4, weight streaming, rotating over > L2 worth of weights, CUDA graph
+        dec = {}
+        for (n, k) in [(14336, 4096), (4096, 14336), (6144, 4096), (4096, 4096)]:
+            wbytes = n * k / 2 + n * k / 16 + 4 * n
+            nrot = max(2, int(300e6 // wbytes) + 1)
+            mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
+                    for _ in range(nrot)]
+            for m_tok in (1, 16, 64, 128, 256):
+                xdec = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
+                kb = (k + 255) // 256
+                splits = max(1, min(kb, (148 + n // 128 - 1) // (n // 128)))
+                stream = torch.cuda.Stream()
+                with torch.cuda.stream(stream):
+                    for m in mods[:2]:
+                        m.forward(xdec, splits=splits)
+                    stream.synchronize()
+                    gph = torch.cuda.CUDAGraph()
+                    try:
+                        with torch.cuda.graph(gph, stream=stream):
+                            for m in mods:
+                                m.forward(xdec, splits=splits)
+                        for _ in range(3):
+                            gph.replay()
+                        stream.synchronize()
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(stream)
+                        for _ in range(5):
+                            gph.replay()
+                        b.record(stream)
+                        stream.synchronize()
+                        tl = a.elapsed_time(b) / 5 / nrot * 1e-3
+                        mode = "cuda-graph"
+                    except Exception as e:  # capture refused: time eagerly, say so
+                        torch.cuda.synchronize()
+                        tl = ev_time(lambda: [m.forward(xdec, splits=splits) for m in mods], 3) / nrot
+                        mode = f"eager ({type(e).__name__})"
+                algo = wbytes + 2 * m_tok * k + 2 * m_tok * n
+                dec[f"N{n}_K{k}_M{m_tok}"] = {"us": tl * 1e6, "gbs": algo / tl / 1e9, "frac_of_measured_hbm": algo / tl / 1e9 / hbm_gbs,
+                                              "splits": splits, "timing": mode}
+            del mods
+        line["decode_dense"] = dec
+
+        # ---- end to end through the module API with host buffers (H2D + quantise + GEMM + D2H)
+        hx = [torch.randn(TOK, L["k"]).to(torch.bfloat16).pin_memory() for L in layers]
+        hy = [torch.empty((TOK, L["n"]), dtype=torch.bfloat16).pin_memory() for L in layers]
+
+        def e2e_step():
+            for L, xin, yout in zip(layers, hx, hy):
+                xd = xin.to(dev, non_blocking=True)
+                yout.copy_(L["lin"].forward(xd), non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        n_e2e = max(3, min(args.steps, 20))
+        t0 = time.perf_counter()
+        te = ev_time(e2e_step, n_e2e)
+        _ = time.perf_counter() - t0
+        line["e2e"] = {"value": set_flops(TOK) / te / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": int(sum(TOK * L["k"] * 2 for L in layers)),
+                       "d2h_bytes_per_step": int(sum(TOK * L["n"] * 2 for L in layers)),
+                       "what": "QuadbitLinear.forward on pinned host activations: H2D, quantise, GEMM, D2H of the bf16 result"}
+
+        # ---- roofline of the dominant kernel (the sparse GEMM), live numbers
+        sparse_peak = bf16_sust * 8.0
+        line["roofline"] = {"bound": "tensor", "achieved": value, "peak": sparse_peak, "unit": "TFLOP/s", "frac": value / sparse_peak,
+                            "traffic": None,
+                            "peak_basis": f"{peak_src} bf16_tflops_sustained {bf16_sust} x 8 (nominal 2:4-sparse FP4 : dense bf16 = 18 : 2.25 PF)",
+                            "frac_of_nominal_18PF": value / 18000.0,
+                            "kernel": "nvfp4_gemm_kernel<sparse, BN=256>", "launches_per_step": len(layers)}
+
+        # ---- CPU baseline (oracle port), bounded sample
+        tok_s = 256
+        tc = cpu_port_time(tok_s, SHAPES, 3)
+        line["cpu_baseline"] = {"value": set_flops(tok_s) / tc / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                                "sample": f"{tok_s} of {TOK} tokens of the same 5-GEMM set, act fake-quant + fp32 GEMM, best of 3"}
+    elif rank == 0:
+        line["e2e"] = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                       "what": "measured at N=1 only"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
+    ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
+                    "and skip the per-shape / decode / e2e / CPU extras")
+    ap.add_argument("--dense", action="store_true", help="with --only: the dense NVFP4 GEMM instead of the 2:4-sparse one")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
