@@ -42,6 +42,7 @@ extern "C" {
 #define QB_ERR_TIMEOUT 1002      /* a bounded device-side wait expired (status = 100200 + site) */
 #define QB_ERR_UNSUPPORTED 1003
 #define QB_ERR_DRIVER 1004
+#define QB_ERR_TOO_LARGE 1005    /* problem exceeds a fixed built-in capacity */
 
 /* ------------------------------------------------------------------ reference symbols */
 
@@ -117,6 +118,24 @@ long long qb_meta_native_bytes(int out, int K);
 int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
             const void* gB, void* C, void* Cf, const void* eblk, const void* bias, const void* row_w, int a_rows, int out,
             int tok, int K, int sparse, int out_mode, int splits, int bn, void* stream);
+/* Split-K GEMM without a caller workspace (no counterpart in the reference library, whose
+ * split-K entry sparse_down_sk_2lvl always takes the workspace Cf from the caller). Same
+ * operands and meaning as qb_gemm with splits > 1, out_mode 0 or 1, plain (not grouped) mode;
+ * the fp32 partial sums go to an 8 MiB array built into the library instead of a Cf argument.
+ * It exists for callers that cannot allocate: an engine whose memory pool already owns the
+ * whole GPU, code inside CUDA-graph capture, a hook that only receives inputs and outputs.
+ *   - out * tok must not exceed qb_gemm_splitk_static_max_elems() (2 Mi): otherwise
+ *     QB_ERR_TOO_LARGE is returned and nothing is launched.
+ *   - The first call on each device looks up the array's device address (a host-side query,
+ *     no allocation); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array. It is zeroed on `stream` at the start of
+ *     each call and holds the last call's partial sums afterwards; two calls whose kernels
+ *     overlap on the GPU (different streams, or replays of two graphs at once) race on it.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int qb_gemm_splitk_static(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native,
+                          const void* gA, const void* gB, void* C, int out, int tok, int K, int sparse, int out_mode,
+                          int splits, void* stream);
+long long qb_gemm_splitk_static_max_elems(void);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

@@ -41,6 +41,8 @@ _SIGS = {
     "qb_sf_atoms_bytes": ([I] * 3, c_longlong),
     "qb_meta_native_bytes": ([I] * 2, c_longlong),
     "qb_gemm": ([P] * 12 + [I] * 8 + [P], I),
+    "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
+    "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),
     "qb_version": ([], ctypes.c_char_p),
