@@ -64,6 +64,20 @@ void quantize_act_nvfp4b(const void* x, void* Bbytes, void* scaleB, int tok, int
 void quantize_act_nvfp4_2lvl(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K);
 /* cuda/sparse_fp4_lib.cu:781 — stream variant. */
 void quantize_act_nvfp4_2lvl_s(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K, void* stream);
+/* cuda/sparse_fp4_lib.cu:1133-1137 — fused SwiGLU MLP: quantise x[tp][H], gate/up GEMM (weights gu_*,
+ * gu_out = 2*Iw rows: gate features then up features), h = silu(g)*u quantised two-level per token,
+ * down GEMM -> Cout[tp][dn_out] bf16. Bb, sBg, gBg, Cgu, Hb, sH, gH are caller scratch with the
+ * reference's sizes (Cgu holds gu_out*tp bf16; here it is written token-major, sBg / sH are unused).
+ * Runs on `stream`, never synchronises. */
+int fused_mlp_2lvl(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
+                   const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* sBg, void* gBg,
+                   void* Cgu, void* Hb, void* sH, void* gH, void* Cout, int tp, int H, int Iw, int gu_out, int dn_out,
+                   void* stream);
+/* cuda/sparse_fp4_lib.cu:1892-1896 — same with a split-K down projection (Cf: fp32 workspace [tp][dn_out]). */
+int fused_mlp_2lvl_skdown(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
+                          const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* sBg,
+                          void* gBg, void* Cgu, void* Hb, void* sH, void* gH, void* Cout, void* Cf, int tp, int H, int Iw,
+                          int gu_out, int dn_out, int splits, void* stream);
 /* cuda/sparse_fp4_lib.cu:1347 — split-K 2:4-sparse GEMM for decode; Cf = fp32 workspace [tok][out];
  * output token-major C[tok][out]; synchronises. */
 int sparse_down_sk_2lvl(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta,
@@ -136,6 +150,17 @@ int qb_gemm_splitk_static(const void* A, const void* B, const void* sfa, const v
                           const void* gA, const void* gB, void* C, int out, int tok, int K, int sparse, int out_mode,
                           int splits, void* stream);
 long long qb_gemm_splitk_static_max_elems(void);
+/* SwiGLU + two-level per-32 quantiser over a token-major gate/up output Cgu[tok][2*I] bf16 (gate
+ * features first): Hb[tok][I/2], scales (ref layout and/or atoms), gH[tok]. One pass; replaces
+ * swiglu_amax + swiglu_finalize + swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894). */
+int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream);
+/* fused_mlp_2lvl on native layouts (weights from qb_compress_2to4; sfb_x / sfb_h are scale-atom
+ * scratch of qb_sf_atoms_bytes(tok, H | I, 32) bytes; Cf may be NULL or an fp32 [tok][dn_out]
+ * workspace for a split-K down projection). Four launches, no synchronisation, no allocation. */
+int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
+                 const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
+                 void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits,
+                 void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

@@ -201,11 +201,12 @@ def act_quant_2lvl(x: torch.Tensor, block: int):
     return Bbytes, scale, g.reshape(t).contiguous()
 
 
-def act_dequant_2lvl(x: torch.Tensor, block: int) -> torch.Tensor:
-    """Fake-quant of activations: act_2lvl_deq_p32 (block=32) / act_fp4_dequant (block=16)."""
+def act_dequant_2lvl(x: torch.Tensor, block: int, round_bf16: bool = True) -> torch.Tensor:
+    """Fake-quant of activations: act_2lvl_deq_p32 (block=32) / act_fp4_dequant (block=16).
+    round_bf16=False quantises fp32 values directly (the fused SwiGLU quantiser's input)."""
     lead = x.shape[:-1]
     i = x.shape[-1]
-    b = x.to(torch.bfloat16).float().reshape(-1, i)
+    b = (x.to(torch.bfloat16).float() if round_bf16 else x.float()).reshape(-1, i)
     g = (b.abs().amax(-1, keepdim=True) / GLOBAL_DIV).clamp_min(1e-30)
     bb = b.reshape(b.shape[0], i // block, block)
     sdeq = UE4M3[enc_ue4m3((bb.abs().amax(-1) / 6.0) / g)] * g
@@ -251,6 +252,17 @@ def linear_sparse(x: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
 
 def linear_dense(x: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
     return F.linear(act_dequant_2lvl(x.float(), 16), dense_fp4_dequant(W.float()))
+
+
+def fused_mlp_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """Reference arithmetic of the fused SwiGLU MLP (cuda/sparse_fp4_lib.cu:1133-1150 with
+    swiglu_amax / swiglu_quant_g :837-884): gate/up linear rounded to bf16, h = silu(g)*u in
+    fp32, two-level per-32 fake-quant of h, down linear. w_gate_up rows: gate then up."""
+    I = w_down.shape[1]
+    gu = linear_sparse(x, w_gate_up).to(torch.bfloat16).float()
+    g, u = gu[..., :I], gu[..., I:]
+    h = (g / (1.0 + torch.exp(-g))) * u
+    return F.linear(act_dequant_2lvl(h, 32, round_bf16=False), sparse_fp4_dequant_2lvl(w_down.float()))
 
 
 # ---------------------------------------------------------------- native (tcgen05) layouts

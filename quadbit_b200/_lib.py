@@ -41,6 +41,10 @@ _SIGS = {
     "qb_sf_atoms_bytes": ([I] * 3, c_longlong),
     "qb_meta_native_bytes": ([I] * 2, c_longlong),
     "qb_gemm": ([P] * 12 + [I] * 8 + [P], I),
+    "fused_mlp_2lvl": ([P] * 17 + [I] * 5 + [P], I),
+    "fused_mlp_2lvl_skdown": ([P] * 18 + [I] * 6 + [P], I),
+    "qb_swiglu_quant": ([P] * 5 + [I] * 2 + [P], I),
+    "qb_fused_mlp": ([P] * 18 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_status": ([P], I),

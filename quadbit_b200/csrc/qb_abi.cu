@@ -100,6 +100,66 @@ int finish_sync(int rc, cudaStream_t st) {
 
 }  // namespace
 
+// Fused SwiGLU MLP on native layouts: quantise x -> gate/up GEMM (token-major Cgu[tok][2I]) ->
+// SwiGLU + two-level quantise -> down GEMM (token-major Cout[tok][dn_out]). Four launches on
+// `stream`, no synchronisation, no allocation. Replaces fused_mlp_2lvl / fused_mlp_2lvl_skdown
+// (cuda/sparse_fp4_lib.cu:1133-1150,1892-1909: seven launches and a feature-major Cgu).
+static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA,
+                            const void* dn_A, const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x,
+                            void* gBx, void* Cgu, void* Hb, void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I,
+                            int gu_out, int dn_out, int splits, cudaStream_t st) {
+    if (tok < 0 || H <= 0 || I <= 0 || gu_out != 2 * I || dn_out <= 0) return QB_ERR_ARG;
+    if (tok == 0) return QB_OK;
+    int rc = 0;
+    if (H % 256) rc = (int)cudaMemsetAsync(sfb_x, 0, sf_atoms_bytes(tok, H, 32), st);
+    if (!rc && (I % 256)) rc = (int)cudaMemsetAsync(sfb_h, 0, sf_atoms_bytes(tok, I, 32), st);
+    if (rc) return rc;
+    rc = qb::quantize_act(x, Bb, nullptr, sfb_x, gBx, tok, H, 32, st);
+    if (rc) return rc;
+    qb::GemmArgs g{};
+    g.A = gu_A; g.B = Bb; g.sfa = gu_sfa; g.sfb = sfb_x; g.meta = gu_meta; g.gA = (const float*)gu_gA; g.gB = (const float*)gBx;
+    g.C = Cgu; g.a_rows = gu_out; g.out_f = gu_out; g.tok = tok; g.K = H; g.sparse = 1; g.out_mode = 1; g.splits = 1;
+    g.bn = tok > 128 ? 256 : 0;
+    rc = qb::gemm_nvfp4(g, st);
+    if (rc) return rc;
+    rc = qb::swiglu_quant(Cgu, Hb, nullptr, sfb_h, gH, tok, I, st);
+    if (rc) return rc;
+    qb::GemmArgs d{};
+    d.A = dn_A; d.B = Hb; d.sfa = dn_sfa; d.sfb = sfb_h; d.meta = dn_meta; d.gA = (const float*)dn_gA; d.gB = (const float*)gH;
+    d.C = Cout; d.Cf = (float*)Cf; d.a_rows = dn_out; d.out_f = dn_out; d.tok = tok; d.K = I; d.sparse = 1; d.out_mode = 1;
+    d.splits = (Cf && splits > 1) ? splits : 1;
+    d.bn = tok > 128 ? 256 : 0;
+    return qb::gemm_nvfp4(d, st);
+}
+
+// Reference-layout front end: weights' scales / metadata and the two activation scale arrays
+// live in the per-device scratch buffer for the duration of the call.
+static int fused_mlp_ref(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
+                         const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* gBg,
+                         void* Cgu, void* Hb, void* gH, void* Cout, void* Cf, int tp, int H, int Iw, int gu_out, int dn_out,
+                         int splits, cudaStream_t st) {
+    if (tp < 0 || H <= 0 || Iw <= 0 || H % 128 || Iw % 128 || gu_out % 128 || dn_out % 128 || gu_out != 2 * Iw) return QB_ERR_ARG;
+    if (tp == 0) return QB_OK;
+    size_t n1 = align256(sf_atoms_bytes(gu_out, H, 32)), n2 = align256(meta_native_bytes(gu_out, H));
+    size_t n3 = align256(sf_atoms_bytes(dn_out, Iw, 32)), n4 = align256(meta_native_bytes(dn_out, Iw));
+    size_t n5 = align256(sf_atoms_bytes(tp, H, 32)), n6 = align256(sf_atoms_bytes(tp, Iw, 32));
+    void* base = nullptr;
+    int rc = scratch_get(n1 + n2 + n3 + n4 + n5 + n6, &base);
+    if (rc) return rc;
+    uint8_t* p1 = (uint8_t*)base; uint8_t* p2 = p1 + n1; uint8_t* p3 = p2 + n2; uint8_t* p4 = p3 + n3;
+    uint8_t* p5 = p4 + n4; uint8_t* p6 = p5 + n5;
+    if ((H % 256) || (Iw % 256)) {
+        rc = (int)cudaMemsetAsync(base, 0, n1 + n2 + n3 + n4, st);
+        if (rc) return rc;
+    }
+    if ((rc = qb::relayout_sf(gu_scaleA, p1, gu_out, H, 32, st))) return rc;
+    if ((rc = qb::relayout_meta(gu_meta, p2, gu_out, H, st))) return rc;
+    if ((rc = qb::relayout_sf(dn_scaleA, p3, dn_out, Iw, 32, st))) return rc;
+    if ((rc = qb::relayout_meta(dn_meta, p4, dn_out, Iw, st))) return rc;
+    return fused_mlp_native(x, gu_Ac, p1, p2, gu_gA, dn_Ac, p3, p4, dn_gA, Bb, p5, gBg, Cgu, Hb, p6, gH, Cout, Cf, tp, H, Iw, gu_out,
+                            dn_out, splits, st);
+}
+
 extern "C" {
 
 const char* qb_version(void) { return "quadbit_b200 0.1 (sm_100a, tcgen05)"; }
@@ -143,6 +203,32 @@ int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, cons
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
 int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
+int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {
+    return qb::swiglu_quant(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, (cudaStream_t)stream);
+}
+int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
+                 const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
+                 void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits,
+                 void* stream) {
+    return fused_mlp_native(x, gu_A, gu_sfa, gu_meta, gu_gA, dn_A, dn_sfa, dn_meta, dn_gA, Bb, sfb_x, gBx, Cgu, Hb, sfb_h, gH, Cout,
+                            Cf, tok, H, I, gu_out, dn_out, splits, (cudaStream_t)stream);
+}
+int fused_mlp_2lvl(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
+                   const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* sBg, void* gBg,
+                   void* Cgu, void* Hb, void* sH, void* gH, void* Cout, int tp, int H, int Iw, int gu_out, int dn_out,
+                   void* stream) {
+    (void)sBg; (void)sH;   // the scale arrays are kept in the tensor-core layout internally
+    return fused_mlp_ref(x, gu_Ac, gu_scaleA, gu_meta, gu_gA, dn_Ac, dn_scaleA, dn_meta, dn_gA, Bb, gBg, Cgu, Hb, gH, Cout, nullptr,
+                         tp, H, Iw, gu_out, dn_out, 1, (cudaStream_t)stream);
+}
+int fused_mlp_2lvl_skdown(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
+                          const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* sBg,
+                          void* gBg, void* Cgu, void* Hb, void* sH, void* gH, void* Cout, void* Cf, int tp, int H, int Iw,
+                          int gu_out, int dn_out, int splits, void* stream) {
+    (void)sBg; (void)sH;
+    return fused_mlp_ref(x, gu_Ac, gu_scaleA, gu_meta, gu_gA, dn_Ac, dn_scaleA, dn_meta, dn_gA, Bb, gBg, Cgu, Hb, gH, Cout, Cf, tp, H,
+                         Iw, gu_out, dn_out, splits, (cudaStream_t)stream);
+}
 
 // ------------------------------------------------------------------ reference symbols
 int sparse_fp4_mm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, int out,

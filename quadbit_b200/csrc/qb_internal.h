@@ -9,6 +9,8 @@ namespace qb {
 // ---- qb_quant.cu
 int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
                  cudaStream_t st);
+// cgu: token-major gate/up GEMM output [tok][2*I] bf16 -> Hb[tok][I/2], per-32 scales, gH[tok]
+int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
 int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st);
 int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st);
 

@@ -92,6 +92,97 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     }
 }
 
+// SwiGLU + two-level per-32 quantiser for the fused MLP: reads the token-major gate/up GEMM
+// output Cgu[tok][2*I] (gate features 0..I-1, up features I..2I-1, bf16), forms
+// h = silu(g) * u in fp32 and quantises h exactly like an activation row (per-token global
+// gH = amax/2688, per-32 UE4M3 local scale, E2M1 codes) into Hb[tok][I/2] + scale atoms, the
+// B operand of the down projection. One pass, one CTA per token, h stays in registers.
+// Replaces swiglu_amax / swiglu_finalize / swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894),
+// which make three passes over a feature-major Cgu.
+template <int NJ>
+__global__ void __launch_bounds__(1024) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
+                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
+                                                             float* __restrict__ g_out, int tok, int I) {
+    const int row = blockIdx.x;
+    const int nchunks = I >> 3;
+    const int lane = threadIdx.x & 31;
+    const uint4* gr = cgu + (size_t)row * (nchunks * 2);
+    const uint4* ur = gr + nchunks;
+    float h[NJ][8];
+    float cmax[NJ];
+    float tmax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
+        if (c < nchunks) { gv = __ldg(gr + c); uv = __ldg(ur + c); }
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
+            float a = (g2.x / (1.f + __expf(-g2.x))) * u2.x;
+            float b = (g2.y / (1.f + __expf(-g2.y))) * u2.y;
+            h[j][2 * i] = a; h[j][2 * i + 1] = b;
+            m = fmaxf(m, fmaxf(fabsf(a), fabsf(b)));
+        }
+        cmax[j] = m;
+        tmax = fmaxf(tmax, m);
+    }
+    __shared__ float red[32];
+    tmax = warp_max(tmax);
+    if (lane == 0) red[threadIdx.x >> 5] = tmax;
+    __syncthreads();
+    float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+    r = warp_max(r);
+    const float gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
+    if (threadIdx.x == 0) g_out[row] = gl;
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        float bmax = cmax[j];
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+        uint32_t code = enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl));
+        float sg = fmaxf(__fmul_rn(dec_ue4m3(code), gl), 1e-30f);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) w |= (q_fp4_div(h[j][2 * i], sg) | (q_fp4_div(h[j][2 * i + 1], sg) << 4)) << (8 * i);
+        uint32_t sw = 0;
+        int base = lane & ~15;
+#pragma unroll
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * 4) << (8 * i);
+        if (c < nchunks) {
+            Hwords[(size_t)row * nchunks + c] = w;
+            if ((lane & 15) == 0) {
+                int jcol = c >> 2;
+                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol >> 2) * tok + row) * 4) = sw;
+                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(I) / 128)) = sw;
+            }
+        }
+    }
+}
+
+int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st) {
+    if (tok < 0 || I <= 0 || I % 128 != 0) return QB_ERR_ARG;
+    if (tok == 0) return QB_OK;
+    if (!cgu || !Hb || !gH || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
+    if (((uintptr_t)cgu & 15) || ((uintptr_t)Hb & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3)) return QB_ERR_ARG;
+    int nchunks = I / 8;
+    int threads = nchunks <= 2048 ? 256 : (nchunks <= 4096 ? 512 : 1024);
+    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
+    int nj = (nchunks + threads - 1) / threads;
+#define QB_LS(NJ) swiglu_quant_kernel<NJ><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I)
+    if (nj <= 1) QB_LS(1);
+    else if (nj <= 2) QB_LS(2);
+    else if (nj <= 4) QB_LS(4);
+    else if (nj <= 8) QB_LS(8);
+    else return QB_ERR_UNSUPPORTED;
+#undef QB_LS
+    return (int)cudaGetLastError();
+}
+
 template <int BLOCK, bool TWO_LEVEL>
 static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
                         cudaStream_t st) {

@@ -1,0 +1,171 @@
+"""Sparse-NVFP4 MoE helpers with the contract of the reference's `fused_moe.py` entry point and
+of the plugin's `_load_sparse_moe()` namespace (harness/fused_moe.py:372-435,
+harness/qb_vllm_plugin/qb_sm120_plugin.py:1124-1368): pack / stack / quant_act / seg_gemm /
+build_routing / route / seg_bw / combine, on the sm_100a library.
+
+Expert weights are packed on the GPU and stacked along the output-feature axis; routed rows are
+sorted by expert and every expert segment is padded to 128 rows, so one grouped GEMM launch
+covers all experts (`eblk[row_block] -> expert`)."""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+
+from ._lib import check, load
+from .linear import _ptr, _stream, quantize_act
+
+BN = 128   # routed-row block (reference: _BN, harness/fused_moe.py:352)
+
+
+def pad_w(W: torch.Tensor) -> torch.Tensor:
+    """Zero-pad [out,in] to out%256, in%128 (harness/fused_moe.py:444-448)."""
+    out_f, in_f = W.shape
+    outp, inp = (out_f + 255) // 256 * 256, (in_f + 127) // 128 * 128
+    if (outp, inp) == (out_f, in_f):
+        return W
+    Wp = W.new_zeros(outp, inp)
+    Wp[:out_f, :in_f] = W
+    return Wp
+
+
+def pack(lib, w: torch.Tensor):
+    """[out,in] -> native packed expert weight (Ac, meta_native, sfa atoms, gA)."""
+    w = w.contiguous()
+    if w.dtype not in (torch.float32, torch.bfloat16):
+        w = w.float()
+    out_f, in_f = w.shape
+    dev = w.device
+    z = torch.zeros if in_f % 256 else torch.empty
+    Ac = torch.empty((out_f, in_f // 4), dtype=torch.uint8, device=dev)
+    meta = z(lib.qb_meta_native_bytes(out_f, in_f), dtype=torch.uint8, device=dev)
+    sfa = z(lib.qb_sf_atoms_bytes(out_f, in_f, 32), dtype=torch.uint8, device=dev)
+    gA = torch.empty((out_f,), dtype=torch.float32, device=dev)
+    check(lib.qb_compress_2to4(w.data_ptr(), 1 if w.dtype == torch.bfloat16 else 0, Ac.data_ptr(), 0, meta.data_ptr(), 0,
+                               sfa.data_ptr(), gA.data_ptr(), out_f, in_f, _stream()), "qb_compress_2to4")
+    return Ac, meta, sfa, gA
+
+
+def stack(packs):
+    """Concatenate per-expert packs along the output-feature axis (every native array is
+    row-block major, so this is a plain cat; out%128 per expert)."""
+    return tuple(torch.cat([p[i] for p in packs], 0).contiguous() for i in range(4))
+
+
+def build_routing(assign: torch.Tensor, e: int):
+    """Sort routed slots by expert and pad segments to BN rows: (src, eblk, r_pad), as
+    harness/fused_moe.py:421-435 but without the per-expert host loop."""
+    dev = assign.device
+    order = torch.argsort(assign, stable=True)
+    counts = torch.bincount(assign, minlength=e)
+    padc = (counts + BN - 1) // BN * BN
+    poff = torch.cumsum(padc, 0) - padc
+    r_pad = int(padc.sum().item())
+    src = torch.full((r_pad,), -1, dtype=torch.long, device=dev)
+    coff = torch.cumsum(counts, 0) - counts
+    sorted_e = assign[order]
+    within = torch.arange(order.numel(), device=dev) - coff[sorted_e]
+    src[poff[sorted_e] + within] = order
+    eblk = torch.repeat_interleave(torch.arange(e, device=dev, dtype=torch.int32), (padc // BN))
+    return src, eblk.contiguous(), r_pad
+
+
+def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None):
+    """Quantise routed rows and run the grouped GEMM: [r_pad, mpe] bf16 (token-major);
+    with bias / row_w the epilogue computes (acc + bias[expert]) * row_w[row]."""
+    Ac, meta, sfa, gA = w
+    r = x_rows.shape[0]
+    Bb, sfb, gB = quantize_act(lib, x_rows, 32, True)
+    C = torch.empty((r, mpe), dtype=torch.bfloat16, device=x_rows.device)
+    mode = 3 if (bias is not None or row_w is not None) else 1
+    check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
+                      C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
+                      _stream()), "qb_gemm(grouped)")
+    return C
+
+
+def combine(lib, dbuf: torch.Tensor, inverse: torch.Tensor, t: int, H: int, topk: int):
+    y = torch.empty((t, H), dtype=torch.bfloat16, device=dbuf.device)
+    check(lib.moe_combine_topk(dbuf.data_ptr(), inverse.data_ptr(), y.data_ptr(), t, H, topk, dbuf.shape[1], _stream()),
+          "moe_combine_topk")
+    return y
+
+
+def swiglu(gate, up):
+    """gpt-oss clamped SwiGLU (harness/fused_moe.py:450-452)."""
+    gate = gate.clamp(max=7.0)
+    up = up.clamp(-7.0, 7.0)
+    return (gate * torch.sigmoid(1.702 * gate)) * (up + 1.0)
+
+
+class SparseMoE:
+    """Top-k routed SwiGLU MoE layer on 2:4-sparse NVFP4 experts: route -> gather -> grouped
+    gate/up GEMM -> SwiGLU -> grouped down GEMM with the routing weight in the epilogue ->
+    top-k combine. `experts` (optional) restricts the layer to a contiguous expert range
+    [e0, e1) for expert parallelism; slots of other experts are skipped."""
+
+    def __init__(self, w_gate_up: list[torch.Tensor], w_down: list[torch.Tensor], topk: int, act: str = "silu",
+                 expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None):
+        self.lib = lib = load("sparse_fp4")
+        self.E = len(w_gate_up)
+        self.topk, self.act = topk, act
+        self.H = w_gate_up[0].shape[1]
+        self.I = w_down[0].shape[1]
+        self.Hp = (self.H + 127) // 128 * 128
+        self.Ip = (self.I + 127) // 128 * 128
+        self.mpe_gu = (2 * self.Ip + 127) // 128 * 128
+        self.mpe_dn = (self.H + 127) // 128 * 128
+        gus, dns = [], []
+        for wg, wd in zip(w_gate_up, w_down):
+            g = wg.new_zeros(self.mpe_gu, self.Hp)                 # gate rows [0,I), up rows [Ip, Ip+I)
+            g[: self.I, : self.H] = wg[: self.I]
+            g[self.Ip: self.Ip + self.I, : self.H] = wg[self.I:]
+            d = wd.new_zeros(self.mpe_dn, self.Ip)
+            d[: self.H, : self.I] = wd
+            gus.append(pack(lib, g))
+            dns.append(pack(lib, d))
+        self.w_gu, self.w_dn = stack(gus), stack(dns)
+        self.e0, self.e1 = expert_range if expert_range else (0, self.E)
+        self.E_total = n_experts_total or self.E
+
+    def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+        """x [T,H] bf16, topk_idx [T,topk] global expert ids, topk_w [T,topk] -> [T,H] bf16
+        (the partial sum over this rank's experts under expert parallelism)."""
+        lib = self.lib
+        T = x.shape[0]
+        dev = x.device
+        assign_g = topk_idx.reshape(-1).long()
+        local = (assign_g >= self.e0) & (assign_g < self.e1)
+        slots = torch.nonzero(local).squeeze(1)                          # routed slots owned here
+        assign = (assign_g[slots] - self.e0)
+        src, eblk, r_pad = build_routing(assign, self.e1 - self.e0)
+        if r_pad == 0:
+            return torch.zeros((T, self.H), dtype=torch.bfloat16, device=dev)
+        valid = src >= 0
+        slot_of_row = torch.full((r_pad,), -1, dtype=torch.long, device=dev)
+        slot_of_row[valid] = slots[src[valid]]
+        rows = torch.zeros((r_pad, self.Hp), dtype=torch.bfloat16, device=dev)
+        rows[valid, : self.H] = x[slot_of_row[valid] // self.topk].to(torch.bfloat16)
+        gu = seg_gemm(lib, rows, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, mpe_gu]
+        g, u = gu[:, : self.Ip].float(), gu[:, self.Ip: 2 * self.Ip].float()
+        h = (swiglu(g, u) if self.act == "gptoss" else torch.nn.functional.silu(g) * u).to(torch.bfloat16)
+        h[~valid] = 0
+        row_w = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
+        row_w[valid] = topk_w.reshape(-1)[slot_of_row[valid]].float()
+        d = seg_gemm(lib, h.contiguous(), self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=row_w)   # [r_pad, mpe_dn]
+        inverse = torch.full((T * self.topk,), -1, dtype=torch.int32, device=dev)
+        inverse[slot_of_row[valid]] = torch.nonzero(valid).squeeze(1).int()
+        return combine(lib, d, inverse, T, self.H, self.topk)
+
+    __call__ = forward
+
+
+def load_sparse_moe():
+    """Namespace with the names of the plugin's `_load_sparse_moe()` (qb_sm120_plugin.py:1364-1368)."""
+    lib = load("sparse_fp4")
+    return SimpleNamespace(lib=lib, pack=lambda w: pack(lib, w), stack=stack,
+                           quant_act=lambda x, in_f=None: quantize_act(lib, x, 32, True),
+                           seg_gemm=lambda x, w, mpe, in_f, eblk: seg_gemm(lib, x, w, mpe, in_f, eblk),
+                           seg_bw=lambda x, w, mpe, in_f, eblk, row_w, bias=None: seg_gemm(lib, x, w, mpe, in_f, eblk, bias, row_w),
+                           build_routing=build_routing, combine=lambda d, inv, t, H, topk: combine(lib, d, inv, t, H, topk),
+                           pad_w=pad_w, swiglu=swiglu)

@@ -1,0 +1,176 @@
+"""GPU parity of the fused SwiGLU MLP and the MoE layer against the CPU oracle."""
+import pytest
+import torch
+
+from oracle import fakequant as fq
+
+pytestmark = pytest.mark.gpu
+
+
+def S():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def rel(y, ref):
+    y = y.float().cpu()
+    assert torch.isfinite(y).all()
+    return ((y - ref).norm() / ref.norm()).item()
+
+
+def test_swiglu_quant_kernel_against_oracle():
+    """One-pass SwiGLU + two-level quantiser: globals exact up to exp rounding, codes match the
+    oracle on all but boundary cases, dequantised values at the FP4 quantisation floor."""
+    import quadbit_b200 as qb
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(0)
+    for tok, I in ((5, 256), (37, 2944), (16, 14336)):
+        cgu = (torch.randn(tok, 2 * I) * 1.5).to(torch.bfloat16)
+        g, u = cgu[:, :I].float(), cgu[:, I:].float()
+        h = (g / (1.0 + torch.exp(-g))) * u
+        d = cgu.cuda()
+        Hb = torch.empty((tok, I // 2), dtype=torch.uint8, device="cuda")
+        sref = torch.empty((I // 128, tok, 4), dtype=torch.uint8, device="cuda")
+        atoms = torch.zeros(lib.qb_sf_atoms_bytes(tok, I, 32), dtype=torch.uint8, device="cuda")
+        gH = torch.empty(tok, device="cuda")
+        assert lib.qb_swiglu_quant(d.data_ptr(), Hb.data_ptr(), sref.data_ptr(), atoms.data_ptr(), gH.data_ptr(), tok, I, S()) == 0
+        assert lib.qb_status(S()) == 0
+        deq = fq.unpack_act(Hb.cpu(), sref.cpu(), gH.cpu(), 32)
+        want = fq.act_dequant_2lvl(h, 32, round_bf16=False)
+        torch.testing.assert_close(gH.cpu(), (h.abs().amax(-1) / 2688.0).clamp_min(1e-30), rtol=1e-5, atol=0)
+        assert (deq != want).float().mean().item() < 2e-3          # exp() rounding moves a few boundary cases
+        assert ((deq - h).norm() / h.norm()).item() < 0.12           # FP4 floor
+        mask = fq.sf_to_atoms(torch.ones(I // 128, tok, 4, dtype=torch.uint8)).view(-1).bool()
+        assert torch.equal(atoms.cpu()[mask], fq.sf_to_atoms(sref.cpu()).view(-1)[mask])
+
+
+@pytest.mark.parametrize("tok", [1, 48, 300])
+def test_fused_mlp_matches_oracle(tok):
+    import quadbit_b200 as qb
+    torch.manual_seed(tok)
+    H, I = 512, 768
+    wgu = torch.randn(2 * I, H) * 0.05
+    wdn = torch.randn(H, I) * 0.05
+    x = torch.randn(tok, H)
+    mlp = qb.FusedSparseMLP(wgu.cuda(), wdn.cuda())
+    y = mlp.forward(x.cuda().bfloat16())
+    assert mlp.lib.qb_status(0) == 0
+    ref = fq.fused_mlp_sparse(x, wgu, wdn)
+    assert y.shape == (tok, H) and rel(y, ref) < 0.02       # reference gate: RED < 0.02 (harness/verify_sparse_2lvl.py:211)
+    # unfused composition through the module API gives the same thing
+    gu = mlp.gu.forward(x.cuda().bfloat16()).float()
+    h = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    Bb, sfb, gB = qb.quantize_act(mlp.lib, h.to(torch.bfloat16), 32, True)
+    y2 = mlp.dn.run(Bb, sfb, tok, gB, out_t=True)
+    assert rel(y2, ref) < 0.05      # h takes an extra bf16 rounding on this path
+
+
+def test_fused_mlp_reference_named_entry_points():
+    """fused_mlp_2lvl / fused_mlp_2lvl_skdown with reference-layout weights and the reference's
+    scratch sizes (harness/quadbit_serve.py:427-450)."""
+    import quadbit_b200 as qb
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(3)
+    H, I, tp = 512, 768, 128
+    wgu = torch.randn(2 * I, H) * 0.05
+    wdn = torch.randn(H, I) * 0.05
+    x = torch.randn(tp, H)
+    gu = [t.cuda() for t in fq.pack_weight_sparse_2lvl(wgu)]
+    dn = [t.cuda() for t in fq.pack_weight_sparse_2lvl(wdn)]
+    dev = "cuda"
+    x2 = x.to(torch.bfloat16).cuda()
+    Bb = torch.empty((tp, H // 2), dtype=torch.uint8, device=dev)
+    sBg = torch.empty((H // 128, tp, 4), dtype=torch.uint8, device=dev)
+    gBg = torch.empty((tp,), dtype=torch.float32, device=dev)
+    Cgu = torch.empty((2 * I, tp), dtype=torch.bfloat16, device=dev)
+    Hb = torch.empty((tp, I // 2), dtype=torch.uint8, device=dev)
+    sH = torch.empty((I // 128, tp, 4), dtype=torch.uint8, device=dev)
+    gH = torch.empty((tp,), dtype=torch.float32, device=dev)
+    ref = fq.fused_mlp_sparse(x, wgu, wdn)
+    for sk in (False, True):
+        Cout = torch.full((tp, H), float("nan"), dtype=torch.bfloat16, device=dev)
+        args = [x2.data_ptr(), gu[0].data_ptr(), gu[2].data_ptr(), gu[1].data_ptr(), gu[3].data_ptr(), dn[0].data_ptr(),
+                dn[2].data_ptr(), dn[1].data_ptr(), dn[3].data_ptr(), Bb.data_ptr(), sBg.data_ptr(), gBg.data_ptr(), Cgu.data_ptr(),
+                Hb.data_ptr(), sH.data_ptr(), gH.data_ptr(), Cout.data_ptr()]
+        if sk:
+            Cf = torch.empty((H * tp,), dtype=torch.float32, device=dev)
+            rc = lib.fused_mlp_2lvl_skdown(*args, Cf.data_ptr(), tp, H, I, 2 * I, H, 3, S())
+        else:
+            rc = lib.fused_mlp_2lvl(*args, tp, H, I, 2 * I, H, S())
+        assert rc == 0 and lib.qb_status(S()) == 0
+        assert rel(Cout, ref) < 0.02
+
+
+def test_fused_mlp_custom_op_and_graph_capture():
+    """quadbit::fused_mlp custom op; the call is capturable in a CUDA graph and replays to the
+    same result (reference checks: harness/p4_capture.py, quadbit_serve.py graph_probe)."""
+    import quadbit_b200 as qb
+    torch.manual_seed(5)
+    H, I, tok = 256, 512, 64
+    mlp = qb.FusedSparseMLP((torch.randn(2 * I, H) * 0.05).cuda(), (torch.randn(H, I) * 0.05).cuda())
+    qb.register_fused_mlp_op([mlp])
+    x = torch.randn(tok, H, device="cuda").bfloat16()
+    y_eager = torch.ops.quadbit.fused_mlp(x, 0, H)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        mlp.forward(x)
+        stream.synchronize()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph, stream=stream):
+            y_graph = mlp.forward(x)
+        gph.replay()
+        stream.synchronize()
+    assert torch.equal(y_graph, y_eager)
+    assert mlp.lib.qb_status(0) == 0
+
+
+def moe_reference(x, wgu, wdn, idx, w, act_fn):
+    T, H = x.shape
+    y = torch.zeros(T, wdn[0].shape[0])
+    for e in range(len(wgu)):
+        sel = (idx == e)
+        toks = torch.nonzero(sel.any(1)).squeeze(1)
+        if toks.numel() == 0:
+            continue
+        I = wdn[e].shape[1]
+        gu = fq.linear_sparse(x[toks], wgu[e]).to(torch.bfloat16).float()
+        h = act_fn(gu[:, :I], gu[:, I:]).to(torch.bfloat16).float()
+        d = fq.linear_sparse(h, wdn[e])
+        wt = (w * sel)[toks].sum(1, keepdim=True)
+        y[toks] += (d * wt).to(torch.bfloat16).float()
+    return y
+
+
+@pytest.mark.parametrize("H,I,E,topk,T", [(256, 384, 8, 2, 200), (384, 256, 4, 4, 64)])
+def test_moe_layer_matches_per_expert_reference(H, I, E, topk, T):
+    """Routed MoE layer (route, gather, grouped GEMMs, weight epilogue, combine) against a
+    per-expert loop of the oracle (reference: harness/fused_moe.py:503-613 cosine gates)."""
+    import quadbit_b200 as qb
+    torch.manual_seed(E + T)
+    wgu = [torch.randn(2 * I, H) * 0.05 for _ in range(E)]
+    wdn = [torch.randn(H, I) * 0.05 for _ in range(E)]
+    x = torch.randn(T, H)
+    idx, w = fq.route_topk(torch.randn(T, E), topk)
+    moe = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk)
+    y = moe.forward(x.cuda().bfloat16(), idx.cuda(), w.cuda())
+    assert moe.lib.qb_status(0) == 0
+    ref = moe_reference(x, wgu, wdn, idx, w, lambda g, u: torch.nn.functional.silu(g) * u)
+    cos = torch.nn.functional.cosine_similarity(y.float().cpu().flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.999 and rel(y, ref) < 0.03
+    # expert-parallel shards sum to the full layer (reference: harness/p4_m3c.py, moe_dist.py:199-206)
+    parts = []
+    for r in range(2):
+        e0, e1 = r * E // 2, (r + 1) * E // 2
+        sh = qb.SparseMoE([t.cuda() for t in wgu[e0:e1]], [t.cuda() for t in wdn[e0:e1]], topk, expert_range=(e0, e1),
+                          n_experts_total=E)
+        parts.append(sh.forward(x.cuda().bfloat16(), idx.cuda(), w.cuda()).float())
+    assert rel(parts[0] + parts[1], ref) < 0.03
+
+
+def test_build_routing_matches_reference_helper():
+    import quadbit_b200.moe as moe
+    torch.manual_seed(1)
+    assign = torch.randint(0, 8, (300,))
+    src, eblk, r_pad = moe.build_routing(assign.cuda(), 8)
+    esrc, eeblk, erp = fq.build_routing(assign, 8)
+    assert r_pad == erp and torch.equal(src.cpu(), esrc) and torch.equal(eblk.cpu(), eeblk)
