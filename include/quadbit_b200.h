@@ -161,6 +161,13 @@ int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
                  void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits,
                  void* stream);
+/* Issue-only throughput probe of the block-scaled FP4 MMA (analogue of the reference's
+ * cuda/mma_peak.cu): every SM runs `kblocks` K blocks of 256 (dense: 4 MMAs of 128xbnx64,
+ * sparse: 2 of 128xbnx128) on operands resident in shared memory. mode bit 0 issues the MMAs,
+ * bit 1 the per-block scale-factor / metadata tcgen05.cp copies. cycles_per_sm: optional
+ * u64[SM count] of SM clock cycles; status_word: i32, non-zero if a bounded wait expired.
+ * bn = 128 or 256. Time it with events around the call. */
+int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, void* status_word, void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

@@ -47,6 +47,7 @@ _SIGS = {
     "qb_fused_mlp": ([P] * 18 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
+    "qb_mma_peak": ([I] * 4 + [P] * 3, I),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),
     "qb_version": ([], ctypes.c_char_p),

@@ -30,6 +30,7 @@
 // and frees its TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "qb_common.cuh"
@@ -38,6 +39,7 @@
 namespace qb {
 
 __device__ int g_status = 0;
+unsigned long long* g_prof_ptr = nullptr;   // experiment counters (QB_PROF)
 
 struct KParams {
     const uint8_t* sfa;
@@ -55,6 +57,8 @@ struct KParams {
     int sfb_rowblocks;                   // ceil(tok/128)
     int b_box_bytes;                     // bytes one B TMA box delivers (box rows * 128)
     int out_mode;
+    int dbg;                             // experiment switches (QB_DEBUG_SKIP), 0 in normal use
+    unsigned long long* prof;            // optional per-CTA cycle counters [grid][8]
 };
 
 template <bool SPARSE, int BN>
@@ -142,6 +146,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // ------------------------------------------------------------ producer
         int stage = 0;
         uint32_t phase = 0;
+        long long c_wait_empty = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
@@ -152,11 +157,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int nsfb = min(C::NB128, p.sfb_rowblocks - rb0);
             const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
             for (int kb = kb0; kb < kb1; kb++) {
+                long long ce = clock64();
                 if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
+                c_wait_empty += clock64() - ce;
                 if (lane == 0) {
-                    mbar_expect_tx(full_bar(stage), tx);
-                    tma_load_2d(stageA(stage), &tmA, full_bar(stage), kb * C::A_ROW, a_row0);
-                    tma_load_2d(stageB(stage), &tmB, full_bar(stage), kb * 128, n0);
+                    uint32_t txx = tx;
+                    const bool skipA = (p.dbg & 4) && kb >= kb0 + C::STAGES, skipB = (p.dbg & 2) && kb >= kb0 + C::STAGES;
+                    if (skipA) txx -= C::A_BYTES;
+                    if (skipB) txx -= (uint32_t)p.b_box_bytes;
+                    mbar_expect_tx(full_bar(stage), txx);
+                    if (!skipA) tma_load_2d(stageA(stage), &tmA, full_bar(stage), kb * C::A_ROW, a_row0);
+                    if (!skipB) tma_load_2d(stageB(stage), &tmB, full_bar(stage), kb * 128, n0);
                     bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
                               C::SFA_BYTES, full_bar(stage));
                     for (int i = 0; i < nsfb; i++)
@@ -171,6 +182,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (p.prof && lane == 0) p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_empty;
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         const uint32_t idesc = make_idesc_nvf4(BN, SPARSE);
@@ -179,22 +191,29 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int acc = 0;
         uint32_t acc_phase = 0;
         uint32_t kiter = 0;
+        long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = clock64();
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int n = mn / p.num_m;
             const int n0 = n * BN;
             const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
             const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
+            long long ca = clock64();
             if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+            c_wait_acc += clock64() - ca;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
             bool ok = true;
             for (int kb = kb0; kb < kb1; kb++, kiter++) {
+                long long cf = clock64();
                 if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
+                long long cg = clock64();
+                c_wait_full += cg - cf;
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t sfset = tmem_base + C::TM_SF0 + (kiter & 1) * C::SF_SET;
                     const uint32_t t_sfa = sfset, t_sfb = sfset + C::SFA_COLS, t_e = sfset + C::SFA_COLS + C::SFB_COLS;
+                    if (!((p.dbg & 1) && kiter >= 2)) {
 #pragma unroll
                     for (int i = 0; i < C::MMAS; i++)
                         tc_cp_32x128b_warpx4(t_sfa + 4 * i, make_smem_desc(stageSFA(stage) + i * 512, 128, 0, 0));
@@ -205,6 +224,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             tc_cp_32x128b_warpx4(t_sfb + i * (4 * C::NB128) + 4 * nb,
                                                  make_smem_desc(stageSFB(stage) + (nb * C::MMAS + i) * 512, 128, 0, 0));
                     if (SPARSE) tc_cp_128x128b(t_e, make_smem_desc(stageMETA(stage), 128, 0, 0));
+                    }
 #pragma unroll
                     for (int i = 0; i < C::MMAS; i++) {
                         const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
@@ -219,6 +239,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     tc_commit(empty_bar(stage));
                 }
                 __syncwarp();
+                c_issue += clock64() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
@@ -226,13 +247,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
+        if (p.prof && lane == 0) {
+            unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
+            o[0] = clock64() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
+        }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int q = warp & 3;                     // TMEM lane quadrant this warp may read
         const int r_in_tile = q * 32 + lane;        // accumulator row = output feature in tile
-        uint8_t* stg = smem_gen + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
+        const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
         int acc = 0;
         uint32_t acc_phase = 0;
+        long long c_wait_accf = 0, c_epi = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
@@ -241,18 +267,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int o = m * 128 + r_in_tile;                    // output feature index
             const int a_row = expert * p.out_f + o;               // row of A / gA
             (void)z;
-            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
-            tc_fence_after();
+            // per-tile constants first: their load latency hides behind the accumulator wait
             const float ga = p.gA ? __ldg(p.gA + a_row) : 1.f;
+            float gbv[BN / C::CH];
+#pragma unroll
+            for (int c = 0; c < BN / C::CH; c++) {
+                const int col = n0 + c * C::CH + (lane % C::CH);
+                gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
+            }
+            long long cw = clock64();
+            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            long long cx = clock64();
+            c_wait_accf += cx - cw;
+            tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
+#pragma unroll
             for (int c0 = 0; c0 < BN; c0 += C::CH) {
+                if (p.dbg & 8) break;
                 uint32_t r[C::CH];
                 if constexpr (C::CH == 32) tc_ld_32x32(t_acc + c0, r); else tc_ld_32x8(t_acc + c0, r);
                 tc_wait_ld();
                 const int col_l = n0 + c0 + (lane % C::CH);
-                float gbl = 1.f;
-                if (p.gB && col_l < p.tok) gbl = __ldg(p.gB + col_l);
+                const float gbl = gbv[c0 / C::CH];
                 if (p.splits > 1) {
                     // split-K: raw partial sums into the fp32 workspace Cf[tok][out]
 #pragma unroll
@@ -302,19 +338,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         float g0 = __shfl_sync(0xffffffffu, gbl, j);
                         float v = __uint_as_float(r[j]) * (ga * g0);
                         if (p.out_mode == 3) v = (v + bias_v) * __shfl_sync(0xffffffffu, rw, j);
-                        *reinterpret_cast<__nv_bfloat16*>(stg + j * 80 + lane * 2) = __float2bfloat16_rn(v);
+                        __nv_bfloat16 h = __float2bfloat16_rn(v);
+                        sts_u16(stg_s + j * 80 + lane * 2, *reinterpret_cast<uint16_t*>(&h));
                     }
                     __syncwarp();
-                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C);
+                    uint4 val[C::CH / 8];
+#pragma unroll
+                    for (int it = 0; it < C::CH / 8; it++) val[it] = lds_v4(stg_s + ((it * 32 + lane) >> 2) * 80 + (lane & 3) * 16);
+                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + m * 128 + q * 32 + (lane & 3) * 8;
 #pragma unroll
                     for (int it = 0; it < C::CH / 8; it++) {
-                        const int idx = it * 32 + lane;
-                        const int trow = idx >> 2, chunk = idx & 3;
-                        const int col = n0 + c0 + trow;
-                        if (col < p.tok) {
-                            uint4 val = *reinterpret_cast<const uint4*>(stg + trow * 80 + chunk * 16);
-                            *reinterpret_cast<uint4*>(Cp + (size_t)col * p.out_f + m * 128 + q * 32 + chunk * 8) = val;
-                        }
+                        const int col = n0 + c0 + ((it * 32 + lane) >> 2);
+                        if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val[it]);
                     }
                     __syncwarp();
                 }
@@ -322,8 +357,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(acc));
+            c_epi += clock64() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
+        if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
     }
 
     // teardown: every role has left its loop (all waits are bounded)
@@ -332,6 +369,385 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TM_COLS);
+    }
+}
+
+
+// ------------------------------------------------------------------ CTA-pair kernel (prefill)
+// The prefill kernel: a cluster of two CTAs issues tcgen05.mma.cta_group::2 with M = 256,
+// N = 256. CTA r of the pair owns weight rows [256*m2 + 128*r, +128) and loads only token rows
+// [n0 + 128*r, +128) of B (the pair shares B through the MMA), which makes a stage 29 KB
+// (sparse) / 38 KB (dense) per CTA and leaves room for 7 / 5 stages: measured on the GPU the
+// single-CTA kernel cannot keep enough bytes in flight to cover the ~1.6 us refill round trip
+// at the MMA rate. 320 threads per CTA:
+//   warp 0     producer: plain TMA tile loads (no multicast) of this CTA's A rows, B rows,
+//              scale-factor atoms and metadata, completing on this CTA's full barrier.
+//   warps 6-9  scale-factor warps: copy scale factors / metadata of the landed stage from
+//              shared memory into the stage's own TMEM slot with tcgen05.st (each warp its lane
+//              quadrant) and tell the leader. Measured: a tcgen05.cp costs ~50 cycles of the
+//              MMA pipe and 7-12 of them per K block cap the pipe at 57 % (dense) / 60 %
+//              (sparse) of its MMA-only rate; stores from registers run beside the MMAs.
+//   warp 1     MMA issuer (even CTA only): waits for both CTAs' scale-factor warps, issues the
+//              MMAs for the pair, releases the stage in both CTAs and publishes the accumulator
+//              with multicast commits.
+//   warps 2-5  epilogue: each CTA drains its own 128 x 256 accumulator half (loads of the next
+//              32 columns overlap the conversion of the current ones) and frees it as soon as
+//              the last column is in registers.
+// Requires out % 256 == 0 and tok >= 128.
+template <bool SPARSE>
+struct Cfg2 {
+    static constexpr int BN = 256;
+    static constexpr int THREADS = 320;
+    static constexpr int A_ROW = SPARSE ? 64 : 128;
+    static constexpr int A_BYTES = 128 * A_ROW;
+    static constexpr int B_BYTES = 128 * 128;             // this CTA's half of the token tile
+    static constexpr int MMAS = SPARSE ? 2 : 4;
+    static constexpr int B_KSTEP = SPARSE ? 64 : 32;
+    static constexpr int SFA_BYTES = MMAS * 512;
+    static constexpr int SFB_BYTES = 2 * MMAS * 512;      // all 256 token rows, in both CTAs
+    static constexpr int META_BYTES = SPARSE ? 2048 : 0;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + META_BYTES;
+    static constexpr int EPI_BYTES = 4 * 32 * 80;
+    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 512;
+    static constexpr int SFA_COLS = MMAS * 4;
+    static constexpr int SFB_COLS = MMAS * 8;
+    static constexpr int E_COLS = SPARSE ? 4 : 0;
+    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // one TMEM slot per smem stage
+    static constexpr int STAGES_SMEM = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES_TMEM = 256 / SF_SET;
+    static constexpr int STAGES_MIN = STAGES_SMEM < STAGES_TMEM ? STAGES_SMEM : STAGES_TMEM;
+    static constexpr int STAGES = STAGES_MIN > 8 ? 8 : STAGES_MIN;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 512;
+    static constexpr int TM_SF0 = 256;
+    static constexpr int TM_COLS = 512;
+    static_assert(TM_SF0 + STAGES * SF_SET <= 512, "TMEM budget");
+    static_assert(STAGES >= 3, "smem budget");
+};
+
+struct KParams2 {
+    const float* gA;
+    const float* gB;
+    void* C;
+    int out_f, tok;
+    int num_m2, num_n, kblocks;
+    int out_mode;
+    int dbg;
+    unsigned long long* prof;
+};
+
+enum { SITE_SF = 5 };
+
+template <bool SPARSE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
+    using C = Cfg2<SPARSE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ volatile int abort_flag;
+    __shared__ uint32_t tmem_base_slot;
+
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
+    const uint32_t bars = smem0 + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto sfr_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + s); };
+    const uint32_t accf_bar = bars + 8u * (3 * C::STAGES);
+    const uint32_t acce_bar = bars + 8u * (3 * C::STAGES + 1);
+    auto stageA = [&](int s) { return smem0 + (uint32_t)s * C::STAGE_BYTES; };
+    auto stageB = [&](int s) { return stageA(s) + C::A_BYTES; };
+    auto stageSFA = [&](int s) { return stageB(s) + C::B_BYTES; };
+    auto stageSFB = [&](int s) { return stageSFA(s) + C::SFA_BYTES; };
+    auto stageMETA = [&](int s) { return stageSFB(s) + C::SFB_BYTES; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+            mbar_init(sfr_bar(s), 8);             // 4 scale-factor warps of each CTA arrive on the leader's
+        }
+        mbar_init(accf_bar, 1);
+        mbar_init(acce_bar, 8);                   // 4 epilogue warps of each CTA arrive on the leader's
+        fence_barrier_init();
+        tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
+        if (SPARSE) tma_prefetch_desc(&tmMETA);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&tmem_base_slot), C::TM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int total_tiles = p.num_m2 * p.num_n;
+    const int atoms_per_rb = p.kblocks * C::MMAS;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int a_row0 = m2 * 256 + (int)rank * 128;
+            const int n0 = n * 256;
+            const int rb_a = a_row0 >> 7, rb_b = n0 >> 7;
+            for (int kb = 0; kb < p.kblocks; kb++) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
+                if (lane == 0) {
+                    const uint32_t fb = full_bar(stage);
+                    mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES);
+                    tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                    tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * 128);
+                    tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
+                    tma_load_2d(stageSFB(stage), &tmSFB, fb, 0, rb_b * atoms_per_rb + kb * C::MMAS);
+                    tma_load_2d(stageSFB(stage) + C::MMAS * 512, &tmSFB, fb, 0, (rb_b + 1) * atoms_per_rb + kb * C::MMAS);
+                    if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0) {
+            const uint32_t idesc = make_idesc_nvf4(256, SPARSE, 256);
+            int stage = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = clock64();
+            for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+                long long ca = clock64();
+                if (!mbar_wait(acce_bar, acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+                c_wait_acc += clock64() - ca;
+                tc_fence_after();
+                bool ok = true;
+                for (int kb = 0; kb < p.kblocks; kb++) {
+                    long long cf = clock64();
+                    if (!mbar_wait(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
+                    long long cg = clock64();
+                    c_wait_sf += cg - cf;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
+                        const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+#pragma unroll
+                        for (int i = 0; i < C::MMAS; i++) {
+                            const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                            const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
+                            const uint32_t accum = (kb > 0 || i > 0) ? 1u : 0u;
+                            if (SPARSE) tc_mma_nvf4_sp_pair(tmem_base, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 8 * i, t_e + 2 * i, accum);
+                            else tc_mma_nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 8 * i, accum);
+                        }
+                        tc_commit_pair(empty_bar(stage), 3);
+                    }
+                    __syncwarp();
+                    c_issue += clock64() - cg;
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if (lane == 0) tc_commit_pair(accf_bar, 3);
+                __syncwarp();
+                acc_phase ^= 1;
+            }
+            if (p.prof && lane == 0) {
+                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
+                o[0] = clock64() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
+            }
+        }
+    } else if (warp >= 6) {
+        // ------------------------------------------------------------ scale-factor warps (both CTAs)
+        const int q = warp & 3;
+        const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+        int stage = 0;
+        uint32_t phase = 0;
+        long long c_wait_full = 0, c_sf = 0, c_st = 0, c_ld = 0, c_arr = 0, c_fence = 0, c_sw = 0;
+        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            bool ok = true;
+            for (int kb = 0; kb < p.kblocks; kb++) {
+                long long cf = clock64();
+                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF)) { ok = false; break; }
+                long long cg = clock64();
+                c_wait_full += cg - cf;
+                const uint8_t* sf = smem_gen + (size_t)stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
+                const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
+                const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                if constexpr (SPARSE) {
+                    uint32_t a[8], b[16], e[4];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        uint4 v = *reinterpret_cast<const uint4*>(sf + i * 512);
+                        a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+#pragma unroll
+                        for (int nb = 0; nb < 2; nb++) {
+                            uint4 v = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 2 + i) * 512);
+                            b[8 * i + 4 * nb] = v.x; b[8 * i + 4 * nb + 1] = v.y; b[8 * i + 4 * nb + 2] = v.z; b[8 * i + 4 * nb + 3] = v.w;
+                        }
+                    {
+                        uint4 v = *reinterpret_cast<const uint4*>(smem_gen + (size_t)stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES +
+                                                                  C::SFA_BYTES + C::SFB_BYTES + (q * 32 + lane) * 16);
+                        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                    }
+                    c_ld += clock64() - cg;
+                    tc_st_32x8(t_sfa, a);
+                    tc_st_32x16(t_sfb, b);
+                    tc_st_32x4(t_e, e);
+                } else {
+                    uint32_t a[16], b0[16], b1[16];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint4 v = *reinterpret_cast<const uint4*>(sf + i * 512);
+                        a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+#pragma unroll
+                        for (int nb = 0; nb < 2; nb++) {
+                            uint4 v = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 4 + i) * 512);
+                            b0[8 * i + 4 * nb] = v.x; b0[8 * i + 4 * nb + 1] = v.y; b0[8 * i + 4 * nb + 2] = v.z; b0[8 * i + 4 * nb + 3] = v.w;
+                            uint4 w = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 4 + i + 2) * 512);
+                            b1[8 * i + 4 * nb] = w.x; b1[8 * i + 4 * nb + 1] = w.y; b1[8 * i + 4 * nb + 2] = w.z; b1[8 * i + 4 * nb + 3] = w.w;
+                        }
+                    c_ld += clock64() - cg;
+                    tc_st_32x16(t_sfa, a);
+                    tc_st_32x16(t_sfb, b0);
+                    tc_st_32x16(t_sfb + 16, b1);
+                }
+                long long ch = clock64();
+                tc_wait_st();
+                long long ci = clock64();
+                c_st += ci - ch;
+                tc_fence_before();
+                long long ck = clock64();
+                __syncwarp();
+                long long cl = clock64();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
+                long long cj = clock64();
+                c_arr += cj - cl;
+                c_ld += 0;
+                c_fence += ck - ci;
+                c_sw += cl - ck;
+                c_sf += cj - cg;
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+        }
+        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; p.prof[(size_t)blockIdx.x * 8 + 1] += 0; }
+        if (false) { p.prof[(size_t)blockIdx.x * 8 + 0] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 1] = c_sf; p.prof[(size_t)blockIdx.x * 8 + 2] = c_st; p.prof[(size_t)blockIdx.x * 8 + 3] = c_ld; p.prof[(size_t)blockIdx.x * 8 + 5] = c_arr; p.prof[(size_t)blockIdx.x * 8 + 6] = c_fence; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sw; }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own rows)
+        const int q = warp & 3;
+        const int r_in_tile = q * 32 + lane;
+        const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
+        const uint32_t acce_leader = mapa_shared(acce_bar, 0);
+        uint32_t acc_phase = 0;
+        long long c_wait_accf = 0, c_epi = 0;
+        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int n0 = n * 256;
+            const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
+            const int o = o0 + r_in_tile;
+            // per-tile constants first, so their latency hides behind the accumulator wait
+            const float ga = p.gA ? __ldg(p.gA + o) : 1.f;
+            float gbv[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const int col = n0 + 32 * c + lane;
+                gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
+            }
+            long long cw = clock64();
+            if (!mbar_wait(accf_bar, acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            long long cx = clock64();
+            c_wait_accf += cx - cw;
+            tc_fence_after();
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16);
+            uint32_t ra[32], rb[32];
+            tc_ld_32x32(t_acc, ra);
+            auto emit = [&](const uint32_t (&r)[32], int c) {
+                const int c0 = 32 * c;
+                const float gbl = gbv[c];
+                if (p.out_mode == 0) {
+                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)o * p.tok;
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float g0 = __shfl_sync(0xffffffffu, gbl, j), g1 = __shfl_sync(0xffffffffu, gbl, j + 1);
+                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]) * (ga * g0), __uint_as_float(r[j + 1]) * (ga * g1));
+                        pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    const int col0 = n0 + c0;
+                    if (col0 + 32 <= p.tok && (p.tok & 7) == 0) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            *reinterpret_cast<uint4*>(Cp + col0 + 8 * v) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col0 + j < p.tok) {
+                                uint32_t w = pk[j / 2];
+                                reinterpret_cast<uint16_t*>(Cp)[col0 + j] = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffff);
+                            }
+                    }
+                } else {
+                    // transpose a 32(out) x 32(tok) block through shared memory -> 16-byte token-major stores
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float g0 = __shfl_sync(0xffffffffu, gbl, j);
+                        __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(r[j]) * (ga * g0));
+                        sts_u16(stg_s + j * 80 + lane * 2, *reinterpret_cast<uint16_t*>(&h));
+                    }
+                    __syncwarp();
+                    uint4 val[4];
+#pragma unroll
+                    for (int it = 0; it < 4; it++) val[it] = lds_v4(stg_s + ((it * 32 + lane) >> 2) * 80 + (lane & 3) * 16);
+                    __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + o0 + q * 32 + (lane & 3) * 8;
+#pragma unroll
+                    for (int it = 0; it < 4; it++) {
+                        const int col = n0 + c0 + ((it * 32 + lane) >> 2);
+                        if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val[it]);
+                    }
+                    __syncwarp();
+                }
+            };
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                tc_wait_ld();
+                tc_ld_32x32(t_acc + 32 * (c + 1), rb);
+                emit(ra, c);
+                tc_wait_ld();
+                if (c + 2 < 8) {
+                    tc_ld_32x32(t_acc + 32 * (c + 2), ra);
+                } else {
+                    // every column is in registers: hand the accumulator back before the last stores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(acce_leader);
+                }
+                emit(rb, c + 1);
+            }
+            c_epi += clock64() - cx;
+            acc_phase ^= 1;
+        }
+        if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
+    }
+
+    // teardown: no CTA may leave while its partner can still signal its barriers
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::TM_COLS);
     }
 }
 
@@ -409,6 +825,9 @@ static int sm_count() {
     return n;
 }
 
+// The pair kernel's TMA box for B is 128 rows; a token count below 128 would need a shorter box.
+static bool b_tail_ok(int tok) { return tok >= 128; }
+
 template <bool SPARSE, int BN>
 static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     using C = Cfg<SPARSE, BN>;
@@ -423,6 +842,57 @@ static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     int total = kp.num_m * kp.num_n * kp.splits;
     int grid = total < sm_count() ? total : sm_count();
     nvfp4_gemm_kernel<SPARSE, BN><<<grid, 192, C::SMEM_BYTES, st>>>(tmA, tmB, kp);
+    return (int)cudaGetLastError();
+}
+
+
+static int make_map_u32_rows(CUtensorMap* m, const void* base, uint64_t rows, uint32_t box_rows) {
+    // [rows][128 x u32] = rows of 512 bytes (scale-factor atoms, quarter blocks of metadata), no swizzle
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return QB_ERR_DRIVER;
+    cuuint64_t dims[2] = {128, rows};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QB_OK : QB_ERR_DRIVER;
+}
+
+template <bool SPARSE>
+static int launch_pair(const GemmArgs& a, cudaStream_t st) {
+    using C = Cfg2<SPARSE>;
+    static int attr_rc = -1;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        attr_rc = (int)cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    });
+    if (attr_rc) return attr_rc;
+    const int kblocks = (a.K + 255) / 256;
+    const int atoms_per_rb = kblocks * C::MMAS;
+    CUtensorMap tmA, tmB, tmSFA, tmSFB, tmMETA;
+    int rc = make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
+                         SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    const uint32_t b_rows = a.tok < 128 ? (uint32_t)a.tok : 128u;
+    if ((rc = make_map_u8(&tmB, a.B, (uint64_t)a.K / 2, (uint64_t)a.tok, 128, b_rows, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_map_u32_rows(&tmSFA, a.sfa, (uint64_t)(a.a_rows / 128) * atoms_per_rb, C::MMAS))) return rc;
+    if ((rc = make_map_u32_rows(&tmSFB, a.sfb, (uint64_t)((a.tok + 127) / 128) * atoms_per_rb, C::MMAS))) return rc;
+    if (SPARSE) {
+        if ((rc = make_map_u32_rows(&tmMETA, a.meta, (uint64_t)(a.a_rows / 128) * kblocks * 4, 4))) return rc;
+    } else {
+        tmMETA = tmSFA;
+    }
+    KParams2 kp;
+    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.out_f = a.out_f; kp.tok = a.tok;
+    kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + 255) / 256; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
+    int total = kp.num_m2 * kp.num_n;
+    int nclusters = sm_count() / 2;
+    if (total < nclusters) nclusters = total;
+    kp.prof = g_prof_ptr;
+    { const char* e = getenv("QB_DEBUG_SKIP"); kp.dbg = e ? atoi(e) : 0; }
+    nvfp4_gemm_pair_kernel<SPARSE><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
     return (int)cudaGetLastError();
 }
 
@@ -441,10 +911,18 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     int rc = gemm_init_attrs();
     if (rc) return rc;
 
+    // CTA-pair kernel: plain bf16 GEMM, enough tokens to fill a 256-wide tile, out % 256 == 0.
+    // bn == 512 requests it explicitly, bn == 0 (auto) picks it for prefill-sized problems.
+    const bool pair_ok = !a.eblk && splits == 1 && (a.out_mode == 0 || a.out_mode == 1) && a.out_f % 256 == 0 && a.tok >= 128 &&
+                         b_tail_ok(a.tok);
+    if ((a.bn == 512 && !pair_ok)) return QB_ERR_ARG;
+    if (pair_ok && (a.bn == 512 || (a.bn == 0 && a.tok >= 512))) {
+        return a.sparse ? launch_pair<true>(a, st) : launch_pair<false>(a, st);
+    }
     int bn = a.bn;
     if (a.eblk) bn = 128;
     if (bn == 0) bn = a.tok <= 16 ? 16 : a.tok <= 32 ? 32 : a.tok <= 64 ? 64 : 128;
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return QB_ERR_ARG;
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return QB_ERR_ARG;   // 512 = pair kernel, handled above
     // a token tile starts at scale-atom column (n0 % 128) / 32 and the MMA only accepts even
     // scale-factor columns, so tiles narrower than 64 tokens must be the only tile
     if (bn < 64 && a.tok > bn) return QB_ERR_ARG;
@@ -462,6 +940,12 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     kp.splits = splits;
     kp.sfb_rowblocks = (a.tok + 127) / 128;
     kp.out_mode = a.out_mode;
+    {
+        static int dbg = -1;
+        if (dbg < 0) { const char* e = getenv("QB_DEBUG_SKIP"); dbg = e ? atoi(e) : 0; }
+        kp.dbg = dbg;
+        kp.prof = g_prof_ptr;
+    }
     if (splits > 1) {
         rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
         if (rc) return rc;
@@ -485,6 +969,8 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     }
     return rc;
 }
+
+extern "C" void qb_debug_set_prof(void* p) { g_prof_ptr = (unsigned long long*)p; }
 
 int read_status(cudaStream_t st) {
     int rc = (int)cudaStreamSynchronize(st);
