@@ -212,7 +212,7 @@ def run_gpu(args):
         del W
     launches = [0]
 
-    def gemm_into(L, bn=256):
+    def gemm_into(L, bn=0):
         lin = L["lin"]
         if isinstance(lin, qb.DenseNVLinear):
             rc = lib.qb_gemm(lin.Ab.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(), 0, lin.gA.data_ptr(),
@@ -258,7 +258,7 @@ def run_gpu(args):
             "config": {"workload": WORKLOAD, "tokens": TOK, "parallelism": f"tp{world}" if world > 1 else "single",
                        "l2": "no explicit flush: one step touches ~0.45 GB of distinct operands and outputs (> 126 MB L2) "
                              "before any buffer is reused",
-                       "token_tile": 256},
+                       "tile": "CTA pair: 256 out x 256 tok x 256 K per stage"},
             "gpu_launches": n_launch, "clocks": cs.summary()}
 
     if args.only:
@@ -281,8 +281,8 @@ def run_gpu(args):
             del Wd
             Bs, sBs, gBs = sp.pack_act(xd)
             Bd, sBd, gBd = qb.quantize_act(dn.lib, xd, 16, True)
-            ts = ev_time(lambda: sp.run(Bs, sBs, tokL, gBs, out_t=True, bn=256), 10, 3)
-            td = ev_time(lambda: dn.run(Bd, sBd, tokL, gBd, out_t=True, bn=256), 10, 3)
+            ts = ev_time(lambda: sp.run(Bs, sBs, tokL, gBs, out_t=True, bn=0), 10, 3)
+            td = ev_time(lambda: dn.run(Bd, sBd, tokL, gBd, out_t=True, bn=0), 10, 3)
             tq = ev_time(lambda: sp.pack_act(xd), 10, 3)
             fl = 2.0 * tokL * n * k
             shapes[name] = {"sparse_tflops": fl / ts / 1e12, "dense_tflops": fl / td / 1e12, "sparse_us": ts * 1e6,
@@ -300,18 +300,17 @@ def run_gpu(args):
                     for _ in range(nrot)]
             for m_tok in (1, 16, 64, 128, 256):
                 xdec = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
-                kb = (k + 255) // 256
-                splits = max(1, min(kb, (148 + n // 128 - 1) // (n // 128)))
+                splits = "auto"
                 stream = torch.cuda.Stream()
                 with torch.cuda.stream(stream):
                     for m in mods[:2]:
-                        m.forward(xdec, splits=splits)
+                        m.forward(xdec)
                     stream.synchronize()
                     gph = torch.cuda.CUDAGraph()
                     try:
                         with torch.cuda.graph(gph, stream=stream):
                             for m in mods:
-                                m.forward(xdec, splits=splits)
+                                m.forward(xdec)
                         for _ in range(3):
                             gph.replay()
                         stream.synchronize()
@@ -325,7 +324,7 @@ def run_gpu(args):
                         mode = "cuda-graph"
                     except Exception as e:  # capture refused: time eagerly, say so
                         torch.cuda.synchronize()
-                        tl = ev_time(lambda: [m.forward(xdec, splits=splits) for m in mods], 3) / nrot
+                        tl = ev_time(lambda: [m.forward(xdec) for m in mods], 3) / nrot
                         mode = f"eager ({type(e).__name__})"
                 algo = wbytes + 2 * m_tok * k + 2 * m_tok * n
                 dec[f"N{n}_K{k}_M{m_tok}"] = {"us": tl * 1e6, "gbs": algo / tl / 1e9, "frac_of_measured_hbm": algo / tl / 1e9 / hbm_gbs,
@@ -360,7 +359,7 @@ def run_gpu(args):
                             "traffic": None,
                             "peak_basis": f"{peak_src} bf16_tflops_sustained {bf16_sust} x 8 (nominal 2:4-sparse FP4 : dense bf16 = 18 : 2.25 PF)",
                             "frac_of_nominal_18PF": value / 18000.0,
-                            "kernel": "nvfp4_gemm_kernel<sparse, BN=256>", "launches_per_step": len(layers)}
+                            "kernel": "nvfp4_gemm_pair_kernel<sparse, 256>", "launches_per_step": len(layers)}
 
         # ---- CPU baseline (oracle port), bounded sample
         tok_s = 256

@@ -64,6 +64,16 @@ void quantize_act_nvfp4b(const void* x, void* Bbytes, void* scaleB, int tok, int
 void quantize_act_nvfp4_2lvl(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K);
 /* cuda/sparse_fp4_lib.cu:781 — stream variant. */
 void quantize_act_nvfp4_2lvl_s(const void* x, void* Bbytes, void* scaleB, void* gB, int tok, int K, void* stream);
+/* cuda/sparse_fp4_lib.cu:821,886 — SwiGLU + per-32 quantiser over the reference's feature-major GEMM
+ * outputs g, u [hidden][batch] bf16: h = silu(g)*u -> Hbytes[batch][hidden/2], scaleH[hidden/128][batch][4]
+ * (single level), and gH[batch] for the two-level form (gH need not be pre-zeroed here). */
+void fused_swiglu_quant(const void* g, const void* u, void* Hbytes, void* scaleH, int batch, int hidden);
+void fused_swiglu_quant_2lvl(const void* g, const void* u, void* Hbytes, void* scaleH, void* gH, int batch, int hidden);
+/* cuda/sparse_fp4_lib.cu:944,1003 — RMSNorm (after an optional residual add whose sum is written to hout
+ * as the new residual stream) fused with the single-level per-32 quantiser; x, res, wt, hout bf16. */
+void rmsnorm_quant(const void* x, const void* wt, void* Bbytes, void* scaleB, int batch, int hidden, float eps);
+void add_rmsnorm_quant(const void* inp, const void* res, const void* wt, void* hout, void* Bbytes, void* scaleB, int batch,
+                       int hidden, float eps);
 /* cuda/sparse_fp4_lib.cu:1133-1137 — fused SwiGLU MLP: quantise x[tp][H], gate/up GEMM (weights gu_*,
  * gu_out = 2*Iw rows: gate features then up features), h = silu(g)*u quantised two-level per token,
  * down GEMM -> Cout[tp][dn_out] bf16. Bb, sBg, gBg, Cgu, Hb, sH, gH are caller scratch with the
@@ -132,6 +142,17 @@ long long qb_meta_native_bytes(int out, int K);
 int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
             const void* gB, void* C, void* Cf, const void* eblk, const void* bias, const void* row_w, int a_rows, int out,
             int tok, int K, int sparse, int out_mode, int splits, int bn, void* stream);
+/* Thin-token (decode) GEMM: streams the weight once with the K range split over CTAs so that all SMs
+ * pull from HBM; each split writes fp32 partial sums to its own slab of `ws` and the last split to
+ * arrive for a tile sums them and writes bf16 (one launch: no memset, no finish pass). The split
+ * count and token tile come from the shapes. `ws`: qb_gemm_decode_ws_bytes(out, tok, K) bytes,
+ * 256-byte aligned, ZERO-FILLED ONCE when allocated (its head holds arrival counters that every call
+ * leaves at zero again); calls sharing a workspace must not overlap on the GPU. out_mode 0 / 1 as in
+ * qb_gemm. Replaces the memset + atomics + convert sequence of the reference's split-K decode path
+ * (cuda/sparse_fp4_lib.cu:1160-1344) and its unit-scale split-N decode (cuda/dense_decode_lib.cu:19-141). */
+int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
+                   const void* gB, void* C, void* ws, int out, int tok, int K, int sparse, int out_mode, void* stream);
+long long qb_gemm_decode_ws_bytes(int out, int tok, int K);
 /* Split-K GEMM without a caller workspace (no counterpart in the reference library, whose
  * split-K entry sparse_down_sk_2lvl always takes the workspace Cf from the caller). Same
  * operands and meaning as qb_gemm with splits > 1, out_mode 0 or 1, plain (not grouped) mode;
@@ -150,6 +171,10 @@ int qb_gemm_splitk_static(const void* A, const void* B, const void* sfa, const v
                           const void* gA, const void* gB, void* C, int out, int tok, int K, int sparse, int out_mode,
                           int splits, void* stream);
 long long qb_gemm_splitk_static_max_elems(void);
+/* RMSNorm [+ residual add] + quantiser, general form: res / hout may be NULL (no add), g NULL selects the
+ * single-level recipe, block 16 or 32, scales to the reference layout and/or atoms. */
+int qb_norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
+                  int tok, int H, float eps, int block, void* stream);
 /* SwiGLU + two-level per-32 quantiser over a token-major gate/up output Cgu[tok][2*I] bf16 (gate
  * features first): Hb[tok][I/2], scales (ref layout and/or atoms), gH[tok]. One pass; replaces
  * swiglu_amax + swiglu_finalize + swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894). */

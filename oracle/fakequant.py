@@ -184,11 +184,11 @@ def unpack_weight_dense(Ab, SFA, gA) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- activations
-def act_quant_2lvl(x: torch.Tensor, block: int):
+def act_quant_2lvl(x: torch.Tensor, block: int, round_bf16: bool = True):
     """bf16-rounded [tok,K] -> (Bbytes[tok,K/2] u8, scale[K/128,tok,128/block] u8, g[tok] f32).
     block = 32 for the sparse path, 16 for the dense path."""
     i = x.shape[-1]
-    b = x.to(torch.bfloat16).float().reshape(-1, i)
+    b = (x.to(torch.bfloat16).float() if round_bf16 else x.float()).reshape(-1, i)
     t = b.shape[0]
     g = (b.abs().amax(-1, keepdim=True) / GLOBAL_DIV).clamp_min(1e-30)
     bb = b.reshape(t, i // block, block)
@@ -213,12 +213,12 @@ def act_dequant_2lvl(x: torch.Tensor, block: int, round_bf16: bool = True) -> to
     return (FP4[q_fp4(bb / sdeq.clamp_min(1e-30)[..., None])] * sdeq[..., None]).reshape(*lead, i)
 
 
-def act_quant_1lvl(x: torch.Tensor, block: int):
+def act_quant_1lvl(x: torch.Tensor, block: int, round_bf16: bool = True):
     """Single-level quantiser (no global): code = enc(amax/6), as quant_act /
     quant_act_nv (cuda/sparse_fp4_lib.cu:704-732, cuda/dense_nvfp4_fast_lib.cu:175-206)
     restated with the same guard/tie rules as the two-level oracle."""
     i = x.shape[-1]
-    b = x.to(torch.bfloat16).float().reshape(-1, i)
+    b = (x.to(torch.bfloat16).float() if round_bf16 else x.float()).reshape(-1, i)
     t = b.shape[0]
     bb = b.reshape(t, i // block, block)
     code = enc_ue4m3(bb.abs().amax(-1) / 6.0)
@@ -252,6 +252,16 @@ def linear_sparse(x: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
 
 def linear_dense(x: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
     return F.linear(act_dequant_2lvl(x.float(), 16), dense_fp4_dequant(W.float()))
+
+
+def rmsnorm_fp32(x: torch.Tensor, w: torch.Tensor, eps: float, res: torch.Tensor | None = None):
+    """fp32 RMSNorm of bf16 inputs as the fused quantisers compute it (cuda/sparse_fp4_lib.cu:902-1011):
+    v = x (+ res); y = v * rsqrt(mean(v^2) + eps) * w. Returns (y, bf16(v))."""
+    v = x.to(torch.bfloat16).float()
+    if res is not None:
+        v = v + res.to(torch.bfloat16).float()
+    y = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.to(torch.bfloat16).float()
+    return y, v.to(torch.bfloat16)
 
 
 def fused_mlp_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:

@@ -41,10 +41,17 @@ _SIGS = {
     "qb_sf_atoms_bytes": ([I] * 3, c_longlong),
     "qb_meta_native_bytes": ([I] * 2, c_longlong),
     "qb_gemm": ([P] * 12 + [I] * 8 + [P], I),
+    "fused_swiglu_quant": ([P] * 4 + [I] * 2, None),
+    "fused_swiglu_quant_2lvl": ([P] * 5 + [I] * 2, None),
+    "rmsnorm_quant": ([P] * 4 + [I] * 2 + [c_float], None),
+    "add_rmsnorm_quant": ([P] * 6 + [I] * 2 + [c_float], None),
+    "qb_norm_quant": ([P] * 8 + [I] * 2 + [c_float, I, P], I),
     "fused_mlp_2lvl": ([P] * 17 + [I] * 5 + [P], I),
     "fused_mlp_2lvl_skdown": ([P] * 18 + [I] * 6 + [P], I),
     "qb_swiglu_quant": ([P] * 5 + [I] * 2 + [P], I),
     "qb_fused_mlp": ([P] * 18 + [I] * 6 + [P], I),
+    "qb_gemm_decode": ([P] * 9 + [I] * 5 + [P], I),
+    "qb_gemm_decode_ws_bytes": ([I] * 3, c_longlong),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),

@@ -202,6 +202,30 @@ int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, cons
     g.bn = bn;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
+static size_t decode_counter_bytes(int out, int tok) {
+    const int bn = tok <= 16 ? 16 : tok <= 32 ? 32 : tok <= 64 ? 64 : 128;
+    const size_t tiles = (size_t)(out / 128) * ((tok + bn - 1) / bn);
+    return (tiles * 4 * sizeof(int) + 1023) & ~(size_t)1023;
+}
+long long qb_gemm_decode_ws_bytes(int out, int tok, int K) {
+    if (out <= 0 || tok <= 0 || K <= 0 || out % 128) return -1;
+    int splits = 1, bn = 16;
+    qb::decode_plan(out, tok, K, &splits, &bn);
+    return (long long)(decode_counter_bytes(out, tok) + (size_t)splits * tok * out * sizeof(float));
+}
+int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
+                   const void* gB, void* C, void* ws, int out, int tok, int K, int sparse, int out_mode, void* stream) {
+    if (out <= 0 || tok < 0 || K <= 0 || out % 128 || (out_mode != 0 && out_mode != 1)) return QB_ERR_ARG;
+    if (tok == 0) return QB_OK;
+    if (!ws || ((uintptr_t)ws & 255)) return QB_ERR_ARG;
+    int splits = 1, bn = 16;
+    qb::decode_plan(out, tok, K, &splits, &bn);
+    qb::GemmArgs g{};
+    g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
+    g.C = C; g.sk_counters = ws; g.Cf = (float*)((uint8_t*)ws + decode_counter_bytes(out, tok));
+    g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode; g.splits = splits; g.bn = bn;
+    return qb::gemm_nvfp4(g, (cudaStream_t)stream);
+}
 int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {
     return qb::swiglu_quant(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, (cudaStream_t)stream);
@@ -280,6 +304,24 @@ int moe_route(const void* assign, const void* poff, void* counter, void* src, in
 int moe_combine_topk(const void* dbuf, const void* inverse, void* y, int t, int H, int topk, int Mpe, void* stream) {
     int rc = qb::moe_combine_topk(dbuf, inverse, y, t, H, topk, Mpe, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);
+}
+void fused_swiglu_quant(const void* g, const void* u, void* Hbytes, void* scaleH, int batch, int hidden) {
+    t_last_error = qb::swiglu_quant_feature_major(g, u, Hbytes, scaleH, nullptr, batch, hidden, 0);
+}
+void fused_swiglu_quant_2lvl(const void* g, const void* u, void* Hbytes, void* scaleH, void* gH, int batch, int hidden) {
+    t_last_error = gH ? qb::swiglu_quant_feature_major(g, u, Hbytes, scaleH, gH, batch, hidden, 0) : QB_ERR_ARG;
+}
+void rmsnorm_quant(const void* x, const void* wt, void* Bbytes, void* scaleB, int batch, int hidden, float eps) {
+    t_last_error = qb::norm_quant(x, nullptr, wt, nullptr, Bbytes, scaleB, nullptr, nullptr, batch, hidden, eps, 32, 0);
+}
+void add_rmsnorm_quant(const void* inp, const void* res, const void* wt, void* hout, void* Bbytes, void* scaleB, int batch,
+                       int hidden, float eps) {
+    t_last_error = (res && hout) ? qb::norm_quant(inp, res, wt, hout, Bbytes, scaleB, nullptr, nullptr, batch, hidden, eps, 32, 0)
+                                 : QB_ERR_ARG;
+}
+int qb_norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
+                  int tok, int H, float eps, int block, void* stream) {
+    return qb::norm_quant(x, res, wt, hout, Bbytes, sf_ref, sf_atoms, g, tok, H, eps, block, (cudaStream_t)stream);
 }
 void qb_init_func_attrs(void) { t_last_error = qb::gemm_init_attrs(); }
 void qb_init_sk_attrs(void) { t_last_error = qb::gemm_init_attrs(); }

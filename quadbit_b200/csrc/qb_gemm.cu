@@ -58,6 +58,7 @@ struct KParams {
     int b_box_bytes;                     // bytes one B TMA box delivers (box rows * 128)
     int out_mode;
     int dbg;                             // experiment switches (QB_DEBUG_SKIP), 0 in normal use
+    int* sk_counters;                    // slab split-K: 4 arrival counters per output tile (zero between calls)
     unsigned long long* prof;            // optional per-CTA cycle counters [grid][8]
 };
 
@@ -289,7 +290,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 tc_wait_ld();
                 const int col_l = n0 + c0 + (lane % C::CH);
                 const float gbl = gbv[c0 / C::CH];
-                if (p.splits > 1) {
+                if (p.splits > 1 && p.sk_counters) {
+                    // slab split-K: this split's raw partial sums go to its own fp32 slab [z][tok][out]
+                    float* slab = p.Cf + (size_t)z * p.tok * p.out_f;
+#pragma unroll
+                    for (int j = 0; j < C::CH; j++) {
+                        const int col = n0 + c0 + j;
+                        if (col < p.tok) __stcg(slab + (size_t)col * p.out_f + o, __uint_as_float(r[j]));
+                    }
+                } else if (p.splits > 1) {
                     // split-K: raw partial sums into the fp32 workspace Cf[tok][out]
 #pragma unroll
                     for (int j = 0; j < C::CH; j++) {
@@ -357,6 +366,32 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(acc));
+            if (p.splits > 1 && p.sk_counters) {
+                // The warp that arrives last among the same-quadrant warps of all K splits owns rows
+                // [32q, 32q+32) of this tile: it sums the slabs, applies the globals and writes bf16.
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    int* cnt = p.sk_counters + (size_t)mn * 4 + q;
+                    last = (atomicAdd(cnt, 1) == p.splits - 1);
+                    if (last) *cnt = 0;            // every split has arrived: leave the counter clean for the next call
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const int ncol = min(BN, p.tok - n0);
+                    for (int j = 0; j < ncol; j++) {
+                        const int col = n0 + j;
+                        float sum = 0.f;
+                        for (int zz = 0; zz < p.splits; zz++) sum += __ldcg(p.Cf + ((size_t)zz * p.tok + col) * p.out_f + o);
+                        const float gb = p.gB ? __ldg(p.gB + col) : 1.f;
+                        const __nv_bfloat16 h = __float2bfloat16_rn(sum * (ga * gb));
+                        if (p.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)o * p.tok + col] = h;
+                        else reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)col * p.out_f + o] = h;
+                    }
+                }
+            }
             c_epi += clock64() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
@@ -394,33 +429,37 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 //              32 columns overlap the conversion of the current ones) and frees it as soon as
 //              the last column is in registers.
 // Requires out % 256 == 0 and tok >= 128.
-template <bool SPARSE>
+template <bool SPARSE, int BN_>
 struct Cfg2 {
-    static constexpr int BN = 256;
+    static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
     static constexpr int THREADS = 320;
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
-    static constexpr int B_BYTES = 128 * 128;             // this CTA's half of the token tile
+    static constexpr int B_ROWS = BN / 2;                 // this CTA's half of the token tile
+    static constexpr int B_BYTES = B_ROWS * 128;
     static constexpr int MMAS = SPARSE ? 2 : 4;
     static constexpr int B_KSTEP = SPARSE ? 64 : 32;
+    static constexpr int NBA = BN / 128;                  // scale-factor atoms (128 rows) per token tile
     static constexpr int SFA_BYTES = MMAS * 512;
-    static constexpr int SFB_BYTES = 2 * MMAS * 512;      // all 256 token rows, in both CTAs
+    static constexpr int SFB_BYTES = NBA * MMAS * 512;    // all BN token rows, in both CTAs
     static constexpr int META_BYTES = SPARSE ? 2048 : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + META_BYTES;
+    static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
     static constexpr int EPI_BYTES = 4 * 32 * 80;
     static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 512;
     static constexpr int SFA_COLS = MMAS * 4;
-    static constexpr int SFB_COLS = MMAS * 8;
+    static constexpr int SFB_COLS = MMAS * 4 * NBA;
     static constexpr int E_COLS = SPARSE ? 4 : 0;
     static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // one TMEM slot per smem stage
     static constexpr int STAGES_SMEM = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES_TMEM = 256 / SF_SET;
     static constexpr int STAGES_MIN = STAGES_SMEM < STAGES_TMEM ? STAGES_SMEM : STAGES_TMEM;
-    static constexpr int STAGES = STAGES_MIN > 8 ? 8 : STAGES_MIN;
+    static constexpr int STAGES = STAGES_MIN > 10 ? 10 : STAGES_MIN;
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 512;
     static constexpr int TM_SF0 = 256;
     static constexpr int TM_COLS = 512;
-    static_assert(TM_SF0 + STAGES * SF_SET <= 512, "TMEM budget");
+    static_assert(BN == 128 || BN == 256, "token tile");
+    static_assert(ACC_STAGES * BN <= 256 && TM_SF0 + STAGES * SF_SET <= 512, "TMEM budget");
     static_assert(STAGES >= 3, "smem budget");
 };
 
@@ -436,13 +475,14 @@ struct KParams2 {
 };
 
 enum { SITE_SF = 5 };
+#define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = clock64(); } while (0)
 
-template <bool SPARSE>
+template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
-    using C = Cfg2<SPARSE>;
+    using C = Cfg2<SPARSE, BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
     __shared__ uint32_t tmem_base_slot;
@@ -453,8 +493,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto sfr_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + s); };
-    const uint32_t accf_bar = bars + 8u * (3 * C::STAGES);
-    const uint32_t acce_bar = bars + 8u * (3 * C::STAGES + 1);
+    auto accf_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + a); };
+    auto acce_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + 2 + a); };
     auto stageA = [&](int s) { return smem0 + (uint32_t)s * C::STAGE_BYTES; };
     auto stageB = [&](int s) { return stageA(s) + C::A_BYTES; };
     auto stageSFA = [&](int s) { return stageB(s) + C::B_BYTES; };
@@ -474,8 +514,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             mbar_init(empty_bar(s), 1);
             mbar_init(sfr_bar(s), 8);             // 4 scale-factor warps of each CTA arrive on the leader's
         }
-        mbar_init(accf_bar, 1);
-        mbar_init(acce_bar, 8);                   // 4 epilogue warps of each CTA arrive on the leader's
+        for (int a = 0; a < 2; a++) {
+            mbar_init(accf_bar(a), 1);
+            mbar_init(acce_bar(a), 8);            // 4 epilogue warps of each CTA arrive on the leader's
+        }
         fence_barrier_init();
         tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
         if (SPARSE) tma_prefetch_desc(&tmMETA);
@@ -499,18 +541,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = m2 * 256 + (int)rank * 128;
-            const int n0 = n * 256;
+            const int n0 = n * BN;
             const int rb_a = a_row0 >> 7, rb_b = n0 >> 7;
             for (int kb = 0; kb < p.kblocks; kb++) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
+                QB_EV(kb, 0);
                 if (lane == 0) {
                     const uint32_t fb = full_bar(stage);
-                    mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES);
-                    tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                    tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * 128);
+                    const bool skipB = (p.dbg & 2) && kb >= C::STAGES, skipA = (p.dbg & 4) && kb >= C::STAGES;
+                    mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES - (skipB ? C::B_BYTES : 0) - (skipA ? C::A_BYTES : 0));
+                    if (!skipA) tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                    if (!skipB) tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
                     tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
-                    tma_load_2d(stageSFB(stage), &tmSFB, fb, 0, rb_b * atoms_per_rb + kb * C::MMAS);
-                    tma_load_2d(stageSFB(stage) + C::MMAS * 512, &tmSFB, fb, 0, (rb_b + 1) * atoms_per_rb + kb * C::MMAS);
+#pragma unroll
+                    for (int nb = 0; nb < C::NBA; nb++)
+                        tma_load_2d(stageSFB(stage) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
                     if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
                 }
                 __syncwarp();
@@ -520,21 +565,24 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (rank == 0) {
-            const uint32_t idesc = make_idesc_nvf4(256, SPARSE, 256);
-            int stage = 0;
+            const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
+            int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = clock64();
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
                 long long ca = clock64();
-                if (!mbar_wait(acce_bar, acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+                if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
                 c_wait_acc += clock64() - ca;
                 tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 bool ok = true;
                 for (int kb = 0; kb < p.kblocks; kb++) {
                     long long cf = clock64();
+                    QB_EV(kb, 3);
                     if (!mbar_wait(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
                     long long cg = clock64();
                     c_wait_sf += cg - cf;
+                    QB_EV(kb, 4);
                     tc_fence_after();
                     if (lane == 0) {
                         const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
@@ -544,19 +592,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
                             const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
                             const uint32_t accum = (kb > 0 || i > 0) ? 1u : 0u;
-                            if (SPARSE) tc_mma_nvf4_sp_pair(tmem_base, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 8 * i, t_e + 2 * i, accum);
-                            else tc_mma_nvf4_pair(tmem_base, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 8 * i, accum);
+                            if (SPARSE)
+                                tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
+                            else
+                                tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
                         }
                         tc_commit_pair(empty_bar(stage), 3);
                     }
                     __syncwarp();
+                    QB_EV(kb, 5);
                     c_issue += clock64() - cg;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                if (lane == 0) tc_commit_pair(accf_bar, 3);
+                if (lane == 0) tc_commit_pair(accf_bar(acc), 3);
                 __syncwarp();
-                acc_phase ^= 1;
+                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
             if (p.prof && lane == 0) {
                 unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
@@ -569,7 +620,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0;
         uint32_t phase = 0;
-        long long c_wait_full = 0, c_sf = 0, c_st = 0, c_ld = 0, c_arr = 0, c_fence = 0, c_sw = 0;
+        long long c_wait_full = 0, c_sf = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             bool ok = true;
             for (int kb = 0; kb < p.kblocks; kb++) {
@@ -577,101 +628,79 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF)) { ok = false; break; }
                 long long cg = clock64();
                 c_wait_full += cg - cf;
-                const uint8_t* sf = smem_gen + (size_t)stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + lane * 16;
+                if (warp == 6) QB_EV(kb, 1);
+                const uint32_t sf = stageSFA(stage) + lane * 16;       // this lane's 16 bytes of every atom
                 const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
                 const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
-                if constexpr (SPARSE) {
-                    uint32_t a[8], b[16], e[4];
+                // SFA: MMAS atoms -> MMAS*4 consecutive columns
+                {
+                    uint32_t a[C::MMAS * 4];
 #pragma unroll
-                    for (int i = 0; i < 2; i++) {
-                        uint4 v = *reinterpret_cast<const uint4*>(sf + i * 512);
+                    for (int i = 0; i < C::MMAS; i++) {
+                        uint4 v = lds_v4(sf + i * 512);
                         a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
                     }
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-#pragma unroll
-                        for (int nb = 0; nb < 2; nb++) {
-                            uint4 v = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 2 + i) * 512);
-                            b[8 * i + 4 * nb] = v.x; b[8 * i + 4 * nb + 1] = v.y; b[8 * i + 4 * nb + 2] = v.z; b[8 * i + 4 * nb + 3] = v.w;
-                        }
-                    {
-                        uint4 v = *reinterpret_cast<const uint4*>(smem_gen + (size_t)stage * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES +
-                                                                  C::SFA_BYTES + C::SFB_BYTES + (q * 32 + lane) * 16);
-                        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
-                    }
-                    c_ld += clock64() - cg;
-                    tc_st_32x8(t_sfa, a);
-                    tc_st_32x16(t_sfb, b);
-                    tc_st_32x4(t_e, e);
-                } else {
-                    uint32_t a[16], b0[16], b1[16];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        uint4 v = *reinterpret_cast<const uint4*>(sf + i * 512);
-                        a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-#pragma unroll
-                        for (int nb = 0; nb < 2; nb++) {
-                            uint4 v = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 4 + i) * 512);
-                            b0[8 * i + 4 * nb] = v.x; b0[8 * i + 4 * nb + 1] = v.y; b0[8 * i + 4 * nb + 2] = v.z; b0[8 * i + 4 * nb + 3] = v.w;
-                            uint4 w = *reinterpret_cast<const uint4*>(sf + C::SFA_BYTES + (nb * 4 + i + 2) * 512);
-                            b1[8 * i + 4 * nb] = w.x; b1[8 * i + 4 * nb + 1] = w.y; b1[8 * i + 4 * nb + 2] = w.z; b1[8 * i + 4 * nb + 3] = w.w;
-                        }
-                    c_ld += clock64() - cg;
-                    tc_st_32x16(t_sfa, a);
-                    tc_st_32x16(t_sfb, b0);
-                    tc_st_32x16(t_sfb + 16, b1);
+                    if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
                 }
-                long long ch = clock64();
+                // SFB: column 4*NBA*i + 4*nb + c  <-  atom (nb, i), word c
+#pragma unroll
+                for (int h = 0; h < (C::MMAS * C::NBA * 4) / 8; h++) {
+                    uint32_t b[8];
+#pragma unroll
+                    for (int w = 0; w < 2; w++) {
+                        const int g = h * 2 + w;               // group of 4 columns
+                        const int i = g / C::NBA, nb = g % C::NBA;
+                        uint4 v = lds_v4(sf + C::SFA_BYTES + (nb * C::MMAS + i) * 512);
+                        b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
+                    }
+                    tc_st_32x8(t_sfb + 8 * h, b);
+                }
+                if constexpr (SPARSE) {
+                    uint32_t e[4];
+                    uint4 v = lds_v4(stageMETA(stage) + (q * 32 + lane) * 16);
+                    e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                    tc_st_32x4(t_e, e);
+                }
                 tc_wait_st();
-                long long ci = clock64();
-                c_st += ci - ch;
                 tc_fence_before();
-                long long ck = clock64();
                 __syncwarp();
-                long long cl = clock64();
                 if (lane == 0) mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
-                long long cj = clock64();
-                c_arr += cj - cl;
-                c_ld += 0;
-                c_fence += ck - ci;
-                c_sw += cl - ck;
-                c_sf += cj - cg;
+                if (warp == 6) QB_EV(kb, 2);
+                c_sf += clock64() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; p.prof[(size_t)blockIdx.x * 8 + 1] += 0; }
-        if (false) { p.prof[(size_t)blockIdx.x * 8 + 0] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 1] = c_sf; p.prof[(size_t)blockIdx.x * 8 + 2] = c_st; p.prof[(size_t)blockIdx.x * 8 + 3] = c_ld; p.prof[(size_t)blockIdx.x * 8 + 5] = c_arr; p.prof[(size_t)blockIdx.x * 8 + 6] = c_fence; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sw; }
+        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         const int q = warp & 3;
         const int r_in_tile = q * 32 + lane;
         const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
-        const uint32_t acce_leader = mapa_shared(acce_bar, 0);
+        int acc = 0;
         uint32_t acc_phase = 0;
         long long c_wait_accf = 0, c_epi = 0;
+        constexpr int NCH = BN / 32;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
-            const int n0 = n * 256;
+            const int n0 = n * BN;
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
             // per-tile constants first, so their latency hides behind the accumulator wait
             const float ga = p.gA ? __ldg(p.gA + o) : 1.f;
-            float gbv[8];
+            float gbv[NCH];
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < NCH; c++) {
                 const int col = n0 + 32 * c + lane;
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
             long long cw = clock64();
-            if (!mbar_wait(accf_bar, acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
             long long cx = clock64();
             c_wait_accf += cx - cw;
             tc_fence_after();
-            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t acce_leader = mapa_shared(acce_bar(acc), 0);
             uint32_t ra[32], rb[32];
             tc_ld_32x32(t_acc, ra);
             auto emit = [&](const uint32_t (&r)[32], int c) {
@@ -721,12 +750,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
             };
 #pragma unroll
-            for (int c = 0; c < 8; c += 2) {
+            for (int c = 0; c < NCH; c += 2) {
                 tc_wait_ld();
                 tc_ld_32x32(t_acc + 32 * (c + 1), rb);
                 emit(ra, c);
                 tc_wait_ld();
-                if (c + 2 < 8) {
+                if (c + 2 < NCH) {
                     tc_ld_32x32(t_acc + 32 * (c + 2), ra);
                 } else {
                     // every column is in registers: hand the accumulator back before the last stores
@@ -737,7 +766,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 emit(rb, c + 1);
             }
             c_epi += clock64() - cx;
-            acc_phase ^= 1;
+            if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
         if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
     }
@@ -860,13 +889,13 @@ static int make_map_u32_rows(CUtensorMap* m, const void* base, uint64_t rows, ui
     return r == CUDA_SUCCESS ? QB_OK : QB_ERR_DRIVER;
 }
 
-template <bool SPARSE>
+template <bool SPARSE, int BN>
 static int launch_pair(const GemmArgs& a, cudaStream_t st) {
-    using C = Cfg2<SPARSE>;
+    using C = Cfg2<SPARSE, BN>;
     static int attr_rc = -1;
     static std::once_flag once;
     std::call_once(once, [] {
-        attr_rc = (int)cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        attr_rc = (int)cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<SPARSE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     });
     if (attr_rc) return attr_rc;
     const int kblocks = (a.K + 255) / 256;
@@ -875,7 +904,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     int rc = make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
                          SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    const uint32_t b_rows = a.tok < 128 ? (uint32_t)a.tok : 128u;
+    const uint32_t b_rows = (uint32_t)C::B_ROWS;
     if ((rc = make_map_u8(&tmB, a.B, (uint64_t)a.K / 2, (uint64_t)a.tok, 128, b_rows, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     if ((rc = make_map_u32_rows(&tmSFA, a.sfa, (uint64_t)(a.a_rows / 128) * atoms_per_rb, C::MMAS))) return rc;
     if ((rc = make_map_u32_rows(&tmSFB, a.sfb, (uint64_t)((a.tok + 127) / 128) * atoms_per_rb, C::MMAS))) return rc;
@@ -886,13 +915,13 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     }
     KParams2 kp;
     kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.out_f = a.out_f; kp.tok = a.tok;
-    kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + 255) / 256; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
+    kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
     kp.prof = g_prof_ptr;
     { const char* e = getenv("QB_DEBUG_SKIP"); kp.dbg = e ? atoi(e) : 0; }
-    nvfp4_gemm_pair_kernel<SPARSE><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
+    nvfp4_gemm_pair_kernel<SPARSE, BN><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
     return (int)cudaGetLastError();
 }
 
@@ -915,10 +944,11 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     // bn == 512 requests it explicitly, bn == 0 (auto) picks it for prefill-sized problems.
     const bool pair_ok = !a.eblk && splits == 1 && (a.out_mode == 0 || a.out_mode == 1) && a.out_f % 256 == 0 && a.tok >= 128 &&
                          b_tail_ok(a.tok);
-    if ((a.bn == 512 && !pair_ok)) return QB_ERR_ARG;
-    if (pair_ok && (a.bn == 512 || (a.bn == 0 && a.tok >= 512))) {
-        return a.sparse ? launch_pair<true>(a, st) : launch_pair<false>(a, st);
-    }
+    if ((a.bn == 512 || a.bn == 384) && !pair_ok) return QB_ERR_ARG;
+    if (pair_ok && (a.bn == 512 || (a.bn == 0 && a.tok >= 512)))   // 512: pair kernel, 256-token tile
+        return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
+    if (pair_ok && a.bn == 384)                                     // 384: pair kernel, 128-token tile, two accumulators
+        return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
     int bn = a.bn;
     if (a.eblk) bn = 128;
     if (bn == 0) bn = a.tok <= 16 ? 16 : a.tok <= 32 ? 32 : a.tok <= 64 ? 64 : 128;
@@ -929,7 +959,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
 
     KParams kp;
     kp.sfa = (const uint8_t*)a.sfa; kp.sfb = (const uint8_t*)a.sfb; kp.meta = (const uint8_t*)a.meta;
-    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.Cf = a.Cf; kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
+    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.Cf = a.Cf; kp.sk_counters = (int*)a.sk_counters; kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
     kp.out_f = a.out_f; kp.tok = a.tok; kp.K = a.K;
     kp.num_m = a.out_f / 128;
     kp.num_n = (a.tok + bn - 1) / bn;
@@ -946,7 +976,9 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
         kp.dbg = dbg;
         kp.prof = g_prof_ptr;
     }
-    if (splits > 1) {
+    const bool slab = splits > 1 && a.sk_counters != nullptr;
+    if (!slab) kp.sk_counters = nullptr;
+    if (splits > 1 && !slab) {
         rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
         if (rc) return rc;
     }
@@ -960,7 +992,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     }
 #undef QB_GO
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && !slab) {
         size_t n = (size_t)a.out_f * a.tok;
         int blocks = (int)((n + 255) / 256);
         if (blocks > sm_count() * 8) blocks = sm_count() * 8;
@@ -968,6 +1000,26 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
         rc = (int)cudaGetLastError();
     }
     return rc;
+}
+
+void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
+    int b = tok <= 16 ? 16 : tok <= 32 ? 32 : tok <= 64 ? 64 : 128;
+    const int num_n = (tok + b - 1) / b;
+    const int tiles = (out_f / 128) * num_n;
+    const int kb = (K + 255) / 256;
+    const int sms = sm_count();
+    int best_s = 1;
+    double best = 1e30;
+    for (int s = 1; s <= kb && s <= 32; s++) {
+        const int per = (kb + s - 1) / s;
+        if (s > 1 && per * (s - 1) >= kb) continue;      // an empty split
+        const int waves = (tiles * s + sms - 1) / sms;
+        // K blocks per unit + ~3 block-times of pipeline fill / epilogue per unit (+1 for the cross-split sum)
+        const double cost = waves * (per + 3.0 + (s > 1 ? 1.0 : 0.0));
+        if (cost < best - 1e-9) { best = cost; best_s = s; }
+    }
+    *splits = best_s;
+    *bn = b;
 }
 
 extern "C" void qb_debug_set_prof(void* p) { g_prof_ptr = (unsigned long long*)p; }

@@ -11,6 +11,11 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
                  cudaStream_t st);
 // cgu: token-major gate/up GEMM output [tok][2*I] bf16 -> Hb[tok][I/2], per-32 scales, gH[tok]
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
+// RMSNorm (+ residual add) fused with the quantiser; res / hout / g may be null (g null = single level)
+int norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
+               int tok, int H, float eps, int block, cudaStream_t st);
+// SwiGLU quantiser over feature-major g, u [hidden][batch]; gH null = single level
+int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st);
 int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st);
 int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st);
 
@@ -31,7 +36,8 @@ struct GemmArgs {
     const float* gA;       // per-row global scale of A (null = 1)
     const float* gB;       // per-row global scale of B (null = 1)
     void* C;               // output
-    float* Cf;             // fp32 split-K workspace [tok][out] (splits > 1)
+    float* Cf;             // fp32 split-K workspace: [tok][out] (atomic mode) or [splits][tok][out] (slab mode)
+    void* sk_counters;     // slab mode: int[4 * tiles], zero before the first call, left zero by the kernel (null = atomic mode)
     const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
     const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
     const float* row_w;    // epilogue 3: fp32 per-routed-row weight [tok] (may be null)
@@ -47,6 +53,8 @@ struct GemmArgs {
 };
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);
 int gemm_init_attrs();
+// splits / token tile that stream the weight over the SMs with the fewest idle waves (thin token counts)
+void decode_plan(int out_f, int tok, int K, int* splits, int* bn);
 int read_status(cudaStream_t st);   // synchronises st and returns + clears the device status word
 
 // ---- qb_moe.cu

@@ -183,6 +183,186 @@ int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* 
     return (int)cudaGetLastError();
 }
 
+// RMSNorm (optionally after a residual add that is written back as the new residual stream)
+// fused with the NVFP4 quantiser: y = (x [+ res]) * rsqrt(mean(.^2) + eps) * w in fp32, quantised
+// per BLOCK without passing through bf16. Replaces rmsnorm_quant_k / add_rmsnorm_quant_k
+// (cuda/sparse_fp4_lib.cu:902-1011, single-level per-32) and, with TWO_LEVEL, also emits the
+// per-token global so the following GEMM runs two-level. One CTA per row, row kept in registers.
+template <int BLOCK, int NJ, bool ADD, bool TWO_LEVEL>
+__global__ void __launch_bounds__(1024) norm_quant_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
+                                                           const uint4* __restrict__ wt, uint4* __restrict__ hout,
+                                                           uint32_t* __restrict__ Bwords, uint8_t* __restrict__ sf_ref,
+                                                           uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok, int H,
+                                                           float eps) {
+    constexpr int LPB = BLOCK / 8, G = 4 * LPB, P = 128 / BLOCK;
+    const int row = blockIdx.x;
+    const int nchunks = H >> 3;
+    const int lane = threadIdx.x & 31;
+    __shared__ float red[32];
+    float v[NJ][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+        if (c < nchunks) { a = __ldg(x + (size_t)row * nchunks + c); if (ADD) b = __ldg(res + (size_t)row * nchunks + c); }
+        const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __bfloat1622float2(ah[i]);
+            if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); f.x = __fadd_rn(f.x, r2.x); f.y = __fadd_rn(f.y, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
+            v[j][2 * i] = f.x; v[j][2 * i + 1] = f.y;
+            ss += f.x * f.x + f.y * f.y;
+        }
+        if (ADD && hout && c < nchunks) hout[(size_t)row * nchunks + c] = o;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    const float rms = rsqrtf(tot / (float)H + eps);
+    float cmax[NJ];
+    float tmax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        uint4 w4 = make_uint4(0, 0, 0, 0);
+        if (c < nchunks) w4 = __ldg(wt + c);
+        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&w4);
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 w2 = __bfloat1622float2(wh[i]);
+            v[j][2 * i] = __fmul_rn(__fmul_rn(v[j][2 * i], rms), w2.x);
+            v[j][2 * i + 1] = __fmul_rn(__fmul_rn(v[j][2 * i + 1], rms), w2.y);
+            m = fmaxf(m, fmaxf(fabsf(v[j][2 * i]), fabsf(v[j][2 * i + 1])));
+        }
+        cmax[j] = m;
+        tmax = fmaxf(tmax, m);
+    }
+    float gl = 1.f;
+    if (TWO_LEVEL) {
+        __syncthreads();
+        tmax = warp_max(tmax);
+        if (lane == 0) red[threadIdx.x >> 5] = tmax;
+        __syncthreads();
+        float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+        r = warp_max(r);
+        gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
+        if (threadIdx.x == 0) g_out[row] = gl;
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        int c = threadIdx.x + j * blockDim.x;
+        float bmax = cmax[j];
+#pragma unroll
+        for (int o = 1; o < LPB; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+        uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax, 6.f));
+        float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) w |= (q_fp4_div(v[j][2 * i], sg) | (q_fp4_div(v[j][2 * i + 1], sg) << 4)) << (8 * i);
+        uint32_t sw = 0;
+        int base = lane & ~(G - 1);
+#pragma unroll
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * LPB) << (8 * i);
+        if (c < nchunks) {
+            Bwords[(size_t)row * nchunks + c] = w;
+            if ((lane & (G - 1)) == 0) {
+                int jcol = c / LPB;
+                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
+                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(H) / BLOCK / 4)) = sw;
+            }
+        }
+    }
+}
+
+int norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
+               int tok, int H, float eps, int block, cudaStream_t st) {
+    if (tok < 0 || H <= 0 || H % 128 != 0 || (block != 16 && block != 32)) return QB_ERR_ARG;
+    if (tok == 0) return QB_OK;
+    if (!x || !wt || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
+    if (((uintptr_t)x & 15) || ((uintptr_t)res & 15) || ((uintptr_t)wt & 15) || ((uintptr_t)hout & 15) || ((uintptr_t)Bbytes & 3) ||
+        ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3))
+        return QB_ERR_ARG;
+    int nchunks = H / 8;
+    int threads = nchunks <= 1024 ? 256 : (nchunks <= 2048 ? 512 : 1024);
+    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
+    int nj = (nchunks + threads - 1) / threads;
+    if (nj > 4) return QB_ERR_UNSUPPORTED;     // H <= 32768
+#define QB_LN3(B, NJ, ADD, TL)                                                                                                   \
+    norm_quant_kernel<B, NJ, ADD, TL><<<tok, threads, 0, st>>>((const uint4*)x, (const uint4*)res, (const uint4*)wt, (uint4*)hout, \
+                                                               (uint32_t*)Bbytes, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)g, tok, H, eps)
+#define QB_LN2(B, NJ) do { if (res) { if (g) QB_LN3(B, NJ, true, true); else QB_LN3(B, NJ, true, false); } \
+                           else { if (g) QB_LN3(B, NJ, false, true); else QB_LN3(B, NJ, false, false); } } while (0)
+#define QB_LN1(B) do { if (nj <= 1) QB_LN2(B, 1); else if (nj <= 2) QB_LN2(B, 2); else QB_LN2(B, 4); } while (0)
+    if (block == 32) QB_LN1(32); else QB_LN1(16);
+#undef QB_LN1
+#undef QB_LN2
+#undef QB_LN3
+    return (int)cudaGetLastError();
+}
+
+// SwiGLU quantisers over the reference's feature-major operands g, u [hidden][batch] (two separate
+// GEMM outputs): fused_swiglu_quant / fused_swiglu_quant_2lvl, cuda/sparse_fp4_lib.cu:794-894.
+// One thread per (token, 32-feature block), tokens fastest so the strided reads coalesce.
+template <bool TWO_LEVEL, bool AMAX_ONLY>
+__global__ void swiglu_fm_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u, uint32_t* __restrict__ Hwords,
+                                 uint8_t* __restrict__ scaleH, float* __restrict__ gH, int batch, int hidden) {
+    const int hb = hidden / 32;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)batch * hb) return;
+    const int hblock = (int)(t / batch), b = (int)(t % batch);
+    const long long base = (long long)(hblock * 32) * batch + b;
+    float val[32], amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        float gv = __bfloat162float(g[base + (long long)i * batch]);
+        float uv = __bfloat162float(u[base + (long long)i * batch]);
+        float h = (gv / (1.f + __expf(-gv))) * uv;
+        val[i] = h;
+        amax = fmaxf(amax, fabsf(h));
+    }
+    if (AMAX_ONLY) { atomicMax(reinterpret_cast<int*>(gH) + b, __float_as_int(amax)); return; }
+    const float gl = TWO_LEVEL ? fmaxf(__fdiv_rn(gH[b], 2688.f), 1e-30f) : 1.f;
+    const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(amax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(amax, 6.f));
+    scaleH[((long long)(hblock / 4) * batch + b) * 4 + (hblock % 4)] = (uint8_t)code;
+    const float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 16; i++) w[i >> 2] |= (q_fp4_div(val[2 * i], sg) | (q_fp4_div(val[2 * i + 1], sg) << 4)) << ((i & 3) * 8);
+    *reinterpret_cast<uint4*>(Hwords + (long long)b * (hidden / 8) + hblock * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__global__ void swiglu_fm_finalize(float* gH, int batch) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) gH[b] = fmaxf(__fdiv_rn(gH[b], 2688.f), 1e-30f);
+}
+
+int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st) {
+    if (batch < 0 || hidden <= 0 || hidden % 128) return QB_ERR_ARG;
+    if (batch == 0) return QB_OK;
+    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 15)) return QB_ERR_ARG;
+    long long total = (long long)batch * (hidden / 32);
+    int blocks = (int)((total + 255) / 256);
+    if (gH) {
+        int rc = (int)cudaMemsetAsync(gH, 0, (size_t)batch * sizeof(float), st);
+        if (rc) return rc;
+        swiglu_fm_kernel<true, true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, nullptr, nullptr, (float*)gH, batch, hidden);
+        // quantise against amax/2688 (read raw amax), then turn gH into the global the GEMM multiplies by
+        swiglu_fm_kernel<true, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, (float*)gH, batch, hidden);
+        swiglu_fm_finalize<<<(batch + 255) / 256, 256, 0, st>>>((float*)gH, batch);
+    } else {
+        swiglu_fm_kernel<false, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, nullptr, batch, hidden);
+    }
+    return (int)cudaGetLastError();
+}
+
 template <int BLOCK, bool TWO_LEVEL>
 static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
                         cudaStream_t st) {

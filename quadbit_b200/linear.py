@@ -44,6 +44,23 @@ def quantize_act(lib, x: torch.Tensor, block: int, two_level: bool = True, want_
     return (Bb, atoms, g, ref) if want_ref else (Bb, atoms, g)
 
 
+DECODE_MAX_TOK = 256
+
+
+def _run_decode(mod, A, meta, sparse, out_f, in_f, Bbytes, sfb, tok, gB):
+    """qb_gemm_decode with a per-module workspace (zeroed once; the kernel keeps its counters clean)."""
+    lib = mod.lib
+    need = lib.qb_gemm_decode_ws_bytes(out_f, tok, in_f)
+    ws = getattr(mod, "_decode_ws", None)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=Bbytes.device)
+        mod._decode_ws = ws
+    C = torch.empty((tok, out_f), dtype=torch.bfloat16, device=Bbytes.device)
+    check(lib.qb_gemm_decode(A.data_ptr(), Bbytes.data_ptr(), mod.sfa.data_ptr(), sfb.data_ptr(), _ptr(meta), mod.gA.data_ptr(),
+                             _ptr(gB), C.data_ptr(), ws.data_ptr(), out_f, tok, in_f, sparse, 1, _stream()), "qb_gemm_decode")
+    return C
+
+
 class QuadbitLinear:
     """Drop-in for nn.Linear(in, out, bias=False): 2:4-sparse two-level NVFP4 weight.
 
@@ -94,11 +111,18 @@ class QuadbitLinear:
               "qb_gemm(sparse)")
         return C
 
+    def run_decode(self, Bbytes, scaleB, tok: int, gB):
+        """Thin-token GEMM (tok <= 256): weight streamed once, K split over the SMs, [tok,out] bf16."""
+        return _run_decode(self, self.Ac, self.meta_native, 1, self.out_f, self.in_f, Bbytes, scaleB, tok, gB)
+
     def forward(self, x: torch.Tensor, splits: int = 1, bn: int = 0) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_f)
         Bb, sB, gB = self.pack_act(x2)
-        return self.run(Bb, sB, x2.shape[0], gB, out_t=True, splits=splits, bn=bn).reshape(*lead, self.out_f)
+        tok = x2.shape[0]
+        if tok <= DECODE_MAX_TOK and splits == 1 and bn == 0:
+            return self.run_decode(Bb, sB, tok, gB).reshape(*lead, self.out_f)
+        return self.run(Bb, sB, tok, gB, out_t=True, splits=splits, bn=bn).reshape(*lead, self.out_f)
 
     __call__ = forward
 
@@ -144,8 +168,14 @@ class DenseNVLinear(torch.nn.Module):
                                self.inn, 0, 1 if out_t else 0, splits, bn, _stream()), "qb_gemm(dense)")
         return C
 
+    def run_decode(self, Bbytes, sfb, tok: int, gB):
+        return _run_decode(self, self.Ab, None, 0, self.out, self.inn, Bbytes, sfb, tok, gB)
+
     def forward(self, x: torch.Tensor, splits: int = 1, bn: int = 0) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.inn)
         Bb, sfb, gB = quantize_act(self.lib, x2, 16, True)
-        return self.run(Bb, sfb, x2.shape[0], gB, out_t=True, splits=splits, bn=bn).reshape(*lead, self.out).to(x.dtype)
+        tok = x2.shape[0]
+        if tok <= DECODE_MAX_TOK and splits == 1 and bn == 0:
+            return self.run_decode(Bb, sfb, tok, gB).reshape(*lead, self.out).to(x.dtype)
+        return self.run(Bb, sfb, tok, gB, out_t=True, splits=splits, bn=bn).reshape(*lead, self.out).to(x.dtype)

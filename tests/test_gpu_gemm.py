@@ -101,6 +101,29 @@ def test_gemm_bf16_outputs_match_fake_quant(lib, sparse, mode, out_f, tok, K, bn
     assert bf16_err(y, ref) < 6e-3
 
 
+PAIR_CASES = [(256, 128, 256, 512), (512, 768, 1024, 512), (256, 300, 1152, 512), (1024, 512, 4096, 0), (768, 1000, 2048, 0),
+              (256, 256, 512, 384), (512, 640, 1024, 384)]
+
+
+@pytest.mark.parametrize("sparse", [1, 0])
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("out_f,tok,K,bn", PAIR_CASES)
+def test_cta_pair_kernel_matches_fake_quant(lib, sparse, mode, out_f, tok, K, bn):
+    """The prefill kernel (tcgen05.mma.cta_group::2; bn 512 / 384 select its 256- / 128-token tile,
+    bn 0 lets the library choose it for tok >= 512) against the oracle and against the single-CTA
+    kernel, which must agree bit for bit (same products, same fp32 accumulation per K block)."""
+    torch.manual_seed(out_f + tok + K + 7)
+    W = torch.randn(out_f, K) * 0.02
+    x = torch.randn(tok, K)
+    ops = native_operands(W, x, sparse)
+    C = gemm(lib, ops, out_f, tok, K, sparse, mode, bn=bn)
+    ref = (fq.linear_sparse if sparse else fq.linear_dense)(x, W)
+    y = C if mode == 1 else C.t()
+    assert bf16_err(y, ref) < 6e-3
+    C1 = gemm(lib, ops, out_f, tok, K, sparse, mode, bn=128)
+    assert bf16_err(C, C1.float().cpu()) < 6e-3
+
+
 @pytest.mark.parametrize("sparse", [1, 0])
 def test_token_major_output_is_bitwise_transpose(lib, sparse):
     """Reference check (harness/verify_sparse_2lvl.py:196-197): the zero-copy [tok,out] output
@@ -126,6 +149,29 @@ def test_split_k_matches_single_pass(lib, sparse, out_f, tok, K, splits):
     assert bf16_err(y, ref) < 6e-3
     y0 = gemm(lib, ops, out_f, tok, K, sparse, 0, splits=splits)
     assert bf16_err(y0.t(), ref) < 6e-3
+
+
+@pytest.mark.parametrize("sparse", [1, 0])
+@pytest.mark.parametrize("out_f,tok,K", [(4096, 1, 4096), (512, 16, 14336), (1024, 64, 2048), (256, 128, 4096), (384, 200, 1152),
+                                          (14336, 16, 512)])
+def test_decode_gemm_single_launch_split_k(lib, sparse, out_f, tok, K):
+    """qb_gemm_decode: K split over CTAs, partial sums in per-split slabs, last arriver reduces.
+    Two calls on one workspace: the arrival counters must be left clean by the first call."""
+    torch.manual_seed(out_f + tok + K + 3)
+    W = torch.randn(out_f, K) * 0.02
+    x = torch.randn(tok, K)
+    ops = native_operands(W, x, sparse)
+    ref = (fq.linear_sparse if sparse else fq.linear_dense)(x, W)
+    ws = torch.zeros(lib.qb_gemm_decode_ws_bytes(out_f, tok, K), dtype=torch.uint8, device="cuda")
+    p = lambda t: 0 if t is None else t.data_ptr()
+    for mode in (1, 0, 1):
+        C = torch.full((tok, out_f) if mode == 1 else (out_f, tok), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rc = lib.qb_gemm_decode(p(ops["A"]), p(ops["B"]), p(ops["sfa"]), p(ops["sfb"]), p(ops["meta"]), p(ops["gA"]), p(ops["gB"]),
+                                p(C), p(ws), out_f, tok, K, sparse, mode, S())
+        assert rc == 0 and lib.qb_status(S()) == 0
+        assert bf16_err(C if mode == 1 else C.t(), ref) < 6e-3
+    ntile = (out_f // 128) * 4 * 2
+    assert int(ws[: ntile * 4].view(torch.int32).abs().sum()) == 0
 
 
 def test_all_ones_known_answer(lib):

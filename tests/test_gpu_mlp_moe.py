@@ -35,9 +35,9 @@ def test_swiglu_quant_kernel_against_oracle():
         assert lib.qb_swiglu_quant(d.data_ptr(), Hb.data_ptr(), sref.data_ptr(), atoms.data_ptr(), gH.data_ptr(), tok, I, S()) == 0
         assert lib.qb_status(S()) == 0
         deq = fq.unpack_act(Hb.cpu(), sref.cpu(), gH.cpu(), 32)
-        want = fq.act_dequant_2lvl(h, 32, round_bf16=False)
-        torch.testing.assert_close(gH.cpu(), (h.abs().amax(-1) / 2688.0).clamp_min(1e-30), rtol=1e-5, atol=0)
-        assert (deq != want).float().mean().item() < 2e-3          # exp() rounding moves a few boundary cases
+        eB, eS, eg = fq.act_quant_2lvl(h, 32, round_bf16=False)
+        torch.testing.assert_close(gH.cpu(), eg, rtol=1e-5, atol=0)
+        assert (Hb.cpu() != eB).float().mean().item() < 5e-3      # exp() rounding moves a few boundary cases
         assert ((deq - h).norm() / h.norm()).item() < 0.12           # FP4 floor
         mask = fq.sf_to_atoms(torch.ones(I // 128, tok, 4, dtype=torch.uint8)).view(-1).bool()
         assert torch.equal(atoms.cpu()[mask], fq.sf_to_atoms(sref.cpu()).view(-1)[mask])
