@@ -95,6 +95,12 @@ struct Cfg {
     static constexpr int CH = (BN % 32 == 0) ? 32 : 8;   // epilogue column chunk
 };
 
+#ifndef QB_BACKOFF
+#define QB_BACKOFF 64
+#endif
+#ifndef QB_BACKOFF_SF
+#define QB_BACKOFF_SF 32
+#endif
 enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4 };
 
 template <bool SPARSE, int BN>
@@ -159,7 +165,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
             for (int kb = kb0; kb < kb1; kb++) {
                 long long ce = clock64();
-                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
                 c_wait_empty += clock64() - ce;
                 if (lane == 0) {
                     uint32_t txx = tx;
@@ -277,7 +283,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
             long long cw = clock64();
-            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
             long long cx = clock64();
             c_wait_accf += cx - cw;
             tc_fence_after();
@@ -318,7 +324,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < C::CH; j += 2) {
                         float g0 = __shfl_sync(0xffffffffu, gbl, j), g1 = __shfl_sync(0xffffffffu, gbl, j + 1);
-                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]) * (ga * g0), __uint_as_float(r[j + 1]) * (ga * g1));
+                        __nv_bfloat162 h = __floats2bfloat162_rn((__uint_as_float(r[j]) * ga) * g0, (__uint_as_float(r[j + 1]) * ga) * g1);
                         pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
                     }
                     const int col0 = n0 + c0;
@@ -345,7 +351,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < C::CH; j++) {
                         float g0 = __shfl_sync(0xffffffffu, gbl, j);
-                        float v = __uint_as_float(r[j]) * (ga * g0);
+                        float v = (__uint_as_float(r[j]) * ga) * g0;
                         if (p.out_mode == 3) v = (v + bias_v) * __shfl_sync(0xffffffffu, rw, j);
                         __nv_bfloat16 h = __float2bfloat16_rn(v);
                         sts_u16(stg_s + j * 80 + lane * 2, *reinterpret_cast<uint16_t*>(&h));
@@ -381,14 +387,31 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (last) {
                     __threadfence();
                     const int ncol = min(BN, p.tok - n0);
-                    for (int j = 0; j < ncol; j++) {
-                        const int col = n0 + j;
-                        float sum = 0.f;
-                        for (int zz = 0; zz < p.splits; zz++) sum += __ldcg(p.Cf + ((size_t)zz * p.tok + col) * p.out_f + o);
-                        const float gb = p.gB ? __ldg(p.gB + col) : 1.f;
-                        const __nv_bfloat16 h = __float2bfloat16_rn(sum * (ga * gb));
-                        if (p.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)o * p.tok + col] = h;
-                        else reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)col * p.out_f + o] = h;
+                    const size_t slab_elems = (size_t)p.tok * p.out_f;
+                    for (int j0 = 0; j0 < ncol; j0 += 16) {
+                        // 16 columns x all splits: independent loads, summed split by split
+                        float sum[16];
+#pragma unroll
+                        for (int jj = 0; jj < 16; jj++) sum[jj] = 0.f;
+                        const float* base = p.Cf + (size_t)(n0 + j0) * p.out_f + o;
+#pragma unroll 4
+                        for (int zz = 0; zz < p.splits; zz++) {
+#pragma unroll
+                            for (int jj = 0; jj < 16; jj++) {
+                                const int jc = (j0 + jj < ncol) ? jj : 0;      // clamp: keep the load unconditional
+                                sum[jj] += __ldcg(base + (size_t)zz * slab_elems + (size_t)jc * p.out_f);
+                            }
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 16; jj++) {
+                            const int col = n0 + j0 + jj;
+                            if (j0 + jj < ncol) {
+                                const float gb = p.gB ? __ldg(p.gB + col) : 1.f;
+                                const __nv_bfloat16 h = __float2bfloat16_rn((sum[jj] * ga) * gb);
+                                if (p.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)o * p.tok + col] = h;
+                                else reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)col * p.out_f + o] = h;
+                            }
+                        }
                     }
                 }
             }
@@ -432,7 +455,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <bool SPARSE, int BN_>
 struct Cfg2 {
     static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
-    static constexpr int THREADS = 320;
+    static constexpr int NPROD = 4;                       // producer warps: warp 0 and warps 10..12
+    static constexpr int NSFG = 1;                        // scale-factor warp groups: warps 6..9 and 13..16, alternating K blocks
+    static constexpr int THREADS = 320 + 32 * (NPROD - 1) + 128 * (NSFG - 1);
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
     static constexpr int B_ROWS = BN / 2;                 // this CTA's half of the token tile
@@ -445,7 +470,8 @@ struct Cfg2 {
     static constexpr int META_BYTES = SPARSE ? 2048 : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + META_BYTES;
     static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
-    static constexpr int EPI_BYTES = 4 * 32 * 80;
+    static constexpr int EPI_PITCH = 144;                 // 32 fp32 + 16 B pad per token row of a warp's transpose tile
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH;
     static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 512;
     static constexpr int SFA_COLS = MMAS * 4;
     static constexpr int SFB_COLS = MMAS * 4 * NBA;
@@ -475,10 +501,11 @@ struct KParams2 {
 };
 
 enum { SITE_SF = 5 };
+#define QB_EV2(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + 128 + ((kbv) - 8) * 8 + (id)] = clock64(); } while (0)
 #define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = clock64(); } while (0)
 
 template <bool SPARSE, int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(416, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
@@ -534,34 +561,44 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int total_tiles = p.num_m2 * p.num_n;
     const int atoms_per_rb = p.kblocks * C::MMAS;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer (both CTAs)
+    if (warp == 0 || (warp >= 10 && warp < 13)) {
+        // ------------------------------------------------------------ producers (both CTAs)
+        // NPROD warps take the K blocks round-robin: one thread needs ~90 cycles to issue one TMA load
+        // (measured), 6-7 loads per stage, so a single producer caps the pipeline at ~1 stage / 900 cycles.
+        const int pw = warp == 0 ? 0 : warp - 9;
         int stage = 0;
         uint32_t phase = 0;
+        uint32_t it = 0;
+        long long pc_wait = 0, pc_ab = 0, pc_t0 = clock64();
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = m2 * 256 + (int)rank * 128;
             const int n0 = n * BN;
             const int rb_a = a_row0 >> 7, rb_b = n0 >> 7;
-            for (int kb = 0; kb < p.kblocks; kb++) {
-                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) break;
-                QB_EV(kb, 0);
-                if (lane == 0) {
-                    const uint32_t fb = full_bar(stage);
-                    const bool skipB = (p.dbg & 2) && kb >= C::STAGES, skipA = (p.dbg & 4) && kb >= C::STAGES;
-                    mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES - (skipB ? C::B_BYTES : 0) - (skipA ? C::A_BYTES : 0));
-                    if (!skipA) tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                    if (!skipB) tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
-                    tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
+            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+                if ((int)(it % C::NPROD) == pw) {
+                    long long pa = clock64();
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
+                    long long pb = clock64();
+                    pc_wait += pb - pa;
+                    if (lane == 0) {
+                        const uint32_t fb = full_bar(stage);
+                        mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES);
+                        tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                        tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
+                        tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
 #pragma unroll
-                    for (int nb = 0; nb < C::NBA; nb++)
-                        tma_load_2d(stageSFB(stage) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
-                    if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
+                        for (int nb = 0; nb < C::NBA; nb++)
+                            tma_load_2d(stageSFB(stage) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
+                        if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
+                    }
+                    __syncwarp();
+                    pc_ab += clock64() - pb;
                 }
-                __syncwarp();
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
+        if (p.prof && lane == 0 && rank == 1 && pw == 0) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[0] = clock64() - pc_t0; o[1] = pc_wait; o[2] = pc_ab; o[3] = 0; }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (rank == 0) {
@@ -601,6 +638,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     }
                     __syncwarp();
                     QB_EV(kb, 5);
+                    if (p.prof && blockIdx.x == 0 && tile == cluster_id && kb >= 8 && kb < 24 && lane == 0) p.prof[2048 + (kb - 8) * 8 + 6] = globaltimer_ns();
                     c_issue += clock64() - cg;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -613,25 +651,37 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
                 o[0] = clock64() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
             }
+        } else if (p.prof && blockIdx.x == 1) {
+            // experiment: the idle MMA warp of the peer CTA timestamps stage releases of the first tile
+            int stage = 0; uint32_t phase = 0;
+            for (int kb = 0; kb < p.kblocks && kb < 24; kb++) {
+                if (!mbar_wait(empty_bar(stage), phase, &abort_flag, &g_status, 13)) break;
+                if (kb >= 8 && lane == 0) p.prof[2048 + (kb - 8) * 8 + 7] = globaltimer_ns();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && (warp < 10 || warp >= 13)) {
         // ------------------------------------------------------------ scale-factor warps (both CTAs)
         const int q = warp & 3;
+        const int sfg = warp >= 13 ? 1 : 0;          // group g takes K-block iterations with it % NSFG == g
+        uint32_t it = 0;
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0;
         uint32_t phase = 0;
-        long long c_wait_full = 0, c_sf = 0;
+        long long c_wait_full = 0, c_sf = 0, c_copy = 0, c_fence = 0, c_sw = 0, c_arr = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks; kb++) {
+            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+                if ((int)(it % C::NSFG) != sfg) { if (++stage == C::STAGES) { stage = 0; phase ^= 1; } continue; }
                 long long cf = clock64();
-                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF)) { ok = false; break; }
+                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF)) { ok = false; break; }
                 long long cg = clock64();
                 c_wait_full += cg - cf;
                 if (warp == 6) QB_EV(kb, 1);
                 const uint32_t sf = stageSFA(stage) + lane * 16;       // this lane's 16 bytes of every atom
                 const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
                 const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                if (!((p.dbg & 1) && kb >= 2)) {
                 // SFA: MMAS atoms -> MMAS*4 consecutive columns
                 {
                     uint32_t a[C::MMAS * 4];
@@ -662,21 +712,28 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     tc_st_32x4(t_e, e);
                 }
                 tc_wait_st();
+                }
+                long long s1 = clock64();
                 tc_fence_before();
+                long long s2 = clock64();
                 __syncwarp();
+                long long s3 = clock64();
                 if (lane == 0) mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
+                long long s4 = clock64();
+                c_copy += s1 - cg; c_fence += s2 - s1; c_sw += s3 - s2; c_arr += s4 - s3;
                 if (warp == 6) QB_EV(kb, 2);
                 c_sf += clock64() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; }
+        if (p.prof && warp == 6 && lane == 0 && rank == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; }
+        if (p.prof && warp == 6 && lane == 0 && rank == 1) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[4] = c_copy; o[5] = c_fence; o[6] = c_sw; o[7] = c_arr; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         const int q = warp & 3;
         const int r_in_tile = q * 32 + lane;
-        const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
+        const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * C::EPI_PITCH);
         int acc = 0;
         uint32_t acc_phase = 0;
         long long c_wait_accf = 0, c_epi = 0;
@@ -695,7 +752,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
             long long cw = clock64();
-            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI)) break;
+            if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
             long long cx = clock64();
             c_wait_accf += cx - cw;
             tc_fence_after();
@@ -712,7 +769,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         float g0 = __shfl_sync(0xffffffffu, gbl, j), g1 = __shfl_sync(0xffffffffu, gbl, j + 1);
-                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j]) * (ga * g0), __uint_as_float(r[j + 1]) * (ga * g1));
+                        __nv_bfloat162 h = __floats2bfloat162_rn((__uint_as_float(r[j]) * ga) * g0, (__uint_as_float(r[j + 1]) * ga) * g1);
                         pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
                     }
                     const int col0 = n0 + c0;
@@ -729,22 +786,26 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             }
                     }
                 } else {
-                    // transpose a 32(out) x 32(tok) block through shared memory -> 16-byte token-major stores
+                    // transpose a 32(out) x 32(tok) fp32 block through shared memory: phase 1 scales by the
+                    // row global and stores one word per value (conflict-free), phase 2 reads 8 features of
+                    // one token, scales by the token global, packs to bf16 and stores 16 bytes token-major
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float g0 = __shfl_sync(0xffffffffu, gbl, j);
-                        __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(r[j]) * (ga * g0));
-                        sts_u16(stg_s + j * 80 + lane * 2, *reinterpret_cast<uint16_t*>(&h));
-                    }
+                    for (int j = 0; j < 32; j++) sts_u32(stg_s + j * C::EPI_PITCH + lane * 4, __float_as_uint(__uint_as_float(r[j]) * ga));
                     __syncwarp();
-                    uint4 val[4];
-#pragma unroll
-                    for (int it = 0; it < 4; it++) val[it] = lds_v4(stg_s + ((it * 32 + lane) >> 2) * 80 + (lane & 3) * 16);
                     __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + o0 + q * 32 + (lane & 3) * 8;
 #pragma unroll
                     for (int it = 0; it < 4; it++) {
-                        const int col = n0 + c0 + ((it * 32 + lane) >> 2);
-                        if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val[it]);
+                        const int trow = (it * 32 + lane) >> 2;
+                        const float gt = __shfl_sync(0xffffffffu, gbl, trow);
+                        const uint4 lo = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32);
+                        const uint4 hi = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32 + 16);
+                        uint4 val;
+                        val.x = pack_bf16x2(__uint_as_float(lo.x) * gt, __uint_as_float(lo.y) * gt);
+                        val.y = pack_bf16x2(__uint_as_float(lo.z) * gt, __uint_as_float(lo.w) * gt);
+                        val.z = pack_bf16x2(__uint_as_float(hi.x) * gt, __uint_as_float(hi.y) * gt);
+                        val.w = pack_bf16x2(__uint_as_float(hi.z) * gt, __uint_as_float(hi.w) * gt);
+                        const int col = n0 + c0 + trow;
+                        if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val);
                     }
                     __syncwarp();
                 }
@@ -768,7 +829,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             c_epi += clock64() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
+        if (p.prof && warp == 2 && lane == 0 && rank == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
     }
 
     // teardown: no CTA may leave while its partner can still signal its barriers
@@ -787,7 +848,7 @@ __global__ void splitk_finish_kernel(const float* __restrict__ Cf, const float* 
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         int o = (int)(i % out_f);
         int t = (int)(i / out_f);
-        float v = Cf[i] * ((gA ? gA[o] : 1.f) * (gB ? gB[t] : 1.f));
+        float v = (Cf[i] * (gA ? gA[o] : 1.f)) * (gB ? gB[t] : 1.f);
         if (out_mode == 0) C[(size_t)o * tok + t] = __float2bfloat16_rn(v);
         else C[i] = __float2bfloat16_rn(v);
     }
@@ -920,7 +981,11 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
     kp.prof = g_prof_ptr;
+#ifdef QB_EXPERIMENT
     { const char* e = getenv("QB_DEBUG_SKIP"); kp.dbg = e ? atoi(e) : 0; }
+#else
+    kp.dbg = 0;
+#endif
     nvfp4_gemm_pair_kernel<SPARSE, BN><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
     return (int)cudaGetLastError();
 }
@@ -972,7 +1037,11 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     kp.out_mode = a.out_mode;
     {
         static int dbg = -1;
+#ifdef QB_EXPERIMENT   // load / copy / epilogue skipping switches used while locating bottlenecks; results are wrong when set
         if (dbg < 0) { const char* e = getenv("QB_DEBUG_SKIP"); dbg = e ? atoi(e) : 0; }
+#else
+        dbg = 0;
+#endif
         kp.dbg = dbg;
         kp.prof = g_prof_ptr;
     }
@@ -1014,8 +1083,10 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
         const int per = (kb + s - 1) / s;
         if (s > 1 && per * (s - 1) >= kb) continue;      // an empty split
         const int waves = (tiles * s + sms - 1) / sms;
-        // K blocks per unit + ~3 block-times of pipeline fill / epilogue per unit (+1 for the cross-split sum)
-        const double cost = waves * (per + 3.0 + (s > 1 ? 1.0 : 0.0));
+        // K blocks per unit + ~3 block-times of pipeline fill / epilogue per unit; the cross-split sum reads
+        // tok * s values per output row from L2, about a K-block time per 48 of them
+        const int ncol = tok < b ? tok : b;
+        const double cost = waves * (per + 3.0 + (s > 1 ? 1.0 + ncol * s / 48.0 : 0.0));
         if (cost < best - 1e-9) { best = cost; best_s = s; }
     }
     *splits = best_s;
