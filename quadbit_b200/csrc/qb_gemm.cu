@@ -7,10 +7,11 @@
 // (cuda/sparse_fp4_lib.cu:1362-1566), which are warp-level mma.sync / mma.sp kernels that
 // do not exist on this architecture.
 //
-// Structure (one persistent CTA per SM, 192 threads):
-//   warp 0      producer: TMA tiles of A (weights, 128 rows) and B (tokens, BN rows) with
-//               hardware swizzle, plus bulk copies of the scale-factor atoms and the 2:4
-//               metadata, into a multi-stage shared-memory ring (mbarrier full/empty).
+// Structure (one persistent CTA per SM, 288 threads):
+//   warp 0, 6-8 producers, K blocks round-robin: TMA tiles of A (weights, 128 rows) and B
+//               (tokens, BN rows) with hardware swizzle, plus bulk copies of the scale-factor
+//               atoms and the 2:4 metadata, into a multi-stage shared-memory ring (mbarrier
+//               full/empty).
 //   warp 1      MMA issuer: one lane copies scale factors / metadata smem -> TMEM
 //               (tcgen05.cp) and issues tcgen05.mma[.sp] kind::mxf4nvf4 block_scale with
 //               the accumulator in TMEM; tcgen05.commit releases smem stages and hands
@@ -101,10 +102,12 @@ struct Cfg {
 #ifndef QB_BACKOFF_SF
 #define QB_BACKOFF_SF 32
 #endif
+constexpr int NPROD1 = 4;                      // producer warps of the single-CTA kernel (warp 0 and warps 6..8)
+constexpr int NTHREADS1 = (6 + NPROD1 - 1) * 32;
 enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4 };
 
 template <bool SPARSE, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(NTHREADS1, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
     using C = Cfg<SPARSE, BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -149,12 +152,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
     const int atoms_per_rb = p.kblocks * C::MMAS;   // scale atoms per 128-row block along K
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ producer
+    if (warp == 0 || warp >= 6) {
+        // ------------------------------------------------------------ producers
+        // Four warps take the K blocks round-robin: one thread needs ~90 cycles to issue one bulk load
+        // (measured) and a stage takes 5-6 of them, so one producer cannot keep a thin-token stream fed.
+        // A producer may run at most one ring revolution ahead of the consumer or the parity wait on the
+        // empty barrier aliases; with in-order consumption that holds iff producers <= stages.
+        constexpr int NP = C::STAGES < NPROD1 ? C::STAGES : NPROD1;
+        const int pw = warp == 0 ? 0 : warp - 5;
         int stage = 0;
         uint32_t phase = 0;
-        long long c_wait_empty = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag && pw < NP; tile += gridDim.x) {
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
             const int n0 = n * BN;
@@ -163,33 +172,27 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int rb0 = n0 >> 7;
             const int nsfb = min(C::NB128, p.sfb_rowblocks - rb0);
             const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
-            for (int kb = kb0; kb < kb1; kb++) {
-                long long ce = clock64();
-                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
-                c_wait_empty += clock64() - ce;
-                if (lane == 0) {
-                    uint32_t txx = tx;
-                    const bool skipA = (p.dbg & 4) && kb >= kb0 + C::STAGES, skipB = (p.dbg & 2) && kb >= kb0 + C::STAGES;
-                    if (skipA) txx -= C::A_BYTES;
-                    if (skipB) txx -= (uint32_t)p.b_box_bytes;
-                    mbar_expect_tx(full_bar(stage), txx);
-                    if (!skipA) tma_load_2d(stageA(stage), &tmA, full_bar(stage), kb * C::A_ROW, a_row0);
-                    if (!skipB) tma_load_2d(stageB(stage), &tmB, full_bar(stage), kb * 128, n0);
-                    bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
-                              C::SFA_BYTES, full_bar(stage));
-                    for (int i = 0; i < nsfb; i++)
-                        bulk_load(stageSFB(stage) + i * C::MMAS * 512,
-                                  p.sfb + ((size_t)(rb0 + i) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::MMAS * 512,
-                                  full_bar(stage));
-                    if (SPARSE)
-                        bulk_load(stageMETA(stage), p.meta + ((size_t)(a_row0 >> 7) * p.kblocks + kb) * 2048, 2048,
-                                  full_bar(stage));
+            for (int kb = kb0; kb < kb1; kb++, it++) {
+                if ((int)(it % NP) == pw) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
+                    if (lane == 0) {
+                        const uint32_t fb = full_bar(stage);
+                        mbar_expect_tx(fb, tx);
+                        tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                        tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0);
+                        bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
+                                  C::SFA_BYTES, fb);
+                        for (int i = 0; i < nsfb; i++)
+                            bulk_load(stageSFB(stage) + i * C::MMAS * 512,
+                                      p.sfb + ((size_t)(rb0 + i) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::MMAS * 512, fb);
+                        if (SPARSE)
+                            bulk_load(stageMETA(stage), p.meta + ((size_t)(a_row0 >> 7) * p.kblocks + kb) * 2048, 2048, fb);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (p.prof && lane == 0) p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_empty;
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         const uint32_t idesc = make_idesc_nvf4(BN, SPARSE);
@@ -481,6 +484,7 @@ struct Cfg2 {
     static constexpr int STAGES_TMEM = 256 / SF_SET;
     static constexpr int STAGES_MIN = STAGES_SMEM < STAGES_TMEM ? STAGES_SMEM : STAGES_TMEM;
     static constexpr int STAGES = STAGES_MIN > 10 ? 10 : STAGES_MIN;
+    static_assert(NPROD <= STAGES, "a producer more than one ring revolution ahead aliases the empty-barrier parity");
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 512;
     static constexpr int TM_SF0 = 256;
     static constexpr int TM_COLS = 512;
@@ -931,7 +935,7 @@ static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     if (rc) return rc;
     int total = kp.num_m * kp.num_n * kp.splits;
     int grid = total < sm_count() ? total : sm_count();
-    nvfp4_gemm_kernel<SPARSE, BN><<<grid, 192, C::SMEM_BYTES, st>>>(tmA, tmB, kp);
+    nvfp4_gemm_kernel<SPARSE, BN><<<grid, NTHREADS1, C::SMEM_BYTES, st>>>(tmA, tmB, kp);
     return (int)cudaGetLastError();
 }
 
