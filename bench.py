@@ -360,6 +360,19 @@ def run_gpu(args):
                             "peak_basis": f"{peak_src} bf16_tflops_sustained {bf16_sust} x 8 (nominal 2:4-sparse FP4 : dense bf16 = 18 : 2.25 PF)",
                             "frac_of_nominal_18PF": value / 18000.0,
                             "kernel": "nvfp4_gemm_pair_kernel<sparse, 256>", "launches_per_step": len(layers)}
+        # second denominator, measured live: the same tcgen05.mma.sp stream with no loads, scale copies or epilogue
+        try:
+            kbp = 2048
+            cyc = torch.zeros(256, dtype=torch.int64, device=dev)
+            stw = torch.zeros(1, dtype=torch.int32, device=dev)
+            tp = ev_time(lambda: lib.qb_mma_peak(1, 256, kbp, 17, cyc.data_ptr(), stw.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream), 3, 2)
+            n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+            issue_peak = 2.0 * 128 * 256 * 256 * kbp * (n_sm // 2 * 2) / tp / 1e12
+            line["roofline"]["mma_issue_only_tflops"] = issue_peak
+            line["roofline"]["frac_of_mma_issue_only"] = value / issue_peak
+        except Exception as e:
+            line["roofline"]["mma_issue_only_tflops"] = f"unavailable ({type(e).__name__})"
 
         # ---- CPU baseline (oracle port), bounded sample
         tok_s = 256

@@ -51,7 +51,8 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, Path]:
         out[flavour] = target
         if not force and not _stale(target):
             continue
-        cmd = [nvcc, *NVCC_FLAGS, *defs, "-o", str(target), *[str(CSRC / s) for s in SOURCES]]
+        extra = os.environ.get("QB_NVCC_EXTRA", "").split()     # developer hook, e.g. -DQB_EXPERIMENT
+        cmd = [nvcc, *NVCC_FLAGS, *defs, *extra, "-o", str(target), *[str(CSRC / s) for s in SOURCES]]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -96,6 +96,12 @@ struct Cfg {
     static constexpr int CH = (BN % 32 == 0) ? 32 : 8;   // epilogue column chunk
 };
 
+// cycle counters of the roles are compiled in only for experiments: the reads sit on the serial paths
+#ifdef QB_PROFILE
+#define QB_CLK() clock64()
+#else
+#define QB_CLK() 0ll
+#endif
 #ifndef QB_BACKOFF
 #define QB_BACKOFF 64
 #endif
@@ -201,23 +207,23 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int acc = 0;
         uint32_t acc_phase = 0;
         uint32_t kiter = 0;
-        long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = clock64();
+        long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = QB_CLK();
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int n = mn / p.num_m;
             const int n0 = n * BN;
             const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
             const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
-            long long ca = clock64();
+            long long ca = QB_CLK();
             if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-            c_wait_acc += clock64() - ca;
+            c_wait_acc += QB_CLK() - ca;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
             bool ok = true;
             for (int kb = kb0; kb < kb1; kb++, kiter++) {
-                long long cf = clock64();
+                long long cf = QB_CLK();
                 if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
-                long long cg = clock64();
+                long long cg = QB_CLK();
                 c_wait_full += cg - cf;
                 tc_fence_after();
                 if (lane == 0) {
@@ -249,7 +255,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     tc_commit(empty_bar(stage));
                 }
                 __syncwarp();
-                c_issue += clock64() - cg;
+                c_issue += QB_CLK() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
@@ -259,7 +265,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         if (p.prof && lane == 0) {
             unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-            o[0] = clock64() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
+            o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -285,9 +291,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int col = n0 + c * C::CH + (lane % C::CH);
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
-            long long cw = clock64();
+            long long cw = QB_CLK();
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
-            long long cx = clock64();
+            long long cx = QB_CLK();
             c_wait_accf += cx - cw;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
@@ -418,7 +424,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     }
                 }
             }
-            c_epi += clock64() - cx;
+            c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
         if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
@@ -459,6 +465,7 @@ template <bool SPARSE, int BN_>
 struct Cfg2 {
     static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
     static constexpr int NPROD = 4;                       // producer warps: warp 0 and warps 10..12
+    static constexpr int KB_BATCH = 1;                    // K blocks the MMA warp issues per barrier wait
     static constexpr int NSFG = 1;                        // scale-factor warp groups: warps 6..9 and 13..16, alternating K blocks
     static constexpr int THREADS = 320 + 32 * (NPROD - 1) + 128 * (NSFG - 1);
     static constexpr int A_ROW = SPARSE ? 64 : 128;
@@ -505,8 +512,8 @@ struct KParams2 {
 };
 
 enum { SITE_SF = 5 };
-#define QB_EV2(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + 128 + ((kbv) - 8) * 8 + (id)] = clock64(); } while (0)
-#define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = clock64(); } while (0)
+#define QB_EV2(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + 128 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
+#define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
 
 template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(416, 1)
@@ -573,7 +580,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         uint32_t it = 0;
-        long long pc_wait = 0, pc_ab = 0, pc_t0 = clock64();
+        long long pc_wait = 0, pc_ab = 0, pc_t0 = QB_CLK();
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = m2 * 256 + (int)rank * 128;
@@ -581,15 +588,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int rb_a = a_row0 >> 7, rb_b = n0 >> 7;
             for (int kb = 0; kb < p.kblocks; kb++, it++) {
                 if ((int)(it % C::NPROD) == pw) {
-                    long long pa = clock64();
+                    long long pa = QB_CLK();
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
-                    long long pb = clock64();
+                    long long pb = QB_CLK();
                     pc_wait += pb - pa;
                     if (lane == 0) {
                         const uint32_t fb = full_bar(stage);
+#ifdef QB_EXPERIMENT
+                        const bool skipA = (p.dbg & 4) && it >= (uint32_t)C::STAGES, skipB = (p.dbg & 2) && it >= (uint32_t)C::STAGES;
+                        mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES - (skipA ? C::A_BYTES : 0) - (skipB ? C::B_BYTES : 0));
+                        if (!skipA) tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                        if (!skipB) tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
+#else
                         mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES);
                         tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
                         tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
+#endif
                         tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
 #pragma unroll
                         for (int nb = 0; nb < C::NBA; nb++)
@@ -597,72 +611,92 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
                     }
                     __syncwarp();
-                    pc_ab += clock64() - pb;
+                    pc_ab += QB_CLK() - pb;
                 }
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
-        if (p.prof && lane == 0 && rank == 1 && pw == 0) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[0] = clock64() - pc_t0; o[1] = pc_wait; o[2] = pc_ab; o[3] = 0; }
+        if (p.prof && lane == 0 && rank == 1 && pw == 0) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[0] = QB_CLK() - pc_t0; o[1] = pc_wait; o[2] = pc_ab; o[3] = 0; }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (rank == 0) {
-            const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
-            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = clock64();
-            for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
-                long long ca = clock64();
-                if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-                c_wait_acc += clock64() - ca;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                bool ok = true;
-                for (int kb = 0; kb < p.kblocks; kb++) {
-                    long long cf = clock64();
-                    QB_EV(kb, 3);
-                    if (!mbar_wait(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
-                    long long cg = clock64();
-                    c_wait_sf += cg - cf;
-                    QB_EV(kb, 4);
+            // One thread runs the whole issue loop: no warp-wide broadcast or re-convergence sits between a
+            // barrier wait and the MMAs it gates.
+            if (lane == 0) {
+                const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
+                int stage = 0, acc = 0;
+                uint32_t phase = 0, acc_phase = 0;
+                long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = QB_CLK();
+#ifdef QB_EXPERIMENT
+                long long c_fence = 0, c_mma = 0, c_commit = 0;
+#endif
+                for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+                    long long ca = QB_CLK();
+                    if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+                    c_wait_acc += QB_CLK() - ca;
                     tc_fence_after();
-                    if (lane == 0) {
-                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
-                        const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                    bool ok = true;
+                    for (int kb = 0; kb < p.kblocks; kb += C::KB_BATCH) {
+                        // One barrier wait covers KB_BATCH K blocks: the scale-factor warps of both CTAs handle
+                        // the stages in ring order, so the last stage's "ready" implies the earlier ones'.
+                        const int nb = min(C::KB_BATCH, p.kblocks - kb);
+                        int ls = stage + nb - 1;
+                        uint32_t lph = phase;
+                        if (ls >= C::STAGES) { ls -= C::STAGES; lph ^= 1; }
+                        long long cf = QB_CLK();
+                        if (!mbar_wait_thread(sfr_bar(ls), lph, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
+                        long long cg = QB_CLK();
+                        c_wait_sf += cg - cf;
+                        tc_fence_after();
+#ifdef QB_EXPERIMENT
+                        long long t1 = QB_CLK();
+                        c_fence += t1 - cg;
+#endif
+                        for (int j = 0; j < nb; j++) {
+                            const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
+                            const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+#ifdef QB_EXPERIMENT
+                            long long t2 = QB_CLK();
+#endif
 #pragma unroll
-                        for (int i = 0; i < C::MMAS; i++) {
-                            const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
-                            const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
-                            const uint32_t accum = (kb > 0 || i > 0) ? 1u : 0u;
-                            if (SPARSE)
-                                tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
-                            else
-                                tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
+                            for (int i = 0; i < C::MMAS; i++) {
+#ifdef QB_EXPERIMENT
+                                if ((p.dbg & 8) && kb >= 2) break;
+#endif
+                                const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                                const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
+                                const uint32_t accum = (kb + j > 0 || i > 0) ? 1u : 0u;
+                                if (SPARSE)
+                                    tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
+                                else
+                                    tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
+                            }
+#ifdef QB_EXPERIMENT
+                            long long t3 = QB_CLK();
+                            tc_commit_pair(empty_bar(stage), 3);
+                            long long t4 = QB_CLK();
+                            c_mma += t3 - t2; c_commit += t4 - t3;
+#else
+                            tc_commit_pair(empty_bar(stage), 3);
+#endif
+                            if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                         }
-                        tc_commit_pair(empty_bar(stage), 3);
+                        c_issue += QB_CLK() - cg;
                     }
-                    __syncwarp();
-                    QB_EV(kb, 5);
-                    if (p.prof && blockIdx.x == 0 && tile == cluster_id && kb >= 8 && kb < 24 && lane == 0) p.prof[2048 + (kb - 8) * 8 + 6] = globaltimer_ns();
-                    c_issue += clock64() - cg;
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    if (!ok) break;
+                    tc_commit_pair(accf_bar(acc), 3);
+                    if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
                 }
-                if (!ok) break;
-                if (lane == 0) tc_commit_pair(accf_bar(acc), 3);
-                __syncwarp();
-                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+                if (p.prof) {
+                    unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
+                    o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
+#ifdef QB_EXPERIMENT
+                    p.prof[4096 + blockIdx.x * 4] = c_fence; p.prof[4096 + blockIdx.x * 4 + 1] = c_mma; p.prof[4096 + blockIdx.x * 4 + 2] = c_commit;
+#endif
+                }
             }
-            if (p.prof && lane == 0) {
-                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-                o[0] = clock64() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
-            }
-        } else if (p.prof && blockIdx.x == 1) {
-            // experiment: the idle MMA warp of the peer CTA timestamps stage releases of the first tile
-            int stage = 0; uint32_t phase = 0;
-            for (int kb = 0; kb < p.kblocks && kb < 24; kb++) {
-                if (!mbar_wait(empty_bar(stage), phase, &abort_flag, &g_status, 13)) break;
-                if (kb >= 8 && lane == 0) p.prof[2048 + (kb - 8) * 8 + 7] = globaltimer_ns();
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-            }
+            __syncwarp();
         }
     } else if (warp >= 6 && (warp < 10 || warp >= 13)) {
         // ------------------------------------------------------------ scale-factor warps (both CTAs)
@@ -677,9 +711,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             bool ok = true;
             for (int kb = 0; kb < p.kblocks; kb++, it++) {
                 if ((int)(it % C::NSFG) != sfg) { if (++stage == C::STAGES) { stage = 0; phase ^= 1; } continue; }
-                long long cf = clock64();
+                long long cf = QB_CLK();
                 if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF)) { ok = false; break; }
-                long long cg = clock64();
+                long long cg = QB_CLK();
                 c_wait_full += cg - cf;
                 if (warp == 6) QB_EV(kb, 1);
                 const uint32_t sf = stageSFA(stage) + lane * 16;       // this lane's 16 bytes of every atom
@@ -717,16 +751,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
                 tc_wait_st();
                 }
-                long long s1 = clock64();
+                long long s1 = QB_CLK();
                 tc_fence_before();
-                long long s2 = clock64();
+                long long s2 = QB_CLK();
                 __syncwarp();
-                long long s3 = clock64();
+                long long s3 = QB_CLK();
                 if (lane == 0) mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
-                long long s4 = clock64();
+                long long s4 = QB_CLK();
                 c_copy += s1 - cg; c_fence += s2 - s1; c_sw += s3 - s2; c_arr += s4 - s3;
                 if (warp == 6) QB_EV(kb, 2);
-                c_sf += clock64() - cg;
+                c_sf += QB_CLK() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
@@ -755,13 +789,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 const int col = n0 + 32 * c + lane;
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
-            long long cw = clock64();
+            long long cw = QB_CLK();
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
-            long long cx = clock64();
+            long long cx = QB_CLK();
             c_wait_accf += cx - cw;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
             const uint32_t acce_leader = mapa_shared(acce_bar(acc), 0);
+#ifdef QB_EXPERIMENT
+            if (p.dbg & 16) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acce_leader);
+                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+                continue;
+            }
+#endif
             uint32_t ra[32], rb[32];
             tc_ld_32x32(t_acc, ra);
             auto emit = [&](const uint32_t (&r)[32], int c) {
@@ -830,7 +873,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
                 emit(rb, c + 1);
             }
-            c_epi += clock64() - cx;
+            c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
         if (p.prof && warp == 2 && lane == 0 && rank == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
@@ -1097,7 +1140,9 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
     *bn = b;
 }
 
+#ifdef QB_EXPERIMENT
 extern "C" void qb_debug_set_prof(void* p) { g_prof_ptr = (unsigned long long*)p; }
+#endif
 
 int read_status(cudaStream_t st) {
     int rc = (int)cudaStreamSynchronize(st);
