@@ -55,6 +55,7 @@ _SIGS = {
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),
+    "qb_sync_probe": ([I] * 2 + [P] * 3, I),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),
     "qb_version": ([], ctypes.c_char_p),

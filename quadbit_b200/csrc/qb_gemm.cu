@@ -443,20 +443,29 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // ------------------------------------------------------------------ CTA-pair kernel (prefill)
 // The prefill kernel: a cluster of two CTAs issues tcgen05.mma.cta_group::2 with M = 256,
 // N = 256. CTA r of the pair owns weight rows [256*m2 + 128*r, +128) and loads only token rows
-// [n0 + 128*r, +128) of B (the pair shares B through the MMA), which makes a stage 29 KB
-// (sparse) / 38 KB (dense) per CTA and leaves room for 7 / 5 stages: measured on the GPU the
-// single-CTA kernel cannot keep enough bytes in flight to cover the ~1.6 us refill round trip
-// at the MMA rate. 320 threads per CTA:
-//   warp 0     producer: plain TMA tile loads (no multicast) of this CTA's A rows, B rows,
-//              scale-factor atoms and metadata, completing on this CTA's full barrier.
-//   warps 6-9  scale-factor warps: copy scale factors / metadata of the landed stage from
-//              shared memory into the stage's own TMEM slot with tcgen05.st (each warp its lane
-//              quadrant) and tell the leader. Measured: a tcgen05.cp costs ~50 cycles of the
-//              MMA pipe and 7-12 of them per K block cap the pipe at 57 % (dense) / 60 %
-//              (sparse) of its MMA-only rate; stores from registers run beside the MMAs.
-//   warp 1     MMA issuer (even CTA only): waits for both CTAs' scale-factor warps, issues the
-//              MMAs for the pair, releases the stage in both CTAs and publishes the accumulator
-//              with multicast commits.
+// [n0 + 128*r, +128) of B (the pair shares B through the MMA).
+//
+// Two rings per CTA. The operand ring (A and B tiles, 24 KB sparse / 32 KB dense per slot, 7 / 5
+// slots) is released by the MMAs that read it. The sideband ring (scale-factor atoms and 2:4
+// metadata, 5-6 KB per slot, 4 slots) is released as soon as its content has been copied into the
+// tensor memory slot of the operand stage, so sideband loads run several K blocks ahead and the
+// copy into tensor memory overlaps the operand loads of the same stage instead of following them.
+// Measured with every MMA, load and epilogue switched off, the barrier round trip
+// (release -> load issue -> landing -> scale-factor copy -> remote arrive -> issue -> commit) is what
+// bounds the K-block rate, so each hop is kept off the others' critical path. 416 threads per CTA:
+//   warp 0     A producer, warp 10 B producer: one TMA tile load per K block each, completing (from
+//              both CTAs) on the LEADER's full barrier; no multicast.
+//   warp 11    sideband producer for scale-factor atoms of A and the metadata, warp 12 for the
+//              scale-factor atoms of B; they complete on this CTA's sideband barrier.
+//   warps 6-9  scale-factor warps: once the sideband slot has landed and the tensor memory slot of
+//              the stage is free, copy scale factors / metadata from shared memory into that slot
+//              with tcgen05.st (each warp its lane quadrant), free the sideband slot and tell the
+//              leader. Measured: a tcgen05.cp costs ~50 cycles of the MMA pipe and 7-12 of them per
+//              K block cap the pipe at 57 % (dense) / 60 % (sparse) of its MMA-only rate; stores
+//              from registers run beside the MMAs.
+//   warp 1     MMA issuer (one thread of the even CTA): waits for the operands of both CTAs and for
+//              both CTAs' scale-factor warps, issues the MMAs for the pair, releases the stage in
+//              both CTAs and publishes the accumulator with multicast commits.
 //   warps 2-5  epilogue: each CTA drains its own 128 x 256 accumulator half (loads of the next
 //              32 columns overlap the conversion of the current ones) and frees it as soon as
 //              the last column is in registers.
@@ -464,10 +473,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <bool SPARSE, int BN_>
 struct Cfg2 {
     static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
-    static constexpr int NPROD = 4;                       // producer warps: warp 0 and warps 10..12
-    static constexpr int KB_BATCH = 1;                    // K blocks the MMA warp issues per barrier wait
-    static constexpr int NSFG = 1;                        // scale-factor warp groups: warps 6..9 and 13..16, alternating K blocks
-    static constexpr int THREADS = 320 + 32 * (NPROD - 1) + 128 * (NSFG - 1);
+    static constexpr int THREADS = 416;                   // 13 warps, roles above
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
     static constexpr int B_ROWS = BN / 2;                 // this CTA's half of the token tile
@@ -478,26 +484,28 @@ struct Cfg2 {
     static constexpr int SFA_BYTES = MMAS * 512;
     static constexpr int SFB_BYTES = NBA * MMAS * 512;    // all BN token rows, in both CTAs
     static constexpr int META_BYTES = SPARSE ? 2048 : 0;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES + META_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;                       // operand ring slot
+    static constexpr int SIDE_BYTES = SFA_BYTES + SFB_BYTES + META_BYTES;       // sideband ring slot
+    static constexpr int NSB = 4;                                               // sideband ring slots
     static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
     static constexpr int EPI_PITCH = 144;                 // 32 fp32 + 16 B pad per token row of a warp's transpose tile
     static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH;
-    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 512;
+    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - NSB * SIDE_BYTES - 512;
     static constexpr int SFA_COLS = MMAS * 4;
     static constexpr int SFB_COLS = MMAS * 4 * NBA;
     static constexpr int E_COLS = SPARSE ? 4 : 0;
-    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // one TMEM slot per smem stage
+    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // one TMEM slot per operand stage
     static constexpr int STAGES_SMEM = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES_TMEM = 256 / SF_SET;
     static constexpr int STAGES_MIN = STAGES_SMEM < STAGES_TMEM ? STAGES_SMEM : STAGES_TMEM;
     static constexpr int STAGES = STAGES_MIN > 10 ? 10 : STAGES_MIN;
-    static_assert(NPROD <= STAGES, "a producer more than one ring revolution ahead aliases the empty-barrier parity");
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 512;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NSB * SIDE_BYTES + EPI_BYTES + 512;
     static constexpr int TM_SF0 = 256;
     static constexpr int TM_COLS = 512;
     static_assert(BN == 128 || BN == 256, "token tile");
     static_assert(ACC_STAGES * BN <= 256 && TM_SF0 + STAGES * SF_SET <= 512, "TMEM budget");
     static_assert(STAGES >= 3, "smem budget");
+    static_assert((3 * STAGES + 2 * NSB + 4) * 8 <= 512, "barrier block");
 };
 
 struct KParams2 {
@@ -511,7 +519,7 @@ struct KParams2 {
     unsigned long long* prof;
 };
 
-enum { SITE_SF = 5 };
+enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
 #define QB_EV2(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + 128 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
 #define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
 
@@ -526,18 +534,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     __shared__ uint32_t tmem_base_slot;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
-    const uint32_t bars = smem0 + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
+    const uint32_t side0 = smem0 + C::STAGES * C::STAGE_BYTES;
+    const uint32_t epi0 = side0 + C::NSB * C::SIDE_BYTES;
+    const uint32_t bars = epi0 + C::EPI_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };                               // leader's is the one used
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-    auto sfr_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + s); };
-    auto accf_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + a); };
-    auto acce_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + 2 + a); };
+    auto sfr_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + s); };               // leader's
+    auto sbf_bar = [&](int j) { return bars + 8u * (3 * C::STAGES + j); };               // sideband slot landed
+    auto sbe_bar = [&](int j) { return bars + 8u * (3 * C::STAGES + C::NSB + j); };      // sideband slot copied out
+    auto accf_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + 2 * C::NSB + a); };
+    auto acce_bar = [&](int a) { return bars + 8u * (3 * C::STAGES + 2 * C::NSB + 2 + a); };
     auto stageA = [&](int s) { return smem0 + (uint32_t)s * C::STAGE_BYTES; };
     auto stageB = [&](int s) { return stageA(s) + C::A_BYTES; };
-    auto stageSFA = [&](int s) { return stageB(s) + C::B_BYTES; };
-    auto stageSFB = [&](int s) { return stageSFA(s) + C::SFA_BYTES; };
-    auto stageMETA = [&](int s) { return stageSFB(s) + C::SFB_BYTES; };
+    auto sideSFA = [&](int j) { return side0 + (uint32_t)j * C::SIDE_BYTES; };
+    auto sideSFB = [&](int j) { return sideSFA(j) + C::SFA_BYTES; };
+    auto sideMETA = [&](int j) { return sideSFB(j) + C::SFB_BYTES; };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -548,9 +559,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < C::STAGES; s++) {
-            mbar_init(full_bar(s), 1);
+            mbar_init(full_bar(s), 2);            // the leader's A and B producers announce both CTAs' bytes
             mbar_init(empty_bar(s), 1);
+#ifdef QB_EXPERIMENT
+            mbar_init(sfr_bar(s), (p.dbg & 64) ? 4 : 8);
+#else
             mbar_init(sfr_bar(s), 8);             // 4 scale-factor warps of each CTA arrive on the leader's
+#endif
+        }
+        for (int j = 0; j < C::NSB; j++) {
+            mbar_init(sbf_bar(j), 2);             // the two sideband producers
+            mbar_init(sbe_bar(j), 4);             // the four scale-factor warps
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(accf_bar(a), 1);
@@ -572,206 +591,214 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int total_tiles = p.num_m2 * p.num_n;
     const int atoms_per_rb = p.kblocks * C::MMAS;
 
-    if (warp == 0 || (warp >= 10 && warp < 13)) {
-        // ------------------------------------------------------------ producers (both CTAs)
-        // NPROD warps take the K blocks round-robin: one thread needs ~90 cycles to issue one TMA load
-        // (measured), 6-7 loads per stage, so a single producer caps the pipeline at ~1 stage / 900 cycles.
-        const int pw = warp == 0 ? 0 : warp - 9;
+    if (warp == 0 || warp == 10) {
+        // ------------------------------------------------------------ operand producers (both CTAs)
+        // warp 0 loads A, warp 10 loads B; one thread needs ~90 cycles to issue one TMA load (measured),
+        // so every load of a stage has its own issuing warp. The loads of both CTAs complete on the
+        // leader's full barrier, whose two arrivals (with the byte count of the pair) come from the
+        // leader's producers; a peer load that lands first only drives the pending count negative.
+        const bool isA = warp == 0;
         int stage = 0;
         uint32_t phase = 0;
-        uint32_t it = 0;
-        long long pc_wait = 0, pc_ab = 0, pc_t0 = QB_CLK();
+        long long c_pw = 0, c_pb = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = m2 * 256 + (int)rank * 128;
-            const int n0 = n * BN;
-            const int rb_a = a_row0 >> 7, rb_b = n0 >> 7;
-            for (int kb = 0; kb < p.kblocks; kb++, it++) {
-                if ((int)(it % C::NPROD) == pw) {
-                    long long pa = QB_CLK();
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
-                    long long pb = QB_CLK();
-                    pc_wait += pb - pa;
-                    if (lane == 0) {
-                        const uint32_t fb = full_bar(stage);
-#ifdef QB_EXPERIMENT
-                        const bool skipA = (p.dbg & 4) && it >= (uint32_t)C::STAGES, skipB = (p.dbg & 2) && it >= (uint32_t)C::STAGES;
-                        mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES - (skipA ? C::A_BYTES : 0) - (skipB ? C::B_BYTES : 0));
-                        if (!skipA) tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                        if (!skipB) tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
-#else
-                        mbar_expect_tx(fb, (uint32_t)C::STAGE_BYTES);
-                        tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                        tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0 + (int)rank * C::B_ROWS);
-#endif
-                        tma_load_2d(stageSFA(stage), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
-#pragma unroll
-                        for (int nb = 0; nb < C::NBA; nb++)
-                            tma_load_2d(stageSFB(stage) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
-                        if (SPARSE) tma_load_2d(stageMETA(stage), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
-                    }
-                    __syncwarp();
-                    pc_ab += QB_CLK() - pb;
-                }
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-            }
-        }
-        if (p.prof && lane == 0 && rank == 1 && pw == 0) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[0] = QB_CLK() - pc_t0; o[1] = pc_wait; o[2] = pc_ab; o[3] = 0; }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (rank == 0) {
-            // One thread runs the whole issue loop: no warp-wide broadcast or re-convergence sits between a
-            // barrier wait and the MMAs it gates.
-            if (lane == 0) {
-                const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
-                int stage = 0, acc = 0;
-                uint32_t phase = 0, acc_phase = 0;
-                long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = QB_CLK();
-#ifdef QB_EXPERIMENT
-                long long c_fence = 0, c_mma = 0, c_commit = 0;
-#endif
-                for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
-                    long long ca = QB_CLK();
-                    if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-                    c_wait_acc += QB_CLK() - ca;
-                    tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                    bool ok = true;
-                    for (int kb = 0; kb < p.kblocks; kb += C::KB_BATCH) {
-                        // One barrier wait covers KB_BATCH K blocks: the scale-factor warps of both CTAs handle
-                        // the stages in ring order, so the last stage's "ready" implies the earlier ones'.
-                        const int nb = min(C::KB_BATCH, p.kblocks - kb);
-                        int ls = stage + nb - 1;
-                        uint32_t lph = phase;
-                        if (ls >= C::STAGES) { ls -= C::STAGES; lph ^= 1; }
-                        long long cf = QB_CLK();
-                        if (!mbar_wait_thread(sfr_bar(ls), lph, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
-                        long long cg = QB_CLK();
-                        c_wait_sf += cg - cf;
-                        tc_fence_after();
-#ifdef QB_EXPERIMENT
-                        long long t1 = QB_CLK();
-                        c_fence += t1 - cg;
-#endif
-                        for (int j = 0; j < nb; j++) {
-                            const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
-                            const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
-#ifdef QB_EXPERIMENT
-                            long long t2 = QB_CLK();
-#endif
-#pragma unroll
-                            for (int i = 0; i < C::MMAS; i++) {
-#ifdef QB_EXPERIMENT
-                                if ((p.dbg & 8) && kb >= 2) break;
-#endif
-                                const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
-                                const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
-                                const uint32_t accum = (kb + j > 0 || i > 0) ? 1u : 0u;
-                                if (SPARSE)
-                                    tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
-                                else
-                                    tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
-                            }
-#ifdef QB_EXPERIMENT
-                            long long t3 = QB_CLK();
-                            tc_commit_pair(empty_bar(stage), 3);
-                            long long t4 = QB_CLK();
-                            c_mma += t3 - t2; c_commit += t4 - t3;
-#else
-                            tc_commit_pair(empty_bar(stage), 3);
-#endif
-                            if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                        }
-                        c_issue += QB_CLK() - cg;
-                    }
-                    if (!ok) break;
-                    tc_commit_pair(accf_bar(acc), 3);
-                    if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
-                }
-                if (p.prof) {
-                    unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-                    o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
-#ifdef QB_EXPERIMENT
-                    p.prof[4096 + blockIdx.x * 4] = c_fence; p.prof[4096 + blockIdx.x * 4 + 1] = c_mma; p.prof[4096 + blockIdx.x * 4 + 2] = c_commit;
-#endif
-                }
-            }
-            __syncwarp();
-        }
-    } else if (warp >= 6 && (warp < 10 || warp >= 13)) {
-        // ------------------------------------------------------------ scale-factor warps (both CTAs)
-        const int q = warp & 3;
-        const int sfg = warp >= 13 ? 1 : 0;          // group g takes K-block iterations with it % NSFG == g
-        uint32_t it = 0;
-        const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
-        int stage = 0;
-        uint32_t phase = 0;
-        long long c_wait_full = 0, c_sf = 0, c_copy = 0, c_fence = 0, c_sw = 0, c_arr = 0;
-        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks; kb++, it++) {
-                if ((int)(it % C::NSFG) != sfg) { if (++stage == C::STAGES) { stage = 0; phase ^= 1; } continue; }
-                long long cf = QB_CLK();
-                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF)) { ok = false; break; }
-                long long cg = QB_CLK();
-                c_wait_full += cg - cf;
-                if (warp == 6) QB_EV(kb, 1);
-                const uint32_t sf = stageSFA(stage) + lane * 16;       // this lane's 16 bytes of every atom
-                const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
-                const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
-                if (!((p.dbg & 1) && kb >= 2)) {
-                // SFA: MMAS atoms -> MMAS*4 consecutive columns
-                {
-                    uint32_t a[C::MMAS * 4];
-#pragma unroll
-                    for (int i = 0; i < C::MMAS; i++) {
-                        uint4 v = lds_v4(sf + i * 512);
-                        a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+            for (int kb = 0; kb < p.kblocks; kb++) {
+                long long q0 = QB_CLK();
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) { ok = false; break; }
+                long long q1 = QB_CLK();
+                if (lane == 0) {
+                    const uint32_t fb = mapa_shared(full_bar(stage), 0);
+#ifdef QB_EXPERIMENT
+                    const bool skip = (p.dbg & (isA ? 4 : 2)) && kb >= 2;
+#else
+                    constexpr bool skip = false;
+#endif
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
+                    if (!skip) {
+                        if (isA) tma_load_2d_pair(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                        else tma_load_2d_pair(stageB(stage), &tmB, fb, kb * 128, b_row0);
                     }
-                    if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
                 }
-                // SFB: column 4*NBA*i + 4*nb + c  <-  atom (nb, i), word c
-#pragma unroll
-                for (int h = 0; h < (C::MMAS * C::NBA * 4) / 8; h++) {
-                    uint32_t b[8];
-#pragma unroll
-                    for (int w = 0; w < 2; w++) {
-                        const int g = h * 2 + w;               // group of 4 columns
-                        const int i = g / C::NBA, nb = g % C::NBA;
-                        uint4 v = lds_v4(sf + C::SFA_BYTES + (nb * C::MMAS + i) * 512);
-                        b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
-                    }
-                    tc_st_32x8(t_sfb + 8 * h, b);
-                }
-                if constexpr (SPARSE) {
-                    uint32_t e[4];
-                    uint4 v = lds_v4(stageMETA(stage) + (q * 32 + lane) * 16);
-                    e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
-                    tc_st_32x4(t_e, e);
-                }
-                tc_wait_st();
-                }
-                long long s1 = QB_CLK();
-                tc_fence_before();
-                long long s2 = QB_CLK();
                 __syncwarp();
-                long long s3 = QB_CLK();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
-                long long s4 = QB_CLK();
-                c_copy += s1 - cg; c_fence += s2 - s1; c_sw += s3 - s2; c_arr += s4 - s3;
-                if (warp == 6) QB_EV(kb, 2);
-                c_sf += QB_CLK() - cg;
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                long long q2 = QB_CLK();
+                c_pw += q1 - q0; c_pb += q2 - q1;
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 6 && lane == 0 && rank == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_wait_full; p.prof[(size_t)blockIdx.x * 8 + 7] = c_sf; }
-        if (p.prof && warp == 6 && lane == 0 && rank == 1) { unsigned long long* o = p.prof + (size_t)blockIdx.x * 8; o[4] = c_copy; o[5] = c_fence; o[6] = c_sw; o[7] = c_arr; }
+        if (p.prof && isA && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 6] = c_pw; p.prof[(size_t)blockIdx.x * 8 + 7] = c_pb; }
+    } else if (warp == 11 || warp == 12) {
+        // ------------------------------------------------------------ sideband producers (both CTAs)
+        const bool isW = warp == 11;               // weight side: scale factors of A and metadata
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int rb_a = (m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
+            bool ok = true;
+            for (int kb = 0; kb < p.kblocks; kb++) {
+                if (!mbar_wait(sbe_bar(slot), phase ^ 1, &abort_flag, &g_status, SITE_SIDE)) { ok = false; break; }
+                if (lane == 0) {
+                    const uint32_t fb = sbf_bar(slot);
+#ifdef QB_EXPERIMENT
+                    if ((p.dbg & 32) && kb >= 2) { mbar_expect_tx(fb, 0u); } else
+#endif
+                    if (isW) {
+                        mbar_expect_tx(fb, (uint32_t)(C::SFA_BYTES + C::META_BYTES));
+                        tma_load_2d(sideSFA(slot), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
+                        if (SPARSE) tma_load_2d(sideMETA(slot), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
+                    } else {
+                        mbar_expect_tx(fb, (uint32_t)C::SFB_BYTES);
+#pragma unroll
+                        for (int nb = 0; nb < C::NBA; nb++)
+                            tma_load_2d(sideSFB(slot) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
+                    }
+                }
+                __syncwarp();
+                if (++slot == C::NSB) { slot = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        // One thread runs the whole issue loop: no warp-wide broadcast or re-convergence sits between a
+        // barrier wait and the MMAs it gates.
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = QB_CLK();
+            for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+                long long ca = QB_CLK();
+                if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+                c_wait_acc += QB_CLK() - ca;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                bool ok = true;
+                for (int kb = 0; kb < p.kblocks; kb++) {
+                    long long cf = QB_CLK();
+                    // both polls in one instruction pair: a poll takes ~100-200 cycles even on a completed
+                    // barrier (measured), back to back the two latencies overlap
+                    if (!mbar_try_wait2(full_bar(stage), phase, sfr_bar(stage), phase) &&
+                        (!mbar_wait_thread(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL) ||
+                         !mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_SF))) { ok = false; break; }
+                    long long cg = QB_CLK();
+                    c_wait_sf += cg - cf;
+                    tc_fence_after();
+                    const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
+                    const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+#pragma unroll
+                    for (int i = 0; i < C::MMAS; i++) {
+#ifdef QB_EXPERIMENT
+                        if ((p.dbg & 8) && kb >= 2) break;
+#endif
+                        const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                        const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
+                        const uint32_t accum = (kb > 0 || i > 0) ? 1u : 0u;
+                        if (SPARSE)
+                            tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
+                        else
+                            tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
+                    }
+#ifdef QB_EXPERIMENT
+                    if (p.dbg & 128) { mbar_arrive(empty_bar(stage)); mbar_arrive_cluster(mapa_shared(empty_bar(stage), 1)); } else
+#endif
+                    tc_commit_pair(empty_bar(stage), 3);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    c_issue += QB_CLK() - cg;
+                }
+                if (!ok) break;
+                tc_commit_pair(accf_bar(acc), 3);
+                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+            if (p.prof) {
+                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
+                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 6 && warp < 10) {
+        // ------------------------------------------------------------ scale-factor warps (both CTAs)
+        const int q = warp & 3;
+        const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+        int stage = 0, slot = 0;
+        uint32_t phase = 0, sphase = 0;
+        long long c_sfw = 0, c_sfb = 0;
+        for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            bool ok = true;
+            for (int kb = 0; kb < p.kblocks; kb++) {
+                long long s0 = QB_CLK();
+                // sideband landed, and the MMAs that read this stage's tensor memory slot one ring
+                // revolution ago have completed (same barrier that frees the operand slot)
+                if (!mbar_try_wait2(sbf_bar(slot), sphase, empty_bar(stage), phase ^ 1) &&
+                    (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF) ||
+                     !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_SF_SLOT))) { ok = false; break; }
+                long long s1 = QB_CLK();
+                tc_fence_after();
+                const uint32_t sf = sideSFA(slot) + lane * 16;       // this lane's 16 bytes of every atom
+                const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
+                const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+#ifdef QB_EXPERIMENT
+                if (!((p.dbg & 1) && kb >= 2))
+#endif
+                {
+                    // SFA: MMAS atoms -> MMAS*4 consecutive columns
+                    {
+                        uint32_t a[C::MMAS * 4];
+#pragma unroll
+                        for (int i = 0; i < C::MMAS; i++) {
+                            uint4 v = lds_v4(sf + i * 512);
+                            a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+                        }
+                        if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
+                    }
+                    // SFB: column 4*NBA*i + 4*nb + c  <-  atom (nb, i), word c
+#pragma unroll
+                    for (int h = 0; h < (C::MMAS * C::NBA * 4) / 8; h++) {
+                        uint32_t b[8];
+#pragma unroll
+                        for (int w = 0; w < 2; w++) {
+                            const int g = h * 2 + w;               // group of 4 columns
+                            const int i = g / C::NBA, nb = g % C::NBA;
+                            uint4 v = lds_v4(sf + C::SFA_BYTES + (nb * C::MMAS + i) * 512);
+                            b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
+                        }
+                        tc_st_32x8(t_sfb + 8 * h, b);
+                    }
+                    if constexpr (SPARSE) {
+                        uint32_t e[4];
+                        uint4 v = lds_v4(sideMETA(slot) + (q * 32 + lane) * 16);
+                        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                        tc_st_32x4(t_e, e);
+                    }
+                    tc_wait_st();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+#ifdef QB_EXPERIMENT
+                    if (!((p.dbg & 64) && rank == 1))
+#endif
+                    mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
+                    mbar_arrive(sbe_bar(slot));
+                }
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (++slot == C::NSB) { slot = 0; sphase ^= 1; }
+                long long s2 = QB_CLK();
+                c_sfw += s1 - s0; c_sfb += s2 - s1;
+            }
+            if (!ok) break;
+        }
+        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_sfw; p.prof[(size_t)blockIdx.x * 8 + 5] = c_sfb; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         const int q = warp & 3;
         const int r_in_tile = q * 32 + lane;
-        const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * C::EPI_PITCH);
+        const uint32_t stg_s = epi0 + (warp - 2) * (32 * C::EPI_PITCH);
         int acc = 0;
         uint32_t acc_phase = 0;
         long long c_wait_accf = 0, c_epi = 0;
@@ -876,7 +903,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (p.prof && warp == 2 && lane == 0 && rank == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
+        if (p.prof && warp == 2 && lane == 0) { p.prof[4096 + (size_t)blockIdx.x * 2] = c_wait_accf; p.prof[4096 + (size_t)blockIdx.x * 2 + 1] = c_epi; }
     }
 
     // teardown: no CTA may leave while its partner can still signal its barriers
