@@ -486,7 +486,7 @@ struct Cfg2 {
     static constexpr int META_BYTES = SPARSE ? 2048 : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;                       // operand ring slot
     static constexpr int SIDE_BYTES = SFA_BYTES + SFB_BYTES + META_BYTES;       // sideband ring slot
-    static constexpr int NSB = 4;                                               // sideband ring slots
+    static constexpr int NSB = 6;                                               // sideband ring slots
     static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
     static constexpr int EPI_PITCH = 144;                 // 32 fp32 + 16 B pad per token row of a warp's transpose tile
     static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH;
@@ -561,11 +561,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int s = 0; s < C::STAGES; s++) {
             mbar_init(full_bar(s), 2);            // the leader's A and B producers announce both CTAs' bytes
             mbar_init(empty_bar(s), 1);
-#ifdef QB_EXPERIMENT
-            mbar_init(sfr_bar(s), (p.dbg & 64) ? 4 : 8);
-#else
             mbar_init(sfr_bar(s), 8);             // 4 scale-factor warps of each CTA arrive on the leader's
-#endif
         }
         for (int j = 0; j < C::NSB; j++) {
             mbar_init(sbf_bar(j), 2);             // the two sideband producers
@@ -591,6 +587,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int total_tiles = p.num_m2 * p.num_n;
     const int atoms_per_rb = p.kblocks * C::MMAS;
 
+    // Every role below handles two K blocks per barrier poll whenever the later one is ready as well: a
+    // poll costs 100-200 cycles even on a completed barrier (measured with the round-trip probe), which
+    // per K block is more than the tensor pipe needs for the MMAs. Ring barriers that are signalled in
+    // ring order (empty, sbe, sfr) are polled for the later block only.
     if (warp == 0 || warp == 10) {
         // ------------------------------------------------------------ operand producers (both CTAs)
         // warp 0 loads A, warp 10 loads B; one thread needs ~90 cycles to issue one TMA load (measured),
@@ -600,37 +600,43 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const bool isA = warp == 0;
         int stage = 0;
         uint32_t phase = 0;
-        long long c_pw = 0, c_pb = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks; kb++) {
-                long long q0 = QB_CLK();
-                if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) { ok = false; break; }
-                long long q1 = QB_CLK();
+            for (int kb = 0; kb < p.kblocks;) {
+                int s1 = stage + 1;
+                uint32_t ph1 = phase;
+                if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
+                int nb = 2;
+                if (kb + 1 >= p.kblocks || !mbar_try_wait(empty_bar(s1), ph1 ^ 1)) {
+                    nb = 1;
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) { ok = false; break; }
+                }
                 if (lane == 0) {
-                    const uint32_t fb = mapa_shared(full_bar(stage), 0);
+                    for (int u = 0; u < nb; u++) {
+                        const int s = u ? s1 : stage;
+                        const uint32_t fb = mapa_shared(full_bar(s), 0);
 #ifdef QB_EXPERIMENT
-                    const bool skip = (p.dbg & (isA ? 4 : 2)) && kb >= 2;
+                        const bool skip = (p.dbg & (isA ? 4 : 2)) && kb >= 2;
 #else
-                    constexpr bool skip = false;
+                        constexpr bool skip = false;
 #endif
-                    if (rank == 0) mbar_expect_tx(full_bar(stage), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
-                    if (!skip) {
-                        if (isA) tma_load_2d_pair(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                        else tma_load_2d_pair(stageB(stage), &tmB, fb, kb * 128, b_row0);
+                        if (rank == 0) mbar_expect_tx(full_bar(s), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
+                        if (!skip) {
+                            if (isA) tma_load_2d_pair(stageA(s), &tmA, fb, (kb + u) * C::A_ROW, a_row0);
+                            else tma_load_2d_pair(stageB(s), &tmB, fb, (kb + u) * 128, b_row0);
+                        }
                     }
                 }
                 __syncwarp();
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                long long q2 = QB_CLK();
-                c_pw += q1 - q0; c_pb += q2 - q1;
+                kb += nb;
+                stage += nb;
+                if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
             }
             if (!ok) break;
         }
-        if (p.prof && isA && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 6] = c_pw; p.prof[(size_t)blockIdx.x * 8 + 7] = c_pb; }
     } else if (warp == 11 || warp == 12) {
         // ------------------------------------------------------------ sideband producers (both CTAs)
         const bool isW = warp == 11;               // weight side: scale factors of A and metadata
@@ -640,26 +646,38 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int rb_a = (m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks; kb++) {
-                if (!mbar_wait(sbe_bar(slot), phase ^ 1, &abort_flag, &g_status, SITE_SIDE)) { ok = false; break; }
+            for (int kb = 0; kb < p.kblocks;) {
+                int j1 = slot + 1;
+                uint32_t ph1 = phase;
+                if (j1 == C::NSB) { j1 = 0; ph1 ^= 1; }
+                int nb = 2;
+                if (kb + 1 >= p.kblocks || !mbar_try_wait(sbe_bar(j1), ph1 ^ 1)) {
+                    nb = 1;
+                    if (!mbar_wait(sbe_bar(slot), phase ^ 1, &abort_flag, &g_status, SITE_SIDE)) { ok = false; break; }
+                }
                 if (lane == 0) {
-                    const uint32_t fb = sbf_bar(slot);
+                    for (int u = 0; u < nb; u++) {
+                        const int j = u ? j1 : slot;
+                        const uint32_t fb = sbf_bar(j);
 #ifdef QB_EXPERIMENT
-                    if ((p.dbg & 32) && kb >= 2) { mbar_expect_tx(fb, 0u); } else
+                        if ((p.dbg & 32) && kb >= 2) { mbar_expect_tx(fb, 0u); } else
 #endif
-                    if (isW) {
-                        mbar_expect_tx(fb, (uint32_t)(C::SFA_BYTES + C::META_BYTES));
-                        tma_load_2d(sideSFA(slot), &tmSFA, fb, 0, rb_a * atoms_per_rb + kb * C::MMAS);
-                        if (SPARSE) tma_load_2d(sideMETA(slot), &tmMETA, fb, 0, (rb_a * p.kblocks + kb) * 4);
-                    } else {
-                        mbar_expect_tx(fb, (uint32_t)C::SFB_BYTES);
+                        if (isW) {
+                            mbar_expect_tx(fb, (uint32_t)(C::SFA_BYTES + C::META_BYTES));
+                            tma_load_2d(sideSFA(j), &tmSFA, fb, 0, rb_a * atoms_per_rb + (kb + u) * C::MMAS);
+                            if (SPARSE) tma_load_2d(sideMETA(j), &tmMETA, fb, 0, (rb_a * p.kblocks + kb + u) * 4);
+                        } else {
+                            mbar_expect_tx(fb, (uint32_t)C::SFB_BYTES);
 #pragma unroll
-                        for (int nb = 0; nb < C::NBA; nb++)
-                            tma_load_2d(sideSFB(slot) + nb * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nb) * atoms_per_rb + kb * C::MMAS);
+                            for (int nbk = 0; nbk < C::NBA; nbk++)
+                                tma_load_2d(sideSFB(j) + nbk * C::MMAS * 512, &tmSFB, fb, 0, (rb_b + nbk) * atoms_per_rb + (kb + u) * C::MMAS);
+                        }
                     }
                 }
                 __syncwarp();
-                if (++slot == C::NSB) { slot = 0; phase ^= 1; }
+                kb += nb;
+                slot += nb;
+                if (slot >= C::NSB) { slot -= C::NSB; phase ^= 1; }
             }
             if (!ok) break;
         }
@@ -679,36 +697,45 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 bool ok = true;
-                for (int kb = 0; kb < p.kblocks; kb++) {
+                for (int kb = 0; kb < p.kblocks;) {
                     long long cf = QB_CLK();
-                    // both polls in one instruction pair: a poll takes ~100-200 cycles even on a completed
-                    // barrier (measured), back to back the two latencies overlap
-                    if (!mbar_try_wait2(full_bar(stage), phase, sfr_bar(stage), phase) &&
-                        (!mbar_wait_thread(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL) ||
-                         !mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_SF))) { ok = false; break; }
+                    int s1 = stage + 1;
+                    uint32_t ph1 = phase;
+                    if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
+                    int nb = 2;
+                    // operands of both blocks landed (loads complete in any order) and the scale factors
+                    // of the later block (hence of both) are in tensor memory
+                    if (kb + 1 >= p.kblocks || !mbar_try_wait3(full_bar(stage), phase, full_bar(s1), ph1, sfr_bar(s1), ph1)) {
+                        nb = 1;
+                        if (!mbar_try_wait2(full_bar(stage), phase, sfr_bar(stage), phase) &&
+                            (!mbar_wait_thread(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL) ||
+                             !mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_SF))) { ok = false; break; }
+                    }
                     long long cg = QB_CLK();
                     c_wait_sf += cg - cf;
                     tc_fence_after();
-                    const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET;
-                    const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                    for (int u = 0; u < nb; u++) {
+                        const int s = u ? s1 : stage;
+                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + s * C::SF_SET;
+                        const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
 #pragma unroll
-                    for (int i = 0; i < C::MMAS; i++) {
+                        for (int i = 0; i < C::MMAS; i++) {
 #ifdef QB_EXPERIMENT
-                        if ((p.dbg & 8) && kb >= 2) break;
+                            if ((p.dbg & 8) && kb >= 2) break;
 #endif
-                        const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
-                        const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
-                        const uint32_t accum = (kb > 0 || i > 0) ? 1u : 0u;
-                        if (SPARSE)
-                            tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
-                        else
-                            tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
+                            const uint64_t adesc = make_smem_desc(stageA(s) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                            const uint64_t bdesc = make_smem_desc(stageB(s) + i * C::B_KSTEP, 1024, 16, 2);
+                            const uint32_t accum = (kb + u > 0 || i > 0) ? 1u : 0u;
+                            if (SPARSE)
+                                tc_mma_nvf4_sp_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, t_e + 2 * i, accum);
+                            else
+                                tc_mma_nvf4_pair(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + 4 * C::NBA * i, accum);
+                        }
+                        tc_commit_pair(empty_bar(s), 3);
                     }
-#ifdef QB_EXPERIMENT
-                    if (p.dbg & 128) { mbar_arrive(empty_bar(stage)); mbar_arrive_cluster(mapa_shared(empty_bar(stage), 1)); } else
-#endif
-                    tc_commit_pair(empty_bar(stage), 3);
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    kb += nb;
+                    stage += nb;
+                    if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
                     c_issue += QB_CLK() - cg;
                 }
                 if (!ok) break;
@@ -727,73 +754,83 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0, slot = 0;
         uint32_t phase = 0, sphase = 0;
-        long long c_sfw = 0, c_sfb = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks; kb++) {
-                long long s0 = QB_CLK();
-                // sideband landed, and the MMAs that read this stage's tensor memory slot one ring
-                // revolution ago have completed (same barrier that frees the operand slot)
-                if (!mbar_try_wait2(sbf_bar(slot), sphase, empty_bar(stage), phase ^ 1) &&
-                    (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF) ||
-                     !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_SF_SLOT))) { ok = false; break; }
-                long long s1 = QB_CLK();
+            for (int kb = 0; kb < p.kblocks;) {
+                int s1 = stage + 1, j1 = slot + 1;
+                uint32_t ph1 = phase, sph1 = sphase;
+                if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
+                if (j1 == C::NSB) { j1 = 0; sph1 ^= 1; }
+                int nb = 2;
+                // sideband slots landed (in any order), and the MMAs that read the later stage's tensor
+                // memory slot one ring revolution ago (hence the earlier stage's too) have completed: the
+                // same barrier that frees the operand slot
+                if (kb + 1 >= p.kblocks || !mbar_try_wait3(sbf_bar(slot), sphase, sbf_bar(j1), sph1, empty_bar(s1), ph1 ^ 1)) {
+                    nb = 1;
+                    if (!mbar_try_wait2(sbf_bar(slot), sphase, empty_bar(stage), phase ^ 1) &&
+                        (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF) ||
+                         !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_SF_SLOT))) { ok = false; break; }
+                }
                 tc_fence_after();
-                const uint32_t sf = sideSFA(slot) + lane * 16;       // this lane's 16 bytes of every atom
-                const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
-                const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
 #ifdef QB_EXPERIMENT
                 if (!((p.dbg & 1) && kb >= 2))
 #endif
                 {
-                    // SFA: MMAS atoms -> MMAS*4 consecutive columns
-                    {
-                        uint32_t a[C::MMAS * 4];
+                    for (int u = 0; u < nb; u++) {
+                        const int s = u ? s1 : stage, j = u ? j1 : slot;
+                        const uint32_t sf = sideSFA(j) + lane * 16;       // this lane's 16 bytes of every atom
+                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + s * C::SF_SET + lane_sel;
+                        const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                        // SFA: MMAS atoms -> MMAS*4 consecutive columns
+                        {
+                            uint32_t a[C::MMAS * 4];
 #pragma unroll
-                        for (int i = 0; i < C::MMAS; i++) {
-                            uint4 v = lds_v4(sf + i * 512);
-                            a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+                            for (int i = 0; i < C::MMAS; i++) {
+                                uint4 v = lds_v4(sf + i * 512);
+                                a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
+                            }
+                            if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
                         }
-                        if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
-                    }
-                    // SFB: column 4*NBA*i + 4*nb + c  <-  atom (nb, i), word c
+                        // SFB: column 4*NBA*i + 4*nb + c  <-  atom (nb, i), word c
 #pragma unroll
-                    for (int h = 0; h < (C::MMAS * C::NBA * 4) / 8; h++) {
-                        uint32_t b[8];
+                        for (int h = 0; h < (C::MMAS * C::NBA * 4) / 8; h++) {
+                            uint32_t b[8];
 #pragma unroll
-                        for (int w = 0; w < 2; w++) {
-                            const int g = h * 2 + w;               // group of 4 columns
-                            const int i = g / C::NBA, nb = g % C::NBA;
-                            uint4 v = lds_v4(sf + C::SFA_BYTES + (nb * C::MMAS + i) * 512);
-                            b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
+                            for (int w = 0; w < 2; w++) {
+                                const int g = h * 2 + w;               // group of 4 columns
+                                const int i = g / C::NBA, nbk = g % C::NBA;
+                                uint4 v = lds_v4(sf + C::SFA_BYTES + (nbk * C::MMAS + i) * 512);
+                                b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
+                            }
+                            tc_st_32x8(t_sfb + 8 * h, b);
                         }
-                        tc_st_32x8(t_sfb + 8 * h, b);
-                    }
-                    if constexpr (SPARSE) {
-                        uint32_t e[4];
-                        uint4 v = lds_v4(sideMETA(slot) + (q * 32 + lane) * 16);
-                        e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
-                        tc_st_32x4(t_e, e);
+                        if constexpr (SPARSE) {
+                            uint32_t e[4];
+                            uint4 v = lds_v4(sideMETA(j) + (q * 32 + lane) * 16);
+                            e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                            tc_st_32x4(t_e, e);
+                        }
                     }
                     tc_wait_st();
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-#ifdef QB_EXPERIMENT
-                    if (!((p.dbg & 64) && rank == 1))
-#endif
                     mbar_arrive_cluster(mapa_shared(sfr_bar(stage), 0));
                     mbar_arrive(sbe_bar(slot));
+                    if (nb == 2) {
+                        mbar_arrive_cluster(mapa_shared(sfr_bar(s1), 0));
+                        mbar_arrive(sbe_bar(j1));
+                    }
                 }
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
-                if (++slot == C::NSB) { slot = 0; sphase ^= 1; }
-                long long s2 = QB_CLK();
-                c_sfw += s1 - s0; c_sfb += s2 - s1;
+                kb += nb;
+                stage += nb;
+                if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
+                slot += nb;
+                if (slot >= C::NSB) { slot -= C::NSB; sphase ^= 1; }
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 6 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 4] = c_sfw; p.prof[(size_t)blockIdx.x * 8 + 5] = c_sfb; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         const int q = warp & 3;
