@@ -473,7 +473,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <bool SPARSE, int BN_>
 struct Cfg2 {
     static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
-    static constexpr int THREADS = 416;                   // 13 warps, roles above
+    static constexpr int THREADS = 544;                   // 17 warps, roles above
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
     static constexpr int B_ROWS = BN / 2;                 // this CTA's half of the token tile
@@ -489,7 +489,7 @@ struct Cfg2 {
     static constexpr int NSB = 6;                                               // sideband ring slots
     static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
     static constexpr int EPI_PITCH = 144;                 // 32 fp32 + 16 B pad per token row of a warp's transpose tile
-    static constexpr int EPI_BYTES = 4 * 32 * EPI_PITCH;
+    static constexpr int EPI_BYTES = 8 * 16 * EPI_PITCH;  // eight epilogue warps, 16 token rows each
     static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - NSB * SIDE_BYTES - 512;
     static constexpr int SFA_COLS = MMAS * 4;
     static constexpr int SFB_COLS = MMAS * 4 * NBA;
@@ -524,7 +524,7 @@ enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
 #define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
 
 template <bool SPARSE, int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(416, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(544, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
@@ -569,7 +569,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(accf_bar(a), 1);
-            mbar_init(acce_bar(a), 8);            // 4 epilogue warps of each CTA arrive on the leader's
+            mbar_init(acce_bar(a), 16);           // 8 epilogue warps of each CTA arrive on the leader's
         }
         fence_barrier_init();
         tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
@@ -833,16 +833,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
+        // Eight warps: warps 2-5 drain the first half of the tile's columns, warps 13-16 the second half;
+        // a warp reads the TMEM lane quadrant (warp % 4) it is allowed to.
         const int q = warp & 3;
+        const int half = warp >= 13 ? 1 : 0;
+        const int ew = half ? 4 + (warp - 13) : warp - 2;
         const int r_in_tile = q * 32 + lane;
-        const uint32_t stg_s = epi0 + (warp - 2) * (32 * C::EPI_PITCH);
+        const uint32_t stg_s = epi0 + ew * (16 * C::EPI_PITCH);
         int acc = 0;
         uint32_t acc_phase = 0;
         long long c_wait_accf = 0, c_epi = 0;
-        constexpr int NCH = BN / 32;
+        constexpr int HCOLS = BN / 2;          // columns per warp
+        constexpr int NCH = HCOLS / 16;        // chunks of 16 columns
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
-            const int n0 = n * BN;
+            const int n0 = n * BN + half * HCOLS;          // first token column of this warp
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
             // per-tile constants first, so their latency hides behind the accumulator wait
@@ -850,7 +855,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             float gbv[NCH];
 #pragma unroll
             for (int c = 0; c < NCH; c++) {
-                const int col = n0 + 32 * c + lane;
+                const int col = n0 + 16 * c + (lane & 15);
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
             long long cw = QB_CLK();
@@ -858,7 +863,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             long long cx = QB_CLK();
             c_wait_accf += cx - cw;
             tc_fence_after();
-            const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN + half * HCOLS) + ((uint32_t)(q * 32) << 16);
             const uint32_t acce_leader = mapa_shared(acce_bar(acc), 0);
 #ifdef QB_EXPERIMENT
             if (p.dbg & 16) {
@@ -869,43 +874,42 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 continue;
             }
 #endif
-            uint32_t ra[32], rb[32];
-            tc_ld_32x32(t_acc, ra);
-            auto emit = [&](const uint32_t (&r)[32], int c) {
-                const int c0 = 32 * c;
+            uint32_t ra[16], rb[16];
+            tc_ld_32x16(t_acc, ra);
+            auto emit = [&](const uint32_t (&r)[16], int c) {
+                const int c0 = 16 * c;
                 const float gbl = gbv[c];
                 if (p.out_mode == 0) {
                     __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)o * p.tok;
-                    uint32_t pk[16];
+                    uint32_t pk[8];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
+                    for (int j = 0; j < 16; j += 2) {
                         float g0 = __shfl_sync(0xffffffffu, gbl, j), g1 = __shfl_sync(0xffffffffu, gbl, j + 1);
-                        __nv_bfloat162 h = __floats2bfloat162_rn((__uint_as_float(r[j]) * ga) * g0, (__uint_as_float(r[j + 1]) * ga) * g1);
-                        pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+                        pk[j / 2] = pack_bf16x2((__uint_as_float(r[j]) * ga) * g0, (__uint_as_float(r[j + 1]) * ga) * g1);
                     }
                     const int col0 = n0 + c0;
-                    if (col0 + 32 <= p.tok && (p.tok & 7) == 0) {
+                    if (col0 + 16 <= p.tok && (p.tok & 7) == 0) {
 #pragma unroll
-                        for (int v = 0; v < 4; v++)
+                        for (int v = 0; v < 2; v++)
                             *reinterpret_cast<uint4*>(Cp + col0 + 8 * v) = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
+                        for (int j = 0; j < 16; j++)
                             if (col0 + j < p.tok) {
                                 uint32_t w = pk[j / 2];
                                 reinterpret_cast<uint16_t*>(Cp)[col0 + j] = (j & 1) ? (uint16_t)(w >> 16) : (uint16_t)(w & 0xffff);
                             }
                     }
                 } else {
-                    // transpose a 32(out) x 32(tok) fp32 block through shared memory: phase 1 scales by the
+                    // transpose a 32(out) x 16(tok) fp32 block through shared memory: phase 1 scales by the
                     // row global and stores one word per value (conflict-free), phase 2 reads 8 features of
                     // one token, scales by the token global, packs to bf16 and stores 16 bytes token-major
 #pragma unroll
-                    for (int j = 0; j < 32; j++) sts_u32(stg_s + j * C::EPI_PITCH + lane * 4, __float_as_uint(__uint_as_float(r[j]) * ga));
+                    for (int j = 0; j < 16; j++) sts_u32(stg_s + j * C::EPI_PITCH + lane * 4, __float_as_uint(__uint_as_float(r[j]) * ga));
                     __syncwarp();
                     __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + o0 + q * 32 + (lane & 3) * 8;
 #pragma unroll
-                    for (int it = 0; it < 4; it++) {
+                    for (int it = 0; it < 2; it++) {
                         const int trow = (it * 32 + lane) >> 2;
                         const float gt = __shfl_sync(0xffffffffu, gbl, trow);
                         const uint4 lo = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32);
@@ -924,11 +928,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
             for (int c = 0; c < NCH; c += 2) {
                 tc_wait_ld();
-                tc_ld_32x32(t_acc + 32 * (c + 1), rb);
+                tc_ld_32x16(t_acc + 16 * (c + 1), rb);
                 emit(ra, c);
                 tc_wait_ld();
                 if (c + 2 < NCH) {
-                    tc_ld_32x32(t_acc + 32 * (c + 2), ra);
+                    tc_ld_32x16(t_acc + 16 * (c + 2), ra);
                 } else {
                     // every column is in registers: hand the accumulator back before the last stores
                     tc_fence_before();
