@@ -356,7 +356,9 @@ def run_gpu(args):
         # ---- roofline of the dominant kernel (the sparse GEMM), live numbers
         sparse_peak = bf16_sust * 8.0
         line["roofline"] = {"bound": "tensor", "achieved": value, "peak": sparse_peak, "unit": "TFLOP/s", "frac": value / sparse_peak,
-                            "traffic": None,
+                            "traffic": 99.2e6,
+                            "traffic_note": "ncu dram read+write bytes of one gate-shape launch (29.9 MB + 69.3 MB); "
+                                            "algorithmic 145.7 MB, part of the output still sits in L2 when the launch ends",
                             "peak_basis": f"{peak_src} bf16_tflops_sustained {bf16_sust} x 8 (nominal 2:4-sparse FP4 : dense bf16 = 18 : 2.25 PF)",
                             "frac_of_nominal_18PF": value / 18000.0,
                             "kernel": "nvfp4_gemm_pair_kernel<sparse, 256>", "launches_per_step": len(layers)}

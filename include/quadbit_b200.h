@@ -198,7 +198,8 @@ int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, 
  * CTA through shared::cta mbarriers; 1: the two CTAs through mbarrier.arrive.shared::cluster;
  * 2: tcgen05.commit multicast to the peer and a remote arrive back; 3: mode 0 with the warp-wide
  * wait; 4: one thread, arrive then a try_wait that succeeds at once; 5: the same on two barriers with
- * the two try_waits back to back. Bounded waits; asynchronous on `stream`. */
+ * the two try_waits back to back; 6+n: mode 0 with n (<= 14) more warps polling an incomplete barrier.
+ * Bounded waits; asynchronous on `stream`. */
 int qb_sync_probe(int mode, int iters, void* cycles_out, void* status_word, void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);

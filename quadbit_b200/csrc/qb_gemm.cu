@@ -1206,6 +1206,9 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
     }
     *splits = best_s;
     *bn = b;
+#ifdef QB_EXPERIMENT
+    { const char* e = getenv("QB_DECODE_SPLITS"); if (e && atoi(e) > 0 && atoi(e) <= kb) *splits = atoi(e); }
+#endif
 }
 
 #ifdef QB_EXPERIMENT

@@ -8,6 +8,7 @@
 //   mode 3  as mode 0 with the warp-wide wait
 //   mode 4  one thread: arrive on its own barrier, then a try_wait that succeeds at once
 //   mode 5  one thread: two barriers, both arrives, then both try_waits issued back to back
+//   mode 6+n  mode 0 while n further warps (n <= 14) of each CTA poll a barrier that stays incomplete
 // Every wait is bounded; on expiry the status word gets QB_ERR_TIMEOUT * 100 + 50 + mode.
 #include <cuda.h>
 
@@ -17,11 +18,12 @@
 
 namespace qb {
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
 sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
     __shared__ volatile int abort_flag;
     __shared__ uint32_t tmem_slot;
-    __shared__ __align__(8) unsigned long long bar_mem[2];
+    __shared__ __align__(8) unsigned long long bar_mem[3];
+    __shared__ volatile int stop_flag;
     const uint32_t barA = smem_u32(&bar_mem[0]), barB = smem_u32(&bar_mem[1]);
     const uint32_t rank = cluster_ctarank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -29,6 +31,8 @@ sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
         abort_flag = 0;
         mbar_init(barA, 1);
         mbar_init(barB, 1);
+        mbar_init(smem_u32(&bar_mem[2]), 1);
+        stop_flag = 0;
         fence_barrier_init();
     }
     if (warp == 0) { tmem_alloc_pair(smem_u32(&tmem_slot), 32); tmem_relinquish_pair(); }
@@ -37,7 +41,15 @@ sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
     tc_fence_after();
     const uint64_t limit = 200000000ull;   // 0.2 s per wait
     const int site = 50 + mode;
+    if (warp >= 2) {
+        // background pollers (modes 6+): warps 2.. poll a barrier that nobody completes until warp 0 raises
+        // the stop flag; at most 2^22 polls each
+        const uint32_t barC = smem_u32(&bar_mem[2]);
+        for (int i = 0; i < (1 << 22) && !stop_flag; i++)
+            if (mbar_try_wait(barC, 0)) break;
+    }
     long long t0 = clock64();
+    if (mode >= 6) mode = 0;
     if (mode == 0 || mode == 3) {
         if (rank == 0) {
             if (warp == 0) {
@@ -46,7 +58,7 @@ sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
                     if (mode == 0) { if (lane == 0 && !mbar_wait_thread(barB, i & 1, &abort_flag, status, site, limit)) break; }
                     else if (!mbar_wait(barB, i & 1, &abort_flag, status, site, 0, limit)) break;
                 }
-            } else {
+            } else if (warp == 1) {
                 for (int i = 0; i < iters && !abort_flag; i++) {
                     if (mode == 0) { if (lane == 0 && !mbar_wait_thread(barA, i & 1, &abort_flag, status, site, limit)) break; }
                     else if (!mbar_wait(barA, i & 1, &abort_flag, status, site, 0, limit)) break;
@@ -81,6 +93,7 @@ sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
         }
     }
     long long t1 = clock64();
+    if (warp == 0) stop_flag = 1;
     if (rank == 0 && threadIdx.x == 0) { out[0] = (unsigned long long)(t1 - t0); out[1] = (unsigned long long)iters; }
     __syncwarp();
     tc_fence_before();
@@ -91,7 +104,8 @@ sync_probe_kernel(int mode, int iters, unsigned long long* out, int* status) {
 }  // namespace qb
 
 extern "C" int qb_sync_probe(int mode, int iters, void* cycles_out, void* status_word, void* stream) {
-    if (mode < 0 || mode > 5 || iters <= 0 || iters > (1 << 20) || !cycles_out || !status_word) return QB_ERR_ARG;
-    qb::sync_probe_kernel<<<2, 64, 0, (cudaStream_t)stream>>>(mode, iters, (unsigned long long*)cycles_out, (int*)status_word);
+    if (mode < 0 || mode > 6 + 14 || iters <= 0 || iters > (1 << 20) || !cycles_out || !status_word) return QB_ERR_ARG;
+    const int extra = mode >= 6 ? mode - 6 : 0;      // mode 6 + n: mode 0 with n background polling warps
+    qb::sync_probe_kernel<<<2, 64 + 32 * extra, 0, (cudaStream_t)stream>>>(mode, iters, (unsigned long long*)cycles_out, (int*)status_word);
     return (int)cudaGetLastError();
 }
