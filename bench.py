@@ -215,13 +215,13 @@ def run_gpu(args):
     def gemm_into(L, bn=0):
         lin = L["lin"]
         if isinstance(lin, qb.DenseNVLinear):
-            rc = lib.qb_gemm(lin.Ab.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(), 0, lin.gA.data_ptr(),
-                             L["gB"].data_ptr(), L["out"].data_ptr(), 0, 0, 0, 0, lin.out, lin.out, TOK, lin.inn, 0, 1, 1, bn,
+            rc = lib.qb_gemm(lin.At.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(), 0, lin.gA.data_ptr(),
+                             L["gB"].data_ptr(), L["out"].data_ptr(), 0, 0, 0, 0, lin.out, lin.out, TOK, lin.inn, 2, 1, 1, bn,
                              torch.cuda.current_stream().cuda_stream)
         else:
-            rc = lib.qb_gemm(lin.Ac.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(),
+            rc = lib.qb_gemm(lin.At.data_ptr(), L["Bb"].data_ptr(), lin.sfa.data_ptr(), L["sB"].data_ptr(),
                              lin.meta_native.data_ptr(), lin.gA.data_ptr(), L["gB"].data_ptr(), L["out"].data_ptr(), 0, 0, 0, 0,
-                             lin.out_f, lin.out_f, TOK, lin.in_f, 1, 1, 1, bn, torch.cuda.current_stream().cuda_stream)
+                             lin.out_f, lin.out_f, TOK, lin.in_f, 3, 1, 1, bn, torch.cuda.current_stream().cuda_stream)
         if rc:
             raise RuntimeError(f"qb_gemm rc {rc}")
         launches[0] += 1

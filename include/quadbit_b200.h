@@ -142,6 +142,14 @@ long long qb_meta_native_bytes(int out, int K);
 int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
             const void* gB, void* C, void* Cf, const void* eblk, const void* bias, const void* row_w, int a_rows, int out,
             int tok, int K, int sparse, int out_mode, int splits, int bn, void* stream);
+/* Tiled weight layout (no reference counterpart: the reference keeps packed weight rows row-major).
+ * Re-lays A[rows][K/4 (sparse) or K/2 (dense)] as contiguous 128-row x 256-K tiles
+ * [rows/128][ceil(K/256)][128][64 or 128 B], zero beyond K, so that one pipeline stage of the GEMM is one
+ * contiguous 8 / 16 KB read (weight streaming at thin token counts otherwise reads 128-byte pieces at a
+ * stride of a whole row). qb_gemm / qb_gemm_decode take the tiled array as A when bit 1 of `sparse` is set
+ * (sparse = 2: dense tiled, 3: 2:4-sparse tiled). rows % 128 == 0, K % 128 == 0, 16-byte aligned pointers. */
+int qb_tile_weights(const void* A, void* A_tiled, int rows, int K, int sparse, void* stream);
+long long qb_tiled_weight_bytes(int rows, int K, int sparse);
 /* Thin-token (decode) GEMM: streams the weight once with the K range split over CTAs so that all SMs
  * pull from HBM; each split writes fp32 partial sums to its own slab of `ws` and the last split to
  * arrive for a tile sums them and writes bf16 (one launch: no memset, no finish pass). The split

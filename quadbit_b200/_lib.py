@@ -51,6 +51,8 @@ _SIGS = {
     "qb_swiglu_quant": ([P] * 5 + [I] * 2 + [P], I),
     "qb_fused_mlp": ([P] * 18 + [I] * 6 + [P], I),
     "qb_gemm_decode": ([P] * 9 + [I] * 5 + [P], I),
+    "qb_tile_weights": ([P] * 2 + [I] * 3 + [P], I),
+    "qb_tiled_weight_bytes": ([I] * 3, c_longlong),
     "qb_gemm_decode_ws_bytes": ([I] * 3, c_longlong),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),

@@ -198,7 +198,8 @@ int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, cons
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
     g.C = C; g.Cf = (float*)Cf; g.eblk = (const int*)eblk; g.bias = bias; g.row_w = (const float*)row_w;
-    g.a_rows = a_rows; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode; g.splits = splits;
+    g.a_rows = a_rows; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse & 1; g.a_tiled = (sparse >> 1) & 1;
+    g.out_mode = out_mode; g.splits = splits;
     g.bn = bn;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
@@ -223,8 +224,16 @@ int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sf
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
     g.C = C; g.sk_counters = ws; g.Cf = (float*)((uint8_t*)ws + decode_counter_bytes(out, tok));
-    g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode; g.splits = splits; g.bn = bn;
+    g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse & 1; g.a_tiled = (sparse >> 1) & 1;
+    g.out_mode = out_mode; g.splits = splits; g.bn = bn;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
+}
+int qb_tile_weights(const void* A, void* A_tiled, int rows, int K, int sparse, void* stream) {
+    return qb::tile_weights(A, A_tiled, rows, K, sparse, (cudaStream_t)stream);
+}
+long long qb_tiled_weight_bytes(int rows, int K, int sparse) {
+    if (rows <= 0 || K <= 0 || rows % 128) return -1;
+    return (long long)rows * (((K + 255) & ~255) / 256) * (sparse ? 64 : 128);
 }
 int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {

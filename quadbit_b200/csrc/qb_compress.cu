@@ -247,4 +247,36 @@ int pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atom
     return (int)cudaGetLastError();
 }
 
+// 16 bytes per thread: dst chunk index -> (tile, row, chunk) -> source row / byte offset
+__global__ void tile_weights_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int rows, int row_bytes, int kblocks,
+                                    int a_row) {
+    const int cpr = a_row / 16;                                   // 16-byte chunks per tile row
+    const size_t n = (size_t)rows * kblocks * cpr;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cpr);
+        const size_t t = i / cpr;
+        const int r = (int)(t % 128);
+        const size_t tile = t / 128;
+        const int kb = (int)(tile % kblocks);
+        const int rb = (int)(tile / kblocks);
+        const int byte = kb * a_row + c * 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (byte < row_bytes) v = src[((size_t)(rb * 128 + r) * row_bytes + byte) / 16];
+        dst[i] = v;
+    }
+}
+
+int tile_weights(const void* A, void* At, int rows, int K, int sparse, cudaStream_t st) {
+    if (rows <= 0 || K <= 0 || rows % 128 || K % 128) return QB_ERR_ARG;
+    if (!A || !At || ((uintptr_t)A & 15) || ((uintptr_t)At & 15)) return QB_ERR_ARG;
+    const int row_bytes = sparse ? K / 4 : K / 2;                 // multiple of 32 for K % 128 == 0
+    const int a_row = sparse ? 64 : 128;
+    const int kblocks = kpad256(K) / 256;
+    const size_t n = (size_t)rows * kblocks * (a_row / 16);
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    tile_weights_kernel<<<blocks, 256, 0, st>>>((const uint4*)A, (uint4*)At, rows, row_bytes, kblocks, a_row);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace qb

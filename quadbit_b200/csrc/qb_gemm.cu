@@ -58,6 +58,7 @@ struct KParams {
     int sfb_rowblocks;                   // ceil(tok/128)
     int b_box_bytes;                     // bytes one B TMA box delivers (box rows * 128)
     int out_mode;
+    int a_tiled;                         // A in 128-row x 256-K tiles: TMA row coordinate = tile * 128, column 0
     int dbg;                             // experiment switches (QB_DEBUG_SKIP), 0 in normal use
     int* sk_counters;                    // slab split-K: 4 arrival counters per output tile (zero between calls)
     unsigned long long* prof;            // optional per-CTA cycle counters [grid][8]
@@ -184,7 +185,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     if (lane == 0) {
                         const uint32_t fb = full_bar(stage);
                         mbar_expect_tx(fb, tx);
-                        tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                        if (p.a_tiled) tma_load_2d(stageA(stage), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb) * 128);
+                        else tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
                         tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0);
                         bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
                                   C::SFA_BYTES, fb);
@@ -515,6 +517,7 @@ struct KParams2 {
     int out_f, tok;
     int num_m2, num_n, kblocks;
     int out_mode;
+    int a_tiled;
     int dbg;
     unsigned long long* prof;
 };
@@ -625,7 +628,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #endif
                         if (rank == 0) mbar_expect_tx(full_bar(s), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
                         if (!skip) {
-                            if (isA) tma_load_2d_pair(stageA(s), &tmA, fb, (kb + u) * C::A_ROW, a_row0);
+                            if (isA) {
+                                if (p.a_tiled) tma_load_2d_pair(stageA(s), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb + u) * 128);
+                                else tma_load_2d_pair(stageA(s), &tmA, fb, (kb + u) * C::A_ROW, a_row0);
+                            }
                             else tma_load_2d_pair(stageB(s), &tmB, fb, (kb + u) * 128, b_row0);
                         }
                     }
@@ -1037,9 +1043,14 @@ template <bool SPARSE, int BN>
 static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     using C = Cfg<SPARSE, BN>;
     CUtensorMap tmA, tmB;
-    int rc = make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
-                         SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+    // tiled A: a matrix of (rows * K blocks) tile rows of A_ROW bytes, so one box is one contiguous tile
+    int rc = a.a_tiled
+                 ? make_map_u8(&tmA, a.A, (uint64_t)C::A_ROW, (uint64_t)a.a_rows * kp.kblocks, C::A_ROW, 128,
+                               SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B)
+                 : make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
+                               SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    kp.a_tiled = a.a_tiled;
     const uint32_t b_rows = a.tok < BN ? (uint32_t)a.tok : (uint32_t)BN;   // box never taller than the tensor
     kp.b_box_bytes = (int)(b_rows * 128);
     rc = make_map_u8(&tmB, a.B, (uint64_t)a.K / 2, (uint64_t)a.tok, 128, b_rows, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1077,8 +1088,11 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     const int kblocks = (a.K + 255) / 256;
     const int atoms_per_rb = kblocks * C::MMAS;
     CUtensorMap tmA, tmB, tmSFA, tmSFB, tmMETA;
-    int rc = make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
-                         SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = a.a_tiled
+                 ? make_map_u8(&tmA, a.A, (uint64_t)C::A_ROW, (uint64_t)a.a_rows * kblocks, C::A_ROW, 128,
+                               SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B)
+                 : make_map_u8(&tmA, a.A, (uint64_t)(SPARSE ? a.K / 4 : a.K / 2), (uint64_t)a.a_rows, C::A_ROW, 128,
+                               SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     const uint32_t b_rows = (uint32_t)C::B_ROWS;
     if ((rc = make_map_u8(&tmB, a.B, (uint64_t)a.K / 2, (uint64_t)a.tok, 128, b_rows, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
@@ -1092,6 +1106,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     KParams2 kp;
     kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.out_f = a.out_f; kp.tok = a.tok;
     kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
+    kp.a_tiled = a.a_tiled;
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;

@@ -26,6 +26,10 @@ int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* me
 int pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out_f, int K,
                cudaStream_t st);
 
+// Re-lay packed weight rows [rows][K/4 (sparse) or K/2 (dense)] as contiguous 128-row x 256-K tiles
+// [rows/128][Kp/256][128][64 or 128 B] (zero beyond K): one tile is one contiguous 8 / 16 KB read.
+int tile_weights(const void* A, void* At, int rows, int K, int sparse, cudaStream_t st);
+
 // ---- qb_gemm.cu
 struct GemmArgs {
     const void* A;         // packed weights: dense [out][K/2], sparse [out][K/4]
@@ -46,6 +50,7 @@ struct GemmArgs {
     int tok;               // rows of B
     int K;                 // logical reduction length
     int sparse;            // 1 = 2:4-sparse A
+    int a_tiled;           // 1 = A is in the tiled layout [rows/128][Kp/256][128][64 or 128 B] (see tile_weights)
     int out_mode;          // 0: bf16 C[out][tok]  1: bf16 C[tok][out]  2: fp32 raw accumulators C[out][tok]
                            // 3: bf16 C[tok][out] = (acc*gA*gB + bias)*row_w
     int splits;            // K splits (>1 uses Cf + a convert pass)

@@ -47,6 +47,13 @@ def quantize_act(lib, x: torch.Tensor, block: int, two_level: bool = True, want_
 DECODE_MAX_TOK = 256
 
 
+def tile_weights(lib, A: torch.Tensor, rows: int, K: int, sparse: int) -> torch.Tensor:
+    """Packed weight rows -> contiguous 128-row x 256-K tiles (what the GEMMs stream; qb_tile_weights)."""
+    At = torch.empty(lib.qb_tiled_weight_bytes(rows, K, sparse), dtype=torch.uint8, device=A.device)
+    check(lib.qb_tile_weights(A.data_ptr(), At.data_ptr(), rows, K, sparse, _stream()), "qb_tile_weights")
+    return At
+
+
 def _run_decode(mod, A, meta, sparse, out_f, in_f, Bbytes, sfb, tok, gB):
     """qb_gemm_decode with a per-module workspace (zeroed once; the kernel keeps its counters clean)."""
     lib = mod.lib
@@ -94,6 +101,7 @@ class QuadbitLinear:
         check(lib.qb_compress_2to4(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, self.Ac.data_ptr(), _ptr(self.meta),
                                    self.meta_native.data_ptr(), _ptr(self.scaleA), self.sfa.data_ptr(), self.gA.data_ptr(),
                                    out_f, in_f, _stream()), "qb_compress_2to4")
+        self.At = tile_weights(lib, self.Ac, out_f, in_f, 1)      # what the GEMMs read; Ac stays as the reference attribute
 
     def pack_act(self, x: torch.Tensor):
         """x [tok,in] -> (Bbytes, scaleB atoms, gB)."""
@@ -105,15 +113,15 @@ class QuadbitLinear:
         dev = Bbytes.device
         C = torch.empty((tok, self.out_f) if out_t else (self.out_f, tok), dtype=torch.bfloat16, device=dev)
         Cf = torch.empty((tok, self.out_f), dtype=torch.float32, device=dev) if splits > 1 else None
-        check(self.lib.qb_gemm(self.Ac.data_ptr(), Bbytes.data_ptr(), self.sfa.data_ptr(), scaleB.data_ptr(),
+        check(self.lib.qb_gemm(self.At.data_ptr(), Bbytes.data_ptr(), self.sfa.data_ptr(), scaleB.data_ptr(),
                                self.meta_native.data_ptr(), self.gA.data_ptr(), _ptr(gB), C.data_ptr(), _ptr(Cf), 0, 0, 0,
-                               self.out_f, self.out_f, tok, self.in_f, 1, 1 if out_t else 0, splits, bn, _stream()),
+                               self.out_f, self.out_f, tok, self.in_f, 3, 1 if out_t else 0, splits, bn, _stream()),
               "qb_gemm(sparse)")
         return C
 
     def run_decode(self, Bbytes, scaleB, tok: int, gB):
         """Thin-token GEMM (tok <= 256): weight streamed once, K split over the SMs, [tok,out] bf16."""
-        return _run_decode(self, self.Ac, self.meta_native, 1, self.out_f, self.in_f, Bbytes, scaleB, tok, gB)
+        return _run_decode(self, self.At, self.meta_native, 3, self.out_f, self.in_f, Bbytes, scaleB, tok, gB)
 
     def forward(self, x: torch.Tensor, splits: int = 1, bn: int = 0) -> torch.Tensor:
         lead = x.shape[:-1]
@@ -153,6 +161,7 @@ class DenseNVLinear(torch.nn.Module):
         check(lib.qb_pack_dense(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, Ab.data_ptr(), _ptr(SFA), sfa.data_ptr(),
                                 gA.data_ptr(), out_f, in_f, _stream()), "qb_pack_dense")
         self.register_buffer("Ab", Ab)
+        self.register_buffer("At", tile_weights(lib, Ab, out_f, in_f, 0))   # what the GEMMs read
         self.register_buffer("gA", gA)
         self.register_buffer("sfa", sfa)
         if SFA is not None:
@@ -163,13 +172,13 @@ class DenseNVLinear(torch.nn.Module):
         dev = Bbytes.device
         C = torch.empty((tok, self.out) if out_t else (self.out, tok), dtype=torch.bfloat16, device=dev)
         Cf = torch.empty((tok, self.out), dtype=torch.float32, device=dev) if splits > 1 else None
-        check(self.lib.qb_gemm(self.Ab.data_ptr(), Bbytes.data_ptr(), self.sfa.data_ptr(), sfb.data_ptr(), 0,
+        check(self.lib.qb_gemm(self.At.data_ptr(), Bbytes.data_ptr(), self.sfa.data_ptr(), sfb.data_ptr(), 0,
                                self.gA.data_ptr(), _ptr(gB), C.data_ptr(), _ptr(Cf), 0, 0, 0, self.out, self.out, tok,
-                               self.inn, 0, 1 if out_t else 0, splits, bn, _stream()), "qb_gemm(dense)")
+                               self.inn, 2, 1 if out_t else 0, splits, bn, _stream()), "qb_gemm(dense)")
         return C
 
     def run_decode(self, Bbytes, sfb, tok: int, gB):
-        return _run_decode(self, self.Ab, None, 0, self.out, self.inn, Bbytes, sfb, tok, gB)
+        return _run_decode(self, self.At, None, 2, self.out, self.inn, Bbytes, sfb, tok, gB)
 
     def forward(self, x: torch.Tensor, splits: int = 1, bn: int = 0) -> torch.Tensor:
         lead = x.shape[:-1]

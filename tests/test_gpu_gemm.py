@@ -342,3 +342,49 @@ def test_moe_route_kernel_groups_slots(lib):
     for e in range(E):
         seg = src[int(poff[e]): int(poff[e] + counts[e])]
         assert (seg >= 0).all() and (assign[seg.long()] == e).all()
+
+
+# ----------------------------------------------------------------------------- tiled weight layout
+def tiled_reference(A: torch.Tensor, sparse: int) -> torch.Tensor:
+    """[rows][row_bytes] -> [rows/128][ceil(K/256)][128][64 or 128] with a zero tail, on the CPU."""
+    rows, rb = A.shape
+    a_row = 64 if sparse else 128
+    kblocks = (rb + a_row - 1) // a_row
+    P = torch.zeros((rows, kblocks * a_row), dtype=torch.uint8)
+    P[:, :rb] = A
+    return P.view(rows // 128, 128, kblocks, a_row).permute(0, 2, 1, 3).contiguous().view(-1)
+
+
+@pytest.mark.parametrize("sparse", [1, 0])
+@pytest.mark.parametrize("rows,K", [(128, 128), (256, 384), (512, 1024), (1024, 4096)])
+def test_tile_weights_is_the_permutation(lib, sparse, rows, K):
+    torch.manual_seed(rows + K)
+    A = torch.randint(0, 256, (rows, K // 4 if sparse else K // 2), dtype=torch.uint8)
+    n = lib.qb_tiled_weight_bytes(rows, K, sparse)
+    ref = tiled_reference(A, sparse)
+    assert n == ref.numel()
+    Ad = A.cuda()
+    At = torch.full((n,), 0xAB, dtype=torch.uint8, device="cuda")
+    assert lib.qb_tile_weights(Ad.data_ptr(), At.data_ptr(), rows, K, sparse, S()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(At.cpu(), ref)
+
+
+@pytest.mark.parametrize("sparse", [1, 0])
+@pytest.mark.parametrize("out_f,tok,K,bn,splits", [(256, 16, 1024, 16, 1), (512, 200, 768, 0, 1), (1024, 512, 2048, 512, 1),
+                                                  (512, 640, 1024, 0, 1), (256, 16, 2048, 16, 4)])
+def test_gemm_tiled_weights_bitwise_equal(lib, sparse, out_f, tok, K, bn, splits):
+    torch.manual_seed(out_f + tok + K + 7)
+    W = torch.randn(out_f, K) * 0.02
+    x = torch.randn(tok, K)
+    ops = native_operands(W, x, sparse)
+    Cr = gemm(lib, ops, out_f, tok, K, sparse, 1, splits=splits, bn=bn)
+    At = torch.empty(lib.qb_tiled_weight_bytes(out_f, K, sparse), dtype=torch.uint8, device="cuda")
+    assert lib.qb_tile_weights(ops["A"].data_ptr(), At.data_ptr(), out_f, K, sparse, S()) == 0
+    ops_t = dict(ops)
+    ops_t["A"] = At
+    Ct = gemm(lib, ops_t, out_f, tok, K, int(sparse) | 2, 1, splits=splits, bn=bn)
+    if splits == 1:
+        assert torch.equal(Cr, Ct)
+    else:   # atomic split-K adds in arrival order
+        assert (Cr.float() - Ct.float()).abs().max() <= 2e-2 * Cr.float().abs().max()
