@@ -291,46 +291,51 @@ def run_gpu(args):
             del dn, Bs, sBs, gBs, Bd, sBd, gBd
         line["shapes"] = shapes
 
-        # ---- thin-M decode: dense NVFP4, weight streaming, rotating over > L2 worth of weights, CUDA graph
-        dec = {}
-        for (n, k) in [(14336, 4096), (4096, 14336), (6144, 4096), (4096, 4096)]:
-            wbytes = n * k / 2 + n * k / 16 + 4 * n
-            nrot = max(2, int(300e6 // wbytes) + 1)
-            mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
-                    for _ in range(nrot)]
-            for m_tok in (1, 16, 64, 128, 256):
-                xdec = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
-                splits = "auto"
-                stream = torch.cuda.Stream()
-                with torch.cuda.stream(stream):
-                    for m in mods[:2]:
-                        m.forward(xdec)
-                    stream.synchronize()
-                    gph = torch.cuda.CUDAGraph()
-                    try:
-                        with torch.cuda.graph(gph, stream=stream):
-                            for m in mods:
-                                m.forward(xdec)
-                        for _ in range(3):
-                            gph.replay()
+        # ---- thin-M decode: weight streaming, rotating over > L2 worth of weights, CUDA graph.
+        #      dense NVFP4 for every M, 2:4-sparse for M >= 64 (as the reference quotes them)
+        def decode_sweep(make_mod, wbytes_of, ms):
+            out = {}
+            for (n, k) in [(14336, 4096), (4096, 14336), (6144, 4096), (4096, 4096)]:
+                wbytes = wbytes_of(n, k)
+                nrot = max(2, int(300e6 // wbytes) + 1)
+                mods = [make_mod((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)) for _ in range(nrot)]
+                for m_tok in ms:
+                    xdec = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
+                    stream = torch.cuda.Stream()
+                    with torch.cuda.stream(stream):
+                        for m in mods[:2]:
+                            m.forward(xdec)
                         stream.synchronize()
-                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        a.record(stream)
-                        for _ in range(5):
-                            gph.replay()
-                        b.record(stream)
-                        stream.synchronize()
-                        tl = a.elapsed_time(b) / 5 / nrot * 1e-3
-                        mode = "cuda-graph"
-                    except Exception as e:  # capture refused: time eagerly, say so
-                        torch.cuda.synchronize()
-                        tl = ev_time(lambda: [m.forward(xdec) for m in mods], 3) / nrot
-                        mode = f"eager ({type(e).__name__})"
-                algo = wbytes + 2 * m_tok * k + 2 * m_tok * n
-                dec[f"N{n}_K{k}_M{m_tok}"] = {"us": tl * 1e6, "gbs": algo / tl / 1e9, "frac_of_measured_hbm": algo / tl / 1e9 / hbm_gbs,
-                                              "splits": splits, "timing": mode}
-            del mods
-        line["decode_dense"] = dec
+                        gph = torch.cuda.CUDAGraph()
+                        try:
+                            with torch.cuda.graph(gph, stream=stream):
+                                for m in mods:
+                                    m.forward(xdec)
+                            for _ in range(3):
+                                gph.replay()
+                            stream.synchronize()
+                            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            a.record(stream)
+                            for _ in range(5):
+                                gph.replay()
+                            b.record(stream)
+                            stream.synchronize()
+                            tl = a.elapsed_time(b) / 5 / nrot * 1e-3
+                            mode = "cuda-graph"
+                        except Exception as e:  # capture refused: time eagerly, say so
+                            torch.cuda.synchronize()
+                            tl = ev_time(lambda: [m.forward(xdec) for m in mods], 3) / nrot
+                            mode = f"eager ({type(e).__name__})"
+                    algo = wbytes + 2 * m_tok * k + 2 * m_tok * n
+                    out[f"N{n}_K{k}_M{m_tok}"] = {"us": tl * 1e6, "gbs": algo / tl / 1e9, "frac_of_measured_hbm": algo / tl / 1e9 / hbm_gbs,
+                                                 "timing": mode, "what": "quantise + GEMM per linear (two launches)"}
+                del mods
+            return out
+
+        line["decode_dense"] = decode_sweep(lambda W: qb.DenseNVLinear(W, keep_ref_layout=False),
+                                            lambda n, k: n * k / 2 + n * k / 16 + 4 * n, (1, 16, 64, 128, 256))
+        line["decode_sparse"] = decode_sweep(lambda W: qb.QuadbitLinear(W, keep_ref_layout=False),
+                                             lambda n, k: n * k / 4 + n * k / 16 + n * k / 32 + 4 * n, (64, 128, 256))
 
         # ---- end to end through the module API with host buffers (H2D + quantise + GEMM + D2H)
         hx = [torch.randn(TOK, L["k"]).to(torch.bfloat16).pin_memory() for L in layers]

@@ -80,17 +80,17 @@ struct Cfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_ALLOC + SFA_BYTES + SFB_BYTES + META_BYTES;
     static constexpr int ACC_STAGES = BN <= 128 ? 2 : 1;
     static constexpr int EPI_BYTES = 4 * 32 * 80;   // per-warp 32x32 bf16 transpose tile, 80-byte pitch
-    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 256;
+    static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - 512;
     static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + 512;
     // TMEM columns
     static constexpr int SFA_COLS = MMAS * 4;
     static constexpr int SFB_COLS = MMAS * 4 * NB128;
     static constexpr int E_COLS = SPARSE ? 4 : 0;
     static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;
     static constexpr int TM_SF0 = ((ACC_STAGES * BN + 3) / 4) * 4;
-    static constexpr int TM_USED = TM_SF0 + 2 * SF_SET;
+    static constexpr int TM_USED = TM_SF0 + STAGES * SF_SET;        // one scale-factor slot per ring stage
     static constexpr int TM_COLS = TM_USED <= 32 ? 32 : TM_USED <= 64 ? 64 : TM_USED <= 128 ? 128 : TM_USED <= 256 ? 256 : 512;
     static_assert(TM_USED <= 512, "TMEM budget");
     static_assert(STAGES >= 2, "smem budget");
@@ -110,8 +110,8 @@ struct Cfg {
 #define QB_BACKOFF_SF 32
 #endif
 constexpr int NPROD1 = 4;                      // producer warps of the single-CTA kernel (warp 0 and warps 6..8)
-constexpr int NTHREADS1 = (6 + NPROD1 - 1) * 32;
-enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4 };
+constexpr int NTHREADS1 = (6 + NPROD1 - 1 + 4) * 32;  // + four scale-factor warps (9..12)
+enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4, SITE_SF1 = 9 };
 
 template <bool SPARSE, int BN>
 __global__ void __launch_bounds__(NTHREADS1, 1)
@@ -128,6 +128,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto accf_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
     auto acce_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+    auto sfr_bar = [&](int s) { return bars + 8u * (2 * C::STAGES + 4 + s); };     // scale factors of the stage are in TMEM
     auto stageA = [&](int s) { return smem0 + (uint32_t)s * C::STAGE_BYTES; };
     auto stageB = [&](int s) { return stageA(s) + C::A_BYTES; };
     auto stageSFA = [&](int s) { return stageB(s) + C::B_ALLOC; };
@@ -139,7 +140,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(sfr_bar(s), 4); }
         for (int a = 0; a < 2; a++) { mbar_init(accf_bar(a), 1); mbar_init(acce_bar(a), 4); }
         fence_barrier_init();
         tma_prefetch_desc(&tmA);
@@ -159,7 +160,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
     const int atoms_per_rb = p.kblocks * C::MMAS;   // scale atoms per 128-row block along K
 
-    if (warp == 0 || warp >= 6) {
+    if (warp == 0 || (warp >= 6 && warp < 9)) {
         // ------------------------------------------------------------ producers
         // Four warps take the K blocks round-robin: one thread needs ~90 cycles to issue one bulk load
         // (measured) and a stage takes 5-6 of them, so one producer cannot keep a thin-token stream fed.
@@ -203,71 +204,130 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        const uint32_t idesc = make_idesc_nvf4(BN, SPARSE);
+        // One thread runs the whole issue loop (no warp-wide broadcast or re-convergence between a barrier
+        // wait and the MMAs it gates). It waits for "scale factors of the stage are in tensor memory",
+        // which the scale-factor warps signal after they have seen the stage land.
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_nvf4(BN, SPARSE);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = QB_CLK();
+            for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+                const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
+                const int n = mn / p.num_m;
+                const int n0 = n * BN;
+                const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
+                const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
+                long long ca = QB_CLK();
+                if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
+                c_wait_acc += QB_CLK() - ca;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                bool ok = true;
+                for (int kb = kb0; kb < kb1;) {
+                    long long cf = QB_CLK();
+                    // two K blocks per poll when the later one is ready too (a poll costs 100-200 cycles
+                    // even on a completed barrier; the scale-factor warps signal in ring order)
+                    int s1 = stage + 1;
+                    uint32_t ph1 = phase;
+                    if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
+                    int nb = 2;
+                    if (kb + 1 >= kb1 || !mbar_try_wait(sfr_bar(s1), ph1)) {
+                        nb = 1;
+                        if (!mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
+                    }
+                    long long cg = QB_CLK();
+                    c_wait_full += cg - cf;
+                    tc_fence_after();
+                    for (int u = 0; u < nb; u++) {
+                        const int s = u ? s1 : stage;
+                        const uint32_t sfset = tmem_base + C::TM_SF0 + s * C::SF_SET;
+                        const uint32_t t_sfa = sfset, t_sfb = sfset + C::SFA_COLS, t_e = sfset + C::SFA_COLS + C::SFB_COLS;
+#pragma unroll
+                        for (int i = 0; i < C::MMAS; i++) {
+                            const uint64_t adesc = make_smem_desc(stageA(s) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
+                            const uint64_t bdesc = make_smem_desc(stageB(s) + i * C::B_KSTEP, 1024, 16, 2);
+                            const uint32_t accum = (kb + u > kb0 || i > 0) ? 1u : 0u;
+                            if (SPARSE)
+                                tc_mma_nvf4_sp(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff,
+                                               t_e + 2 * i, accum);
+                            else
+                                tc_mma_nvf4(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff, accum);
+                        }
+                        tc_commit(empty_bar(s));
+                    }
+                    kb += nb;
+                    stage += nb;
+                    if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
+                    c_issue += QB_CLK() - cg;
+                }
+                if (!ok) break;
+                tc_commit(accf_bar(acc));
+                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+            if (p.prof) {
+                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
+                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 9) {
+        // ------------------------------------------------------------ scale-factor warps (9..12)
+        // Copy the landed stage's scale factors / metadata from shared memory into the stage's own
+        // tensor memory slot with tcgen05.st, each warp its lane quadrant (a tcgen05.cp from the issuer
+        // costs ~50 cycles of the MMA pipe, 5-12 of them per K block).
+        const int q = warp & 3;
+        const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0;
         uint32_t phase = 0;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        uint32_t kiter = 0;
-        long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = QB_CLK();
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
-            const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
-            const int n = mn / p.num_m;
-            const int n0 = n * BN;
+            const int z = tile / tiles_mn;
             const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
-            const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
-            long long ca = QB_CLK();
-            if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-            c_wait_acc += QB_CLK() - ca;
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
             bool ok = true;
-            for (int kb = kb0; kb < kb1; kb++, kiter++) {
-                long long cf = QB_CLK();
-                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
-                long long cg = QB_CLK();
-                c_wait_full += cg - cf;
+            for (int kb = kb0; kb < kb1; kb++) {
+                if (!mbar_wait(full_bar(stage), phase, &abort_flag, &g_status, SITE_SF1)) { ok = false; break; }
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t sfset = tmem_base + C::TM_SF0 + (kiter & 1) * C::SF_SET;
-                    const uint32_t t_sfa = sfset, t_sfb = sfset + C::SFA_COLS, t_e = sfset + C::SFA_COLS + C::SFB_COLS;
-                    if (!((p.dbg & 1) && kiter >= 2)) {
-#pragma unroll
-                    for (int i = 0; i < C::MMAS; i++)
-                        tc_cp_32x128b_warpx4(t_sfa + 4 * i, make_smem_desc(stageSFA(stage) + i * 512, 128, 0, 0));
-#pragma unroll
-                    for (int nb = 0; nb < C::NB128; nb++)
-#pragma unroll
-                        for (int i = 0; i < C::MMAS; i++)
-                            tc_cp_32x128b_warpx4(t_sfb + i * (4 * C::NB128) + 4 * nb,
-                                                 make_smem_desc(stageSFB(stage) + (nb * C::MMAS + i) * 512, 128, 0, 0));
-                    if (SPARSE) tc_cp_128x128b(t_e, make_smem_desc(stageMETA(stage), 128, 0, 0));
-                    }
+                const uint32_t sf = stageSFA(stage) + lane * 16;       // this lane's 16 bytes of every atom
+                const uint32_t t_sfa = tmem_base + C::TM_SF0 + stage * C::SF_SET + lane_sel;
+                const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                {
+                    uint32_t a[C::MMAS * 4];
 #pragma unroll
                     for (int i = 0; i < C::MMAS; i++) {
-                        const uint64_t adesc = make_smem_desc(stageA(stage) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
-                        const uint64_t bdesc = make_smem_desc(stageB(stage) + i * C::B_KSTEP, 1024, 16, 2);
-                        const uint32_t accum = (kb > kb0 || i > 0) ? 1u : 0u;
-                        if (SPARSE)
-                            tc_mma_nvf4_sp(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff,
-                                           t_e + 2 * i, accum);
-                        else
-                            tc_mma_nvf4(d_tmem, adesc, bdesc, idesc, t_sfa + 4 * i, t_sfb + i * (4 * C::NB128) + sfb_coloff, accum);
+                        uint4 v = lds_v4(sf + i * 512);
+                        a[4 * i] = v.x; a[4 * i + 1] = v.y; a[4 * i + 2] = v.z; a[4 * i + 3] = v.w;
                     }
-                    tc_commit(empty_bar(stage));
+                    if constexpr (C::MMAS == 2) tc_st_32x8(t_sfa, a); else tc_st_32x16(t_sfa, a);
                 }
+                // SFB: column 4*NB128*i + 4*nb + c  <-  atom (nb, i), word c (atoms beyond the token count
+                // hold stale bytes; their columns are never selected by an MMA that matters)
+#pragma unroll
+                for (int h = 0; h < (C::MMAS * C::NB128 * 4) / 8; h++) {
+                    uint32_t b[8];
+#pragma unroll
+                    for (int w = 0; w < 2; w++) {
+                        const int g = h * 2 + w;               // group of 4 columns
+                        const int i = g / C::NB128, nbk = g % C::NB128;
+                        uint4 v = lds_v4(sf + C::SFA_BYTES + (nbk * C::MMAS + i) * 512);
+                        b[4 * w] = v.x; b[4 * w + 1] = v.y; b[4 * w + 2] = v.z; b[4 * w + 3] = v.w;
+                    }
+                    tc_st_32x8(t_sfb + 8 * h, b);
+                }
+                if constexpr (SPARSE) {
+                    uint32_t e[4];
+                    uint4 v = lds_v4(stageMETA(stage) + (q * 32 + lane) * 16);
+                    e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                    tc_st_32x4(t_e, e);
+                }
+                tc_wait_st();
+                tc_fence_before();
                 __syncwarp();
-                c_issue += QB_CLK() - cg;
+                if (lane == 0) mbar_arrive(sfr_bar(stage));
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) tc_commit(accf_bar(acc));
-            __syncwarp();
-            if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
-        }
-        if (p.prof && lane == 0) {
-            unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-            o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)

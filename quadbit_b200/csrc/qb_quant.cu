@@ -368,6 +368,7 @@ static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atom
                         cudaStream_t st) {
     int nchunks = K / 8;
     int threads = nchunks <= 2048 ? 256 : (nchunks <= 4096 ? 512 : 1024);
+    if (tok <= 512) threads = 1024;      // few rows: the row's latency is the kernel's, so spread it over more threads
     if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
     int nj = (nchunks + threads - 1) / threads;
 #define QB_LQ(NJ)                                                                                                 \
