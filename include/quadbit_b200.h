@@ -151,10 +151,11 @@ int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, cons
 int qb_tile_weights(const void* A, void* A_tiled, int rows, int K, int sparse, void* stream);
 long long qb_tiled_weight_bytes(int rows, int K, int sparse);
 /* Thin-token (decode) GEMM: streams the weight once with the K range split over CTAs so that all SMs
- * pull from HBM; each split writes fp32 partial sums to its own slab of `ws` and the last split to
- * arrive for a tile sums them and writes bf16 (one launch: no memset, no finish pass). The split
- * count and token tile come from the shapes. `ws`: qb_gemm_decode_ws_bytes(out, tok, K) bytes,
- * 256-byte aligned, ZERO-FILLED ONCE when allocated (its head holds arrival counters that every call
+ * pull from HBM; each split adds its fp32 partial sums into `ws` (reductions at the L2) and the last
+ * split to arrive for a tile reads the sums, writes bf16 and zeroes what it read (one launch: no
+ * memset, no finish pass; the summation order, hence the last bits, can differ from run to run). The
+ * split count and token tile come from the shapes. `ws`: qb_gemm_decode_ws_bytes(out, tok, K) bytes,
+ * 256-byte aligned, ZERO-FILLED ONCE when allocated (arrival counters and sums, all of which every call
  * leaves at zero again); calls sharing a workspace must not overlap on the GPU. out_mode 0 / 1 as in
  * qb_gemm. Replaces the memset + atomics + convert sequence of the reference's split-K decode path
  * (cuda/sparse_fp4_lib.cu:1160-1344) and its unit-scale split-N decode (cuda/dense_decode_lib.cu:19-141). */

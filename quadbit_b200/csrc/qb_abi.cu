@@ -212,7 +212,8 @@ long long qb_gemm_decode_ws_bytes(int out, int tok, int K) {
     if (out <= 0 || tok <= 0 || K <= 0 || out % 128) return -1;
     int splits = 1, bn = 16;
     qb::decode_plan(out, tok, K, &splits, &bn);
-    return (long long)(decode_counter_bytes(out, tok) + (size_t)splits * tok * out * sizeof(float));
+    (void)splits;
+    return (long long)(decode_counter_bytes(out, tok) + (size_t)tok * out * sizeof(float));
 }
 int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
                    const void* gB, void* C, void* ws, int out, int tok, int K, int sparse, int out_mode, void* stream) {

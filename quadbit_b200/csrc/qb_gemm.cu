@@ -60,7 +60,7 @@ struct KParams {
     int out_mode;
     int a_tiled;                         // A in 128-row x 256-K tiles: TMA row coordinate = tile * 128, column 0
     int dbg;                             // experiment switches (QB_DEBUG_SKIP), 0 in normal use
-    int* sk_counters;                    // slab split-K: 4 arrival counters per output tile (zero between calls)
+    int* sk_counters;                    // split-K finished in the kernel: 4 arrival counters per output tile (zero between calls)
     unsigned long long* prof;            // optional per-CTA cycle counters [grid][8]
 };
 
@@ -367,16 +367,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 tc_wait_ld();
                 const int col_l = n0 + c0 + (lane % C::CH);
                 const float gbl = gbv[c0 / C::CH];
-                if (p.splits > 1 && p.sk_counters) {
-                    // slab split-K: this split's raw partial sums go to its own fp32 slab [z][tok][out]
-                    float* slab = p.Cf + (size_t)z * p.tok * p.out_f;
-#pragma unroll
-                    for (int j = 0; j < C::CH; j++) {
-                        const int col = n0 + c0 + j;
-                        if (col < p.tok) __stcg(slab + (size_t)col * p.out_f + o, __uint_as_float(r[j]));
-                    }
-                } else if (p.splits > 1) {
-                    // split-K: raw partial sums into the fp32 workspace Cf[tok][out]
+                if (p.splits > 1) {
+                    // split-K: raw partial sums are added into the fp32 workspace Cf[tok][out] (fire-and-forget
+                    // reductions at the L2); finished by the last split of the tile (below) or by a finish kernel
 #pragma unroll
                     for (int j = 0; j < C::CH; j++) {
                         const int col = n0 + c0 + j;
@@ -445,7 +438,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (lane == 0) mbar_arrive(acce_bar(acc));
             if (p.splits > 1 && p.sk_counters) {
                 // The warp that arrives last among the same-quadrant warps of all K splits owns rows
-                // [32q, 32q+32) of this tile: it sums the slabs, applies the globals and writes bf16.
+                // [32q, 32q+32) of this tile: it reads the sums, applies the globals and writes bf16.
                 __threadfence();
                 __syncwarp();
                 int last = 0;
@@ -458,25 +451,21 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (last) {
                     __threadfence();
                     const int ncol = min(BN, p.tok - n0);
-                    const size_t slab_elems = (size_t)p.tok * p.out_f;
+                    float* base = p.Cf + (size_t)n0 * p.out_f + o;
                     for (int j0 = 0; j0 < ncol; j0 += 16) {
-                        // 16 columns x all splits: independent loads, summed split by split
+                        // 16 independent loads in flight per lane; every element is zeroed again right after
+                        // it is read, so the workspace is clean for the next call
                         float sum[16];
 #pragma unroll
-                        for (int jj = 0; jj < 16; jj++) sum[jj] = 0.f;
-                        const float* base = p.Cf + (size_t)(n0 + j0) * p.out_f + o;
-#pragma unroll 4
-                        for (int zz = 0; zz < p.splits; zz++) {
-#pragma unroll
-                            for (int jj = 0; jj < 16; jj++) {
-                                const int jc = (j0 + jj < ncol) ? jj : 0;      // clamp: keep the load unconditional
-                                sum[jj] += __ldcg(base + (size_t)zz * slab_elems + (size_t)jc * p.out_f);
-                            }
+                        for (int jj = 0; jj < 16; jj++) {
+                            const int jc = (j0 + jj < ncol) ? j0 + jj : j0;      // clamp: keep the load unconditional
+                            sum[jj] = __ldcg(base + (size_t)jc * p.out_f);
                         }
 #pragma unroll
                         for (int jj = 0; jj < 16; jj++) {
                             const int col = n0 + j0 + jj;
                             if (j0 + jj < ncol) {
+                                __stcg(base + (size_t)(j0 + jj) * p.out_f, 0.f);
                                 const float gb = p.gB ? __ldg(p.gB + col) : 1.f;
                                 const __nv_bfloat16 h = __float2bfloat16_rn((sum[jj] * ga) * gb);
                                 if (p.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(p.C)[(size_t)o * p.tok + col] = h;
@@ -1235,7 +1224,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
         kp.dbg = dbg;
         kp.prof = g_prof_ptr;
     }
-    const bool slab = splits > 1 && a.sk_counters != nullptr;
+    const bool slab = splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
     if (!slab) kp.sk_counters = nullptr;
     if (splits > 1 && !slab) {
         rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
@@ -1273,10 +1262,11 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
         const int per = (kb + s - 1) / s;
         if (s > 1 && per * (s - 1) >= kb) continue;      // an empty split
         const int waves = (tiles * s + sms - 1) / sms;
-        // K blocks per unit + ~3 block-times of pipeline fill / epilogue per unit; the cross-split sum reads
-        // tok * s values per output row from L2, about a K-block time per 48 of them
+        // in units of one K block of one CTA (~0.33 us measured): K blocks per unit + ~3 for pipeline fill and
+        // epilogue; a split tile pays ~3.5 us + 0.12 us per token column for the reductions at the L2, the
+        // fence, the arrival counter and the read-back by the last split (measured)
         const int ncol = tok < b ? tok : b;
-        const double cost = waves * (per + 3.0 + (s > 1 ? 1.0 + ncol * s / 48.0 : 0.0));
+        const double cost = waves * (per + 3.0 + (s > 1 ? 10.4 + 0.36 * ncol : 0.0));
         if (cost < best - 1e-9) { best = cost; best_s = s; }
     }
     *splits = best_s;

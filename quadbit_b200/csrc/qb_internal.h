@@ -40,8 +40,9 @@ struct GemmArgs {
     const float* gA;       // per-row global scale of A (null = 1)
     const float* gB;       // per-row global scale of B (null = 1)
     void* C;               // output
-    float* Cf;             // fp32 split-K workspace: [tok][out] (atomic mode) or [splits][tok][out] (slab mode)
-    void* sk_counters;     // slab mode: int[4 * tiles], zero before the first call, left zero by the kernel (null = atomic mode)
+    float* Cf;             // fp32 split-K workspace [tok][out]; with sk_counters it must be zero on entry and is left zero
+    void* sk_counters;     // in-kernel finish: int[4 * tiles], zero before the first call, left zero by the kernel
+                           // (null = the host zeroes Cf and launches a finish kernel)
     const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
     const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
     const float* row_w;    // epilogue 3: fp32 per-routed-row weight [tok] (may be null)
