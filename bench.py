@@ -7,9 +7,12 @@ One "step" = the 2:4-sparse NVFP4 GEMM set at Llama-3-8B prefill shapes for M = 
 operands already packed / quantised and resident in HBM. Metric: effective TFLOP/s
 (2*M*N*K per GEMM, pruned zeros count) over the whole set.
 
-N > 1 (one process per GPU under torchrun, NCCL): the set is sharded tensor-parallel, strong
-scaling: QKV / gate / up split the output features (no communication), o_proj / down split
-K and all-reduce their bf16 [tok,out] output over NCCL.
+N > 1 (one process per GPU under torchrun, NCCL for the plumbing): the path shards over tokens with
+no exchange step, so by default every rank runs the full set on its own 4096 tokens (weights
+replicated, weak scaling, value = N x set flops / max-over-ranks device time). `--tp` measures the
+tensor-parallel variant instead (strong scaling at 4096 tokens in total): QKV / gate / up split the
+output features (no communication), o_proj / down split K and all-reduce their bf16 [tok,out]
+output over NCCL.
 
 Extra keys: "shapes" (per-shape sparse and dense figures, 8192^3, the activation quantiser
 and thin-M decode in GB/s), "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks".
@@ -152,7 +155,7 @@ def run_reference(args):
     val = set_flops(tok) * args.steps / dt / 1e12
     sample = f"{tok} of {TOK} tokens per step (act fake-quant + fp32 GEMM, weights dequantised offline), {cores} torch threads"
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp32 (CPU fake-quant of nvfp4)", "data": "synthetic",
             "config": {"workload": WORKLOAD, "sample": sample},
             "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
@@ -196,7 +199,7 @@ def run_gpu(args):
         if args.only and name != args.only:
             continue
         n_l, k_l = n, k
-        if world > 1:
+        if world > 1 and args.tp:
             if par == "col":
                 n_l = n // world
             else:
@@ -205,7 +208,7 @@ def run_gpu(args):
         W = (torch.randn(n_l, k_l, generator=g) * 0.02).to(torch.bfloat16).to(dev)
         dense = bool(args.only and args.dense)
         lin = qb.DenseNVLinear(W, keep_ref_layout=False) if dense else qb.QuadbitLinear(W, keep_ref_layout=False)
-        x = torch.randn(TOK, k_l, generator=torch.Generator(device="cpu").manual_seed(200 + i)).to(torch.bfloat16).to(dev)
+        x = torch.randn(TOK, k_l, generator=torch.Generator(device="cpu").manual_seed(200 + i + 1000 * rank)).to(torch.bfloat16).to(dev)
         Bb, sB, gB = qb.quantize_act(lin.lib, x, lin.block, True)
         out = torch.empty((TOK, n_l), dtype=torch.bfloat16, device=dev)
         layers.append(dict(name=name, lin=lin, x=x, Bb=Bb, sB=sB, gB=gB, out=out, par=par, n=n, k=k))
@@ -229,7 +232,7 @@ def run_gpu(args):
     def step():
         for L in layers:
             gemm_into(L)
-            if world > 1 and L["par"] == "row":
+            if world > 1 and args.tp and L["par"] == "row":
                 dist.all_reduce(L["out"])
 
     for _ in range(max(args.warmup, 3)):
@@ -250,12 +253,17 @@ def run_gpu(args):
     if status:
         raise RuntimeError(f"device status {status}")
     value = sum(2.0 * TOK * L["n"] * L["k"] for L in layers) / t / 1e12
+    if world > 1 and not args.tp:
+        value *= world          # every rank did the whole set on its own tokens
     n_launch = launches[0]
 
     line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": t * 1e3, "higher_is_better": True,
+            "scaling": "strong" if (world > 1 and args.tp) else "weak", "vs_baseline": None,
             "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens": TOK, "parallelism": f"tp{world}" if world > 1 else "single",
+            "config": {"workload": WORKLOAD, "tokens": TOK * (1 if (args.tp or world == 1) else world),
+                       "parallelism": "single" if world == 1 else (f"tp{world} (all-reduce after o_proj and down)" if args.tp else
+                                                                    f"dp{world}: tokens sharded, {TOK} per rank, weights replicated, no collective in the path"),
                        "l2": "no explicit flush: one step touches ~0.45 GB of distinct operands and outputs (> 126 MB L2) "
                              "before any buffer is reused",
                        "tile": "CTA pair: 256 out x 256 tok x 256 K per stage"},
@@ -404,6 +412,8 @@ def main():
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
                     "and skip the per-shape / decode / e2e / CPU extras")
+    ap.add_argument("--tp", action="store_true", help="with --gpus N > 1: tensor-parallel sharding of the set (strong scaling, "
+                    "NCCL all-reduce after the row-parallel GEMMs) instead of sharding the tokens")
     ap.add_argument("--dense", action="store_true", help="with --only: the dense NVFP4 GEMM instead of the 2:4-sparse one")
     args = ap.parse_args()
     if args.impl == "reference":
