@@ -193,6 +193,31 @@ def run_gpu(args):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / iters * 1e-3
 
+    # ---- profiling aids: one small workload of a side kernel, timed with CUDA events, nothing else
+    if args.only in ("quant", "decode"):
+        if args.only == "quant":
+            rows, k = 16384, 4096                      # 134 MB of bf16 input: larger than L2
+            xq = torch.randn(rows, k, device=dev).to(torch.bfloat16)
+            fn = lambda: qb.quantize_act(lib, xq, 32, True)
+            algo = rows * k * 2 + rows * k * (0.5 + 1 / 32) + 4 * rows
+            what = f"quant_act_kernel<32,2,1> on [{rows},{k}] bf16"
+        else:
+            n, k, m_tok = 14336, 4096, 16              # 33 MB of dense weights per linear, six rotating > L2
+            mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
+                    for _ in range(6)]
+            xd = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
+            packs = [qb.quantize_act(m.lib, xd, 16, True) for m in mods]
+            fn = lambda: [m.run_decode(pk[0], pk[1], m_tok, pk[2]) for m, pk in zip(mods, packs)]
+            algo = 6 * (n * k / 2 + n * k / 16 + 4 * n + 2 * m_tok * k + 2 * m_tok * n)
+            what = f"nvfp4_gemm_kernel<dense,16>: six [{m_tok}]x[{n},{k}] decode GEMMs per step"
+        t = ev_time(fn, args.steps, max(args.warmup, 3))
+        print(json.dumps({"metric": "achieved GB/s (algorithmic bytes)", "value": algo / t / 1e9, "unit": "GB/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t * 1e3, "higher_is_better": True,
+                          "config": {"workload": what, "only": args.only},
+                          "roofline": {"bound": "hbm", "achieved": algo / t / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                                       "frac": algo / t / 1e9 / hbm_gbs, "traffic": None}}), flush=True)
+        return
+
     # ---- operands of the sharded set
     layers = []
     for i, (name, n, k, par) in enumerate(SHAPES):
@@ -411,7 +436,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
-                    "and skip the per-shape / decode / e2e / CPU extras")
+                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' time one small workload of "
+                    "the activation quantiser / the thin-token GEMM instead")
     ap.add_argument("--tp", action="store_true", help="with --gpus N > 1: tensor-parallel sharding of the set (strong scaling, "
                     "NCCL all-reduce after the row-parallel GEMMs) instead of sharding the tokens")
     ap.add_argument("--dense", action="store_true", help="with --only: the dense NVFP4 GEMM instead of the 2:4-sparse one")

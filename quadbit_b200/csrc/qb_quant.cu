@@ -17,34 +17,41 @@
 
 namespace qb {
 
+// One CTA per token row; every thread owns whole scale blocks (BLOCK consecutive values, NJ blocks per
+// thread), so the per-block scale arithmetic (two IEEE divisions, the UE4M3 encode / decode, the
+// reciprocal of the divider) runs once per block and lane: with the 8-values-per-lane mapping it ran in
+// all BLOCK/8 lanes of a block, and the kernel was issue-bound (ncu: 92 % issue-active, 59 warp
+// instructions per value) at a fifth of the HBM rate.
 template <int BLOCK, int NJ, bool TWO_LEVEL>
 __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
                                                           uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
                                                           float* __restrict__ g_out, int tok, int K) {
-    constexpr int LPB = BLOCK / 8;   // lanes per scale block
-    constexpr int G = 4 * LPB;       // lanes per 4-scale word
+    constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
     constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
     const int row = blockIdx.x;
-    const int nchunks = K >> 3;
+    const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
-    const uint4* xr = x + (size_t)row * nchunks;
+    const uint4* xr = x + (size_t)row * (K >> 3);
 
-    uint4 v[NJ];
-    float cmax[NJ];
+    uint4 v[NJ][CPB];
+    float bmax[NJ];
     float tmax = 0.f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        v[j] = make_uint4(0, 0, 0, 0);
-        if (c < nchunks) v[j] = __ldg(xr + c);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+        const int b = threadIdx.x + j * blockDim.x;
         float m = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float2 f = __bfloat1622float2(h[i]);
-            m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+        for (int k = 0; k < CPB; k++) {
+            v[j][k] = make_uint4(0, 0, 0, 0);
+            if (b < nblocks) v[j][k] = __ldg(xr + (size_t)b * CPB + k);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j][k]);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 f = __bfloat1622float2(h[i]);
+                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
         }
-        cmax[j] = m;
+        bmax[j] = m;
         tmax = fmaxf(tmax, m);
     }
 
@@ -60,31 +67,41 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
         if (threadIdx.x == 0) g_out[row] = gl;
     }
 
+    const bool wide = (reinterpret_cast<uintptr_t>(Bwords) & 15) == 0;   // rows are multiples of 64 bytes
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        float bmax = cmax[j];
+        const int b = threadIdx.x + j * blockDim.x;
+        const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax[j], 6.f));
+        const float sdeq = TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code);
+        const Fp4Divider dv(fmaxf(sdeq, 1e-30f));
+        uint32_t w[CPB];
 #pragma unroll
-        for (int o = 1; o < LPB; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
-        uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax, 6.f));
-        float sdeq = TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code);
-        float sg = fmaxf(sdeq, 1e-30f);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
-        uint32_t w = 0;
+        for (int k = 0; k < CPB; k++) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j][k]);
+            float f8[8];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float2 f = __bfloat1622float2(h[i]);
-            w |= (q_fp4_div(f.x, sg) | (q_fp4_div(f.y, sg) << 4)) << (8 * i);
+            for (int i = 0; i < 4; i++) {
+                float2 f = __bfloat1622float2(h[i]);
+                f8[2 * i] = f.x; f8[2 * i + 1] = f.y;
+            }
+            w[k] = dv.pack8(f8);
         }
-        // merge the 4 scale codes of 4 consecutive blocks into one word (all lanes shuffle)
+        // the scale codes of 4 consecutive blocks (4 consecutive lanes) make one word (all lanes shuffle)
         uint32_t sw = 0;
-        int base = lane & ~(G - 1);
+        const int base = lane & ~3;
 #pragma unroll
-        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * LPB) << (8 * i);
-        if (c < nchunks) {
-            Bwords[(size_t)row * nchunks + c] = w;
-            if ((lane & (G - 1)) == 0) {
-                int jcol = c / LPB;   // scale column, multiple of 4 here
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i) << (8 * i);
+        if (b < nblocks) {
+            uint32_t* dst = Bwords + (size_t)row * (K >> 3) + (size_t)b * CPB;
+            if (wide) {
+                if constexpr (CPB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < CPB; k++) dst[k] = w[k];
+            }
+            if ((lane & 3) == 0) {
+                const int jcol = b;   // scale column, a multiple of 4 here
                 if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
                 if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(K) / BLOCK / 4)) = sw;
             }
@@ -146,9 +163,7 @@ __global__ void __launch_bounds__(1024) swiglu_quant_kernel(const uint4* __restr
         bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
         uint32_t code = enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl));
         float sg = fmaxf(__fmul_rn(dec_ue4m3(code), gl), 1e-30f);
-        uint32_t w = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++) w |= (q_fp4_div(h[j][2 * i], sg) | (q_fp4_div(h[j][2 * i + 1], sg) << 4)) << (8 * i);
+        const uint32_t w = Fp4Divider(sg).pack8(h[j]);
         uint32_t sw = 0;
         int base = lane & ~15;
 #pragma unroll
@@ -265,9 +280,7 @@ __global__ void __launch_bounds__(1024) norm_quant_kernel(const uint4* __restric
         for (int o = 1; o < LPB; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
         uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax, 6.f));
         float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
-        uint32_t w = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++) w |= (q_fp4_div(v[j][2 * i], sg) | (q_fp4_div(v[j][2 * i + 1], sg) << 4)) << (8 * i);
+        const uint32_t w = Fp4Divider(sg).pack8(v[j]);
         uint32_t sw = 0;
         int base = lane & ~(G - 1);
 #pragma unroll
@@ -334,9 +347,15 @@ __global__ void swiglu_fm_kernel(const __nv_bfloat16* __restrict__ g, const __nv
     const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(amax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(amax, 6.f));
     scaleH[((long long)(hblock / 4) * batch + b) * 4 + (hblock % 4)] = (uint8_t)code;
     const float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
-    uint32_t w[4] = {0, 0, 0, 0};
+    uint32_t w[4];
+    const Fp4Divider dv(sg);
 #pragma unroll
-    for (int i = 0; i < 16; i++) w[i >> 2] |= (q_fp4_div(val[2 * i], sg) | (q_fp4_div(val[2 * i + 1], sg) << 4)) << ((i & 3) * 8);
+    for (int i = 0; i < 4; i++) {
+        float f8[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) f8[e] = val[8 * i + e];
+        w[i] = dv.pack8(f8);
+    }
     *reinterpret_cast<uint4*>(Hwords + (long long)b * (hidden / 8) + hblock * 4) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 __global__ void swiglu_fm_finalize(float* gH, int batch) {
@@ -366,11 +385,10 @@ int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* sca
 template <int BLOCK, bool TWO_LEVEL>
 static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
                         cudaStream_t st) {
-    int nchunks = K / 8;
-    int threads = nchunks <= 2048 ? 256 : (nchunks <= 4096 ? 512 : 1024);
-    if (tok <= 512) threads = 1024;      // few rows: the row's latency is the kernel's, so spread it over more threads
-    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
-    int nj = (nchunks + threads - 1) / threads;
+    const int nblocks = K / BLOCK;
+    int threads = (nblocks + 31) / 32 * 32;
+    if (threads > 1024) threads = 1024;
+    const int nj = (nblocks + threads - 1) / threads;
 #define QB_LQ(NJ)                                                                                                 \
     quant_act_kernel<BLOCK, NJ, TWO_LEVEL><<<tok, threads, 0, st>>>((const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
                                                                     (uint8_t*)sf_atoms, g, tok, K)

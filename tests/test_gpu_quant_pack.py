@@ -191,3 +191,40 @@ def test_argument_validation_returns_codes(lib):
     assert lib.qb_quantize_act(x.data_ptr() + 2, b.data_ptr(), b.data_ptr(), 0, 0, 4, 256, 32, S()) == 1001  # misaligned
     assert lib.qb_quantize_act(0, 0, 0, 0, 0, 0, 256, 32, S()) == 0                                 # empty input is a no-op
     assert lib.qb_gemm(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 128, 128, 16, 256, 1, 0, 1, 0, S()) == 1001
+
+
+@pytest.mark.parametrize("block", [32, 16])
+def test_quantiser_ties_signed_zero_and_odd_scales(lib, block):
+    """Exact E2M1 ties (which the hardware conversion would round to even), signed zeros, values one bf16
+    step around every rounding boundary, and rows whose global scale has a long mantissa."""
+    K = 512
+    bounds = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+    grid = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+    rows = []
+    for scale_pow in (0, -7, 9):
+        for mant in (1.0, 1.0078125, 1.5, 1.9921875):          # bf16-exact multipliers of the row maximum
+            s = mant * 2.0 ** scale_pow
+            x = torch.zeros(K)
+            vals = []
+            for b in bounds:
+                bb = torch.tensor(b).to(torch.bfloat16).float()
+                up = torch.nextafter(bb.to(torch.bfloat16), torch.tensor(100.0, dtype=torch.bfloat16)).float()
+                dn = torch.nextafter(bb.to(torch.bfloat16), torch.tensor(-100.0, dtype=torch.bfloat16)).float()
+                vals += [b, -b, float(up), -float(up), float(dn), -float(dn)]
+            vals += grid + [-g for g in grid] + [7.0, -7.0, 1e-3, -1e-3]
+            v = torch.tensor(vals)
+            nb = K // block
+            for j in range(nb - 1):                             # every block: its maximum 6 (local scale 1), then probes
+                x[j * block] = 6.0
+                seg = v[(j * (block - 1)) % len(v):][: block - 1]
+                x[j * block + 1: j * block + 1 + len(seg)] = seg
+            x[(nb - 1) * block] = 2688.0                        # row maximum: global scale = s exactly when mant = 1
+            x[(nb - 1) * block + 1] = -0.0
+            rows.append(x * s)
+    X = torch.stack(rows)
+    X[3, 5] = -0.0
+    Bb, ref, atoms, g = run_quant(lib, X, block)
+    eB, eS, eg = fq.act_quant_2lvl(X, block)
+    assert torch.equal(g, eg)
+    assert torch.equal(ref, eS)
+    assert torch.equal(Bb, eB)
