@@ -44,12 +44,7 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
         for (int k = 0; k < CPB; k++) {
             v[j][k] = make_uint4(0, 0, 0, 0);
             if (b < nblocks) v[j][k] = __ldg(xr + (size_t)b * CPB + k);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j][k]);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                float2 f = __bfloat1622float2(h[i]);
-                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
-            }
+            m = fmaxf(m, absmax8_bf16(v[j][k]));
         }
         bmax[j] = m;
         tmax = fmaxf(tmax, m);
