@@ -7,13 +7,16 @@
 // (cuda/sparse_fp4_lib.cu:1362-1566), which are warp-level mma.sync / mma.sp kernels that
 // do not exist on this architecture.
 //
-// Structure (one persistent CTA per SM, 288 threads):
+// Two kernels. The CTA-pair kernel further down serves prefill (tok >= 128, out % 256 == 0). The
+// single-CTA kernel right below serves thin token counts, ragged shapes, split-K and the grouped
+// (MoE) form; its structure (one persistent CTA per SM, 416 threads):
 //   warp 0, 6-8 producers, K blocks round-robin: TMA tiles of A (weights, 128 rows) and B
 //               (tokens, BN rows) with hardware swizzle, plus bulk copies of the scale-factor
 //               atoms and the 2:4 metadata, into a multi-stage shared-memory ring (mbarrier
 //               full/empty).
-//   warp 1      MMA issuer: one lane copies scale factors / metadata smem -> TMEM
-//               (tcgen05.cp) and issues tcgen05.mma[.sp] kind::mxf4nvf4 block_scale with
+//   warps 9-12  scale-factor warps: copy scale factors / metadata of a landed stage from shared
+//               memory to the stage's tensor-memory slot (tcgen05.st, one lane quadrant each).
+//   warp 1      MMA issuer (one thread): issues tcgen05.mma[.sp] kind::mxf4nvf4 block_scale with
 //               the accumulator in TMEM; tcgen05.commit releases smem stages and hands
 //               finished accumulators to the epilogue. Allocates / frees TMEM.
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quadrant),
@@ -122,7 +125,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __shared__ uint32_t tmem_base_slot;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));
     const uint32_t bars = smem0 + C::STAGES * C::STAGE_BYTES + C::EPI_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
@@ -361,7 +363,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += C::CH) {
+#ifdef QB_EXPERIMENT
                 if (p.dbg & 8) break;
+#endif
                 uint32_t r[C::CH];
                 if constexpr (C::CH == 32) tc_ld_32x32(t_acc + c0, r); else tc_ld_32x8(t_acc + c0, r);
                 tc_wait_ld();
@@ -572,8 +576,6 @@ struct KParams2 {
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
-#define QB_EV2(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + 128 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
-#define QB_EV(kbv, id) do { if (p.prof && blockIdx.x == 0 && tile == cluster_id && (kbv) >= 8 && (kbv) < 24 && lane == 0) p.prof[2048 + ((kbv) - 8) * 8 + (id)] = QB_CLK(); } while (0)
 
 template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(544, 1)
