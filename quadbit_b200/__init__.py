@@ -5,3 +5,4 @@ from ._lib import EXPORTED, QuadbitError, load  # noqa: F401
 from .linear import DenseNVLinear, QBSparse, QuadbitLinear, quantize_act  # noqa: F401
 from .mlp import FusedSparseMLP, register_fused_mlp_op  # noqa: F401,E402
 from .moe import SparseMoE, load_sparse_moe  # noqa: F401,E402
+from . import vllm_hook  # noqa: F401,E402

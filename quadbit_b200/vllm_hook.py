@@ -1,0 +1,82 @@
+"""Linear-method hook for a serving engine, the counterpart of the reference's vLLM plugin patch
+(harness/qb_vllm_plugin/qb_sm120_plugin.py:1466-1534): the engine's linear method keeps its class and
+its callers; `process_weights_after_loading(layer)` additionally packs the loaded weight once into the
+two-level NVFP4 form, and `apply(layer, x, bias)` runs quantise + GEMM on it.
+
+Nothing here imports the engine: `install()` takes the method class to patch (for vLLM that is e.g.
+`vllm.model_executor.layers.linear.UnquantizedLinearMethod`), `install_vllm()` resolves that class by
+name and fails loudly if the engine is not importable. There is no fallback to the engine's own GEMM for
+layers that were packed; layers whose shape the kernels do not take (out or in not a multiple of 128)
+are left to the engine and counted in STATS."""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+STATS = {"sparse_layers": 0, "dense_layers": 0, "native_layers": 0, "calls": 0}
+
+
+def _default_factory(mode: str) -> Callable[[torch.Tensor], object]:
+    from .linear import DenseNVLinear, QuadbitLinear
+    return (lambda w: QuadbitLinear(w, keep_ref_layout=False)) if mode == "sparse" else (lambda w: DenseNVLinear(w, keep_ref_layout=False))
+
+
+def supported(weight: torch.Tensor) -> bool:
+    return weight.dim() == 2 and weight.shape[0] % 128 == 0 and weight.shape[1] % 128 == 0
+
+
+def install(method_cls, mode: str = "sparse", factory: Callable[[torch.Tensor], object] | None = None,
+            select: Callable[[object], bool] | None = None):
+    """Patch `method_cls.process_weights_after_loading` and `method_cls.apply` in place.
+
+    mode: "sparse" (2:4-sparse two-level NVFP4, the reference's QuadbitLinear) or "dense".
+    factory: weight [out, in] -> module with .forward(x); default builds QuadbitLinear / DenseNVLinear.
+    select: layer -> bool, which layers to take (default: every layer with a supported 2-D weight).
+    Returns a function that restores the original methods."""
+    if mode not in ("sparse", "dense"):
+        raise ValueError(f"mode {mode!r}")
+    make = factory or _default_factory(mode)
+    orig_pw = getattr(method_cls, "process_weights_after_loading", None)
+    orig_apply = method_cls.apply
+
+    def patched_pw(self, layer):
+        if orig_pw is not None:
+            orig_pw(self, layer)             # the engine's own bookkeeping first, as the reference plugin does
+        w = getattr(layer, "weight", None)
+        w = getattr(w, "data", w)
+        if w is None or not supported(w) or (select is not None and not select(layer)):
+            STATS["native_layers"] += 1
+            return None
+        layer._qb_linear = make(w)
+        STATS["sparse_layers" if mode == "sparse" else "dense_layers"] += 1
+        return None
+
+    def patched_apply(self, layer, x, bias=None):
+        lin = getattr(layer, "_qb_linear", None)
+        if lin is None:
+            return orig_apply(self, layer, x, bias)
+        STATS["calls"] += 1
+        out = lin.forward(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16))
+        out = out.to(x.dtype)
+        return out + bias if bias is not None else out
+
+    method_cls.process_weights_after_loading = patched_pw
+    method_cls.apply = patched_apply
+
+    def restore():
+        if orig_pw is None:
+            del method_cls.process_weights_after_loading
+        else:
+            method_cls.process_weights_after_loading = orig_pw
+        method_cls.apply = orig_apply
+
+    return restore
+
+
+def install_vllm(mode: str = "sparse", method: str = "vllm.model_executor.layers.linear.UnquantizedLinearMethod", **kw):
+    """Resolve a vLLM linear-method class by dotted name and patch it (raises ImportError without vLLM)."""
+    import importlib
+    mod_name, cls_name = method.rsplit(".", 1)
+    cls = getattr(importlib.import_module(mod_name), cls_name)
+    return install(cls, mode=mode, **kw)

@@ -1,0 +1,95 @@
+"""The linear-method hook (counterpart of the reference's vLLM plugin patch): host logic on the CPU with
+a stand-in method class and module factory, and the real modules on the GPU."""
+import pytest
+import torch
+
+from quadbit_b200 import vllm_hook
+
+
+class FakeMethod:
+    """The two methods a serving engine's linear method has."""
+
+    def __init__(self):
+        self.pw_calls = 0
+
+    def process_weights_after_loading(self, layer):
+        self.pw_calls += 1
+
+    def apply(self, layer, x, bias=None):
+        y = torch.nn.functional.linear(x, layer.weight)
+        return y + bias if bias is not None else y
+
+
+class FakeLayer:
+    def __init__(self, out_f, in_f, device="cpu"):
+        self.weight = torch.nn.Parameter(torch.randn(out_f, in_f, device=device) * 0.02, requires_grad=False)
+
+
+class Recorder:
+    def __init__(self, w):
+        self.w = w.float()
+
+    def forward(self, x):
+        return torch.nn.functional.linear(x.float(), self.w).to(torch.bfloat16)
+
+
+def test_hook_patches_and_restores_on_cpu():
+    for k in vllm_hook.STATS:
+        vllm_hook.STATS[k] = 0
+    restore = vllm_hook.install(FakeMethod, mode="sparse", factory=Recorder)
+    try:
+        m = FakeMethod()
+        good, odd = FakeLayer(256, 128), FakeLayer(100, 128)
+        m.process_weights_after_loading(good)
+        m.process_weights_after_loading(odd)
+        assert m.pw_calls == 2                                   # the engine's own step still runs
+        assert isinstance(good._qb_linear, Recorder) and not hasattr(odd, "_qb_linear")
+        assert vllm_hook.STATS["sparse_layers"] == 1 and vllm_hook.STATS["native_layers"] == 1
+        x = torch.randn(3, 5, 128)
+        b = torch.randn(256)
+        y = m.apply(good, x, b)
+        assert y.shape == (3, 5, 256) and y.dtype == x.dtype
+        assert torch.allclose(y, torch.nn.functional.linear(x, good.weight) + b, atol=2e-2)
+        y2 = m.apply(odd, x[..., :128])                          # untouched layer: engine path
+        assert torch.allclose(y2, torch.nn.functional.linear(x, odd.weight))
+        assert vllm_hook.STATS["calls"] == 1
+    finally:
+        restore()
+    assert FakeMethod.apply.__name__ == "apply" and "patched" not in FakeMethod.process_weights_after_loading.__name__
+
+
+def test_hook_select_and_mode_validation():
+    with pytest.raises(ValueError):
+        vllm_hook.install(FakeMethod, mode="fp8")
+    restore = vllm_hook.install(FakeMethod, mode="dense", factory=Recorder, select=lambda layer: False)
+    try:
+        layer = FakeLayer(128, 128)
+        FakeMethod().process_weights_after_loading(layer)
+        assert not hasattr(layer, "_qb_linear")
+    finally:
+        restore()
+
+
+def test_install_vllm_needs_a_resolvable_class():
+    with pytest.raises((ImportError, AttributeError)):
+        vllm_hook.install_vllm(method="no_such_engine.layers.LinearMethod")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["sparse", "dense"])
+def test_hook_runs_the_gpu_modules(mode):
+    import quadbit_b200 as qb
+    torch.manual_seed(5)
+    restore = vllm_hook.install(FakeMethod, mode=mode)
+    try:
+        m = FakeMethod()
+        layer = FakeLayer(512, 1024, device="cuda")
+        m.process_weights_after_loading(layer)
+        x = torch.randn(2, 70, 1024, device="cuda", dtype=torch.bfloat16)
+        bias = torch.randn(512, device="cuda", dtype=torch.bfloat16)
+        y = m.apply(layer, x, bias)
+        ref_mod = (qb.QuadbitLinear if mode == "sparse" else qb.DenseNVLinear)(layer.weight.data, keep_ref_layout=False)
+        assert torch.equal(y, ref_mod.forward(x).to(x.dtype) + bias)
+        assert y.shape == (2, 70, 512)
+    finally:
+        restore()
