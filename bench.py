@@ -14,8 +14,9 @@ tensor-parallel variant instead (strong scaling at 4096 tokens in total): QKV / 
 output features (no communication), o_proj / down split K and all-reduce their bf16 [tok,out]
 output over NCCL.
 
-Extra keys: "shapes" (per-shape sparse and dense figures, 8192^3, the activation quantiser
-and thin-M decode in GB/s), "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks".
+Extra keys: "shapes" (per-shape sparse and dense figures, 8192^3, the activation quantiser),
+"decode_dense" / "decode_sparse" (thin-M, GB/s), "fused_mlp" (us per layer and tokens/s of the fused
+sparse SwiGLU MLP), "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks".
 `--impl reference` times the CPU restatement of the reference's torch fake-quant path
 (oracle/) with all host threads on a bounded token sample of the same set.
 """
@@ -369,6 +370,21 @@ def run_gpu(args):
                                             lambda n, k: n * k / 2 + n * k / 16 + 4 * n, (1, 16, 64, 128, 256))
         line["decode_sparse"] = decode_sweep(lambda W: qb.QuadbitLinear(W, keep_ref_layout=False),
                                              lambda n, k: n * k / 4 + n * k / 16 + n * k / 32 + 4 * n, (64, 128, 256))
+
+        # ---- fused 2:4-sparse SwiGLU MLP layer (Llama-3-8B dims), the reference's "MLP tokens/s" figure:
+        #      quantise x, gate/up GEMM, SwiGLU + quantise, down GEMM through one qb_fused_mlp call
+        Hm, Im = 4096, 14336
+        mlp = qb.FusedSparseMLP((torch.randn(2 * Im, Hm, device=dev) * 0.02).to(torch.bfloat16),
+                                (torch.randn(Hm, Im, device=dev) * 0.02).to(torch.bfloat16))
+        mlp_res = {}
+        for tok_m in (2048, 8192, 16384):
+            xm = torch.randn(tok_m, Hm, device=dev).to(torch.bfloat16)
+            tm = ev_time(lambda: mlp.forward(xm), 10, 3)
+            mlp_res[f"tok{tok_m}"] = {"us_per_layer": tm * 1e6, "tokens_per_s": tok_m / tm,
+                                      "eff_tflops": 2.0 * tok_m * (2 * Im * Hm + Hm * Im) / tm / 1e12}
+            del xm
+        line["fused_mlp"] = mlp_res
+        del mlp
 
         # ---- end to end through the module API with host buffers (H2D + quantise + GEMM + D2H)
         hx = [torch.randn(TOK, L["k"]).to(torch.bfloat16).pin_memory() for L in layers]

@@ -119,7 +119,7 @@ static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa,
     qb::GemmArgs g{};
     g.A = gu_A; g.B = Bb; g.sfa = gu_sfa; g.sfb = sfb_x; g.meta = gu_meta; g.gA = (const float*)gu_gA; g.gB = (const float*)gBx;
     g.C = Cgu; g.a_rows = gu_out; g.out_f = gu_out; g.tok = tok; g.K = H; g.sparse = 1; g.out_mode = 1; g.splits = 1;
-    g.bn = tok > 128 ? 256 : 0;
+    g.bn = 0;
     rc = qb::gemm_nvfp4(g, st);
     if (rc) return rc;
     rc = qb::swiglu_quant(Cgu, Hb, nullptr, sfb_h, gH, tok, I, st);
@@ -128,7 +128,7 @@ static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa,
     d.A = dn_A; d.B = Hb; d.sfa = dn_sfa; d.sfb = sfb_h; d.meta = dn_meta; d.gA = (const float*)dn_gA; d.gB = (const float*)gH;
     d.C = Cout; d.Cf = (float*)Cf; d.a_rows = dn_out; d.out_f = dn_out; d.tok = tok; d.K = I; d.sparse = 1; d.out_mode = 1;
     d.splits = (Cf && splits > 1) ? splits : 1;
-    d.bn = tok > 128 ? 256 : 0;
+    d.bn = 0;
     return qb::gemm_nvfp4(d, st);
 }
 

@@ -111,35 +111,40 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 // B operand of the down projection. One pass, one CTA per token, h stays in registers.
 // Replaces swiglu_amax / swiglu_finalize / swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894),
 // which make three passes over a feature-major Cgu.
+// Every lane owns whole 32-value scale blocks (NJ per lane), like quant_act_kernel.
 template <int NJ>
-__global__ void __launch_bounds__(1024) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
-                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                             float* __restrict__ g_out, int tok, int I) {
+__global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
+                                                            uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
+                                                            float* __restrict__ g_out, int tok, int I) {
     const int row = blockIdx.x;
     const int nchunks = I >> 3;
+    const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
     const int lane = threadIdx.x & 31;
     const uint4* gr = cgu + (size_t)row * (nchunks * 2);
     const uint4* ur = gr + nchunks;
-    float h[NJ][8];
-    float cmax[NJ];
+    float h[NJ][32];
+    float bmax[NJ];
     float tmax = 0.f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
-        if (c < nchunks) { gv = __ldg(gr + c); uv = __ldg(ur + c); }
-        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
-        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        const int b = threadIdx.x + j * blockDim.x;
         float m = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
-            float a = (g2.x / (1.f + __expf(-g2.x))) * u2.x;
-            float b = (g2.y / (1.f + __expf(-g2.y))) * u2.y;
-            h[j][2 * i] = a; h[j][2 * i + 1] = b;
-            m = fmaxf(m, fmaxf(fabsf(a), fabsf(b)));
+        for (int k = 0; k < 4; k++) {
+            uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
+            if (b < nblocks) { gv = __ldg(gr + (size_t)b * 4 + k); uv = __ldg(ur + (size_t)b * 4 + k); }
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
+                const float a = __fdividef(g2.x, 1.f + __expf(-g2.x)) * u2.x;
+                const float c = __fdividef(g2.y, 1.f + __expf(-g2.y)) * u2.y;
+                h[j][8 * k + 2 * i] = a; h[j][8 * k + 2 * i + 1] = c;
+                m = fmaxf(m, fmaxf(fabsf(a), fabsf(c)));
+            }
         }
-        cmax[j] = m;
+        bmax[j] = m;
         tmax = fmaxf(tmax, m);
     }
     __shared__ float red[32];
@@ -150,23 +155,30 @@ __global__ void __launch_bounds__(1024) swiglu_quant_kernel(const uint4* __restr
     r = warp_max(r);
     const float gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
     if (threadIdx.x == 0) g_out[row] = gl;
+    const bool wide = (reinterpret_cast<uintptr_t>(Hwords) & 15) == 0;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        float bmax = cmax[j];
-        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
-        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
-        uint32_t code = enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl));
-        float sg = fmaxf(__fmul_rn(dec_ue4m3(code), gl), 1e-30f);
-        const uint32_t w = Fp4Divider(sg).pack8(h[j]);
-        uint32_t sw = 0;
-        int base = lane & ~15;
+        const int b = threadIdx.x + j * blockDim.x;
+        const uint32_t code = enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl));
+        const Fp4Divider dv(fmaxf(__fmul_rn(dec_ue4m3(code), gl), 1e-30f));
+        uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * 4) << (8 * i);
-        if (c < nchunks) {
-            Hwords[(size_t)row * nchunks + c] = w;
-            if ((lane & 15) == 0) {
-                int jcol = c >> 2;
+        for (int k = 0; k < 4; k++) {
+            float f8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f8[e] = h[j][8 * k + e];
+            w[k] = dv.pack8(f8);
+        }
+        uint32_t sw = 0;
+        const int base = lane & ~3;
+#pragma unroll
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i) << (8 * i);
+        if (b < nblocks) {
+            uint32_t* dst = Hwords + (size_t)row * nchunks + (size_t)b * 4;
+            if (wide) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            else { dst[0] = w[0]; dst[1] = w[1]; dst[2] = w[2]; dst[3] = w[3]; }
+            if ((lane & 3) == 0) {
+                const int jcol = b;      // scale column, a multiple of 4 here
                 if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol >> 2) * tok + row) * 4) = sw;
                 if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(I) / 128)) = sw;
             }
@@ -179,15 +191,14 @@ int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* 
     if (tok == 0) return QB_OK;
     if (!cgu || !Hb || !gH || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
     if (((uintptr_t)cgu & 15) || ((uintptr_t)Hb & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3)) return QB_ERR_ARG;
-    int nchunks = I / 8;
-    int threads = nchunks <= 2048 ? 256 : (nchunks <= 4096 ? 512 : 1024);
-    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
-    int nj = (nchunks + threads - 1) / threads;
+    const int nblocks = I / 32;
+    int threads = (nblocks + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    const int nj = (nblocks + threads - 1) / threads;
 #define QB_LS(NJ) swiglu_quant_kernel<NJ><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I)
     if (nj <= 1) QB_LS(1);
     else if (nj <= 2) QB_LS(2);
     else if (nj <= 4) QB_LS(4);
-    else if (nj <= 8) QB_LS(8);
     else return QB_ERR_UNSUPPORTED;
 #undef QB_LS
     return (int)cudaGetLastError();
