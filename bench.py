@@ -386,6 +386,32 @@ def run_gpu(args):
         line["fused_mlp"] = mlp_res
         del mlp
 
+        # ---- grouped (MoE) GEMMs, gpt-oss-120b-shaped (configs[4] at one GPU): 8192 tokens, top-4 of 128 experts,
+        #      hidden 2880 (padded to 2944), gate/up N = 2 x 2944, down N = 2944; routed rows sorted by expert and
+        #      padded to 128 per expert; uniform random routing (seed 3); every expert holds the same random values
+        from quadbit_b200 import moe as qmoe
+        E, topk, Hh = 128, 4, 2880
+        Hp = (Hh + 127) // 128 * 128
+        Hq = (Hh + 255) // 256 * 256                                   # output features per expert padded to 256 (pair kernel)
+        g0 = qmoe.pack(lib, (torch.randn(2 * Hp, Hp, device=dev) * 0.02).to(torch.bfloat16))
+        d0 = qmoe.pack(lib, (torch.randn(Hq, Hp, device=dev) * 0.02).to(torch.bfloat16))
+        w_gu, w_dn = qmoe.stack([g0] * E), qmoe.stack([d0] * E)
+        gen = torch.Generator(device="cpu").manual_seed(3)
+        logits = torch.randn(8192, E, generator=gen)
+        assign = torch.topk(logits, topk, dim=1).indices.reshape(-1).to(dev)
+        src, eblk, r_pad = qmoe.build_routing(assign, E)
+        rows = torch.randn(r_pad, Hp, device=dev).to(torch.bfloat16)
+        hrows = torch.randn(r_pad, Hp, device=dev).to(torch.bfloat16)
+        row_w = torch.rand(r_pad, device=dev)
+        t_gu = ev_time(lambda: qmoe.seg_gemm(lib, rows, w_gu, 2 * Hp, Hp, eblk), 10, 3)
+        t_dn = ev_time(lambda: qmoe.seg_gemm(lib, hrows, w_dn, Hq, Hp, eblk, row_w=row_w), 10, 3)
+        fl_moe = 2.0 * 8192 * topk * (2 * Hh * Hh + Hh * Hh)           # useful flops: unpadded dims, routed rows only
+        line["moe_grouped"] = {"routed_rows": 8192 * topk, "padded_rows": r_pad, "gate_up_us": t_gu * 1e6, "down_us": t_dn * 1e6,
+                               "eff_tflops": fl_moe / (t_gu + t_dn) / 1e12,
+                               "what": "quantise + grouped GEMM (CTA-pair kernel, one expert per 128-token tile) for gate/up and for down with the "
+                                       "routing weight in the epilogue; SwiGLU, gather and combine not included"}
+        del w_gu, w_dn, rows, hrows
+
         # ---- end to end through the module API with host buffers (H2D + quantise + GEMM + D2H)
         hx = [torch.randn(TOK, L["k"]).to(torch.bfloat16).pin_memory() for L in layers]
         hy = [torch.empty((TOK, L["n"]), dtype=torch.bfloat16).pin_memory() for L in layers]

@@ -571,6 +571,9 @@ struct KParams2 {
     int num_m2, num_n, kblocks;
     int out_mode;
     int a_tiled;
+    const int* eblk;                     // grouped mode (BN == 128): expert of every 128-token block, null = plain GEMM
+    const __nv_bfloat16* bias;           // out_mode 3: per-expert bias [E][out_f] (may be null)
+    const float* row_w;                  // out_mode 3: weight of every routed row [tok] (may be null)
     int dbg;
     unsigned long long* prof;
 };
@@ -656,7 +659,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
-            const int a_row0 = m2 * 256 + (int)rank * 128;
+            const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
@@ -701,7 +704,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
-            const int rb_a = (m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
+            const int rb_a = ((p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
                 int j1 = slot + 1;
@@ -907,13 +910,25 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int n0 = n * BN + half * HCOLS;          // first token column of this warp
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
+            const int a_base = p.eblk ? p.eblk[n] * p.out_f : 0;      // first row of this tile's expert in A / gA / bias
             // per-tile constants first, so their latency hides behind the accumulator wait
-            const float ga = p.gA ? __ldg(p.gA + o) : 1.f;
-            float gbv[NCH];
+            const float ga = p.gA ? __ldg(p.gA + a_base + o) : 1.f;
+            float gbv[NCH], rwv[NCH];
 #pragma unroll
             for (int c = 0; c < NCH; c++) {
                 const int col = n0 + 16 * c + (lane & 15);
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
+                rwv[c] = (p.out_mode == 3 && p.row_w && col < p.tok) ? __ldg(p.row_w + col) : 1.f;
+            }
+            // out_mode 3: the bias of the 8 features this lane emits per token in the transposed phase
+            float bias8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) bias8[e] = 0.f;
+            if (p.out_mode == 3 && p.bias) {
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + a_base + o0 + q * 32 + (lane & 3) * 8));
+                const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(bh[e]); bias8[2 * e] = f.x; bias8[2 * e + 1] = f.y; }
             }
             long long cw = QB_CLK();
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
@@ -971,11 +986,19 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         const float gt = __shfl_sync(0xffffffffu, gbl, trow);
                         const uint4 lo = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32);
                         const uint4 hi = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32 + 16);
+                        float f[8] = {__uint_as_float(lo.x) * gt, __uint_as_float(lo.y) * gt, __uint_as_float(lo.z) * gt,
+                                      __uint_as_float(lo.w) * gt, __uint_as_float(hi.x) * gt, __uint_as_float(hi.y) * gt,
+                                      __uint_as_float(hi.z) * gt, __uint_as_float(hi.w) * gt};
+                        if (p.out_mode == 3) {
+                            const float rw = __shfl_sync(0xffffffffu, rwv[c], trow);
+#pragma unroll
+                            for (int e = 0; e < 8; e++) f[e] = (f[e] + bias8[e]) * rw;
+                        }
                         uint4 val;
-                        val.x = pack_bf16x2(__uint_as_float(lo.x) * gt, __uint_as_float(lo.y) * gt);
-                        val.y = pack_bf16x2(__uint_as_float(lo.z) * gt, __uint_as_float(lo.w) * gt);
-                        val.z = pack_bf16x2(__uint_as_float(hi.x) * gt, __uint_as_float(hi.y) * gt);
-                        val.w = pack_bf16x2(__uint_as_float(hi.z) * gt, __uint_as_float(hi.w) * gt);
+                        val.x = pack_bf16x2(f[0], f[1]);
+                        val.y = pack_bf16x2(f[2], f[3]);
+                        val.z = pack_bf16x2(f[4], f[5]);
+                        val.w = pack_bf16x2(f[6], f[7]);
                         const int col = n0 + c0 + trow;
                         if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val);
                     }
@@ -1158,6 +1181,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.out_f = a.out_f; kp.tok = a.tok;
     kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
     kp.a_tiled = a.a_tiled;
+    kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
@@ -1194,6 +1218,10 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     if (pair_ok && (a.bn == 512 || (a.bn == 0 && a.tok >= 512)))   // 512: pair kernel, 256-token tile
         return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
     if (pair_ok && a.bn == 384)                                     // 384: pair kernel, 128-token tile, two accumulators
+        return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
+    // grouped (MoE) form on the pair kernel: one expert per 128-token block = per tile of the 128-token variant
+    if (a.eblk && splits == 1 && (a.out_mode == 1 || a.out_mode == 3) && a.out_f % 256 == 0 && a.tok >= 128 && a.tok % 128 == 0 &&
+        (a.bn == 0 || a.bn == 128) && (((uintptr_t)a.bias & 15) == 0))
         return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
     int bn = a.bn;
     if (a.eblk) bn = 128;

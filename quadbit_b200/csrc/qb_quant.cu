@@ -210,35 +210,41 @@ int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* 
 // (cuda/sparse_fp4_lib.cu:902-1011, single-level per-32) and, with TWO_LEVEL, also emits the
 // per-token global so the following GEMM runs two-level. One CTA per row, row kept in registers.
 template <int BLOCK, int NJ, bool ADD, bool TWO_LEVEL>
-__global__ void __launch_bounds__(1024) norm_quant_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
-                                                           const uint4* __restrict__ wt, uint4* __restrict__ hout,
-                                                           uint32_t* __restrict__ Bwords, uint8_t* __restrict__ sf_ref,
-                                                           uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok, int H,
-                                                           float eps) {
-    constexpr int LPB = BLOCK / 8, G = 4 * LPB, P = 128 / BLOCK;
+__global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
+                                                          const uint4* __restrict__ wt, uint4* __restrict__ hout,
+                                                          uint32_t* __restrict__ Bwords, uint8_t* __restrict__ sf_ref,
+                                                          uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok, int H,
+                                                          float eps) {
+    // every lane owns whole scale blocks (BLOCK values, NJ per lane), like quant_act_kernel
+    constexpr int CPB = BLOCK / 8, P = 128 / BLOCK;
     const int row = blockIdx.x;
     const int nchunks = H >> 3;
+    const int nblocks = H / BLOCK;       // a multiple of 4 (H % 128 == 0)
     const int lane = threadIdx.x & 31;
     __shared__ float red[32];
-    float v[NJ][8];
+    float v[NJ][BLOCK];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-        if (c < nchunks) { a = __ldg(x + (size_t)row * nchunks + c); if (ADD) b = __ldg(res + (size_t)row * nchunks + c); }
-        const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
-        uint4 o;
-        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+        const int blk = threadIdx.x + j * blockDim.x;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float2 f = __bfloat1622float2(ah[i]);
-            if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); f.x = __fadd_rn(f.x, r2.x); f.y = __fadd_rn(f.y, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
-            v[j][2 * i] = f.x; v[j][2 * i + 1] = f.y;
-            ss += f.x * f.x + f.y * f.y;
+        for (int k = 0; k < CPB; k++) {
+            const size_t c = (size_t)blk * CPB + k;
+            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+            if (blk < nblocks) { a = __ldg(x + (size_t)row * nchunks + c); if (ADD) b = __ldg(res + (size_t)row * nchunks + c); }
+            const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 f = __bfloat1622float2(ah[i]);
+                if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); f.x = __fadd_rn(f.x, r2.x); f.y = __fadd_rn(f.y, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
+                v[j][8 * k + 2 * i] = f.x; v[j][8 * k + 2 * i + 1] = f.y;
+                ss += f.x * f.x + f.y * f.y;
+            }
+            if (ADD && hout && blk < nblocks) hout[(size_t)row * nchunks + c] = o;
         }
-        if (ADD && hout && c < nchunks) hout[(size_t)row * nchunks + c] = o;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -248,23 +254,27 @@ __global__ void __launch_bounds__(1024) norm_quant_kernel(const uint4* __restric
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     const float rms = rsqrtf(tot / (float)H + eps);
-    float cmax[NJ];
+    float bmax[NJ];
     float tmax = 0.f;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        uint4 w4 = make_uint4(0, 0, 0, 0);
-        if (c < nchunks) w4 = __ldg(wt + c);
-        const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&w4);
+        const int blk = threadIdx.x + j * blockDim.x;
         float m = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float2 w2 = __bfloat1622float2(wh[i]);
-            v[j][2 * i] = __fmul_rn(__fmul_rn(v[j][2 * i], rms), w2.x);
-            v[j][2 * i + 1] = __fmul_rn(__fmul_rn(v[j][2 * i + 1], rms), w2.y);
-            m = fmaxf(m, fmaxf(fabsf(v[j][2 * i]), fabsf(v[j][2 * i + 1])));
+        for (int k = 0; k < CPB; k++) {
+            uint4 w4 = make_uint4(0, 0, 0, 0);
+            if (blk < nblocks) w4 = __ldg(wt + (size_t)blk * CPB + k);
+            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&w4);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 w2 = __bfloat1622float2(wh[i]);
+                const int e = 8 * k + 2 * i;
+                v[j][e] = __fmul_rn(__fmul_rn(v[j][e], rms), w2.x);
+                v[j][e + 1] = __fmul_rn(__fmul_rn(v[j][e + 1], rms), w2.y);
+                m = fmaxf(m, fmaxf(fabsf(v[j][e]), fabsf(v[j][e + 1])));
+            }
         }
-        cmax[j] = m;
+        bmax[j] = m;
         tmax = fmaxf(tmax, m);
     }
     float gl = 1.f;
@@ -278,23 +288,35 @@ __global__ void __launch_bounds__(1024) norm_quant_kernel(const uint4* __restric
         gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
         if (threadIdx.x == 0) g_out[row] = gl;
     }
+    const bool wide = (reinterpret_cast<uintptr_t>(Bwords) & 15) == 0;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
-        int c = threadIdx.x + j * blockDim.x;
-        float bmax = cmax[j];
+        const int blk = threadIdx.x + j * blockDim.x;
+        const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax[j], 6.f));
+        const Fp4Divider dv(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
+        uint32_t w[CPB];
 #pragma unroll
-        for (int o = 1; o < LPB; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
-        uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax, 6.f));
-        float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
-        const uint32_t w = Fp4Divider(sg).pack8(v[j]);
+        for (int k = 0; k < CPB; k++) {
+            float f8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f8[e] = v[j][8 * k + e];
+            w[k] = dv.pack8(f8);
+        }
         uint32_t sw = 0;
-        int base = lane & ~(G - 1);
+        const int base = lane & ~3;
 #pragma unroll
-        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i * LPB) << (8 * i);
-        if (c < nchunks) {
-            Bwords[(size_t)row * nchunks + c] = w;
-            if ((lane & (G - 1)) == 0) {
-                int jcol = c / LPB;
+        for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i) << (8 * i);
+        if (blk < nblocks) {
+            uint32_t* dst = Bwords + (size_t)row * nchunks + (size_t)blk * CPB;
+            if (wide) {
+                if constexpr (CPB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < CPB; k++) dst[k] = w[k];
+            }
+            if ((lane & 3) == 0) {
+                const int jcol = blk;
                 if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
                 if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(H) / BLOCK / 4)) = sw;
             }
@@ -310,11 +332,11 @@ int norm_quant(const void* x, const void* res, const void* wt, void* hout, void*
     if (((uintptr_t)x & 15) || ((uintptr_t)res & 15) || ((uintptr_t)wt & 15) || ((uintptr_t)hout & 15) || ((uintptr_t)Bbytes & 3) ||
         ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3))
         return QB_ERR_ARG;
-    int nchunks = H / 8;
-    int threads = nchunks <= 1024 ? 256 : (nchunks <= 2048 ? 512 : 1024);
-    if (nchunks < threads) threads = (nchunks + 31) / 32 * 32;
-    int nj = (nchunks + threads - 1) / threads;
-    if (nj > 4) return QB_ERR_UNSUPPORTED;     // H <= 32768
+    const int nblocks = H / block;
+    int threads = (nblocks + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    const int nj = (nblocks + threads - 1) / threads;
+    if (nj > 4) return QB_ERR_UNSUPPORTED;     // H <= 32768 (per-16) / 65536 (per-32)
 #define QB_LN3(B, NJ, ADD, TL)                                                                                                   \
     norm_quant_kernel<B, NJ, ADD, TL><<<tok, threads, 0, st>>>((const uint4*)x, (const uint4*)res, (const uint4*)wt, (uint4*)hout, \
                                                                (uint32_t*)Bbytes, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)g, tok, H, eps)

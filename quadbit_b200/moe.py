@@ -113,8 +113,8 @@ class SparseMoE:
         self.I = w_down[0].shape[1]
         self.Hp = (self.H + 127) // 128 * 128
         self.Ip = (self.I + 127) // 128 * 128
-        self.mpe_gu = (2 * self.Ip + 127) // 128 * 128
-        self.mpe_dn = (self.H + 127) // 128 * 128
+        self.mpe_gu = (2 * self.Ip + 255) // 256 * 256       # multiples of 256: the grouped GEMM then runs on the CTA-pair kernel
+        self.mpe_dn = (self.H + 255) // 256 * 256
         gus, dns = [], []
         for wg, wd in zip(w_gate_up, w_down):
             g = wg.new_zeros(self.mpe_gu, self.Hp)                 # gate rows [0,I), up rows [Ip, Ip+I)
