@@ -657,12 +657,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const bool isA = warp == 0;
         int stage = 0;
         uint32_t phase = 0;
+        long long c_pw = 0, c_pb = 0, c_pn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
+                const long long q0 = QB_CLK();
                 int s1 = stage + 1;
                 uint32_t ph1 = phase;
                 if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
@@ -671,6 +673,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     nb = 1;
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) { ok = false; break; }
                 }
+                const long long q1 = QB_CLK();
+                c_pw += q1 - q0; c_pn += nb;
                 if (lane == 0) {
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
@@ -694,9 +698,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 kb += nb;
                 stage += nb;
                 if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
+                c_pb += QB_CLK() - q1;
             }
             if (!ok) break;
         }
+        if (p.prof && isA && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[0] = c_pw; o[1] = c_pb; o[2] = c_pn; }
     } else if (warp == 11 || warp == 12) {
         // ------------------------------------------------------------ sideband producers (both CTAs)
         const bool isW = warp == 11;               // weight side: scale factors of A and metadata
@@ -749,7 +755,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
-            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_t0 = QB_CLK();
+            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_iters = 0, c_t0 = QB_CLK();
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
                 long long ca = QB_CLK();
                 if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
@@ -764,7 +770,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
                     int nb = 2;
                     // operands of both blocks landed (loads complete in any order) and the scale factors
-                    // of the later block (hence of both) are in tensor memory
+                    // of the later block (hence of both) are in tensor memory; four blocks per poll were
+                    // measured too and were slower
                     if (kb + 1 >= p.kblocks || !mbar_try_wait3(full_bar(stage), phase, full_bar(s1), ph1, sfr_bar(s1), ph1)) {
                         nb = 1;
                         if (!mbar_try_wait2(full_bar(stage), phase, sfr_bar(stage), phase) &&
@@ -772,7 +779,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                              !mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_SF))) { ok = false; break; }
                     }
                     long long cg = QB_CLK();
-                    c_wait_sf += cg - cf;
+                    c_wait_sf += cg - cf; c_iters++;
                     tc_fence_after();
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
@@ -804,7 +811,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
             if (p.prof) {
                 unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue;
+                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue; o[4] = c_iters;
             }
         }
         __syncwarp();
@@ -814,9 +821,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0, slot = 0;
         uint32_t phase = 0, sphase = 0;
+        long long c_sw = 0, c_sb = 0, c_sn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
+                const long long f0 = QB_CLK();
                 int s1 = stage + 1, j1 = slot + 1;
                 uint32_t ph1 = phase, sph1 = sphase;
                 if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
@@ -831,6 +840,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF) ||
                          !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_SF_SLOT))) { ok = false; break; }
                 }
+                const long long f1 = QB_CLK();
+                c_sw += f1 - f0; c_sn += nb;
                 tc_fence_after();
 #ifdef QB_EXPERIMENT
                 if (!((p.dbg & 1) && kb >= 2))
@@ -888,9 +899,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
                 slot += nb;
                 if (slot >= C::NSB) { slot -= C::NSB; sphase ^= 1; }
+                c_sb += QB_CLK() - f1;
             }
             if (!ok) break;
         }
+        if (p.prof && warp == 6 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[3] = c_sw; o[4] = c_sb; o[5] = c_sn; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         // Eight warps: warps 2-5 drain the first half of the tile's columns, warps 13-16 the second half;
@@ -1024,7 +1037,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (p.prof && warp == 2 && lane == 0) { p.prof[4096 + (size_t)blockIdx.x * 2] = c_wait_accf; p.prof[4096 + (size_t)blockIdx.x * 2 + 1] = c_epi; }
+        if (p.prof && warp == 2 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[6] = c_wait_accf; o[7] = c_epi; }
     }
 
     // teardown: no CTA may leave while its partner can still signal its barriers
