@@ -527,7 +527,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // Requires out % 256 == 0 and tok >= 128.
 template <bool SPARSE, int BN_>
 struct Cfg2 {
-    static constexpr int BN = BN_;                        // tokens per pair tile: 128 (two accumulator stages) or 256
+    static constexpr int BN = BN_;                        // tokens per pair tile: 128 or 192 (two accumulator stages) or 256
     static constexpr int THREADS = 544;                   // 17 warps, roles above
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
@@ -535,30 +535,30 @@ struct Cfg2 {
     static constexpr int B_BYTES = B_ROWS * 128;
     static constexpr int MMAS = SPARSE ? 2 : 4;
     static constexpr int B_KSTEP = SPARSE ? 64 : 32;
-    static constexpr int NBA = BN / 128;                  // scale-factor atoms (128 rows) per token tile
+    static constexpr int NBA = (BN + 127) / 128;          // scale-factor atoms (128 rows) a token tile touches
     static constexpr int SFA_BYTES = MMAS * 512;
     static constexpr int SFB_BYTES = NBA * MMAS * 512;    // all BN token rows, in both CTAs
     static constexpr int META_BYTES = SPARSE ? 2048 : 0;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;                       // operand ring slot
     static constexpr int SIDE_BYTES = SFA_BYTES + SFB_BYTES + META_BYTES;       // sideband ring slot
     static constexpr int NSB = 6;                                               // sideband ring slots
-    static constexpr int ACC_STAGES = BN == 128 ? 2 : 1;
+    static constexpr int ACC_STAGES = BN <= 192 ? 2 : 1;
     static constexpr int EPI_PITCH = 144;                 // 32 fp32 + 16 B pad per token row of a warp's transpose tile
     static constexpr int EPI_BYTES = 8 * 16 * EPI_PITCH;  // eight epilogue warps, 16 token rows each
     static constexpr int SMEM_BUDGET = 226 * 1024 - 1024 - EPI_BYTES - NSB * SIDE_BYTES - 512;
     static constexpr int SFA_COLS = MMAS * 4;
     static constexpr int SFB_COLS = MMAS * 4 * NBA;
     static constexpr int E_COLS = SPARSE ? 4 : 0;
-    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // one TMEM slot per operand stage
+    static constexpr int SF_SET = SFA_COLS + SFB_COLS + E_COLS;     // columns of one scale-factor slot in TMEM
     static constexpr int STAGES_SMEM = SMEM_BUDGET / STAGE_BYTES;
-    static constexpr int STAGES_TMEM = 256 / SF_SET;
-    static constexpr int STAGES_MIN = STAGES_SMEM < STAGES_TMEM ? STAGES_SMEM : STAGES_TMEM;
-    static constexpr int STAGES = STAGES_MIN > 10 ? 10 : STAGES_MIN;
+    static constexpr int STAGES = STAGES_SMEM > 10 ? 10 : STAGES_SMEM;
+    static constexpr int TM_SF0 = ACC_STAGES * BN;                   // accumulators first, then the scale-factor slots
+    static constexpr int NSLOT_TMEM = (512 - TM_SF0) / SF_SET;
+    static constexpr int NSLOT = NSLOT_TMEM < STAGES ? NSLOT_TMEM : STAGES;   // slot ring, K block `it` uses slot it % NSLOT
     static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + NSB * SIDE_BYTES + EPI_BYTES + 512;
-    static constexpr int TM_SF0 = 256;
     static constexpr int TM_COLS = 512;
-    static_assert(BN == 128 || BN == 256, "token tile");
-    static_assert(ACC_STAGES * BN <= 256 && TM_SF0 + STAGES * SF_SET <= 512, "TMEM budget");
+    static_assert(BN == 128 || BN == 192 || BN == 256, "token tile");
+    static_assert(NSLOT >= 2 && TM_SF0 + NSLOT * SF_SET <= 512, "TMEM budget");
     static_assert(STAGES >= 3, "smem budget");
     static_assert((3 * STAGES + 2 * NSB + 4) * 8 <= 512, "barrier block");
 };
@@ -753,10 +753,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // barrier wait and the MMAs it gates.
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
-            int stage = 0, acc = 0;
+            int stage = 0, acc = 0, tslot = 0;
             uint32_t phase = 0, acc_phase = 0;
             long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_iters = 0, c_t0 = QB_CLK();
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+                // a 192-token tile starts 0 or 64 rows into a 128-row scale-factor atom: 0 or 2 columns in
+                const uint32_t sfb_coloff = (uint32_t)((((tile / p.num_m2) * BN) & 127) >> 5);
                 long long ca = QB_CLK();
                 if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
                 c_wait_acc += QB_CLK() - ca;
@@ -783,8 +785,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     tc_fence_after();
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
-                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + s * C::SF_SET;
-                        const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
+                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + tslot * C::SF_SET;
+                        const uint32_t t_sfb = t_sfa + C::SFA_COLS + sfb_coloff, t_e = t_sfa + C::SFA_COLS + C::SFB_COLS;
+                        if (++tslot == C::NSLOT) tslot = 0;
 #pragma unroll
                         for (int i = 0; i < C::MMAS; i++) {
 #ifdef QB_EXPERIMENT
@@ -819,26 +822,36 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // ------------------------------------------------------------ scale-factor warps (both CTAs)
         const int q = warp & 3;
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
-        int stage = 0, slot = 0;
-        uint32_t phase = 0, sphase = 0;
+        // K block number `it` (counted over all tiles) uses operand stage it % STAGES, sideband slot it % NSB and
+        // tensor-memory slot it % NSLOT. Its tensor-memory slot is free once the MMAs of K block it - NSLOT have
+        // completed, which the empty barrier of THAT block's stage signals (completions come in ring order).
+        int stage = 0, slot = 0, tslot = 0;
+        uint32_t sphase = 0, it = 0;
         long long c_sw = 0, c_sb = 0, c_sn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
                 const long long f0 = QB_CLK();
-                int s1 = stage + 1, j1 = slot + 1;
-                uint32_t ph1 = phase, sph1 = sphase;
-                if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
+                int s1 = stage + 1, j1 = slot + 1, t1 = tslot + 1;
+                uint32_t sph1 = sphase;
+                if (s1 == C::STAGES) s1 = 0;
                 if (j1 == C::NSB) { j1 = 0; sph1 ^= 1; }
-                int nb = 2;
-                // sideband slots landed (in any order), and the MMAs that read the later stage's tensor
-                // memory slot one ring revolution ago (hence the earlier stage's too) have completed: the
-                // same barrier that frees the operand slot
-                if (kb + 1 >= p.kblocks || !mbar_try_wait3(sbf_bar(slot), sphase, sbf_bar(j1), sph1, empty_bar(s1), ph1 ^ 1)) {
-                    nb = 1;
-                    if (!mbar_try_wait2(sbf_bar(slot), sphase, empty_bar(stage), phase ^ 1) &&
-                        (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF) ||
-                         !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_SF_SLOT))) { ok = false; break; }
+                if (t1 == C::NSLOT) t1 = 0;
+                // barrier / parity that says "the MMAs of K block c have completed"
+                auto done_bar = [&](uint32_t c) { return empty_bar((int)(c % C::STAGES)); };
+                auto done_par = [&](uint32_t c) { return (c / C::STAGES) & 1u; };
+                int nb = 1;
+                if (kb + 1 < p.kblocks) {          // both sideband slots landed (any order) and the later slot is free
+                    const bool two = it + 1 >= (uint32_t)C::NSLOT
+                                         ? mbar_try_wait3(sbf_bar(slot), sphase, sbf_bar(j1), sph1, done_bar(it + 1 - C::NSLOT),
+                                                          done_par(it + 1 - C::NSLOT))
+                                         : mbar_try_wait2(sbf_bar(slot), sphase, sbf_bar(j1), sph1);
+                    if (two) nb = 2;
+                }
+                if (nb == 1) {
+                    if (!mbar_wait(sbf_bar(slot), sphase, &abort_flag, &g_status, SITE_SF, QB_BACKOFF_SF)) { ok = false; break; }
+                    if (it >= (uint32_t)C::NSLOT &&
+                        !mbar_wait(done_bar(it - C::NSLOT), done_par(it - C::NSLOT), &abort_flag, &g_status, SITE_SF_SLOT)) { ok = false; break; }
                 }
                 const long long f1 = QB_CLK();
                 c_sw += f1 - f0; c_sn += nb;
@@ -848,9 +861,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #endif
                 {
                     for (int u = 0; u < nb; u++) {
-                        const int s = u ? s1 : stage, j = u ? j1 : slot;
+                        const int j = u ? j1 : slot, ts = u ? t1 : tslot;
                         const uint32_t sf = sideSFA(j) + lane * 16;       // this lane's 16 bytes of every atom
-                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + s * C::SF_SET + lane_sel;
+                        const uint32_t t_sfa = tmem_base + C::TM_SF0 + ts * C::SF_SET + lane_sel;
                         const uint32_t t_sfb = t_sfa + C::SFA_COLS, t_e = t_sfb + C::SFB_COLS;
                         // SFA: MMAS atoms -> MMAS*4 consecutive columns
                         {
@@ -895,10 +908,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     }
                 }
                 kb += nb;
+                it += nb;
                 stage += nb;
-                if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
+                if (stage >= C::STAGES) stage -= C::STAGES;
                 slot += nb;
                 if (slot >= C::NSB) { slot -= C::NSB; sphase ^= 1; }
+                tslot += nb;
+                if (tslot >= C::NSLOT) tslot -= C::NSLOT;
                 c_sb += QB_CLK() - f1;
             }
             if (!ok) break;
@@ -1227,7 +1243,13 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     // bn == 512 requests it explicitly, bn == 0 (auto) picks it for prefill-sized problems.
     const bool pair_ok = !a.eblk && splits == 1 && (a.out_mode == 0 || a.out_mode == 1) && a.out_f % 256 == 0 && a.tok >= 128 &&
                          b_tail_ok(a.tok);
-    if ((a.bn == 512 || a.bn == 384) && !pair_ok) return QB_ERR_ARG;
+    if ((a.bn == 512 || a.bn == 384 || a.bn == 576) && !pair_ok) return QB_ERR_ARG;
+    // 576: pair kernel with 192-token tiles and two accumulators, so the epilogue of a tile runs under the main
+    // loop of the next one. Never chosen automatically: only 4 (sparse) / 2 (dense) scale-factor slots fit
+    // beside two 192-column accumulators, the scale-factor copy then cannot run far enough ahead of the MMAs,
+    // and the measured K-block time rises from ~500 to ~700 cycles (gate shape 102 us against 91 us).
+    if (pair_ok && a.bn == 576)
+        return a.sparse ? launch_pair<true, 192>(a, st) : launch_pair<false, 192>(a, st);
     if (pair_ok && (a.bn == 512 || (a.bn == 0 && a.tok >= 512)))   // 512: pair kernel, 256-token tile
         return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
     if (pair_ok && a.bn == 384)                                     // 384: pair kernel, 128-token tile, two accumulators

@@ -102,15 +102,17 @@ def test_gemm_bf16_outputs_match_fake_quant(lib, sparse, mode, out_f, tok, K, bn
 
 
 PAIR_CASES = [(256, 128, 256, 512), (512, 768, 1024, 512), (256, 300, 1152, 512), (1024, 512, 4096, 0), (768, 1000, 2048, 0),
-              (256, 256, 512, 384), (512, 640, 1024, 384)]
+              (256, 256, 512, 384), (512, 640, 1024, 384),
+              (256, 192, 256, 576), (512, 768, 2048, 576), (256, 1000, 1152, 576), (768, 4096, 4096, 576), (512, 130, 512, 576),
+              (1024, 2048, 8448, 0), (512, 1536, 12288, 512)]
 
 
 @pytest.mark.parametrize("sparse", [1, 0])
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("out_f,tok,K,bn", PAIR_CASES)
 def test_cta_pair_kernel_matches_fake_quant(lib, sparse, mode, out_f, tok, K, bn):
-    """The prefill kernel (tcgen05.mma.cta_group::2; bn 512 / 384 select its 256- / 128-token tile,
-    bn 0 lets the library choose it for tok >= 512) against the oracle and against the single-CTA
+    """The prefill kernel (tcgen05.mma.cta_group::2; bn 512 / 576 / 384 select its 256- / 192- / 128-token
+    tile, bn 0 lets the library choose the 256-token tile for tok >= 512) against the oracle and against the single-CTA
     kernel, which must agree bit for bit (same products, same fp32 accumulation per K block)."""
     torch.manual_seed(out_f + tok + K + 7)
     W = torch.randn(out_f, K) * 0.02
