@@ -507,28 +507,34 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // copy into tensor memory overlaps the operand loads of the same stage instead of following them.
 // Measured with every MMA, load and epilogue switched off, the barrier round trip
 // (release -> load issue -> landing -> scale-factor copy -> remote arrive -> issue -> commit) is what
-// bounds the K-block rate, so each hop is kept off the others' critical path. 416 threads per CTA:
-//   warp 0     A producer, warp 10 B producer: one TMA tile load per K block each, completing (from
+// bounds the K-block rate, so each hop is kept off the others' critical path. 640 threads per CTA,
+// one kind of role per warpgroup (registers are moved between warpgroups with setmaxnreg):
+//   warp 0     A producer, warp 1 B producer: one TMA tile load per K block each, completing (from
 //              both CTAs) on the LEADER's full barrier; no multicast.
-//   warp 11    sideband producer for scale-factor atoms of A and the metadata, warp 12 for the
+//   warp 2     sideband producer for scale-factor atoms of A and the metadata, warp 3 for the
 //              scale-factor atoms of B; they complete on this CTA's sideband barrier.
-//   warps 6-9  scale-factor warps: once the sideband slot has landed and the tensor memory slot of
+//   warps 4-7  scale-factor warps: once the sideband slot has landed and the tensor memory slot of
 //              the stage is free, copy scale factors / metadata from shared memory into that slot
 //              with tcgen05.st (each warp its lane quadrant), free the sideband slot and tell the
 //              leader. Measured: a tcgen05.cp costs ~50 cycles of the MMA pipe and 7-12 of them per
 //              K block cap the pipe at 57 % (dense) / 60 % (sparse) of its MMA-only rate; stores
 //              from registers run beside the MMAs.
-//   warp 1     MMA issuer (one thread of the even CTA): waits for the operands of both CTAs and for
+//   warps 8-15 epilogue: each CTA drains its own 128 x BN accumulator half. With one accumulator
+//              (256-token tile) the time until it is handed back is exposed, and fp32 -> bf16
+//              conversions run at a fraction of the fp32 rate (measured: ~2700 cycles for the
+//              128 x 256 slice, against ~470 for the tensor-memory loads alone), so these warps take
+//              the registers the others give up, pull their whole slice out of tensor memory as raw
+//              fp32, hand the accumulator back, and scale / convert / transpose / store under the
+//              main loop of the next tile.
+//   warp 16    MMA issuer (one thread of the even CTA): waits for the operands of both CTAs and for
 //              both CTAs' scale-factor warps, issues the MMAs for the pair, releases the stage in
-//              both CTAs and publishes the accumulator with multicast commits.
-//   warps 2-5  epilogue: each CTA drains its own 128 x 256 accumulator half (loads of the next
-//              32 columns overlap the conversion of the current ones) and frees it as soon as
-//              the last column is in registers.
+//              both CTAs and publishes the accumulator with multicast commits. Warps 17-19 only
+//              complete its warpgroup.
 // Requires out % 256 == 0 and tok >= 128.
 template <bool SPARSE, int BN_>
 struct Cfg2 {
     static constexpr int BN = BN_;                        // tokens per pair tile: 128 or 192 (two accumulator stages) or 256
-    static constexpr int THREADS = 544;                   // 17 warps, roles above
+    static constexpr int THREADS = 640;                   // five warpgroups, roles above
     static constexpr int A_ROW = SPARSE ? 64 : 128;
     static constexpr int A_BYTES = 128 * A_ROW;
     static constexpr int B_ROWS = BN / 2;                 // this CTA's half of the token tile
@@ -579,9 +585,15 @@ struct KParams2 {
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
+// Warp roles of the pair kernel, one kind of role per warpgroup so that registers can move between them
+// (setmaxnreg is a warpgroup-wide instruction): the CTA starts with 96 registers per thread and the three
+// service warpgroups hand most of theirs to the two epilogue warpgroups, which then hold a whole fp32
+// accumulator slice (128 words per thread).  640 * 96 = 128 * (40 + 64 + 40) + 256 * 168.
+enum { W_PROD_A = 0, W_PROD_B = 1, W_SIDE_W = 2, W_SIDE_B = 3, W_MMA = 16 };
+constexpr int REGS_PROD = 40, REGS_SF = 64, REGS_MMA = 40, REGS_EPI = 160;
 
 template <bool SPARSE, int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(544, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(640, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
@@ -632,7 +644,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
         if (SPARSE) tma_prefetch_desc(&tmMETA);
     }
-    if (warp == 1) {
+    if (warp == W_MMA) {
         tmem_alloc_pair(smem_u32(&tmem_base_slot), C::TM_COLS);
         tmem_relinquish_pair();
     }
@@ -648,13 +660,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     // poll costs 100-200 cycles even on a completed barrier (measured with the round-trip probe), which
     // per K block is more than the tensor pipe needs for the MMAs. Ring barriers that are signalled in
     // ring order (empty, sbe, sfr) are polled for the later block only.
-    if (warp == 0 || warp == 10) {
+    if (warp < 4) {
+        reg_dealloc<REGS_PROD>();
+    if (warp == W_PROD_A || warp == W_PROD_B) {
         // ------------------------------------------------------------ operand producers (both CTAs)
         // warp 0 loads A, warp 10 loads B; one thread needs ~90 cycles to issue one TMA load (measured),
         // so every load of a stage has its own issuing warp. The loads of both CTAs complete on the
         // leader's full barrier, whose two arrivals (with the byte count of the pair) come from the
         // leader's producers; a peer load that lands first only drives the pending count negative.
-        const bool isA = warp == 0;
+        const bool isA = warp == W_PROD_A;
         int stage = 0;
         uint32_t phase = 0;
         long long c_pw = 0, c_pb = 0, c_pn = 0;
@@ -703,9 +717,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             if (!ok) break;
         }
         if (p.prof && isA && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[0] = c_pw; o[1] = c_pb; o[2] = c_pn; }
-    } else if (warp == 11 || warp == 12) {
+    } else {
         // ------------------------------------------------------------ sideband producers (both CTAs)
-        const bool isW = warp == 11;               // weight side: scale factors of A and metadata
+        const bool isW = warp == W_SIDE_W;               // weight side: scale factors of A and metadata
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -747,11 +761,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
             if (!ok) break;
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    }
+    } else if (warp >= 16) {
+        reg_dealloc<REGS_MMA>();
+        // ------------------------------------------------------------ MMA issuer (leader CTA only); warps 17-19 only fill the warpgroup
         // One thread runs the whole issue loop: no warp-wide broadcast or re-convergence sits between a
         // barrier wait and the MMAs it gates.
-        if (rank == 0 && lane == 0) {
+        if (warp == W_MMA && rank == 0 && lane == 0) {
             const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
             int stage = 0, acc = 0, tslot = 0;
             uint32_t phase = 0, acc_phase = 0;
@@ -818,7 +834,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp >= 6 && warp < 10) {
+    } else if (warp < 8) {
+        reg_dealloc<REGS_SF>();
         // ------------------------------------------------------------ scale-factor warps (both CTAs)
         const int q = warp & 3;
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
@@ -919,19 +936,20 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 6 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[3] = c_sw; o[4] = c_sb; o[5] = c_sn; }
+        if (p.prof && warp == 4 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[3] = c_sw; o[4] = c_sb; o[5] = c_sn; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
-        // Eight warps: warps 2-5 drain the first half of the tile's columns, warps 13-16 the second half;
+        // Eight warps: warps 8-11 drain the first half of the tile's columns, warps 12-15 the second half;
         // a warp reads the TMEM lane quadrant (warp % 4) it is allowed to.
+        reg_alloc<REGS_EPI>();
         const int q = warp & 3;
-        const int half = warp >= 13 ? 1 : 0;
-        const int ew = half ? 4 + (warp - 13) : warp - 2;
+        const int half = warp >= 12 ? 1 : 0;
+        const int ew = warp - 8;
         const int r_in_tile = q * 32 + lane;
         const uint32_t stg_s = epi0 + ew * (16 * C::EPI_PITCH);
         int acc = 0;
         uint32_t acc_phase = 0;
-        long long c_wait_accf = 0, c_epi = 0;
+        long long c_wait_accf = 0, c_epi = 0, c_ph1 = 0;
         constexpr int HCOLS = BN / 2;          // columns per warp
         constexpr int NCH = HCOLS / 16;        // chunks of 16 columns
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -976,7 +994,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
 #endif
             uint32_t ra[16], rb[16];
-            tc_ld_32x16(t_acc, ra);
+            if constexpr (C::ACC_STAGES != 1) tc_ld_32x16(t_acc, ra);
             auto emit = [&](const uint32_t (&r)[16], int c) {
                 const int c0 = 16 * c;
                 const float gbl = gbv[c];
@@ -1034,6 +1052,20 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     __syncwarp();
                 }
             };
+            if constexpr (C::ACC_STAGES == 1) {
+                // one accumulator: all loads first, then give it back, then the (slow) conversions and stores
+                uint32_t held[NCH][16];
+#pragma unroll
+                for (int c = 0; c < NCH; c++) tc_ld_32x16(t_acc + 16 * c, held[c]);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acce_leader);
+                c_ph1 += QB_CLK() - cx;
+#pragma unroll
+                for (int c = 0; c < NCH; c++) emit(held[c], c);
+                acc_phase ^= 1;
+            } else {
 #pragma unroll
             for (int c = 0; c < NCH; c += 2) {
                 tc_wait_ld();
@@ -1050,16 +1082,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
                 emit(rb, c + 1);
             }
-            c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+            c_epi += QB_CLK() - cx;
         }
-        if (p.prof && warp == 2 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[6] = c_wait_accf; o[7] = c_epi; }
+        if (p.prof && warp == 8 && lane == 0) {
+            unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8;
+            o[6] = c_wait_accf; o[7] = c_epi;
+            p.prof[6144 + blockIdx.x] = c_ph1;
+        }
     }
 
     // teardown: no CTA may leave while its partner can still signal its barriers
     tc_fence_before();
     cluster_sync_all();
-    if (warp == 1) {
+    if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, C::TM_COLS);
     }
