@@ -74,6 +74,12 @@ void fused_swiglu_quant_2lvl(const void* g, const void* u, void* Hbytes, void* s
 void rmsnorm_quant(const void* x, const void* wt, void* Bbytes, void* scaleB, int batch, int hidden, float eps);
 void add_rmsnorm_quant(const void* inp, const void* res, const void* wt, void* hout, void* Bbytes, void* scaleB, int batch,
                        int hidden, float eps);
+/* cuda/dense_nvfp4_fast_lib.cu:251,274 — the dense library's glue, per-16 single-level (SFB [hidden/128][batch][8]):
+ * RMSNorm after an optional residual add (res may be null; with res the sum is written to hout), and SwiGLU over
+ * feature-major g, u [hidden][batch]. */
+void rmsnorm_nvfp4(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* SFB, int batch, int hidden,
+                   float eps);
+void swiglu_nvfp4(const void* g, const void* u, void* Hbytes, void* SFB, int batch, int hidden);
 /* cuda/sparse_fp4_lib.cu:1133-1137 — fused SwiGLU MLP: quantise x[tp][H], gate/up GEMM (weights gu_*,
  * gu_out = 2*Iw rows: gate features then up features), h = silu(g)*u quantised two-level per token,
  * down GEMM -> Cout[tp][dn_out] bf16. Bb, sBg, gBg, Cgu, Hb, sH, gH are caller scratch with the
@@ -102,6 +108,19 @@ int sparse_moe_mm_2lvl(const void* A, const void* B, const void* scaleA, const v
 int sparse_moe_mm_2lvl_bw(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
                           int Mtot, int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk,
                           const void* sc_w, const void* bias, int Hout, void* stream);
+/* cuda/sparse_fp4_lib.cu:1649 — fused down GEMM: Out[sc_tok[r]][f] += (acc + bias[expert][f]) * sc_w[r] for routed rows
+ * with sc_tok[r] >= 0 and f < Hout; Out fp32 [tokens][Hout], zeroed by the caller; bias bf16 [E][Hout] (may be null).
+ * The bf16 GEMM tile the reference stages in shared memory is staged in the library's scratch buffer. */
+int sparse_moe_mm_2lvl_scatter(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, int Mtot,
+                               int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk, const void* sc_tok,
+                               const void* sc_w, const void* bias, void* Out, int Hout, void* stream);
+/* cuda/sparse_fp4_lib.cu:1875 — fused GEMM1: grouped gate_up GEMM over pairwise-interleaved (gate, up) weight rows
+ * (Mpe = 2*Ih rows per expert), + guBias bf16 [E][Mpe] (may be null), SwiGLU (act 0: clamped gpt-oss form, 1: plain),
+ * single-level per-32 quantiser -> Hwords[rows][Ih/2 bytes], scaleH[Ih/128][rows][4] (the down GEMM then runs with
+ * gB = 1). Ih % 128 == 0. The bf16 gate_up rows are staged in the library's scratch buffer. */
+int sparse_moe_gu_swiglu(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, int Mtot, int Mpe,
+                         int rows, int K, const void* gA, const void* gB, const void* eblk, const void* guBias, void* Hwords,
+                         void* scaleH, int Ih, int act, void* stream);
 /* cuda/sparse_fp4_lib.cu:1606 — counting-sort routing: src[poff[e]+slot] = i (poff int64, src pre-filled -1). */
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream);
 /* cuda/sparse_fp4_lib.cu:1615 — y[t][f] = sum_k dbuf[inverse[t][k]][f], bf16. */

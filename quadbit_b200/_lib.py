@@ -25,6 +25,10 @@ _SIGS = {
     "sparse_down_sk_2lvl": ([P] * 7 + [I] * 3 + [P] * 2 + [I], I),
     "sparse_moe_mm_2lvl": ([P] * 6 + [I] * 4 + [P] * 3 + [I, P], I),
     "sparse_moe_mm_2lvl_bw": ([P] * 6 + [I] * 4 + [P] * 5 + [I, P], I),
+    "sparse_moe_mm_2lvl_scatter": ([P] * 5 + [I] * 4 + [P] * 7 + [I, P], I),
+    "sparse_moe_gu_swiglu": ([P] * 5 + [I] * 4 + [P] * 6 + [I, I, P], I),
+    "rmsnorm_nvfp4": ([P] * 6 + [I] * 2 + [c_float], None),
+    "swiglu_nvfp4": ([P] * 4 + [I] * 2, None),
     "moe_route": ([P] * 4 + [I] * 2 + [P], I),
     "moe_combine_topk": ([P] * 3 + [I] * 4 + [P], I),
     "qb_init_func_attrs": ([], None),

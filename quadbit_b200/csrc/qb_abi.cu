@@ -59,7 +59,10 @@ size_t meta_native_bytes(int out_f, int K) { return (size_t)((out_f + 127) / 128
 // GEMM on reference-layout operands: re-layout into scratch, then run the native kernel.
 int ref_gemm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, float* Cf,
              int a_rows, int out_f, int tok, int K, const void* gA, const void* gB, const int* eblk, const void* bias,
-             const float* row_w, int sparse, int out_mode, int splits, cudaStream_t st) {
+             const float* row_w, int sparse, int out_mode, int splits, cudaStream_t st, size_t extra_bytes = 0,
+             void** extra = nullptr, int bias_ld = 0) {
+    // extra_bytes / extra: a further region of the scratch buffer for the caller (an intermediate the
+    // reference keeps in shared memory); with it, a null C means "write the GEMM output there"
     if (a_rows <= 0 || out_f <= 0 || tok < 0 || K <= 0 || K % 128 || a_rows % 128) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!scaleA || !scaleB || (sparse && !meta)) return QB_ERR_ARG;
@@ -68,11 +71,15 @@ int ref_gemm(const void* A, const void* B, const void* scaleA, const void* scale
     size_t n_sfb = align256(sf_atoms_bytes(tok, K, block));
     size_t n_meta = sparse ? align256(meta_native_bytes(a_rows, K)) : 0;
     void* base = nullptr;
-    int rc = scratch_get(n_sfa + n_sfb + n_meta, &base);
+    int rc = scratch_get(n_sfa + n_sfb + n_meta + extra_bytes, &base);
     if (rc) return rc;
     uint8_t* p_sfa = (uint8_t*)base;
     uint8_t* p_sfb = p_sfa + n_sfa;
     uint8_t* p_meta = p_sfb + n_sfb;
+    if (extra) {
+        *extra = p_meta + n_meta;
+        if (!C) C = *extra;
+    }
     if (K % 256) {   // zero the K tail of the padded native arrays
         rc = (int)cudaMemsetAsync(base, 0, n_sfa + n_sfb + n_meta, st);
         if (rc) return rc;
@@ -87,7 +94,7 @@ int ref_gemm(const void* A, const void* B, const void* scaleA, const void* scale
     }
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = p_sfa; g.sfb = p_sfb; g.meta = sparse ? p_meta : nullptr;
-    g.gA = (const float*)gA; g.gB = (const float*)gB; g.C = C; g.Cf = Cf; g.eblk = eblk; g.bias = bias; g.row_w = row_w;
+    g.gA = (const float*)gA; g.gB = (const float*)gB; g.C = C; g.Cf = Cf; g.eblk = eblk; g.bias = bias; g.row_w = row_w; g.bias_ld = bias_ld;
     g.a_rows = a_rows; g.out_f = out_f; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode;
     g.splits = splits; g.bn = 0;
     return qb::gemm_nvfp4(g, st);
@@ -301,10 +308,36 @@ int sparse_moe_mm_2lvl(const void* A, const void* B, const void* scaleA, const v
 int sparse_moe_mm_2lvl_bw(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
                           int Mtot, int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk,
                           const void* sc_w, const void* bias, int Hout, void* stream) {
-    (void)Hout;
-    if (rows % 128 || !eblk) return QB_ERR_ARG;
+    if (rows % 128 || !eblk || Hout <= 0 || Hout > Mpe) return QB_ERR_ARG;
     int rc = ref_gemm(A, B, scaleA, scaleB, meta, C, nullptr, Mtot, Mpe, rows, K, gA, gB, (const int*)eblk, bias,
-                      (const float*)sc_w, 1, 3, 1, (cudaStream_t)stream);
+                      (const float*)sc_w, 1, 3, 1, (cudaStream_t)stream, 0, nullptr, Hout);
+    return stream ? rc : finish_sync(rc, 0);
+}
+// Fused-down form: the reference's kernel adds bias, weights and scatter-adds in its epilogue; here the token-major
+// bf16 GEMM output goes to the scratch buffer (where the reference stages it in shared memory, with the same bf16
+// rounding) and a second kernel applies the same tail. Out[tokens][Hout] fp32 is zeroed by the caller.
+int sparse_moe_mm_2lvl_scatter(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, int Mtot,
+                               int Mpe, int rows, int K, const void* gA, const void* gB, const void* eblk, const void* sc_tok,
+                               const void* sc_w, const void* bias, void* Out, int Hout, void* stream) {
+    if (rows % 128 || !eblk || !sc_tok || !Out || Hout <= 0 || Hout > Mpe) return QB_ERR_ARG;
+    void* cs = nullptr;
+    int rc = ref_gemm(A, B, scaleA, scaleB, meta, nullptr, nullptr, Mtot, Mpe, rows, K, gA, gB, (const int*)eblk, nullptr, nullptr,
+                      1, 1, 1, (cudaStream_t)stream, align256((size_t)rows * Mpe * 2), &cs);
+    if (!rc && rows > 0) rc = qb::moe_scatter_add(cs, eblk, sc_tok, sc_w, bias, Out, rows, Mpe, Hout, (cudaStream_t)stream);
+    return stream ? rc : finish_sync(rc, 0);
+}
+// Fused GEMM1 form: grouped gate_up GEMM over pairwise-interleaved (gate, up) weight rows with the per-expert bias
+// added in the epilogue, then SwiGLU (act 0: clamped gpt-oss form, 1: plain) and the single-level per-32 quantiser
+// straight into the down GEMM's B operand: Hwords[rows][Ih/2 bytes], scaleH[Ih/128][rows][4] (down runs with gB = 1).
+// The bf16 gate_up tile the reference keeps in shared memory lives in the scratch buffer here (rows x Mpe x 2 bytes).
+int sparse_moe_gu_swiglu(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, int Mtot, int Mpe,
+                         int rows, int K, const void* gA, const void* gB, const void* eblk, const void* guBias, void* Hwords,
+                         void* scaleH, int Ih, int act, void* stream) {
+    if (rows % 128 || !eblk || !Hwords || !scaleH || Ih * 2 != Mpe || Ih % 128) return QB_ERR_ARG;
+    void* cgu = nullptr;
+    int rc = ref_gemm(A, B, scaleA, scaleB, meta, nullptr, nullptr, Mtot, Mpe, rows, K, gA, gB, (const int*)eblk, guBias, nullptr,
+                      1, guBias ? 3 : 1, 1, (cudaStream_t)stream, align256((size_t)rows * Mpe * 2), &cgu);
+    if (!rc && rows > 0) rc = qb::swiglu_quant_ex(cgu, Hwords, scaleH, nullptr, nullptr, rows, Ih, 1, act, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);
 }
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream) {
@@ -332,6 +365,15 @@ void add_rmsnorm_quant(const void* inp, const void* res, const void* wt, void* h
 int qb_norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
                   int tok, int H, float eps, int block, void* stream) {
     return qb::norm_quant(x, res, wt, hout, Bbytes, sf_ref, sf_atoms, g, tok, H, eps, block, (cudaStream_t)stream);
+}
+// dense library glue (per-16, single-level): cuda/dense_nvfp4_fast_lib.cu:225-278
+void rmsnorm_nvfp4(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* SFB, int batch, int hidden,
+                   float eps) {
+    t_last_error = (res && !hout) ? QB_ERR_ARG
+                                  : qb::norm_quant(x, res, wt, res ? hout : nullptr, Bbytes, SFB, nullptr, nullptr, batch, hidden, eps, 16, 0);
+}
+void swiglu_nvfp4(const void* g, const void* u, void* Hbytes, void* SFB, int batch, int hidden) {
+    t_last_error = qb::swiglu_quant_feature_major16(g, u, Hbytes, SFB, batch, hidden, 0);
 }
 void qb_init_func_attrs(void) { t_last_error = qb::gemm_init_attrs(); }
 void qb_init_sk_attrs(void) { t_last_error = qb::gemm_init_attrs(); }

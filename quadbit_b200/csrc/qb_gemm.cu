@@ -56,6 +56,7 @@ struct KParams {
     const int* eblk;
     const __nv_bfloat16* bias;
     const float* row_w;
+    int bias_ld;                         // features per bias row
     int out_f, tok, K;
     int num_m, num_n, splits, kblocks;   // kblocks = ceil(K/256)
     int sfb_rowblocks;                   // ceil(tok/128)
@@ -413,7 +414,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     // token-major output C[tok][out]: transpose a 32(out) x CH(tok) block through
                     // shared memory so that global stores are 16-byte vectors
                     float bias_v = 0.f;
-                    if (p.out_mode == 3 && p.bias) bias_v = __bfloat162float(p.bias[(size_t)expert * p.out_f + o]);
+                    if (p.out_mode == 3 && p.bias && o < p.bias_ld) bias_v = __bfloat162float(p.bias[(size_t)expert * p.bias_ld + o]);
                     float rw = 1.f;
                     if (p.out_mode == 3 && p.row_w && col_l < p.tok) rw = __ldg(p.row_w + col_l);
 #pragma unroll
@@ -580,6 +581,7 @@ struct KParams2 {
     const int* eblk;                     // grouped mode (BN == 128): expert of every 128-token block, null = plain GEMM
     const __nv_bfloat16* bias;           // out_mode 3: per-expert bias [E][out_f] (may be null)
     const float* row_w;                  // out_mode 3: weight of every routed row [tok] (may be null)
+    int bias_ld;                         // features per bias row (the rest of out_f is padding without bias)
     int dbg;
     unsigned long long* prof;
 };
@@ -971,8 +973,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             float bias8[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) bias8[e] = 0.f;
-            if (p.out_mode == 3 && p.bias) {
-                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + a_base + o0 + q * 32 + (lane & 3) * 8));
+            const int f8 = o0 + q * 32 + (lane & 3) * 8;       // bias rows hold bias_ld (a multiple of 8) valid features
+            if (p.out_mode == 3 && p.bias && f8 + 8 <= p.bias_ld) {
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + (size_t)(p.eblk ? p.eblk[n] : 0) * p.bias_ld + f8));
                 const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(bh[e]); bias8[2 * e] = f.x; bias8[2 * e + 1] = f.y; }
@@ -1247,7 +1250,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.out_f = a.out_f; kp.tok = a.tok;
     kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
     kp.a_tiled = a.a_tiled;
-    kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
+    kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w; kp.bias_ld = a.bias_ld > 0 ? a.bias_ld : a.out_f;
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
@@ -1293,7 +1296,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
         return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
     // grouped (MoE) form on the pair kernel: one expert per 128-token block = per tile of the 128-token variant
     if (a.eblk && splits == 1 && (a.out_mode == 1 || a.out_mode == 3) && a.out_f % 256 == 0 && a.tok >= 128 && a.tok % 128 == 0 &&
-        (a.bn == 0 || a.bn == 128) && (((uintptr_t)a.bias & 15) == 0))
+        (a.bn == 0 || a.bn == 128) && (((uintptr_t)a.bias & 15) == 0) && (a.bias_ld <= 0 || a.bias_ld % 8 == 0))
         return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
     int bn = a.bn;
     if (a.eblk) bn = 128;
@@ -1305,7 +1308,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
 
     KParams kp;
     kp.sfa = (const uint8_t*)a.sfa; kp.sfb = (const uint8_t*)a.sfb; kp.meta = (const uint8_t*)a.meta;
-    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.Cf = a.Cf; kp.sk_counters = (int*)a.sk_counters; kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w;
+    kp.gA = a.gA; kp.gB = a.gB; kp.C = a.C; kp.Cf = a.Cf; kp.sk_counters = (int*)a.sk_counters; kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w; kp.bias_ld = a.bias_ld > 0 ? a.bias_ld : a.out_f;
     kp.out_f = a.out_f; kp.tok = a.tok; kp.K = a.K;
     kp.num_m = a.out_f / 128;
     kp.num_n = (a.tok + bn - 1) / bn;

@@ -11,6 +11,11 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
                  cudaStream_t st);
 // cgu: token-major gate/up GEMM output [tok][2*I] bf16 -> Hb[tok][I/2], per-32 scales, gH[tok]
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
+int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
+                    cudaStream_t st);
+int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st);
+int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const void* sc_w, const void* bias, void* Out, int rows,
+                    int Mpe, int Hout, cudaStream_t st);
 // RMSNorm (+ residual add) fused with the quantiser; res / hout / g may be null (g null = single level)
 int norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
                int tok, int H, float eps, int block, cudaStream_t st);
@@ -46,6 +51,7 @@ struct GemmArgs {
     const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
     const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
     const float* row_w;    // epilogue 3: fp32 per-routed-row weight [tok] (may be null)
+    int bias_ld;           // epilogue 3: features per bias row, a bias is [E][bias_ld]; 0 = out_f (features beyond it get no bias)
     int a_rows;            // rows of A (plain: out; grouped: experts * out_per_expert)
     int out_f;             // output features per GEMM (plain: out; grouped: out_per_expert)
     int tok;               // rows of B

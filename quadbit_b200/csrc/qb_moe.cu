@@ -55,6 +55,35 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ dbuf, const
     }
 }
 
+// Out[sc_tok[r], f] += (Cs[r, f] + bias[eblk[r / 128], f]) * sc_w[r] for every routed row r with sc_tok[r] >= 0 and every
+// feature f < Hout: the bias / routing-weight / scatter-add tail of the reference's fused down GEMM (outT == 2 epilogue
+// of matmul_sp_moe, cuda/sparse_fp4_lib.cu:1533-1546) applied to the token-major bf16 GEMM output Cs[rows][Mpe].
+// One CTA per routed row, fp32 atomics into the caller-zeroed Out[tokens][Hout].
+__global__ void moe_scatter_add_kernel(const __nv_bfloat16* __restrict__ Cs, const int* __restrict__ eblk, const int* __restrict__ sc_tok,
+                                       const float* __restrict__ sc_w, const __nv_bfloat16* __restrict__ bias, float* __restrict__ Out,
+                                       int Mpe, int Hout) {
+    const int r = blockIdx.x;
+    const int tok = sc_tok[r];
+    if (tok < 0) return;
+    const int e = eblk[r >> 7];
+    const float w = sc_w ? sc_w[r] : 1.f;
+    const __nv_bfloat16* src = Cs + (size_t)r * Mpe;
+    const __nv_bfloat16* bb = bias ? bias + (size_t)e * Hout : nullptr;
+    float* dst = Out + (size_t)tok * Hout;
+    for (int f = threadIdx.x; f < Hout; f += blockDim.x)
+        atomicAdd(dst + f, (__bfloat162float(src[f]) + (bb ? __bfloat162float(bb[f]) : 0.f)) * w);
+}
+
+int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const void* sc_w, const void* bias, void* Out, int rows,
+                    int Mpe, int Hout, cudaStream_t st) {
+    if (rows < 0 || Mpe <= 0 || Hout <= 0 || Hout > Mpe) return QB_ERR_ARG;
+    if (rows == 0) return QB_OK;
+    if (!Cs || !eblk || !sc_tok || !Out) return QB_ERR_ARG;
+    moe_scatter_add_kernel<<<rows, 256, 0, st>>>((const __nv_bfloat16*)Cs, (const int*)eblk, (const int*)sc_tok, (const float*)sc_w,
+                                                 (const __nv_bfloat16*)bias, (float*)Out, Mpe, Hout);
+    return (int)cudaGetLastError();
+}
+
 int moe_route(const void* assign, void* poff, void* counter, void* src, int n, int e, cudaStream_t st) {
     if (n < 0 || e <= 0 || !poff || !counter) return QB_ERR_ARG;
     int rc = (int)cudaMemsetAsync(counter, 0, (size_t)e * sizeof(int), st);

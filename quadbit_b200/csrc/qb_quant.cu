@@ -112,10 +112,22 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 // Replaces swiglu_amax / swiglu_finalize / swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894),
 // which make three passes over a feature-major Cgu.
 // Every lane owns whole 32-value scale blocks (NJ per lane), like quant_act_kernel.
-template <int NJ>
+// INTERLEAVED: the row holds (gate, up) pairs [g0,u0,g1,u1,...] as the gpt-oss fused gate_up weight produces
+// them; TWO_LEVEL = false is the single-level quantiser (no per-token global) that the reference's fused MoE
+// GEMM1 epilogue applies (matmul_sp_moe_gu_swiglu, cuda/sparse_fp4_lib.cu:1828-1866); act 0 is the clamped
+// gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1), act 1 the plain silu(g) * u.
+__device__ __forceinline__ float swiglu_h(float g, float u, int act) {
+    if (act == 0) {
+        g = fminf(g, 7.f);
+        u = fmaxf(fminf(u, 7.f), -7.f);
+        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+    }
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
+template <int NJ, bool INTERLEAVED, bool TWO_LEVEL>
 __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                            float* __restrict__ g_out, int tok, int I) {
+                                                            float* __restrict__ g_out, int tok, int I, int act) {
     const int row = blockIdx.x;
     const int nchunks = I >> 3;
     const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
@@ -132,35 +144,50 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
-            if (b < nblocks) { gv = __ldg(gr + (size_t)b * 4 + k); uv = __ldg(ur + (size_t)b * 4 + k); }
+            if (INTERLEAVED) {   // gv, uv: the two halves of 8 consecutive (gate, up) pairs
+                if (b < nblocks) { gv = __ldg(gr + (size_t)b * 8 + 2 * k); uv = __ldg(gr + (size_t)b * 8 + 2 * k + 1); }
+            } else {
+                if (b < nblocks) { gv = __ldg(gr + (size_t)b * 4 + k); uv = __ldg(ur + (size_t)b * 4 + k); }
+            }
             const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
             const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
-                const float a = __fdividef(g2.x, 1.f + __expf(-g2.x)) * u2.x;
-                const float c = __fdividef(g2.y, 1.f + __expf(-g2.y)) * u2.y;
-                h[j][8 * k + 2 * i] = a; h[j][8 * k + 2 * i + 1] = c;
+                float a, c;
+                if (INTERLEAVED) {
+                    const float2 p0 = __bfloat1622float2(gh[i]), p1 = __bfloat1622float2(uh[i]);
+                    a = swiglu_h(p0.x, p0.y, act);
+                    c = swiglu_h(p1.x, p1.y, act);
+                    h[j][8 * k + i] = a; h[j][8 * k + 4 + i] = c;
+                } else {
+                    const float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
+                    a = swiglu_h(g2.x, u2.x, act);
+                    c = swiglu_h(g2.y, u2.y, act);
+                    h[j][8 * k + 2 * i] = a; h[j][8 * k + 2 * i + 1] = c;
+                }
                 m = fmaxf(m, fmaxf(fabsf(a), fabsf(c)));
             }
         }
         bmax[j] = m;
         tmax = fmaxf(tmax, m);
     }
-    __shared__ float red[32];
-    tmax = warp_max(tmax);
-    if (lane == 0) red[threadIdx.x >> 5] = tmax;
-    __syncthreads();
-    float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
-    r = warp_max(r);
-    const float gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
-    if (threadIdx.x == 0) g_out[row] = gl;
+    float gl = 1.f;
+    if (TWO_LEVEL) {
+        __shared__ float red[32];
+        tmax = warp_max(tmax);
+        if (lane == 0) red[threadIdx.x >> 5] = tmax;
+        __syncthreads();
+        float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+        r = warp_max(r);
+        gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
+        if (threadIdx.x == 0) g_out[row] = gl;
+    }
     const bool wide = (reinterpret_cast<uintptr_t>(Hwords) & 15) == 0;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int b = threadIdx.x + j * blockDim.x;
-        const uint32_t code = enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl));
-        const Fp4Divider dv(fmaxf(__fmul_rn(dec_ue4m3(code), gl), 1e-30f));
+        const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax[j], 6.f));
+        const Fp4Divider dv(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -187,20 +214,29 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
 }
 
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st) {
-    if (tok < 0 || I <= 0 || I % 128 != 0) return QB_ERR_ARG;
+    return swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, 0, 1, st);
+}
+
+// interleaved: row layout [g0,u0,g1,u1,...]; gH == nullptr selects the single-level quantiser
+int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
+                    cudaStream_t st) {
+    if (tok < 0 || I <= 0 || I % 128 != 0 || (act != 0 && act != 1)) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
-    if (!cgu || !Hb || !gH || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
+    if (!cgu || !Hb || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
     if (((uintptr_t)cgu & 15) || ((uintptr_t)Hb & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3)) return QB_ERR_ARG;
     const int nblocks = I / 32;
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     const int nj = (nblocks + threads - 1) / threads;
-#define QB_LS(NJ) swiglu_quant_kernel<NJ><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I)
+#define QB_LS3(NJ, IL, TL) swiglu_quant_kernel<NJ, IL, TL><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I, act)
+#define QB_LS(NJ) do { if (interleaved) { if (gH) QB_LS3(NJ, true, true); else QB_LS3(NJ, true, false); } \
+                       else { if (gH) QB_LS3(NJ, false, true); else QB_LS3(NJ, false, false); } } while (0)
     if (nj <= 1) QB_LS(1);
     else if (nj <= 2) QB_LS(2);
     else if (nj <= 4) QB_LS(4);
     else return QB_ERR_UNSUPPORTED;
 #undef QB_LS
+#undef QB_LS3
     return (int)cudaGetLastError();
 }
 
@@ -353,17 +389,18 @@ int norm_quant(const void* x, const void* res, const void* wt, void* hout, void*
 // SwiGLU quantisers over the reference's feature-major operands g, u [hidden][batch] (two separate
 // GEMM outputs): fused_swiglu_quant / fused_swiglu_quant_2lvl, cuda/sparse_fp4_lib.cu:794-894.
 // One thread per (token, 32-feature block), tokens fastest so the strided reads coalesce.
-template <bool TWO_LEVEL, bool AMAX_ONLY>
+template <bool TWO_LEVEL, bool AMAX_ONLY, int BLOCK = 32>
 __global__ void swiglu_fm_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u, uint32_t* __restrict__ Hwords,
                                  uint8_t* __restrict__ scaleH, float* __restrict__ gH, int batch, int hidden) {
-    const int hb = hidden / 32;
+    constexpr int P = 128 / BLOCK;     // scales per 128 features
+    const int hb = hidden / BLOCK;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long long)batch * hb) return;
     const int hblock = (int)(t / batch), b = (int)(t % batch);
-    const long long base = (long long)(hblock * 32) * batch + b;
-    float val[32], amax = 0.f;
+    const long long base = (long long)(hblock * BLOCK) * batch + b;
+    float val[BLOCK], amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
+    for (int i = 0; i < BLOCK; i++) {
         float gv = __bfloat162float(g[base + (long long)i * batch]);
         float uv = __bfloat162float(u[base + (long long)i * batch]);
         float h = (gv / (1.f + __expf(-gv))) * uv;
@@ -373,18 +410,20 @@ __global__ void swiglu_fm_kernel(const __nv_bfloat16* __restrict__ g, const __nv
     if (AMAX_ONLY) { atomicMax(reinterpret_cast<int*>(gH) + b, __float_as_int(amax)); return; }
     const float gl = TWO_LEVEL ? fmaxf(__fdiv_rn(gH[b], 2688.f), 1e-30f) : 1.f;
     const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(amax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(amax, 6.f));
-    scaleH[((long long)(hblock / 4) * batch + b) * 4 + (hblock % 4)] = (uint8_t)code;
+    scaleH[((long long)(hblock / P) * batch + b) * P + (hblock % P)] = (uint8_t)code;
     const float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
-    uint32_t w[4];
+    uint32_t w[BLOCK / 8];
     const Fp4Divider dv(sg);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < BLOCK / 8; i++) {
         float f8[8];
 #pragma unroll
         for (int e = 0; e < 8; e++) f8[e] = val[8 * i + e];
         w[i] = dv.pack8(f8);
     }
-    *reinterpret_cast<uint4*>(Hwords + (long long)b * (hidden / 8) + hblock * 4) = make_uint4(w[0], w[1], w[2], w[3]);
+    uint32_t* dst = Hwords + (long long)b * (hidden / 8) + hblock * (BLOCK / 8);
+    if constexpr (BLOCK == 32) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
 }
 __global__ void swiglu_fm_finalize(float* gH, int batch) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -407,6 +446,18 @@ int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* sca
     } else {
         swiglu_fm_kernel<false, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, nullptr, batch, hidden);
     }
+    return (int)cudaGetLastError();
+}
+
+// per-16 single-level flavour of the feature-major SwiGLU quantiser: swiglu_nvfp4,
+// cuda/dense_nvfp4_fast_lib.cu:258-278
+int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st) {
+    if (batch < 0 || hidden <= 0 || hidden % 128) return QB_ERR_ARG;
+    if (batch == 0) return QB_OK;
+    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 7)) return QB_ERR_ARG;
+    long long total = (long long)batch * (hidden / 16);
+    int blocks = (int)((total + 255) / 256);
+    swiglu_fm_kernel<false, false, 16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, nullptr, batch, hidden);
     return (int)cudaGetLastError();
 }
 
