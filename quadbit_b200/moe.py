@@ -128,34 +128,53 @@ class SparseMoE:
         self.e0, self.e1 = expert_range if expert_range else (0, self.E)
         self.E_total = n_experts_total or self.E
 
+    def expert_rows(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
+        """Run routed rows through this layer's experts: rows_in [n,H] bf16, assign [n] local expert ids,
+        row_w [n] routing weights -> [n,H] bf16 = expert(row) * weight, in the order of rows_in. Every row
+        is quantised on its own and summed over K in a fixed order, so the result of a row does not depend
+        on which other rows share the call (what makes the expert-parallel layer equal the 1-GPU one)."""
+        lib = self.lib
+        dev = rows_in.device
+        n = rows_in.shape[0]
+        out = torch.zeros((n, self.H), dtype=torch.bfloat16, device=dev)
+        if n == 0:
+            return out
+        src, eblk, r_pad = build_routing(assign.long(), self.e1 - self.e0)
+        valid = src >= 0
+        rows = torch.zeros((r_pad, self.Hp), dtype=torch.bfloat16, device=dev)
+        rows[valid, : self.H] = rows_in[src[valid]].to(torch.bfloat16)
+        gu = seg_gemm(lib, rows, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, mpe_gu]
+        g, u = gu[:, : self.Ip].float(), gu[:, self.Ip: 2 * self.Ip].float()
+        h = (swiglu(g, u) if self.act == "gptoss" else torch.nn.functional.silu(g) * u).to(torch.bfloat16)
+        h[~valid] = 0
+        rw = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
+        rw[valid] = row_w[src[valid]].float()
+        d = seg_gemm(lib, h.contiguous(), self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)      # [r_pad, mpe_dn]
+        out[src[valid]] = d[valid, : self.H]
+        return out
+
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         """x [T,H] bf16, topk_idx [T,topk] global expert ids, topk_w [T,topk] -> [T,H] bf16
         (the partial sum over this rank's experts under expert parallelism)."""
-        lib = self.lib
         T = x.shape[0]
         dev = x.device
         assign_g = topk_idx.reshape(-1).long()
         local = (assign_g >= self.e0) & (assign_g < self.e1)
         slots = torch.nonzero(local).squeeze(1)                          # routed slots owned here
-        assign = (assign_g[slots] - self.e0)
-        src, eblk, r_pad = build_routing(assign, self.e1 - self.e0)
-        if r_pad == 0:
+        if slots.numel() == 0:
             return torch.zeros((T, self.H), dtype=torch.bfloat16, device=dev)
-        valid = src >= 0
-        slot_of_row = torch.full((r_pad,), -1, dtype=torch.long, device=dev)
-        slot_of_row[valid] = slots[src[valid]]
-        rows = torch.zeros((r_pad, self.Hp), dtype=torch.bfloat16, device=dev)
-        rows[valid, : self.H] = x[slot_of_row[valid] // self.topk].to(torch.bfloat16)
-        gu = seg_gemm(lib, rows, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, mpe_gu]
-        g, u = gu[:, : self.Ip].float(), gu[:, self.Ip: 2 * self.Ip].float()
-        h = (swiglu(g, u) if self.act == "gptoss" else torch.nn.functional.silu(g) * u).to(torch.bfloat16)
-        h[~valid] = 0
-        row_w = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
-        row_w[valid] = topk_w.reshape(-1)[slot_of_row[valid]].float()
-        d = seg_gemm(lib, h.contiguous(), self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=row_w)   # [r_pad, mpe_dn]
+        d = self.expert_rows(x[slots // self.topk], assign_g[slots] - self.e0, topk_w.reshape(-1)[slots])
         inverse = torch.full((T * self.topk,), -1, dtype=torch.int32, device=dev)
-        inverse[slot_of_row[valid]] = torch.nonzero(valid).squeeze(1).int()
-        return combine(lib, d, inverse, T, self.H, self.topk)
+        inverse[slots] = torch.arange(slots.numel(), dtype=torch.int32, device=dev)
+        return combine(self.lib, d, inverse, T, self.H, self.topk)
+
+    def forward_ep(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, group=None) -> torch.Tensor:
+        """Expert-parallel layer over the ranks of `group`: this rank holds experts [e0, e1) and its own
+        tokens x [T_local,H]; routed rows travel to their expert's rank and back with two all-to-all
+        exchanges (`dist.ep_moe`), the top-k sum runs at home. Equals `forward` of a 1-rank layer."""
+        from . import dist as qd
+        return qd.ep_moe(x, topk_idx, topk_w, self.E_total, self.expert_rows,
+                         lambda d, inverse, T: combine(self.lib, d, inverse, T, self.H, self.topk), group)
 
     __call__ = forward
 

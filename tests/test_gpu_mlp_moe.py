@@ -174,3 +174,68 @@ def test_build_routing_matches_reference_helper():
     src, eblk, r_pad = moe.build_routing(assign.cuda(), 8)
     esrc, eeblk, erp = fq.build_routing(assign, 8)
     assert r_pad == erp and torch.equal(src.cpu(), esrc) and torch.equal(eblk.cpu(), eeblk)
+
+
+def test_moe_forward_ep_single_rank_equals_forward():
+    """Without a process group the all-to-all layer degenerates to sort -> experts -> unsort -> combine and
+    must give the bits of `forward` (rows are computed independently of their neighbours)."""
+    import quadbit_b200 as qb
+    torch.manual_seed(21)
+    H, I, E, topk, T = 256, 256, 4, 2, 150
+    wgu = [torch.randn(2 * I, H) * 0.05 for _ in range(E)]
+    wdn = [torch.randn(H, I) * 0.05 for _ in range(E)]
+    x = torch.randn(T, H).cuda().bfloat16()
+    idx, w = fq.route_topk(torch.randn(T, E), topk)
+    moe = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk)
+    y = moe.forward(x, idx.cuda(), w.cuda())
+    y_ep = moe.forward_ep(x, idx.cuda(), w.cuda())
+    assert moe.lib.qb_status(0) == 0
+    assert torch.equal(y, y_ep)
+
+
+def _ep_gpu_worker(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    import quadbit_b200 as qb
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    torch.manual_seed(22)
+    H, I, E, topk, T = 256, 256, 8, 2, 256
+    wgu = [torch.randn(2 * I, H) * 0.05 for _ in range(E)]
+    wdn = [torch.randn(H, I) * 0.05 for _ in range(E)]
+    x = torch.randn(T, H).cuda().bfloat16()
+    idx, w = fq.route_topk(torch.randn(T, E), topk)
+    idx, w = idx.cuda(), w.cuda()
+    full = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk).forward(x, idx, w)
+    e0, e1 = rank * E // world, (rank + 1) * E // world
+    sh = qb.SparseMoE([t.cuda() for t in wgu[e0:e1]], [t.cuda() for t in wdn[e0:e1]], topk, expert_range=(e0, e1), n_experts_total=E)
+    tl = T // world
+    mine = slice(rank * tl, (rank + 1) * tl)
+    y = sh.forward_ep(x[mine], idx[mine], w[mine])
+    ok = torch.equal(y, full[mine]) and sh.lib.qb_status(0) == 0
+    ret.put((rank, bool(ok)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_moe_forward_ep_two_gpus_equals_one_gpu():
+    """Expert-parallel NCCL all-to-all dispatch / combine over two GPUs against the 1-GPU layer, bit for bit
+    (reference check: harness/moe_dist.py:199-206 compares the distributed output with the single-GPU one)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_ep_gpu_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(ret.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert got[0] and got[1]
