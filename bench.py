@@ -219,6 +219,55 @@ def run_gpu(args):
                                        "frac": algo / t / 1e9 / hbm_gbs, "traffic": None}}), flush=True)
         return
 
+    # ---- expert-parallel MoE layer (gpt-oss-120b-shaped): 8192 tokens in total, 128 experts split over the ranks,
+    #      routed rows dispatched and combined with all-to-all exchanges (strong scaling)
+    if args.ep:
+        Hh, E, topk, T = 2880, 128, 4, 8192
+        assert E % world == 0 and T % world == 0
+        e0, e1 = rank * E // world, (rank + 1) * E // world
+        gen = torch.Generator(device=dev).manual_seed(3)
+        wgu = [(torch.randn(2 * Hh, Hh, device=dev, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(e0, e1)]
+        wdn = [(torch.randn(Hh, Hh, device=dev, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(e0, e1)]
+        moe = qb.SparseMoE(wgu, wdn, topk, act="gptoss", expert_range=(e0, e1), n_experts_total=E)
+        del wgu, wdn
+        g2 = torch.Generator(device="cpu").manual_seed(3)
+        xs = torch.randn(T, Hh, generator=g2).to(torch.bfloat16)
+        logits = torch.randn(T, E, generator=g2)
+        tw, ti = torch.softmax(logits, -1).topk(topk, dim=-1)
+        tw = tw / tw.sum(-1, keepdim=True)
+        tl = T // world
+        mine = slice(rank * tl, (rank + 1) * tl)
+        x_l, i_l, w_l = xs[mine].to(dev), ti[mine].to(dev), tw[mine].to(dev)
+        step_ep = lambda: moe.forward_ep(x_l, i_l, w_l)
+        for _ in range(max(args.warmup, 3)):
+            step_ep()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        with ClockSampler(local) as cs:
+            torch.cuda.synchronize()
+            t = ev_time(step_ep, min(args.steps, 50))
+        if world > 1:
+            tt = torch.tensor([t], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
+            dist.barrier()
+        if lib.qb_status(0):
+            raise RuntimeError("device status")
+        fl = 2.0 * T * topk * (2 * Hh * Hh + Hh * Hh)
+        if rank == 0:
+            print(json.dumps({"metric": "MoE layer tokens/s (2:4-sparse NVFP4 experts, expert parallel)", "value": T / t, "unit": "tokens/s",
+                              "n_gpus": world, "steps": min(args.steps, 50), "warmup": max(args.warmup, 3), "ms_per_step": t * 1e3,
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
+                              "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out)",
+                              "config": {"workload": "gpt-oss-120b-shaped MoE layer: hidden 2880, 128 experts, intermediate 2880, top-4, "
+                                                     "8192 tokens in total", "parallelism": f"ep{world}: {E // world} experts and {tl} tokens per rank, "
+                                                     "all-to-all dispatch and combine of bf16 rows"},
+                              "useful_tflops": fl / t / 1e12, "clocks": cs.summary()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- operands of the sharded set
     layers = []
     for i, (name, n, k, par) in enumerate(SHAPES):
@@ -499,6 +548,8 @@ def main():
                     "the activation quantiser / the thin-token GEMM instead")
     ap.add_argument("--tp", action="store_true", help="with --gpus N > 1: tensor-parallel sharding of the set (strong scaling, "
                     "NCCL all-reduce after the row-parallel GEMMs) instead of sharding the tokens")
+    ap.add_argument("--ep", action="store_true", help="instead of the GEMM set: the gpt-oss-120b-shaped MoE layer with the experts split over "
+                                                      "the ranks and all-to-all dispatch / combine (strong scaling, 8192 tokens in total)")
     ap.add_argument("--dense", action="store_true", help="with --only: the dense NVFP4 GEMM instead of the 2:4-sparse one")
     args = ap.parse_args()
     if args.impl == "reference":
