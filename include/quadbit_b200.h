@@ -140,6 +140,12 @@ int dense_nvfp4_mm(const void* A, const void* B, const void* SFA, const void* SF
  * single-level recipe. sf_ref and/or sf_atoms receive the scales (either may be NULL). */
 int qb_quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
                     void* stream);
+/* The gather of routed MoE rows fused into their quantiser (the reference gathers with torch indexing and then
+ * calls quantize_act_nvfp4_2lvl, harness/fused_moe.py:437-442, harness/qb_vllm_plugin/qb_sm120_plugin.py:2430-2441):
+ * output row r = quantised x[src[r]], x bf16 [.][H] zero-padded to K (H % 8 == 0, H <= K), src int64 [rows],
+ * src[r] < 0 = an all-zero padding row. src == NULL is qb_quantize_act. */
+int qb_gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int rows, int K,
+                           int H, int block, void* stream);
 /* Offline 2:4 compressor (torch packer of harness/verify_sparse_2lvl.py:108-122 as one kernel).
  * w_dtype 0 = fp32, 1 = bf16. Any output may be NULL. */
 int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_native, void* sf_ref,
@@ -207,6 +213,12 @@ int qb_norm_quant(const void* x, const void* res, const void* wt, void* hout, vo
  * features first): Hb[tok][I/2], scales (ref layout and/or atoms), gH[tok]. One pass; replaces
  * swiglu_amax + swiglu_finalize + swiglu_quant_g (cuda/sparse_fp4_lib.cu:837-894). */
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream);
+/* Same with the row layout and the activation as arguments: interleaved = 1 reads (gate, up) pairs
+ * [g0,u0,g1,u1,...] (gpt-oss fused gate_up), act 0 = clamped gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1;
+ * harness/fused_moe.py:450-452), 1 = silu(g)*u; gH == NULL selects the single-level quantiser of the reference's
+ * fused GEMM1 epilogue (cuda/sparse_fp4_lib.cu:1828-1866). */
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
+                        void* stream);
 /* fused_mlp_2lvl on native layouts (weights from qb_compress_2to4; sfb_x / sfb_h are scale-atom
  * scratch of qb_sf_atoms_bytes(tok, H | I, 32) bytes; Cf may be NULL or an fp32 [tok][dn_out]
  * workspace for a split-K down projection). Four launches, no synchronisation, no allocation. */

@@ -177,6 +177,10 @@ int qb_quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, v
                     void* stream) {
     return qb::quantize_act(x, Bbytes, sf_ref, sf_atoms, g, tok, K, block, (cudaStream_t)stream);
 }
+int qb_gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int rows, int K,
+                           int H, int block, void* stream) {
+    return qb::gather_quantize_act(x, src, Bbytes, sf_ref, sf_atoms, g, rows, K, H, block, (cudaStream_t)stream);
+}
 int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_native, void* sf_ref, void* sf_atoms,
                      void* gA, int out, int K, void* stream) {
     return qb::compress_2to4(W, w_dtype, Ac, meta_ref, meta_native, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream);
@@ -246,6 +250,10 @@ long long qb_tiled_weight_bytes(int rows, int K, int sparse) {
 int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {
     return qb::swiglu_quant(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, (cudaStream_t)stream);
+}
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
+                        void* stream) {
+    return qb::swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, interleaved, act, (cudaStream_t)stream);
 }
 int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,

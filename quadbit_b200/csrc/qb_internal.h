@@ -10,6 +10,8 @@ namespace qb {
 int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
                  cudaStream_t st);
 // cgu: token-major gate/up GEMM output [tok][2*I] bf16 -> Hb[tok][I/2], per-32 scales, gH[tok]
+int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
+                        int block, cudaStream_t st);
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
                     cudaStream_t st);

@@ -25,13 +25,17 @@ namespace qb {
 template <int BLOCK, int NJ, bool TWO_LEVEL>
 __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
                                                           uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                          float* __restrict__ g_out, int tok, int K) {
+                                                          float* __restrict__ g_out, int tok, int K,
+                                                          const long long* __restrict__ src, int h8) {
+    // src != nullptr: row `row` of the output quantises source row src[row] of x [.][h8 * 8] zero-padded to K
+    // (src < 0: an all-zero row) — the gather of routed MoE rows fused into their quantiser
     constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
     constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
     const int row = blockIdx.x;
     const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
-    const uint4* xr = x + (size_t)row * (K >> 3);
+    const long long srow = src ? src[row] : (long long)row;
+    const uint4* xr = x + (size_t)(srow < 0 ? 0 : srow) * h8;
 
     uint4 v[NJ][CPB];
     float bmax[NJ];
@@ -43,7 +47,7 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 #pragma unroll
         for (int k = 0; k < CPB; k++) {
             v[j][k] = make_uint4(0, 0, 0, 0);
-            if (b < nblocks) v[j][k] = __ldg(xr + (size_t)b * CPB + k);
+            if (b < nblocks && b * CPB + k < h8 && srow >= 0) v[j][k] = __ldg(xr + (size_t)b * CPB + k);
             m = fmaxf(m, absmax8_bf16(v[j][k]));
         }
         bmax[j] = m;
@@ -463,14 +467,14 @@ int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* s
 
 template <int BLOCK, bool TWO_LEVEL>
 static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
-                        cudaStream_t st) {
+                        cudaStream_t st, const long long* src, int h8) {
     const int nblocks = K / BLOCK;
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
     const int nj = (nblocks + threads - 1) / threads;
 #define QB_LQ(NJ)                                                                                                 \
     quant_act_kernel<BLOCK, NJ, TWO_LEVEL><<<tok, threads, 0, st>>>((const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
-                                                                    (uint8_t*)sf_atoms, g, tok, K)
+                                                                    (uint8_t*)sf_atoms, g, tok, K, src, h8)
     if (nj <= 1) QB_LQ(1);
     else if (nj <= 2) QB_LQ(2);
     else if (nj <= 4) QB_LQ(4);
@@ -482,16 +486,25 @@ static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atom
 
 int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
                  cudaStream_t st) {
-    if (tok < 0 || K <= 0 || K % 128 != 0 || (block != 16 && block != 32)) return QB_ERR_ARG;
+    return gather_quantize_act(x, nullptr, Bbytes, sf_ref, sf_atoms, g, tok, K, K, block, st);
+}
+
+// src == nullptr: plain quantiser of x [tok][K]. Otherwise output row r = quantised x[src[r]] (x rows of H <= K values,
+// zero-padded to K; src[r] < 0 gives a zero row): gather + pad + quantise of routed MoE rows in one pass.
+int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
+                        int block, cudaStream_t st) {
+    if (tok < 0 || K <= 0 || K % 128 != 0 || (block != 16 && block != 32) || H <= 0 || H > K || H % 8) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!x || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
-    if (((uintptr_t)x & 15) || ((uintptr_t)Bbytes & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3)) return QB_ERR_ARG;
+    if (((uintptr_t)x & 15) || ((uintptr_t)Bbytes & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3) || ((uintptr_t)src & 7)) return QB_ERR_ARG;
     if (K > 65536) return QB_ERR_UNSUPPORTED;
+    const long long* sp = (const long long*)src;
+    const int h8 = H >> 3;
     if (block == 32)
-        return g ? launch_quant<32, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st)
-                 : launch_quant<32, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st);
-    return g ? launch_quant<16, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st)
-             : launch_quant<16, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st);
+        return g ? launch_quant<32, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8)
+                 : launch_quant<32, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8);
+    return g ? launch_quant<16, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8)
+             : launch_quant<16, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8);
 }
 
 // ---- re-layout: reference step-major scales [K/128][rows][P] -> 128x4 atoms

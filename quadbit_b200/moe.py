@@ -13,7 +13,7 @@ from types import SimpleNamespace
 import torch
 
 from ._lib import check, load
-from .linear import _ptr, _stream, quantize_act
+from .linear import _ptr, _stream, quantize_act, sf_atoms_empty
 
 BN = 128   # routed-row block (reference: _BN, harness/fused_moe.py:352)
 
@@ -52,9 +52,10 @@ def stack(packs):
     return tuple(torch.cat([p[i] for p in packs], 0).contiguous() for i in range(4))
 
 
-def build_routing(assign: torch.Tensor, e: int):
+def build_routing(assign: torch.Tensor, e: int, with_pos: bool = False):
     """Sort routed slots by expert and pad segments to BN rows: (src, eblk, r_pad), as
-    harness/fused_moe.py:421-435 but without the per-expert host loop."""
+    harness/fused_moe.py:421-435 but without the per-expert host loop. with_pos also returns
+    pos[i] = padded row of routed slot i (the inverse of src on its valid entries)."""
     dev = assign.device
     order = torch.argsort(assign, stable=True)
     counts = torch.bincount(assign, minlength=e)
@@ -65,8 +66,13 @@ def build_routing(assign: torch.Tensor, e: int):
     coff = torch.cumsum(counts, 0) - counts
     sorted_e = assign[order]
     within = torch.arange(order.numel(), device=dev) - coff[sorted_e]
-    src[poff[sorted_e] + within] = order
+    dst = poff[sorted_e] + within
+    src[dst] = order
     eblk = torch.repeat_interleave(torch.arange(e, device=dev, dtype=torch.int32), (padc // BN))
+    if with_pos:
+        pos = torch.empty_like(order)
+        pos[order] = dst
+        return src, eblk.contiguous(), r_pad, pos
     return src, eblk.contiguous(), r_pad
 
 
@@ -77,6 +83,18 @@ def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tens
     r = x_rows.shape[0]
     Bb, sfb, gB = quantize_act(lib, x_rows, 32, True)
     C = torch.empty((r, mpe), dtype=torch.bfloat16, device=x_rows.device)
+    mode = 3 if (bias is not None or row_w is not None) else 1
+    check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
+                      C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
+                      _stream()), "qb_gemm(grouped)")
+    return C
+
+
+def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None):
+    """Grouped GEMM on already quantised routed rows (Bb [r, in_f/2], scale atoms, gB [r])."""
+    Ac, meta, sfa, gA = w
+    r = Bb.shape[0]
+    C = torch.empty((r, mpe), dtype=torch.bfloat16, device=Bb.device)
     mode = 3 if (bias is not None or row_w is not None) else 1
     check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
                       C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
@@ -128,30 +146,46 @@ class SparseMoE:
         self.e0, self.e1 = expert_range if expert_range else (0, self.E)
         self.E_total = n_experts_total or self.E
 
-    def expert_rows(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
-        """Run routed rows through this layer's experts: rows_in [n,H] bf16, assign [n] local expert ids,
-        row_w [n] routing weights -> [n,H] bf16 = expert(row) * weight, in the order of rows_in. Every row
-        is quantised on its own and summed over K in a fixed order, so the result of a row does not depend
-        on which other rows share the call (what makes the expert-parallel layer equal the 1-GPU one)."""
+    def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
+        """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
+        returns (d [r_pad, mpe_dn] bf16 = expert(row) * weight, pos [n] = padded row of routed row i).
+        Routed row i is rows_in[i], or rows_in[row_of[i]] when row_of is given (tokens are then not copied
+        once per routed slot before the gather).
+        Four kernels between the routing and the result: gather + pad + quantise, grouped gate/up GEMM,
+        SwiGLU + quantise, grouped down GEMM with the routing weight in its epilogue."""
         lib = self.lib
         dev = rows_in.device
-        n = rows_in.shape[0]
-        out = torch.zeros((n, self.H), dtype=torch.bfloat16, device=dev)
-        if n == 0:
-            return out
-        src, eblk, r_pad = build_routing(assign.long(), self.e1 - self.e0)
-        valid = src >= 0
-        rows = torch.zeros((r_pad, self.Hp), dtype=torch.bfloat16, device=dev)
-        rows[valid, : self.H] = rows_in[src[valid]].to(torch.bfloat16)
-        gu = seg_gemm(lib, rows, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, mpe_gu]
-        g, u = gu[:, : self.Ip].float(), gu[:, self.Ip: 2 * self.Ip].float()
-        h = (swiglu(g, u) if self.act == "gptoss" else torch.nn.functional.silu(g) * u).to(torch.bfloat16)
-        h[~valid] = 0
+        src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
+        if row_of is not None:
+            src = torch.where(src >= 0, row_of[src.clamp_min(0)], src)
+        x = rows_in.to(torch.bfloat16).contiguous()
+        if self.H % 8:                       # the fused gather reads 16-byte chunks
+            x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
+        Bb = torch.empty((r_pad, self.Hp // 2), dtype=torch.uint8, device=dev)
+        sfb = sf_atoms_empty(lib, r_pad, self.Hp, 32, dev)
+        gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
+        check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
+                                         x.shape[1], 32, _stream()), "qb_gather_quantize_act")
+        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, 2*Ip]: gate | up
+        Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
+        sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
+        gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
+        check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), r_pad, self.Ip, 0,
+                                      0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
         rw = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
-        rw[valid] = row_w[src[valid]].float()
-        d = seg_gemm(lib, h.contiguous(), self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)      # [r_pad, mpe_dn]
-        out[src[valid]] = d[valid, : self.H]
-        return out
+        rw[pos] = row_w.float()
+        d = seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)  # [r_pad, mpe_dn]
+        return d, pos
+
+    def expert_rows(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
+        """rows_in [n,H] bf16, assign [n] local expert ids, row_w [n] routing weights -> [n,H] bf16 =
+        expert(row) * weight, in the order of rows_in. Every row is quantised on its own and summed over K
+        in a fixed order, so the result of a row does not depend on which other rows share the call (what
+        makes the expert-parallel layer equal the 1-GPU one)."""
+        if rows_in.shape[0] == 0:
+            return torch.zeros((0, self.H), dtype=torch.bfloat16, device=rows_in.device)
+        d, pos = self._expert_rows_padded(rows_in, assign, row_w)
+        return d.index_select(0, pos)[:, : self.H].contiguous()
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         """x [T,H] bf16, topk_idx [T,topk] global expert ids, topk_w [T,topk] -> [T,H] bf16
@@ -159,13 +193,16 @@ class SparseMoE:
         T = x.shape[0]
         dev = x.device
         assign_g = topk_idx.reshape(-1).long()
-        local = (assign_g >= self.e0) & (assign_g < self.e1)
-        slots = torch.nonzero(local).squeeze(1)                          # routed slots owned here
-        if slots.numel() == 0:
-            return torch.zeros((T, self.H), dtype=torch.bfloat16, device=dev)
-        d = self.expert_rows(x[slots // self.topk], assign_g[slots] - self.e0, topk_w.reshape(-1)[slots])
+        if self.e0 == 0 and self.e1 == self.E_total:
+            slots = torch.arange(assign_g.numel(), device=dev)
+        else:
+            local = (assign_g >= self.e0) & (assign_g < self.e1)
+            slots = torch.nonzero(local).squeeze(1)                      # routed slots owned here
+            if slots.numel() == 0:
+                return torch.zeros((T, self.H), dtype=torch.bfloat16, device=dev)
+        d, pos = self._expert_rows_padded(x, assign_g[slots] - self.e0, topk_w.reshape(-1)[slots], row_of=slots // self.topk)
         inverse = torch.full((T * self.topk,), -1, dtype=torch.int32, device=dev)
-        inverse[slots] = torch.arange(slots.numel(), dtype=torch.int32, device=dev)
+        inverse[slots] = pos.int()
         return combine(self.lib, d, inverse, T, self.H, self.topk)
 
     def forward_ep(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, group=None) -> torch.Tensor:

@@ -228,3 +228,33 @@ def test_quantiser_ties_signed_zero_and_odd_scales(lib, block):
     assert torch.equal(g, eg)
     assert torch.equal(ref, eS)
     assert torch.equal(Bb, eB)
+
+
+def test_gather_quantise_equals_gather_then_quantise():
+    """qb_gather_quantize_act: rows picked by src, zero-padded from H to K, src < 0 -> zero row; bit-equal to
+    the plain quantiser run on the gathered, padded matrix."""
+    import quadbit_b200 as qb
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(31)
+    n, H, K, r = 50, 200, 256, 128
+    x = torch.randn(n, H).to(torch.bfloat16).cuda()
+    src = torch.randint(0, n, (r,), dtype=torch.long)
+    src[::7] = -1
+    srcd = src.cuda()
+    gathered = torch.zeros(r, K, dtype=torch.bfloat16, device="cuda")
+    ok = srcd >= 0
+    gathered[ok, :H] = x[srcd[ok]]
+    for block in (32, 16):
+        outs = []
+        for fused in (True, False):
+            Bb = torch.empty((r, K // 2), dtype=torch.uint8, device="cuda")
+            sref = torch.empty((K // 128, r, 128 // block), dtype=torch.uint8, device="cuda")
+            g = torch.empty(r, device="cuda")
+            if fused:
+                rc = lib.qb_gather_quantize_act(x.data_ptr(), srcd.data_ptr(), Bb.data_ptr(), sref.data_ptr(), 0, g.data_ptr(), r, K, H, block, 0)
+            else:
+                rc = lib.qb_quantize_act(gathered.data_ptr(), Bb.data_ptr(), sref.data_ptr(), 0, g.data_ptr(), r, K, block, 0)
+            assert rc == 0 and lib.qb_status(0) == 0
+            outs.append((Bb.cpu(), sref.cpu(), g.cpu()))
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
