@@ -120,18 +120,19 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 // them; TWO_LEVEL = false is the single-level quantiser (no per-token global) that the reference's fused MoE
 // GEMM1 epilogue applies (matmul_sp_moe_gu_swiglu, cuda/sparse_fp4_lib.cu:1828-1866); act 0 is the clamped
 // gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1), act 1 the plain silu(g) * u.
-__device__ __forceinline__ float swiglu_h(float g, float u, int act) {
-    if (act == 0) {
+template <int ACT>
+__device__ __forceinline__ float swiglu_h(float g, float u) {
+    if (ACT == 0) {
         g = fminf(g, 7.f);
         u = fmaxf(fminf(u, 7.f), -7.f);
         return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
     }
     return __fdividef(g, 1.f + __expf(-g)) * u;
 }
-template <int NJ, bool INTERLEAVED, bool TWO_LEVEL>
+template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
 __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                            float* __restrict__ g_out, int tok, int I, int act) {
+                                                            float* __restrict__ g_out, int tok, int I) {
     const int row = blockIdx.x;
     const int nchunks = I >> 3;
     const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
@@ -145,14 +146,21 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
     for (int j = 0; j < NJ; j++) {
         const int b = threadIdx.x + j * blockDim.x;
         float m = 0.f;
+        // all eight 16-byte loads of the block are issued before any of the exp / divide chains starts
+        uint4 gq[4], uq[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
-            if (INTERLEAVED) {   // gv, uv: the two halves of 8 consecutive (gate, up) pairs
-                if (b < nblocks) { gv = __ldg(gr + (size_t)b * 8 + 2 * k); uv = __ldg(gr + (size_t)b * 8 + 2 * k + 1); }
+            gq[k] = make_uint4(0, 0, 0, 0);
+            uq[k] = make_uint4(0, 0, 0, 0);
+            if (INTERLEAVED) {   // gq, uq: the two halves of 8 consecutive (gate, up) pairs
+                if (b < nblocks) { gq[k] = __ldg(gr + (size_t)b * 8 + 2 * k); uq[k] = __ldg(gr + (size_t)b * 8 + 2 * k + 1); }
             } else {
-                if (b < nblocks) { gv = __ldg(gr + (size_t)b * 4 + k); uv = __ldg(ur + (size_t)b * 4 + k); }
+                if (b < nblocks) { gq[k] = __ldg(gr + (size_t)b * 4 + k); uq[k] = __ldg(ur + (size_t)b * 4 + k); }
             }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint4 gv = gq[k], uv = uq[k];
             const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
             const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
 #pragma unroll
@@ -160,13 +168,13 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
                 float a, c;
                 if (INTERLEAVED) {
                     const float2 p0 = __bfloat1622float2(gh[i]), p1 = __bfloat1622float2(uh[i]);
-                    a = swiglu_h(p0.x, p0.y, act);
-                    c = swiglu_h(p1.x, p1.y, act);
+                    a = swiglu_h<ACT>(p0.x, p0.y);
+                    c = swiglu_h<ACT>(p1.x, p1.y);
                     h[j][8 * k + i] = a; h[j][8 * k + 4 + i] = c;
                 } else {
                     const float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
-                    a = swiglu_h(g2.x, u2.x, act);
-                    c = swiglu_h(g2.y, u2.y, act);
+                    a = swiglu_h<ACT>(g2.x, u2.x);
+                    c = swiglu_h<ACT>(g2.y, u2.y);
                     h[j][8 * k + 2 * i] = a; h[j][8 * k + 2 * i + 1] = c;
                 }
                 m = fmaxf(m, fmaxf(fabsf(a), fabsf(c)));
@@ -232,7 +240,8 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     const int nj = (nblocks + threads - 1) / threads;
-#define QB_LS3(NJ, IL, TL) swiglu_quant_kernel<NJ, IL, TL><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I, act)
+#define QB_LS4(NJ, IL, TL, ACT) swiglu_quant_kernel<NJ, IL, TL, ACT><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I)
+#define QB_LS3(NJ, IL, TL) do { if (act == 0) QB_LS4(NJ, IL, TL, 0); else QB_LS4(NJ, IL, TL, 1); } while (0)
 #define QB_LS(NJ) do { if (interleaved) { if (gH) QB_LS3(NJ, true, true); else QB_LS3(NJ, true, false); } \
                        else { if (gH) QB_LS3(NJ, false, true); else QB_LS3(NJ, false, false); } } while (0)
     if (nj <= 1) QB_LS(1);
@@ -241,6 +250,7 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
     else return QB_ERR_UNSUPPORTED;
 #undef QB_LS
 #undef QB_LS3
+#undef QB_LS4
     return (int)cudaGetLastError();
 }
 

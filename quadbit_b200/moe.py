@@ -185,7 +185,7 @@ class SparseMoE:
         if rows_in.shape[0] == 0:
             return torch.zeros((0, self.H), dtype=torch.bfloat16, device=rows_in.device)
         d, pos = self._expert_rows_padded(rows_in, assign, row_w)
-        return d.index_select(0, pos)[:, : self.H].contiguous()
+        return torch.index_select(d[:, : self.H], 0, pos)          # one pass: gathers the H valid features of each row
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         """x [T,H] bf16, topk_idx [T,topk] global expert ids, topk_w [T,topk] -> [T,H] bf16
