@@ -150,6 +150,12 @@ int qb_gather_quantize_act(const void* x, const void* src, void* Bbytes, void* s
  * w_dtype 0 = fp32, 1 = bf16. Any output may be NULL. */
 int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_native, void* sf_ref,
                      void* sf_atoms, void* gA, int out, int K, void* stream);
+/* Same with activation-aware pair selection: colnorm fp32 [K] (column norms of calibration activations, Wanda)
+ * makes the importance of a pair |w0|*c0 + |w1|*c1 (pack(w, colnorm), harness/qb_vllm_plugin/qb_sm120_plugin.py:
+ * 1179-1190). colnorm == NULL is qb_compress_2to4; the reference's fallback to the magnitude for an all-zero
+ * colnorm is the caller's to take (pass NULL). */
+int qb_compress_2to4_colnorm(const void* W, int w_dtype, const void* colnorm, void* Ac, void* meta_ref, void* meta_native,
+                             void* sf_ref, void* sf_atoms, void* gA, int out, int K, void* stream);
 /* Dense two-level packer (harness/dense_e2e.py:79-88 as one kernel). */
 int qb_pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out, int K,
                   void* stream);

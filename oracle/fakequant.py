@@ -74,13 +74,18 @@ def enc_ue4m3(s: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- 2:4 pair selection
-def pair24(W: torch.Tensor):
+def pair24(W: torch.Tensor, colnorm: torch.Tensor | None = None):
     """Pair-granular 2:4: in every group of 4 adjacent pairs keep the 2 with the largest
-    |w0|+|w1|. Returns (Wg[out,ks,16,4,2], i01[out,ks,16,2] ascending, keptW, ks)."""
+    |w0|+|w1|. Returns (Wg[out,ks,16,4,2], i01[out,ks,16,2] ascending, keptW, ks).
+    colnorm [K] (activation column norms, Wanda) changes the importance to |w0|*c0 + |w1|*c1; an all-zero
+    colnorm falls back to the magnitude (harness/qb_vllm_plugin/qb_sm120_plugin.py:1179-1190)."""
     out_f, in_f = W.shape
     ks = in_f // 128
     Wg = W.float().reshape(out_f, ks, 16, 4, 2)
-    imp = Wg.abs().sum(-1)
+    if colnorm is None or not bool((colnorm != 0).any()):
+        imp = Wg.abs().sum(-1)
+    else:
+        imp = (Wg.abs() * colnorm.float().view(1, ks, 16, 4, 2)).sum(-1)
     order = torch.sort(imp, dim=-1, descending=True, stable=True).indices[..., :2]
     i01, _ = order.sort(dim=-1)
     keptW = torch.gather(Wg, 3, i01.unsqueeze(-1).expand(-1, -1, -1, -1, 2))
@@ -96,9 +101,9 @@ def tie_groups(W: torch.Tensor) -> int:
     return int((s[..., 1] == s[..., 2]).sum())
 
 
-def _sparse_quant_core(W: torch.Tensor):
+def _sparse_quant_core(W: torch.Tensor, colnorm: torch.Tensor | None = None):
     out_f, in_f = W.shape
-    Wg, i01, keptW, ks = pair24(W)
+    Wg, i01, keptW, ks = pair24(W, colnorm)
     gA = (keptW.abs().amax(dim=(1, 2, 3, 4), keepdim=True) / GLOBAL_DIV).clamp_min(1e-30).reshape(out_f, 1, 1)
     blk = keptW.reshape(out_f, ks, 4, 8, 2)
     scode = enc_ue4m3((blk.abs().amax(dim=(3, 4)) / 6.0) / gA)
@@ -107,14 +112,14 @@ def _sparse_quant_core(W: torch.Tensor):
     return i01, gA, scode, sdeq, kc, ks
 
 
-def pack_weight_sparse_2lvl(W: torch.Tensor):
+def pack_weight_sparse_2lvl(W: torch.Tensor, colnorm: torch.Tensor | None = None):
     """[out,K] -> reference-layout packed tensors:
        Ac[out,K/4] u8 (byte = one kept pair, low nibble = even k),
        meta[K/128,out,2] i32 (group g: word g//8, bits 4*(g%8): i0|(i1<<2)),
        scaleA[K/128,out,4] u8 (one UE4M3 per 16 kept values = 32 logical K),
        gA[out] f32."""
     out_f, in_f = W.shape
-    i01, gA, scode, sdeq, kc, ks = _sparse_quant_core(W)
+    i01, gA, scode, sdeq, kc, ks = _sparse_quant_core(W, colnorm)
     Ac = (kc[..., 0] | (kc[..., 1] << 4)).reshape(out_f, ks * 32).to(torch.uint8).contiguous()
     nib = (i01[..., 0] | (i01[..., 1] << 2)).view(out_f, ks, 2, 8)
     sh = (torch.arange(8) * 4).view(1, 1, 1, 8)

@@ -185,6 +185,10 @@ int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void*
                      void* gA, int out, int K, void* stream) {
     return qb::compress_2to4(W, w_dtype, Ac, meta_ref, meta_native, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream);
 }
+int qb_compress_2to4_colnorm(const void* W, int w_dtype, const void* colnorm, void* Ac, void* meta_ref, void* meta_native,
+                             void* sf_ref, void* sf_atoms, void* gA, int out, int K, void* stream) {
+    return qb::compress_2to4(W, w_dtype, Ac, meta_ref, meta_native, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream, colnorm);
+}
 int qb_pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out, int K,
                   void* stream) {
     return qb::pack_dense(W, w_dtype, Ab, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream);

@@ -62,7 +62,10 @@ template <typename T, int NB>
 __global__ void __launch_bounds__(1024) compress_2to4_kernel(const T* __restrict__ W, uint8_t* __restrict__ Ac,
                                                               uint32_t* __restrict__ meta_ref, uint32_t* __restrict__ meta_nat,
                                                               uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                              float* __restrict__ gA, int out_f, int K) {
+                                                              float* __restrict__ gA, int out_f, int K,
+                                                              const float* __restrict__ colnorm) {
+    // colnorm != nullptr: importance of a pair = |w0|*c0 + |w1|*c1 with c the activation column norms
+    // (Wanda; harness/qb_vllm_plugin/qb_sm120_plugin.py:1183-1190), each product and the sum rounded to fp32
     __shared__ float red[32];
     const int row = blockIdx.x;
     const int nblk = K >> 5;   // 32 logical K = 4 groups of 4 pairs = 16 kept values = one scale
@@ -87,7 +90,15 @@ __global__ void __launch_bounds__(1024) compress_2to4_kernel(const T* __restrict
         for (int g = 0; g < 4; g++) {
             float imp[4];
 #pragma unroll
-            for (int p = 0; p < 4; p++) imp[p] = __fadd_rn(fabsf(w[g * 8 + 2 * p]), fabsf(w[g * 8 + 2 * p + 1]));
+            for (int p = 0; p < 4; p++) {
+                float a0 = fabsf(w[g * 8 + 2 * p]), a1 = fabsf(w[g * 8 + 2 * p + 1]);
+                if (colnorm && b < nblk) {
+                    const float2 c = __ldg(reinterpret_cast<const float2*>(colnorm + (size_t)b * 32 + g * 8 + 2 * p));
+                    a0 = __fmul_rn(a0, c.x);
+                    a1 = __fmul_rn(a1, c.y);
+                }
+                imp[p] = __fadd_rn(a0, a1);
+            }
             // largest importance, lowest index on ties; then the same among the rest
             int a = 0;
 #pragma unroll
@@ -215,9 +226,9 @@ static bool pick_launch(int K, int& threads, int& nb) {
 }
 
 int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_nat, void* sf_ref, void* sf_atoms,
-                  void* gA, int out_f, int K, cudaStream_t st) {
+                  void* gA, int out_f, int K, cudaStream_t st, const void* colnorm) {
     if (out_f <= 0 || K <= 0 || K % 128 != 0 || !W || (w_dtype != 0 && w_dtype != 1)) return QB_ERR_ARG;
-    if (((uintptr_t)W & 15) || ((uintptr_t)Ac & 7) || ((uintptr_t)meta_ref & 3) || ((uintptr_t)meta_nat & 3) ||
+    if (((uintptr_t)W & 15) || ((uintptr_t)Ac & 7) || ((uintptr_t)colnorm & 7) || ((uintptr_t)meta_ref & 3) || ((uintptr_t)meta_nat & 3) ||
         ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3))
         return QB_ERR_ARG;
     int threads, nb;
@@ -225,7 +236,7 @@ int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* me
 #define QB_LC(T, NB)                                                                                            \
     compress_2to4_kernel<T, NB><<<out_f, threads, 0, st>>>((const T*)W, (uint8_t*)Ac, (uint32_t*)meta_ref,      \
                                                            (uint32_t*)meta_nat, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, \
-                                                           (float*)gA, out_f, K)
+                                                           (float*)gA, out_f, K, (const float*)colnorm)
     if (w_dtype == 0) { if (nb <= 1) QB_LC(float, 1); else QB_LC(float, 2); }
     else { if (nb <= 1) QB_LC(__nv_bfloat16, 1); else QB_LC(__nv_bfloat16, 2); }
 #undef QB_LC

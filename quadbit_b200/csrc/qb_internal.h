@@ -29,7 +29,7 @@ int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st)
 // ---- qb_compress.cu
 // w_dtype: 0 = fp32, 1 = bf16. Any output pointer may be null.
 int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_nat, void* sf_ref, void* sf_atoms,
-                  void* gA, int out_f, int K, cudaStream_t st);
+                  void* gA, int out_f, int K, cudaStream_t st, const void* colnorm = nullptr);
 int pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out_f, int K,
                cudaStream_t st);
 

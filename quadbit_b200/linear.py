@@ -73,11 +73,14 @@ class QuadbitLinear:
 
     y = x @ W^T with W pruned 2:4 pair-wise by |w0|+|w1| and quantised to E2M1 with one
     UE4M3 scale per 16 kept values and an fp32 scale per row; activations are quantised per
-    call (E2M1, one UE4M3 scale per 32 along K, fp32 scale per token)."""
+    call (E2M1, one UE4M3 scale per 32 along K, fp32 scale per token).
+    colnorm [in] (column norms of calibration activations) selects the pairs by |w|*colnorm instead
+    (Wanda; the plugin's pack(w, colnorm), harness/qb_vllm_plugin/qb_sm120_plugin.py:1179-1190); an
+    all-zero colnorm falls back to the magnitude as there."""
 
     block = 32
 
-    def __init__(self, W: torch.Tensor, keep_ref_layout: bool = True):
+    def __init__(self, W: torch.Tensor, keep_ref_layout: bool = True, colnorm: torch.Tensor | None = None):
         assert W.is_cuda and W.dim() == 2
         out_f, in_f = W.shape
         assert out_f % 128 == 0 and in_f % 128 == 0, "out%128, in%128"
@@ -98,9 +101,14 @@ class QuadbitLinear:
             self.scaleA = torch.empty((ks, out_f, 4), dtype=torch.uint8, device=dev)
         else:
             self.meta = self.scaleA = None
-        check(lib.qb_compress_2to4(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, self.Ac.data_ptr(), _ptr(self.meta),
-                                   self.meta_native.data_ptr(), _ptr(self.scaleA), self.sfa.data_ptr(), self.gA.data_ptr(),
-                                   out_f, in_f, _stream()), "qb_compress_2to4")
+        if colnorm is not None:
+            colnorm = colnorm.to(device=dev, dtype=torch.float32).contiguous()
+            assert colnorm.numel() == in_f
+            if not bool((colnorm != 0).any()):
+                colnorm = None
+        check(lib.qb_compress_2to4_colnorm(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, _ptr(colnorm), self.Ac.data_ptr(),
+                                           _ptr(self.meta), self.meta_native.data_ptr(), _ptr(self.scaleA), self.sfa.data_ptr(),
+                                           self.gA.data_ptr(), out_f, in_f, _stream()), "qb_compress_2to4_colnorm")
         self.At = tile_weights(lib, self.Ac, out_f, in_f, 1)      # what the GEMMs read; Ac stays as the reference attribute
 
     def pack_act(self, x: torch.Tensor):

@@ -61,6 +61,10 @@ def main(ref_root: str) -> None:
              tables | {"q_fp4", "enc_ue4m3_t", "act_fp4_dequant", "dense_fp4_dequant"})
     d = lift(ref / "harness/dense_e2e.py", tables | {"quant_fp4", "enc_ue4m3", "nvfp4_pack"})
     m = lift(ref / "harness/fused_moe.py", tables | {"q_fp4", "enc", "pack", "build_routing", "_BN"})
+    # the plugin's packer takes activation column norms (Wanda importance) as a second argument
+    pl = lift(ref / "harness/qb_vllm_plugin/qb_sm120_plugin.py", {"fp4", "bnd", "cc", "e_", "m_", "ue4m3", "q_fp4", "enc", "pack"},
+              inside="_load_sparse_moe",
+              extra_ns={"_FP4_VALS": [0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6]})
 
     g = torch.Generator().manual_seed(0)
     out = {}
@@ -111,6 +115,16 @@ def main(ref_root: str) -> None:
     src, eblk, r_pad = m["build_routing"](assign, 8)
     out.update(rt_assign=assign.numpy(), rt_src=src.numpy(), rt_eblk=eblk.numpy(), rt_rpad=np.int64(r_pad),
                rt_bn=np.int64(m["_BN"]))
+
+    # activation-aware pair selection (drawn last so that every array above keeps its values)
+    Ww = torch.randn(64, 256, generator=g) * 0.02
+    cn = torch.exp(torch.empty(256).uniform_(-2, 2, generator=g))
+    impw = (Ww.view(64, 32, 4, 2).abs() * cn.view(1, 32, 4, 2)).sum(-1).sort(-1, descending=True).values
+    assert int((impw[..., 1] == impw[..., 2]).sum()) == 0, "importance tie in the column-norm golden input"
+    pw = pl["pack"](Ww, cn)
+    pz = pl["pack"](Ww, torch.zeros(256))          # all-zero norms: magnitude fallback
+    out.update(ww=Ww.numpy(), ww_cn=cn.numpy(), ww_Ac=pw[0].numpy(), ww_meta=pw[1].numpy(), ww_scaleA=pw[2].numpy(),
+               ww_gA=pw[3].numpy(), wz_Ac=pz[0].numpy(), wz_meta=pz[1].numpy())
 
     dst = Path(__file__).with_name("ref_fakequant.npz")
     np.savez_compressed(dst, **out)

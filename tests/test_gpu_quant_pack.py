@@ -258,3 +258,32 @@ def test_gather_quantise_equals_gather_then_quantise():
             outs.append((Bb.cpu(), sref.cpu(), g.cpu()))
         for a, b in zip(*outs):
             assert torch.equal(a, b)
+
+
+def test_compressor_with_activation_column_norms_matches_golden_and_oracle():
+    """QuadbitLinear(W, colnorm=...): pairs chosen by |w|*colnorm. Bit-exact against the vectors generated from the
+    reference's plugin packer and against the oracle on a larger tie-free matrix; zero norms = magnitude."""
+    import numpy as np
+    from pathlib import Path
+    import quadbit_b200 as qb
+    G = np.load(Path(__file__).parent / "golden" / "ref_fakequant.npz")
+    W, cn = torch.from_numpy(G["ww"]), torch.from_numpy(G["ww_cn"])
+    Wp = torch.zeros(128, 256)
+    Wp[:64] = W                                        # the module wants out % 128
+    lin = qb.QuadbitLinear(Wp.cuda(), colnorm=cn.cuda())
+    assert torch.equal(lin.Ac.cpu()[:64], torch.from_numpy(G["ww_Ac"]))
+    assert torch.equal(lin.meta.cpu()[:, :64], torch.from_numpy(G["ww_meta"]))
+    assert torch.equal(lin.scaleA.cpu()[:, :64], torch.from_numpy(G["ww_scaleA"]))
+    assert torch.equal(lin.gA.cpu()[:64], torch.from_numpy(G["ww_gA"]))
+    lz = qb.QuadbitLinear(Wp.cuda(), colnorm=torch.zeros(256).cuda())
+    assert torch.equal(lz.Ac.cpu()[:64], torch.from_numpy(G["wz_Ac"])) and torch.equal(lz.meta.cpu()[:, :64], torch.from_numpy(G["wz_meta"]))
+    torch.manual_seed(41)
+    W2 = torch.randn(256, 1024) * 0.02
+    cn2 = torch.exp(torch.empty(1024).uniform_(-2, 2))
+    imp = (W2.view(256, 128, 4, 2).abs() * cn2.view(1, 128, 4, 2)).sum(-1).sort(-1, descending=True).values
+    assert int((imp[..., 1] == imp[..., 2]).sum()) == 0
+    l2 = qb.QuadbitLinear(W2.cuda(), colnorm=cn2.cuda())
+    Ac, meta, scaleA, gA = fq.pack_weight_sparse_2lvl(W2, cn2)
+    assert torch.equal(l2.Ac.cpu(), Ac) and torch.equal(l2.meta.cpu(), meta)
+    assert torch.equal(l2.scaleA.cpu(), scaleA) and torch.equal(l2.gA.cpu(), gA)
+    assert lin.lib.qb_status(0) == 0

@@ -35,6 +35,19 @@ def test_sparse_pack_bit_exact():
     assert torch.equal(fq.unpack_weight_sparse_2lvl(Ac, meta, scaleA, gA), t("sw_deq"))
 
 
+def test_sparse_pack_with_activation_column_norms_bit_exact():
+    """Wanda-style importance |w|*||x_col|| (the plugin's pack(w, colnorm)); all-zero norms fall back to magnitude."""
+    W, cn = t("ww"), t("ww_cn")
+    Ac, meta, scaleA, gA = fq.pack_weight_sparse_2lvl(W, cn)
+    assert torch.equal(Ac, t("ww_Ac")) and torch.equal(meta, t("ww_meta"))
+    assert torch.equal(scaleA, t("ww_scaleA")) and torch.equal(gA, t("ww_gA"))
+    assert not torch.equal(meta, t("wz_meta"))               # the norms do change the masks
+    Az, mz, _, _ = fq.pack_weight_sparse_2lvl(W, torch.zeros_like(cn))
+    assert torch.equal(Az, t("wz_Ac")) and torch.equal(mz, t("wz_meta"))
+    A0, m0, _, _ = fq.pack_weight_sparse_2lvl(W)
+    assert torch.equal(A0, Az) and torch.equal(m0, mz)
+
+
 def test_sparse_pack_bf16_weights_outside_ties():
     """bf16 weights have importance ties, where the reference's topk order is unspecified:
     compare every group that has no tie at the keep boundary."""
