@@ -150,6 +150,12 @@ int qb_gather_quantize_act(const void* x, const void* src, void* Bbytes, void* s
  * w_dtype 0 = fp32, 1 = bf16. Any output may be NULL. */
 int qb_compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_native, void* sf_ref,
                      void* sf_atoms, void* gA, int out, int K, void* stream);
+/* Checkpoint block formats -> bf16 [out][ld_out] rows (ld_out >= in, so the result can be written into a zero-padded
+ * buffer) for the compressor: group 32 = gpt-oss MXFP4 (w [out][in/2] E2M1 codes, low nibble = even column; scales
+ * [out][in/32] e8m0; _mxfp4_dequant, harness/qb_vllm_plugin/qb_sm120_plugin.py:2089-2100), group 16 = modelopt NVFP4
+ * (scales [out][in/16] e4m3fn bytes, tensor_scale a device fp32 scalar or NULL; _dequant_nvfp4_expert, :70-95). */
+int qb_dequant_fp4_blocks(const void* w, const void* scales, const void* tensor_scale, void* out, int out_f, int in_f, int group,
+                          long long ld_out, void* stream);
 /* Same with activation-aware pair selection: colnorm fp32 [K] (column norms of calibration activations, Wanda)
  * makes the importance of a pair |w0|*c0 + |w1|*c1 (pack(w, colnorm), harness/qb_vllm_plugin/qb_sm120_plugin.py:
  * 1179-1190). colnorm == NULL is qb_compress_2to4; the reference's fallback to the magnitude for an all-zero

@@ -350,3 +350,29 @@ def moe_seg_linear(x_rows: torch.Tensor, eblk: torch.Tensor, W_experts, bn: int 
         xs = x_rows[b * bn:(b + 1) * bn]
         out[b * bn:(b + 1) * bn] = F.linear(act_dequant_2lvl(xs.float(), 32), deq[ex])
     return out
+
+
+# ---------------------------------------------------------------- checkpoint block formats
+def mxfp4_dequant(w_u8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:
+    """gpt-oss MXFP4 expert weight -> bf16: w [out, in/2] u8 (low nibble = even column), s [out, in/32] u8 e8m0
+    (multiplier 2^(raw-127)); harness/qb_vllm_plugin/qb_sm120_plugin.py:2089-2100."""
+    b = w_u8.to(torch.int32) & 0xFF
+    out_f, inb = b.shape
+    codes = torch.empty(out_f, inb * 2, dtype=torch.long)
+    codes[:, 0::2] = b & 0xF
+    codes[:, 1::2] = (b >> 4) & 0xF
+    mult = torch.exp2(s_u8.float() - 127.0)
+    return (FP4[codes].view(out_f, s_u8.shape[-1], 32) * mult[:, :, None]).reshape(out_f, inb * 2).to(torch.bfloat16)
+
+
+def nvfp4_ckpt_dequant(w_u8: torch.Tensor, scale_e4m3_u8: torch.Tensor, s2: float, group: int = 16) -> torch.Tensor:
+    """modelopt NVFP4 weight -> bf16: FP4[nibble] * e4m3fn block scale [out, in/group] (given as raw bytes) * per-tensor
+    fp32 scale, products in that order in fp32; harness/qb_vllm_plugin/qb_sm120_plugin.py:70-95."""
+    b = w_u8.to(torch.int32) & 0xFF
+    out_f, inb = b.shape
+    k = inb * 2
+    codes = torch.empty(out_f, k, dtype=torch.long)
+    codes[:, 0::2] = b & 0xF
+    codes[:, 1::2] = (b >> 4) & 0xF
+    bs = scale_e4m3_u8.view(torch.float8_e4m3fn).float().repeat_interleave(group, dim=1)[:, :k]
+    return (FP4[codes] * bs * torch.tensor(s2, dtype=torch.float32)).to(torch.bfloat16)

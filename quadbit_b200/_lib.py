@@ -42,6 +42,7 @@ _SIGS = {
     "qb_swiglu_quant_act": ([P] * 5 + [I] * 4 + [P], I),
     "qb_compress_2to4": ([P, I] + [P] * 6 + [I] * 2 + [P], I),
     "qb_compress_2to4_colnorm": ([P, I] + [P] * 7 + [I] * 2 + [P], I),
+    "qb_dequant_fp4_blocks": ([P] * 4 + [I] * 3 + [c_longlong, P], I),
     "qb_pack_dense": ([P, I] + [P] * 4 + [I] * 2 + [P], I),
     "qb_relayout_sf": ([P] * 2 + [I] * 3 + [P], I),
     "qb_relayout_meta": ([P] * 2 + [I] * 2 + [P], I),

@@ -189,6 +189,10 @@ int qb_compress_2to4_colnorm(const void* W, int w_dtype, const void* colnorm, vo
                              void* sf_ref, void* sf_atoms, void* gA, int out, int K, void* stream) {
     return qb::compress_2to4(W, w_dtype, Ac, meta_ref, meta_native, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream, colnorm);
 }
+int qb_dequant_fp4_blocks(const void* w, const void* scales, const void* tensor_scale, void* out, int out_f, int in_f, int group,
+                          long long ld_out, void* stream) {
+    return qb::dequant_fp4_blocks(w, scales, tensor_scale, out, out_f, in_f, group, ld_out, (cudaStream_t)stream);
+}
 int qb_pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out, int K,
                   void* stream) {
     return qb::pack_dense(W, w_dtype, Ab, sf_ref, sf_atoms, gA, out, K, (cudaStream_t)stream);

@@ -290,4 +290,56 @@ int tile_weights(const void* A, void* At, int rows, int K, int sparse, cudaStrea
     return (int)cudaGetLastError();
 }
 
+// Checkpoint block formats -> bf16 rows for the compressor (the reference dequantises with torch:
+// _mxfp4_dequant, harness/qb_vllm_plugin/qb_sm120_plugin.py:2089-2100, gpt-oss MXFP4: E2M1 codes, one e8m0
+// scale 2^(raw-127) per 32; _dequant_nvfp4_expert, :70-95, modelopt NVFP4: one e4m3fn scale per 16 and a
+// per-tensor fp32 scale, product (value * block scale) * tensor scale in fp32, then bf16).
+// One thread per 8 values (4 code bytes in, 16 bytes out); rows of the output have a stride so that the
+// result can land inside a zero-padded [out%256][in%128] buffer. HBM-bound: 0.5 + scale bytes in, 2 out.
+__device__ __forceinline__ float dec_e4m3fn(uint32_t c) {
+    const uint32_t e = (c >> 3) & 0xF, m = c & 7;
+    float v = e == 0 ? (float)m * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
+    if ((c & 0x7f) == 0x7f) v = __int_as_float(0x7fc00000);
+    return (c & 0x80) ? -v : v;
+}
+template <int GROUP>
+__global__ void dequant_fp4_blocks_kernel(const uint32_t* __restrict__ w, const uint8_t* __restrict__ sc, const float* __restrict__ s2,
+                                          __nv_bfloat16* __restrict__ out, int out_f, int in_f, long long ld_out) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = in_f >> 3;
+    if (t >= (long long)out_f * per_row) return;
+    const int r = (int)(t / per_row), c8 = (int)(t % per_row);
+    const uint32_t codes = __ldg(w + t);
+    const uint32_t sraw = __ldg(sc + (size_t)r * (in_f / GROUP) + (c8 * 8) / GROUP);
+    const float bs = GROUP == 32 ? exp2f((float)sraw - 127.f) : dec_e4m3fn(sraw);
+    const float ts = s2 ? __ldg(s2) : 1.f;
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t c0 = (codes >> (8 * i)) & 0xF, c1 = (codes >> (8 * i + 4)) & 0xF;
+        float v0 = (float)((c0 & 7) < 4 ? (c0 & 7) : ((c0 & 7) == 4 ? 4 : ((c0 & 7) == 5 ? 6 : ((c0 & 7) == 6 ? 8 : 12)))) * 0.5f;
+        float v1 = (float)((c1 & 7) < 4 ? (c1 & 7) : ((c1 & 7) == 4 ? 4 : ((c1 & 7) == 5 ? 6 : ((c1 & 7) == 6 ? 8 : 12)))) * 0.5f;
+        if ((c0 & 8) && (c0 & 7)) v0 = -v0;      // code 8 is +0 in the reference table
+        if ((c1 & 8) && (c1 & 7)) v1 = -v1;
+        v0 = __fmul_rn(v0, bs);
+        v1 = __fmul_rn(v1, bs);
+        if (GROUP == 16) { v0 = __fmul_rn(v0, ts); v1 = __fmul_rn(v1, ts); }
+        o[i] = pack_bf16x2(v0, v1);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)r * ld_out + (size_t)c8 * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+int dequant_fp4_blocks(const void* w, const void* scales, const void* s2, void* out, int out_f, int in_f, int group, long long ld_out,
+                       cudaStream_t st) {
+    if (out_f <= 0 || in_f <= 0 || in_f % 32 || (group != 16 && group != 32) || ld_out < in_f || ld_out % 8) return QB_ERR_ARG;
+    if (!w || !scales || !out || ((uintptr_t)w & 3) || ((uintptr_t)out & 15) || ((uintptr_t)s2 & 3)) return QB_ERR_ARG;
+    const long long n = (long long)out_f * (in_f / 8);
+    const int blocks = (int)((n + 255) / 256);
+    if (group == 32)
+        dequant_fp4_blocks_kernel<32><<<blocks, 256, 0, st>>>((const uint32_t*)w, (const uint8_t*)scales, nullptr, (__nv_bfloat16*)out, out_f, in_f, ld_out);
+    else
+        dequant_fp4_blocks_kernel<16><<<blocks, 256, 0, st>>>((const uint32_t*)w, (const uint8_t*)scales, (const float*)s2, (__nv_bfloat16*)out, out_f, in_f, ld_out);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace qb

@@ -28,6 +28,8 @@ int relayout_meta(const void* ref, void* nat, int out_f, int K, cudaStream_t st)
 
 // ---- qb_compress.cu
 // w_dtype: 0 = fp32, 1 = bf16. Any output pointer may be null.
+int dequant_fp4_blocks(const void* w, const void* scales, const void* s2, void* out, int out_f, int in_f, int group, long long ld_out,
+                       cudaStream_t st);
 int compress_2to4(const void* W, int w_dtype, void* Ac, void* meta_ref, void* meta_nat, void* sf_ref, void* sf_atoms,
                   void* gA, int out_f, int K, cudaStream_t st, const void* colnorm = nullptr);
 int pack_dense(const void* W, int w_dtype, void* Ab, void* sf_ref, void* sf_atoms, void* gA, int out_f, int K,

@@ -51,6 +51,20 @@ def lift(path: Path, names: set[str], inside: str = "run", extra_ns: dict | None
     return ns
 
 
+def lift_top(path: Path, names: set[str]) -> dict:
+    """Same for module-level defs / assignments."""
+    tree = ast.parse(path.read_text())
+    picked = []
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            picked.append(node)
+        elif isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id in names for t in node.targets):
+            picked.append(node)
+    ns = {"torch": torch}
+    exec(compile(ast.Module(body=picked, type_ignores=[]), str(path), "exec"), ns)
+    return ns
+
+
 def main(ref_root: str) -> None:
     ref = Path(ref_root)
     tables = {"FP4", "BND", "_cc", "_c", "_e", "_m", "UE4M3"}
@@ -125,6 +139,20 @@ def main(ref_root: str) -> None:
     pz = pl["pack"](Ww, torch.zeros(256))          # all-zero norms: magnitude fallback
     out.update(ww=Ww.numpy(), ww_cn=cn.numpy(), ww_Ac=pw[0].numpy(), ww_meta=pw[1].numpy(), ww_scaleA=pw[2].numpy(),
                ww_gA=pw[3].numpy(), wz_Ac=pz[0].numpy(), wz_meta=pz[1].numpy())
+
+    # checkpoint block formats (drawn after everything else)
+    plugin = ref / "harness/qb_vllm_plugin/qb_sm120_plugin.py"
+    mx = lift(plugin, {"fp4", "_mxfp4_dequant"}, inside="_install_gptoss_moe",
+              extra_ns={"_FP4_VALS": [0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6]})
+    nv = lift_top(plugin, {"_FP4_VALS", "_FP4_LUT_CACHE", "_dequant_nvfp4_expert"})
+    cw = torch.randint(0, 256, (24, 96), generator=g, dtype=torch.int32).to(torch.uint8)            # [out, in/2], in = 192
+    cs8 = torch.randint(100, 150, (24, 6), generator=g, dtype=torch.int32).to(torch.uint8)          # e8m0, one per 32
+    cs4 = torch.randint(0, 0x7f, (24, 12), generator=g, dtype=torch.int32).to(torch.uint8)          # e4m3fn bytes, one per 16
+    cs4[0, :3] = torch.tensor([0, 1, 0x7e], dtype=torch.uint8)                                      # zero, smallest subnormal, 448
+    s2 = 0.01234
+    out.update(ck_w=cw.numpy(), ck_s8=cs8.numpy(), ck_s4=cs4.numpy(), ck_s2=np.float32(s2),
+               ck_mx=mx["_mxfp4_dequant"](cw, cs8).view(torch.int16).numpy(),
+               ck_nv=nv["_dequant_nvfp4_expert"](cw, cs4.view(torch.float8_e4m3fn), torch.tensor(s2)).view(torch.int16).numpy())
 
     dst = Path(__file__).with_name("ref_fakequant.npz")
     np.savez_compressed(dst, **out)

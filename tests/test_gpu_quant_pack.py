@@ -287,3 +287,27 @@ def test_compressor_with_activation_column_norms_matches_golden_and_oracle():
     assert torch.equal(l2.Ac.cpu(), Ac) and torch.equal(l2.meta.cpu(), meta)
     assert torch.equal(l2.scaleA.cpu(), scaleA) and torch.equal(l2.gA.cpu(), gA)
     assert lin.lib.qb_status(0) == 0
+
+
+def test_checkpoint_block_formats_to_bf16():
+    """qb_dequant_fp4_blocks through quadbit_b200.checkpoint: bit-exact against the golden vectors of the reference's
+    torch dequantisers and against the oracle on a larger random tensor, with zero padding of the output."""
+    import numpy as np
+    from pathlib import Path
+    from quadbit_b200 import checkpoint as ck
+    G = np.load(Path(__file__).parent / "golden" / "ref_fakequant.npz")
+    w, s8, s4 = (torch.from_numpy(G[k]).cuda() for k in ("ck_w", "ck_s8", "ck_s4"))
+    mx = ck.mxfp4_to_bf16(w, s8)
+    assert torch.equal(mx.cpu().view(torch.int16), torch.from_numpy(G["ck_mx"]))
+    nv = ck.nvfp4_to_bf16(w, s4.view(torch.float8_e4m3fn), float(G["ck_s2"]))
+    assert torch.equal(nv.cpu().view(torch.int16), torch.from_numpy(G["ck_nv"]))
+    torch.manual_seed(51)
+    w2 = torch.randint(0, 256, (300, 1440), dtype=torch.int32).to(torch.uint8)      # gpt-oss hidden 2880
+    s2 = torch.randint(110, 135, (300, 90), dtype=torch.int32).to(torch.uint8)
+    got = ck.mxfp4_to_bf16(w2.cuda(), s2.cuda(), pad_out=256, pad_in=128)
+    assert got.shape == (512, 2944)
+    ref = fq.mxfp4_dequant(w2, s2)
+    assert torch.equal(got[:300, :2880].cpu().view(torch.int16), ref.view(torch.int16))
+    assert not got[300:].any() and not got[:, 2880:].any()
+    g, u = ck.split_interleaved_gate_up(got[:300])
+    assert torch.equal(g, got[0:300:2]) and torch.equal(u, got[1:300:2])

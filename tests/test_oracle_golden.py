@@ -131,3 +131,10 @@ def test_native_layout_maps():
     assert nm.shape == (2, 2, 128, 16)
     w = nm.view(torch.int32).view(2, 2, 128, 4)
     assert w[1, 1, 5, 2] == meta[3, 133, 0] and w[0, 0, 7, 1] == meta[0, 7, 1]
+
+
+def test_checkpoint_block_formats_bit_exact():
+    """MXFP4 (e8m0 per 32) and modelopt NVFP4 (e4m3fn per 16 + tensor scale) dequantisers against the reference's."""
+    w, s8, s4 = t("ck_w"), t("ck_s8"), t("ck_s4")
+    assert torch.equal(fq.mxfp4_dequant(w, s8).view(torch.int16), t("ck_mx"))
+    assert torch.equal(fq.nvfp4_ckpt_dequant(w, s4, float(t("ck_s2"))).view(torch.int16), t("ck_nv"))
