@@ -160,6 +160,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const int tiles_mn = p.num_m * p.num_n;
     const int total_tiles = tiles_mn * p.splits;
+    // grouped mode: a 128-token block with expert id < 0 is unused capacity of a fixed-capacity routing; every
+    // role skips its tiles (same test everywhere, so the K-block and accumulator counters stay in step)
+    auto tile_skipped = [&](int tile) { return p.eblk != nullptr && p.eblk[(tile % tiles_mn) / p.num_m] < 0; };
     const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
     const int atoms_per_rb = p.kblocks * C::MMAS;   // scale atoms per 128-row block along K
 
@@ -175,6 +178,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t phase = 0;
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag && pw < NP; tile += gridDim.x) {
+            if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
             const int n0 = n * BN;
@@ -218,6 +222,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t acc_phase = 0;
             long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = QB_CLK();
             for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+                if (tile_skipped(tile)) continue;
                 const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
                 const int n = mn / p.num_m;
                 const int n0 = n * BN;
@@ -286,6 +291,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int stage = 0;
         uint32_t phase = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn;
             const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
             bool ok = true;
@@ -341,6 +347,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t acc_phase = 0;
         long long c_wait_accf = 0, c_epi = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
             const int n0 = n * BN;
@@ -656,6 +663,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t tmem_base = tmem_base_slot;
 
     const int total_tiles = p.num_m2 * p.num_n;
+    // grouped mode: a 128-token block with expert id < 0 is unused capacity of a fixed-capacity routing; every
+    // role of both CTAs skips its tiles (same test everywhere, so the ring and accumulator counters stay in step)
+    auto tile_skipped = [&](int tile) { return p.eblk != nullptr && p.eblk[tile / p.num_m2] < 0; };
     const int atoms_per_rb = p.kblocks * C::MMAS;
 
     // Every role below handles two K blocks per barrier poll whenever the later one is ready as well: a
@@ -675,6 +685,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t phase = 0;
         long long c_pw = 0, c_pb = 0, c_pn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
@@ -725,6 +736,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int rb_a = ((p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
             bool ok = true;
@@ -775,6 +787,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             uint32_t phase = 0, acc_phase = 0;
             long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_iters = 0, c_t0 = QB_CLK();
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+                if (tile_skipped(tile)) continue;
                 // a 192-token tile starts 0 or 64 rows into a 128-row scale-factor atom: 0 or 2 columns in
                 const uint32_t sfb_coloff = (uint32_t)((((tile / p.num_m2) * BN) & 127) >> 5);
                 long long ca = QB_CLK();
@@ -848,6 +861,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t sphase = 0, it = 0;
         long long c_sw = 0, c_sb = 0, c_sn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            if (tile_skipped(tile)) continue;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
                 const long long f0 = QB_CLK();
@@ -955,6 +969,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         constexpr int HCOLS = BN / 2;          // columns per warp
         constexpr int NCH = HCOLS / 16;        // chunks of 16 columns
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
+            if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
             const int n0 = n * BN + half * HCOLS;          // first token column of this warp
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half

@@ -76,6 +76,39 @@ def build_routing(assign: torch.Tensor, e: int, with_pos: bool = False):
     return src, eblk.contiguous(), r_pad
 
 
+def fixed_capacity(n: int, e: int) -> int:
+    """Rows that always hold n routed slots of e experts with every segment padded to BN."""
+    return (n + e * (BN - 1) + BN - 1) // BN * BN
+
+
+def build_routing_fixed(assign: torch.Tensor, e: int):
+    """`build_routing` without a host read: the padded row count is the worst case `fixed_capacity(n, e)`, blocks
+    beyond the used ones carry expert id -1 (the grouped GEMM skips them) and their rows src = -1. Everything
+    stays on the device with static shapes, so the layer can be captured in a CUDA graph (the reference's
+    graph-safe fixed-capacity routing: route_fixed_cap, harness/qb_vllm_plugin/qb_sm120_plugin.py:1271-1315).
+    Returns (src [r_cap], eblk [r_cap/BN], r_cap, pos [n])."""
+    dev = assign.device
+    n = assign.numel()
+    r_cap = fixed_capacity(n, e)
+    order = torch.argsort(assign, stable=True)
+    counts = torch.zeros(e, dtype=torch.long, device=dev).scatter_add_(0, assign, torch.ones_like(assign))
+    padc = (counts + BN - 1) // BN * BN
+    pend = torch.cumsum(padc, 0)
+    poff = pend - padc
+    coff = torch.cumsum(counts, 0) - counts
+    sorted_e = assign[order]
+    within = torch.arange(n, device=dev) - coff[sorted_e]
+    dst = poff[sorted_e] + within
+    src = torch.full((r_cap,), -1, dtype=torch.long, device=dev)
+    src[dst] = order
+    pos = torch.empty_like(order)
+    pos[order] = dst
+    blk0 = torch.arange(r_cap // BN, device=dev) * BN
+    eb = torch.bucketize(blk0, pend, right=True)                 # expert whose padded segment holds the block
+    eblk = torch.where(eb < e, eb, torch.full_like(eb, -1)).to(torch.int32)
+    return src, eblk.contiguous(), r_cap, pos
+
+
 def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None):
     """Quantise routed rows and run the grouped GEMM: [r_pad, mpe] bf16 (token-major);
     with bias / row_w the epilogue computes (acc + bias[expert]) * row_w[row]."""
@@ -123,7 +156,7 @@ class SparseMoE:
     [e0, e1) for expert parallelism; slots of other experts are skipped."""
 
     def __init__(self, w_gate_up: list[torch.Tensor], w_down: list[torch.Tensor], topk: int, act: str = "silu",
-                 expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None):
+                 expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None, fixed_capacity: bool = False):
         self.lib = lib = load("sparse_fp4")
         self.E = len(w_gate_up)
         self.topk, self.act = topk, act
@@ -145,6 +178,9 @@ class SparseMoE:
         self.w_gu, self.w_dn = stack(gus), stack(dns)
         self.e0, self.e1 = expert_range if expert_range else (0, self.E)
         self.E_total = n_experts_total or self.E
+        # fixed_capacity: route into the worst-case number of padded rows instead of reading the exact count back
+        # from the device; `forward` then issues no host read and can be captured in a CUDA graph
+        self.fixed_capacity = fixed_capacity
 
     def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
         """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
@@ -155,7 +191,10 @@ class SparseMoE:
         SwiGLU + quantise, grouped down GEMM with the routing weight in its epilogue."""
         lib = self.lib
         dev = rows_in.device
-        src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
+        if self.fixed_capacity:
+            src, eblk, r_pad, pos = build_routing_fixed(assign.long(), self.e1 - self.e0)
+        else:
+            src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
         if row_of is not None:
             src = torch.where(src >= 0, row_of[src.clamp_min(0)], src)
         x = rows_in.to(torch.bfloat16).contiguous()

@@ -239,3 +239,44 @@ def test_moe_forward_ep_two_gpus_equals_one_gpu():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert got[0] and got[1]
+
+
+def test_moe_fixed_capacity_routing_equals_exact_and_captures_in_a_graph():
+    """Fixed-capacity routing (unused 128-row blocks carry expert id -1 and are skipped by the grouped GEMM) gives the
+    bits of the exact-size routing, with no host read, so the whole layer replays from a CUDA graph."""
+    import quadbit_b200 as qb
+    import quadbit_b200.moe as qmoe
+    torch.manual_seed(23)
+    for H, I, E, topk, T in ((256, 256, 8, 2, 300), (384, 128, 4, 4, 96)):      # pair-kernel and single-CTA grouped forms
+        wgu = [torch.randn(2 * I, H).cuda() * 0.05 for _ in range(E)]
+        wdn = [torch.randn(H, I).cuda() * 0.05 for _ in range(E)]
+        x = torch.randn(T, H).cuda().bfloat16()
+        idx, w = fq.route_topk(torch.randn(T, E), topk)
+        idx, w = idx.cuda(), w.cuda()
+        exact = qb.SparseMoE(wgu, wdn, topk)
+        fixed = qb.SparseMoE(wgu, wdn, topk, fixed_capacity=True)
+        y = exact.forward(x, idx, w)
+        yf = fixed.forward(x, idx, w)
+        assert torch.equal(y, yf)
+        src, eblk, r_cap, pos = qmoe.build_routing_fixed(idx.reshape(-1).long(), E)
+        esrc, eeblk, r_pad = qmoe.build_routing(idx.reshape(-1).long(), E)
+        assert r_cap >= r_pad and torch.equal(src[:r_pad], esrc) and bool((src[r_pad:] == -1).all())
+        assert torch.equal(eblk[: r_pad // 128], eeblk) and bool((eblk[r_pad // 128:] == -1).all())
+        # capture and replay with new inputs of the same shape
+        sx, si, sw = x.clone(), idx.clone(), w.clone()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                fixed.forward(sx, si, sw)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = fixed.forward(sx, si, sw)
+        x2 = torch.randn(T, H).cuda().bfloat16()
+        idx2, w2 = fq.route_topk(torch.randn(T, E), topk)
+        sx.copy_(x2); si.copy_(idx2.cuda()); sw.copy_(w2.cuda())
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, exact.forward(x2, idx2.cuda(), w2.cuda()))
+        assert exact.lib.qb_status(0) == 0
