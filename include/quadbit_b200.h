@@ -228,9 +228,10 @@ int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
 /* Same with the row layout and the activation as arguments: interleaved = 1 reads (gate, up) pairs
  * [g0,u0,g1,u1,...] (gpt-oss fused gate_up), act 0 = clamped gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1;
  * harness/fused_moe.py:450-452), 1 = silu(g)*u; gH == NULL selects the single-level quantiser of the reference's
- * fused GEMM1 epilogue (cuda/sparse_fp4_lib.cu:1828-1866). */
-int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                        void* stream);
+ * fused GEMM1 epilogue (cuda/sparse_fp4_lib.cu:1828-1866). row_src (int64 [tok], may be NULL): rows with row_src < 0
+ * are padding of a routed batch, their input is not read and they quantise as all-zero rows. */
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, int tok, int I,
+                        int interleaved, int act, void* stream);
 /* fused_mlp_2lvl on native layouts (weights from qb_compress_2to4; sfb_x / sfb_h are scale-atom
  * scratch of qb_sf_atoms_bytes(tok, H | I, 32) bytes; Cf may be NULL or an fp32 [tok][dn_out]
  * workspace for a split-K down projection). Four launches, no synchronisation, no allocation. */

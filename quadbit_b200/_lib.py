@@ -39,7 +39,7 @@ _SIGS = {
     # native
     "qb_quantize_act": ([P] * 5 + [I] * 3 + [P], I),
     "qb_gather_quantize_act": ([P] * 6 + [I] * 4 + [P], I),
-    "qb_swiglu_quant_act": ([P] * 5 + [I] * 4 + [P], I),
+    "qb_swiglu_quant_act": ([P] * 6 + [I] * 4 + [P], I),
     "qb_compress_2to4": ([P, I] + [P] * 6 + [I] * 2 + [P], I),
     "qb_compress_2to4_colnorm": ([P, I] + [P] * 7 + [I] * 2 + [P], I),
     "qb_dequant_fp4_blocks": ([P] * 4 + [I] * 3 + [c_longlong, P], I),

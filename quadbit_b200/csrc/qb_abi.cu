@@ -259,9 +259,9 @@ int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {
     return qb::swiglu_quant(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, (cudaStream_t)stream);
 }
-int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                        void* stream) {
-    return qb::swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, interleaved, act, (cudaStream_t)stream);
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, int tok, int I,
+                        int interleaved, int act, void* stream) {
+    return qb::swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, interleaved, act, (cudaStream_t)stream, row_src);
 }
 int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,

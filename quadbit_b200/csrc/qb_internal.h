@@ -14,7 +14,7 @@ int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_r
                         int block, cudaStream_t st);
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                    cudaStream_t st);
+                    cudaStream_t st, const void* row_src = nullptr);
 int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st);
 int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const void* sc_w, const void* bias, void* Out, int rows,
                     int Mpe, int Hout, cudaStream_t st);

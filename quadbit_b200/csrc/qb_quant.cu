@@ -36,6 +36,20 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     const int lane = threadIdx.x & 31;
     const long long srow = src ? src[row] : (long long)row;
     const uint4* xr = x + (size_t)(srow < 0 ? 0 : srow) * h8;
+    if (srow < 0) {
+        // padding row: what the full path makes of an all-zero row (codes 0, scale codes 0, global 1e-30), without the passes
+        for (int b = threadIdx.x; b < nblocks; b += blockDim.x) {
+            uint32_t* dst = Bwords + (size_t)row * (K >> 3) + (size_t)b * CPB;
+#pragma unroll
+            for (int k = 0; k < CPB; k++) dst[k] = 0u;
+            if ((b & 3) == 0) {
+                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(b / P) * tok + row) * P + (b % P)) = 0u;
+                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, b, kpad256(K) / BLOCK / 4)) = 0u;
+            }
+        }
+        if (TWO_LEVEL && threadIdx.x == 0) g_out[row] = 1e-30f;
+        return;
+    }
 
     uint4 v[NJ][CPB];
     float bmax[NJ];
@@ -132,13 +146,26 @@ __device__ __forceinline__ float swiglu_h(float g, float u) {
 template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
 __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                            float* __restrict__ g_out, int tok, int I) {
+                                                            float* __restrict__ g_out, int tok, int I, const long long* __restrict__ row_src) {
     const int row = blockIdx.x;
     const int nchunks = I >> 3;
     const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
     const int lane = threadIdx.x & 31;
     const uint4* gr = cgu + (size_t)row * (nchunks * 2);
     const uint4* ur = gr + nchunks;
+    if (row_src && row_src[row] < 0) {
+        // padding row of a routed batch (its gate/up row may never have been written): zeros, as for an all-zero row
+        for (int b = threadIdx.x; b < nblocks; b += blockDim.x) {
+            uint32_t* dst = Hwords + (size_t)row * nchunks + (size_t)b * 4;
+            dst[0] = 0u; dst[1] = 0u; dst[2] = 0u; dst[3] = 0u;
+            if ((b & 3) == 0) {
+                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(b >> 2) * tok + row) * 4) = 0u;
+                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, b, kpad256(I) / 128)) = 0u;
+            }
+        }
+        if (TWO_LEVEL && threadIdx.x == 0) g_out[row] = 1e-30f;
+        return;
+    }
     float h[NJ][32];
     float bmax[NJ];
     float tmax = 0.f;
@@ -226,12 +253,12 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
 }
 
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st) {
-    return swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, 0, 1, st);
+    return swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, 0, 1, st, nullptr);
 }
 
 // interleaved: row layout [g0,u0,g1,u1,...]; gH == nullptr selects the single-level quantiser
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                    cudaStream_t st) {
+                    cudaStream_t st, const void* row_src) {
     if (tok < 0 || I <= 0 || I % 128 != 0 || (act != 0 && act != 1)) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!cgu || !Hb || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
@@ -240,7 +267,7 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     const int nj = (nblocks + threads - 1) / threads;
-#define QB_LS4(NJ, IL, TL, ACT) swiglu_quant_kernel<NJ, IL, TL, ACT><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I)
+#define QB_LS4(NJ, IL, TL, ACT) swiglu_quant_kernel<NJ, IL, TL, ACT><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I, (const long long*)row_src)
 #define QB_LS3(NJ, IL, TL) do { if (act == 0) QB_LS4(NJ, IL, TL, 0); else QB_LS4(NJ, IL, TL, 1); } while (0)
 #define QB_LS(NJ) do { if (interleaved) { if (gH) QB_LS3(NJ, true, true); else QB_LS3(NJ, true, false); } \
                        else { if (gH) QB_LS3(NJ, false, true); else QB_LS3(NJ, false, false); } } while (0)

@@ -85,7 +85,7 @@ def ep_moe(x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, n_expe
     epr = n_experts // world
     T, topk = topk_idx.shape
     flat_e = topk_idx.reshape(-1).long()
-    order = torch.argsort(flat_e, stable=True)
+    order = torch.argsort(flat_e.to(torch.int16) if n_experts < 32768 else flat_e, stable=True)
     send_e = flat_e[order]
     send_rows = x[order // topk].contiguous()
     send_w = topk_w.reshape(-1)[order].float().contiguous()

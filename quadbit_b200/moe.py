@@ -57,7 +57,7 @@ def build_routing(assign: torch.Tensor, e: int, with_pos: bool = False):
     harness/fused_moe.py:421-435 but without the per-expert host loop. with_pos also returns
     pos[i] = padded row of routed slot i (the inverse of src on its valid entries)."""
     dev = assign.device
-    order = torch.argsort(assign, stable=True)
+    order = torch.argsort(assign.to(torch.int16) if e < 32768 else assign, stable=True)    # 16-bit keys: 2 radix passes instead of 8
     counts = torch.bincount(assign, minlength=e)
     padc = (counts + BN - 1) // BN * BN
     poff = torch.cumsum(padc, 0) - padc
@@ -90,7 +90,7 @@ def build_routing_fixed(assign: torch.Tensor, e: int):
     dev = assign.device
     n = assign.numel()
     r_cap = fixed_capacity(n, e)
-    order = torch.argsort(assign, stable=True)
+    order = torch.argsort(assign.to(torch.int16) if e < 32768 else assign, stable=True)    # 16-bit keys: 2 radix passes instead of 8
     counts = torch.zeros(e, dtype=torch.long, device=dev).scatter_add_(0, assign, torch.ones_like(assign))
     padc = (counts + BN - 1) // BN * BN
     pend = torch.cumsum(padc, 0)
@@ -209,7 +209,7 @@ class SparseMoE:
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
-        check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), r_pad, self.Ip, 0,
+        check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
         rw = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
         rw[pos] = row_w.float()
