@@ -157,6 +157,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // launched as a programmatic dependent: barrier set-up, the tensor-memory allocation and the descriptor
+    // prefetch above ran beside the tail of the activation quantiser; its outputs are read only from here on
+    griddep_wait();
 
     const int tiles_mn = p.num_m * p.num_n;
     const int total_tiles = tiles_mn * p.splits;
@@ -1215,8 +1218,17 @@ static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     if (rc) return rc;
     int total = kp.num_m * kp.num_n * kp.splits;
     int grid = total < sm_count() ? total : sm_count();
-    nvfp4_gemm_kernel<SPARSE, BN><<<grid, NTHREADS1, C::SMEM_BYTES, st>>>(tmA, tmB, kp);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NTHREADS1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see griddep_wait() in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<SPARSE, BN>, tmA, tmB, kp);
 }
 
 

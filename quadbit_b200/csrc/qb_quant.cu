@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     // (src < 0: an all-zero row) — the gather of routed MoE rows fused into their quantiser
     constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
     constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
+    griddep_launch_dependents();     // a thin-token GEMM that follows may set itself up while this grid runs
     const int row = blockIdx.x;
     const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
