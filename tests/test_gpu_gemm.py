@@ -390,3 +390,32 @@ def test_gemm_tiled_weights_bitwise_equal(lib, sparse, out_f, tok, K, bn, splits
         assert torch.equal(Cr, Ct)
     else:   # atomic split-K adds in arrival order
         assert (Cr.float() - Ct.float()).abs().max() <= 2e-2 * Cr.float().abs().max()
+
+
+@pytest.mark.parametrize("name,out_f,K", [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 14336, 4096), ("down", 4096, 14336)])
+def test_prefill_set_at_full_size(lib, name, out_f, K):
+    """The Llama-3-8B prefill shapes at 4096 tokens, 2:4-sparse, through the module API: (a) the CTA-pair kernel and
+    the single-CTA kernel, two independent schedules of the same products, give the same bf16 matrix; (b) the
+    first 48 tokens against the CPU oracle's fake-quant linear (bf16 gate 6e-3); (c) the compressor's output
+    against the oracle's packer on the first 256 weight rows, bit for bit."""
+    import quadbit_b200 as qb
+    tok = 4096
+    g = torch.Generator().manual_seed(out_f * 7 + K)
+    W = (torch.randn(out_f, K, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(tok, K, generator=g).to(torch.bfloat16)
+    lin = qb.QuadbitLinear(W.cuda())
+    Bb, sB, gB = lin.pack_act(x.cuda())
+    y_pair = lin.run(Bb, sB, tok, gB, out_t=True, bn=512)
+    y_one = lin.run(Bb, sB, tok, gB, out_t=True, bn=128)
+    assert lib.qb_status(S()) == 0
+    assert torch.equal(y_pair, y_one)
+    ref = fq.linear_sparse(x[:48].float(), W.float())
+    assert bf16_err(y_pair[:48], ref) < 6e-3
+    Wf = W[:256].float()
+    ties = fq.tie_groups(Wf)
+    eAc, emeta, escale, egA = fq.pack_weight_sparse_2lvl(Wf)
+    same_rows = (lin.Ac[:256].cpu() == eAc).all(1)
+    # bf16 weights tie at the keep boundary in a few groups, where both sides keep the lower pair index
+    assert bool(same_rows.all()), (name, int((~same_rows).sum()), ties)
+    assert torch.equal(lin.meta[:, :256].cpu(), emeta) and torch.equal(lin.scaleA[:, :256].cpu(), escale)
+    assert torch.equal(lin.gA[:256].cpu(), egA)
