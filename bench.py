@@ -195,8 +195,33 @@ def run_gpu(args):
         return a.elapsed_time(b) / iters * 1e-3
 
     # ---- profiling aids: one small workload of a side kernel, timed with CUDA events, nothing else
-    if args.only in ("quant", "decode"):
-        if args.only == "quant":
+    if args.only in ("quant", "decode", "swiglu", "gatherq"):
+        if args.only == "swiglu":
+            # SwiGLU + two-level quantiser of the MoE layer: 16384 routed rows x (gate | up) of 2944 features each
+            rows, ih = 16384, 2944
+            cgu = torch.randn(rows, 2 * ih, device=dev).to(torch.bfloat16)          # 193 MB: larger than L2
+            Hb = torch.empty((rows, ih // 2), dtype=torch.uint8, device=dev)
+            sfh = torch.zeros(lib.qb_sf_atoms_bytes(rows, ih, 32), dtype=torch.uint8, device=dev)
+            gH = torch.empty(rows, device=dev)
+            fn = lambda: qb._lib.check(lib.qb_swiglu_quant_act(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), 0, rows, ih, 0, 0,
+                                                                torch.cuda.current_stream().cuda_stream), "qb_swiglu_quant_act")
+            algo = rows * (2 * ih * 2 + ih * (0.5 + 1 / 32) + 4)
+            what = f"swiglu_quant_kernel<1,false,true,0> on [{rows},{2 * ih}] bf16"
+        elif args.only == "gatherq":
+            # gather + pad + quantise of routed MoE rows: 40832 padded rows (a fifth of them padding) from 8192 tokens of 2880
+            n_tok, hh, kp_, rows = 8192, 2880, 2944, 40832
+            xg = torch.randn(n_tok, hh, device=dev).to(torch.bfloat16)
+            src = torch.randint(0, n_tok, (rows,), device=dev)
+            src[torch.rand(rows, device=dev) < 0.2] = -1
+            n_valid = int((src >= 0).sum())
+            Bg = torch.empty((rows, kp_ // 2), dtype=torch.uint8, device=dev)
+            sfg = torch.zeros(lib.qb_sf_atoms_bytes(rows, kp_, 32), dtype=torch.uint8, device=dev)
+            gg = torch.empty(rows, device=dev)
+            fn = lambda: qb._lib.check(lib.qb_gather_quantize_act(xg.data_ptr(), src.data_ptr(), Bg.data_ptr(), 0, sfg.data_ptr(), gg.data_ptr(), rows,
+                                                                   kp_, hh, 32, torch.cuda.current_stream().cuda_stream), "qb_gather_quantize_act")
+            algo = n_valid * hh * 2 + rows * (kp_ * (0.5 + 1 / 32) + 4)
+            what = f"quant_act_kernel<32,1,true> gathering {n_valid} of {rows} rows from [{n_tok},{hh}] bf16 (source rows re-read from L2)"
+        elif args.only == "quant":
             rows, k = 16384, 4096                      # 134 MB of bf16 input: larger than L2
             xq = torch.randn(rows, k, device=dev).to(torch.bfloat16)
             fn = lambda: qb.quantize_act(lib, xq, 32, True)
@@ -564,8 +589,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
-                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' time one small workload of "
-                    "the activation quantiser / the thin-token GEMM instead")
+                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'swiglu' / 'gatherq' time one small workload of "
+                    "the activation quantiser / the thin-token GEMM / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead")
     ap.add_argument("--tp", action="store_true", help="with --gpus N > 1: tensor-parallel sharding of the set (strong scaling, "
                     "NCCL all-reduce after the row-parallel GEMMs) instead of sharding the tokens")
     ap.add_argument("--ep", action="store_true", help="instead of the GEMM set: the gpt-oss-120b-shaped MoE layer with the experts split over "
