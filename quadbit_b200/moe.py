@@ -264,3 +264,119 @@ def load_sparse_moe():
                            seg_bw=lambda x, w, mpe, in_f, eblk, row_w, bias=None: seg_gemm(lib, x, w, mpe, in_f, eblk, bias, row_w),
                            build_routing=build_routing, combine=lambda d, inv, t, H, topk: combine(lib, d, inv, t, H, topk),
                            pad_w=pad_w, swiglu=swiglu)
+
+
+def load_sparse_moe_reference_layout():
+    """The plugin's `_load_sparse_moe()` namespace with its own signatures and the reference's tensor layouts
+    (harness/qb_vllm_plugin/qb_sm120_plugin.py:1124-1368): every helper binds the reference-named entry point of the
+    library, so code written against that namespace runs unchanged. `pack` is the CUDA compressor emitting the
+    reference layout (Ac, meta [K/128,out,2] i32, scaleA [K/128,out,4] u8, gA); `load_sparse_moe()` above is the
+    native-layout variant the modules of this package use."""
+    lib = load("sparse_fp4")
+
+    def _st():
+        return torch.cuda.current_stream().cuda_stream
+
+    def pack_ref(w, colnorm=None):
+        w = w.contiguous()
+        if w.dtype not in (torch.float32, torch.bfloat16):
+            w = w.float()
+        out_f, in_f = w.shape
+        dev = w.device
+        ks = in_f // 128
+        ac = torch.empty((out_f, in_f // 4), dtype=torch.uint8, device=dev)
+        meta = torch.empty((ks, out_f, 2), dtype=torch.int32, device=dev)
+        scale_a = torch.empty((ks, out_f, 4), dtype=torch.uint8, device=dev)
+        ga = torch.empty((out_f,), dtype=torch.float32, device=dev)
+        if colnorm is not None:
+            colnorm = colnorm.to(device=dev, dtype=torch.float32).contiguous()
+            if not bool((colnorm != 0).any()):
+                colnorm = None
+        check(lib.qb_compress_2to4_colnorm(w.data_ptr(), 1 if w.dtype == torch.bfloat16 else 0, _ptr(colnorm), ac.data_ptr(),
+                                           meta.data_ptr(), 0, scale_a.data_ptr(), 0, ga.data_ptr(), out_f, in_f, _st()),
+              "qb_compress_2to4_colnorm")
+        return ac, meta, scale_a, ga
+
+    def stack_ref(packs):
+        return (torch.cat([p[0] for p in packs], 0).contiguous(), torch.cat([p[1] for p in packs], 1).contiguous(),
+                torch.cat([p[2] for p in packs], 1).contiguous(), torch.cat([p[3] for p in packs], 0).contiguous())
+
+    def quant_into(x, bb, sb, gb):
+        r, in_f = x.shape
+        lib.quantize_act_nvfp4_2lvl_s(x.data_ptr(), bb.data_ptr(), sb.data_ptr(), gb.data_ptr(), r, in_f, _st())
+
+    def quant_act_ref(x):
+        r, in_f = x.shape
+        x = x.to(torch.bfloat16).contiguous()
+        bb = torch.empty((r, in_f // 2), dtype=torch.uint8, device=x.device)
+        sb = torch.empty((in_f // 128, r, 4), dtype=torch.uint8, device=x.device)
+        gb = torch.empty((r,), dtype=torch.float32, device=x.device)
+        quant_into(x, bb, sb, gb)
+        return bb, sb, gb
+
+    def seg_into(w, bb, sb, gb, c, mpe, in_f, eblk):
+        ac, meta, scale_a, ga = w
+        check(lib.sparse_moe_mm_2lvl(ac.data_ptr(), bb.data_ptr(), scale_a.data_ptr(), sb.data_ptr(), meta.data_ptr(), c.data_ptr(),
+                                     ac.shape[0], mpe, c.shape[0], in_f, ga.data_ptr(), gb.data_ptr(), eblk.data_ptr(), 1, _st()),
+              "sparse_moe_mm_2lvl")
+
+    def seg_gemm_ref(x, w, mpe, in_f, eblk):
+        bb, sb, gb = quant_act_ref(x)
+        c = torch.empty((x.shape[0], mpe), dtype=torch.bfloat16, device=x.device)
+        seg_into(w, bb, sb, gb, c, mpe, in_f, eblk)
+        return c
+
+    def route_fixed_cap(assign, e, cap, valid=None):
+        """Every expert gets `cap` rows (a multiple of BN); slots beyond an expert's capacity are dropped and counted."""
+        assign = assign.to(torch.long)
+        r = assign.shape[0]
+        dev = assign.device
+        a, nb = (assign, e) if valid is None else (torch.where(valid, assign.clamp(0, e - 1), torch.full_like(assign, e)), e + 1)
+        order = torch.argsort(a, stable=True)
+        sa = a[order]
+        counts = torch.zeros(nb, dtype=torch.long, device=dev).scatter_add_(0, a, torch.ones_like(a))
+        within = torch.arange(r, device=dev) - (torch.cumsum(counts, 0) - counts)[sa]
+        keep = (within < cap) & (sa < e)
+        dest = torch.where(keep, sa * cap + within, torch.full_like(sa, e * cap))
+        src = torch.full((e * cap + 1,), -1, dtype=torch.long, device=dev)
+        src.scatter_(0, dest, order)
+        eblk = (torch.arange(e * cap // BN, device=dev) // (cap // BN)).to(torch.int32)
+        dropped = (r if valid is None else valid.sum()) - keep.sum()
+        return src[: e * cap], eblk, dropped
+
+    def gu_swiglu(w, bb, sb, gb, hw, sh, mpe, r, in_f, eblk, gu_bias, ih, act=0):
+        ac, meta, sa, ga = w
+        check(lib.sparse_moe_gu_swiglu(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), ac.shape[0], mpe, r,
+                                       in_f, ga.data_ptr(), gb.data_ptr(), eblk.data_ptr(), _ptr(gu_bias), hw.data_ptr(), sh.data_ptr(),
+                                       ih, act, _st()), "sparse_moe_gu_swiglu")
+
+    def down_scatter(w, bb, sb, out, mpe, r, in_f, eblk, sc_tok, sc_w, bias, hout):
+        ac, meta, sa, ga = w
+        check(lib.sparse_moe_mm_2lvl_scatter(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), ac.shape[0],
+                                             mpe, r, in_f, ga.data_ptr(), 0, eblk.data_ptr(), sc_tok.data_ptr(), sc_w.data_ptr(),
+                                             _ptr(bias), out.data_ptr(), hout, _st()), "sparse_moe_mm_2lvl_scatter")
+
+    def seg_bw(w, bb, sb, c, mpe, r, in_f, eblk, sc_w, bias, hout):
+        ac, meta, sa, ga = w
+        check(lib.sparse_moe_mm_2lvl_bw(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), c.data_ptr(),
+                                        ac.shape[0], mpe, r, in_f, ga.data_ptr(), 0, eblk.data_ptr(), sc_w.data_ptr(), _ptr(bias), hout,
+                                        _st()), "sparse_moe_mm_2lvl_bw")
+
+    def route(assign, e, rmax):
+        ai = assign.to(torch.int32)
+        counts = torch.zeros(e, dtype=torch.long, device=ai.device).scatter_add_(0, assign.long(), torch.ones_like(assign, dtype=torch.long))
+        padc = ((counts + BN - 1) // BN) * BN
+        ends = torch.cumsum(padc, 0)
+        poff = (ends - padc).to(torch.int64)
+        src = torch.full((rmax,), -1, dtype=torch.int32, device=ai.device)
+        counter = torch.empty(e, dtype=torch.int32, device=ai.device)
+        check(lib.moe_route(ai.data_ptr(), poff.data_ptr(), counter.data_ptr(), src.data_ptr(), ai.numel(), e, _st()), "moe_route")
+        eblk = torch.bucketize(torch.arange(rmax // BN, device=ai.device) * BN, ends, right=True).clamp_max_(e - 1).to(torch.int32)
+        return src.long(), eblk, rmax
+
+    def combine_ref(dbuf, inverse, y, t, hout, topk, mpe):
+        check(lib.moe_combine_topk(dbuf.data_ptr(), inverse.data_ptr(), y.data_ptr(), t, hout, topk, mpe, _st()), "moe_combine_topk")
+
+    return SimpleNamespace(lib=lib, pack=pack_ref, stack=stack_ref, quant_act=quant_act_ref, seg_gemm=seg_gemm_ref,
+                           build_routing=build_routing, quant_into=quant_into, seg_into=seg_into, route_fixed_cap=route_fixed_cap,
+                           gu_swiglu=gu_swiglu, down_scatter=down_scatter, seg_bw=seg_bw, combine=combine_ref, route=route)

@@ -176,3 +176,64 @@ def test_dense_library_glue_per16():
     deq = fq.unpack_act(Hb.cpu(), SFH.cpu(), None, 16)
     assert (deq != want).float().mean().item() < 5e-3
     assert ((deq - h).norm() / h.norm()).item() < 0.12
+
+
+def test_plugin_namespace_with_reference_layouts():
+    """`load_sparse_moe_reference_layout()` carries the 14 names of the plugin's `_load_sparse_moe()` namespace with its
+    signatures: pack -> stack -> route / route_fixed_cap -> quant_into -> seg_into / seg_bw / down_scatter / gu_swiglu -> combine."""
+    import quadbit_b200.moe as qmoe
+    sp = qmoe.load_sparse_moe_reference_layout()
+    for name in ("lib pack stack quant_act seg_gemm build_routing quant_into seg_into route_fixed_cap gu_swiglu down_scatter seg_bw "
+                 "combine route").split():
+        assert hasattr(sp, name), name
+    torch.manual_seed(17)
+    E, Mpe, K, T, topk = 4, 256, 256, 60, 2
+    Ws = [torch.randn(Mpe, K) * 0.02 for _ in range(E)]
+    packs = [sp.pack(w.cuda()) for w in Ws]
+    for p, w in zip(packs, Ws):                                   # the CUDA packer equals the oracle's, bit for bit
+        for a, b in zip(p, fq.pack_weight_sparse_2lvl(w)):
+            assert torch.equal(a.cpu(), b)
+    w = sp.stack(packs)
+    x = torch.randn(T, K)
+    idx, wt = fq.route_topk(torch.randn(T, E), topk)
+    assign = idx.reshape(-1).cuda()
+    src, eblk, r_pad = sp.build_routing(assign, E)
+    src2, eblk2, _ = sp.route(assign, E, r_pad)
+    assert torch.equal(eblk2, eblk) and torch.equal(torch.sort(src2.view(-1, 128), 1).values, torch.sort(src.view(-1, 128), 1).values)
+    valid = src >= 0
+    rows = torch.zeros(r_pad, K, device="cuda", dtype=torch.bfloat16)
+    rows[valid] = x.cuda().bfloat16()[src[valid] // topk]
+    c = sp.seg_gemm(rows, w, Mpe, K, eblk)
+    ref = fq.moe_seg_linear(rows.float().cpu(), eblk.cpu(), Ws)
+    assert ((c.float().cpu() - ref).abs() / (ref.abs() + 1.0)).max().item() < 6e-3
+    bb, sb, gb = sp.quant_act(rows)
+    c2 = torch.empty_like(c)
+    sp.seg_into(w, bb, sb, gb, c2, Mpe, K, eblk)
+    assert torch.equal(c, c2)
+    # weighted rows (seg_bw) + combine == fused scatter (down_scatter)
+    sc_w = torch.zeros(r_pad, device="cuda")
+    sc_w[valid] = wt.reshape(-1).cuda()[src[valid]]
+    cbw = torch.empty_like(c)
+    # the plugin's seg_bw / down_scatter run the down GEMM on single-level rows (gB = 1): quantise accordingly
+    sb1 = torch.empty_like(sb)
+    bb1 = torch.empty_like(bb)
+    sp.lib.quantize_act_nvfp4(rows.data_ptr(), bb1.data_ptr(), sb1.data_ptr(), r_pad, K)
+    sp.seg_bw(w, bb1, sb1, cbw, Mpe, r_pad, K, eblk, sc_w, None, Mpe)
+    inverse = torch.full((T * topk,), -1, dtype=torch.int32, device="cuda")
+    inverse[src[valid]] = torch.nonzero(valid).squeeze(1).int()
+    y = torch.empty((T, Mpe), dtype=torch.bfloat16, device="cuda")
+    sp.combine(cbw, inverse, y, T, Mpe, topk, Mpe)
+    sc_tok = torch.full((r_pad,), -1, dtype=torch.int32, device="cuda")
+    sc_tok[valid] = (src[valid] // topk).int()
+    out = torch.zeros((T, Mpe), dtype=torch.float32, device="cuda")
+    sp.down_scatter(w, bb1, sb1, out, Mpe, r_pad, K, eblk, sc_tok, sc_w, None, Mpe)
+    assert sp.lib.qb_status(0) == 0
+    assert ((out.cpu() - y.float().cpu()).abs() / (y.float().cpu().abs() + 1.0)).max().item() < 6e-3
+    # fixed capacity: every expert owns cap rows, nothing dropped when cap is large enough
+    cap = 128
+    fsrc, feblk, dropped = sp.route_fixed_cap(assign, E, cap)
+    assert int(dropped) == 0 and fsrc.numel() == E * cap and torch.equal(feblk.cpu(), torch.arange(E, dtype=torch.int32))
+    for e in range(E):
+        seg = fsrc[e * cap:(e + 1) * cap]
+        got = torch.sort(seg[seg >= 0]).values
+        assert torch.equal(got, torch.nonzero(assign == e).squeeze(1))
