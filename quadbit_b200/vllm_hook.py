@@ -80,3 +80,70 @@ def install_vllm(mode: str = "sparse", method: str = "vllm.model_executor.layers
     mod_name, cls_name = method.rsplit(".", 1)
     cls = getattr(importlib.import_module(mod_name), cls_name)
     return install(cls, mode=mode, **kw)
+
+
+def install_moe(method_cls, fmt: str = "mxfp4", act: str = "gptoss", fixed_capacity: bool = True,
+                select: Callable[[object], bool] | None = None):
+    """Patch a fused-MoE method class the way the reference patches `GptOssMxfp4MoEMethod`
+    (harness/qb_vllm_plugin/qb_sm120_plugin.py:2086-2498): after the engine's own
+    `process_weights_after_loading(layer)`, the expert tensors of the layer are dequantised on the GPU, pruned 2:4 and
+    packed once into a `SparseMoE`; `apply(layer, x, topk_weights, topk_ids, ...)` then runs the routed layer on it.
+
+    fmt "mxfp4": `layer.w13_weight` [E, 2I, H/2] u8 + `layer.w13_weight_scale` [E, 2I, H/32] e8m0 with gate / up rows
+    interleaved, `layer.w2_weight` [E, H, I/2] + `layer.w2_weight_scale` [E, H, I/32] (gpt-oss checkpoints);
+    fmt "bf16": `layer.w13_weight` [E, 2I, H] (gate rows then up rows) and `layer.w2_weight` [E, H, I] as they are.
+    Biases are not taken here (the reference keeps them for its own epilogues); layers that `select` rejects stay on
+    the engine's path. Returns a function that restores the original methods."""
+    if fmt not in ("mxfp4", "bf16"):
+        raise ValueError(f"fmt {fmt!r}")
+    from . import checkpoint as ck
+    from .moe import SparseMoE
+    orig_pw = getattr(method_cls, "process_weights_after_loading", None)
+    orig_apply = method_cls.apply
+    STATS.setdefault("moe_layers", 0)
+    STATS.setdefault("moe_calls", 0)
+
+    def patched_pw(self, layer):
+        if orig_pw is not None:
+            orig_pw(self, layer)
+        if select is not None and not select(layer):
+            STATS["native_layers"] += 1
+            return None
+        w13 = getattr(layer.w13_weight, "data", layer.w13_weight)
+        w2 = getattr(layer.w2_weight, "data", layer.w2_weight)
+        n_e = w13.shape[0]
+        gus, dns = [], []
+        for e in range(n_e):
+            if fmt == "mxfp4":
+                s13 = getattr(layer.w13_weight_scale, "data", layer.w13_weight_scale)
+                s2 = getattr(layer.w2_weight_scale, "data", layer.w2_weight_scale)
+                gate, up = ck.split_interleaved_gate_up(ck.mxfp4_to_bf16(w13[e], s13[e]))
+                gus.append(torch.cat([gate, up], 0))
+                dns.append(ck.mxfp4_to_bf16(w2[e], s2[e]))
+            else:
+                gus.append(w13[e].to(torch.bfloat16))
+                dns.append(w2[e].to(torch.bfloat16))
+        layer._qb_moe = SparseMoE(gus, dns, topk=1, act=act, fixed_capacity=fixed_capacity)
+        STATS["moe_layers"] += 1
+        return None
+
+    def patched_apply(self, layer, x, topk_weights, topk_ids, *args, **kw):
+        moe = getattr(layer, "_qb_moe", None)
+        if moe is None:
+            return orig_apply(self, layer, x, topk_weights, topk_ids, *args, **kw)
+        STATS["moe_calls"] += 1
+        moe.topk = topk_ids.shape[1]
+        y = moe.forward(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), topk_ids, topk_weights)
+        return y.to(x.dtype)
+
+    method_cls.process_weights_after_loading = patched_pw
+    method_cls.apply = patched_apply
+
+    def restore():
+        if orig_pw is None:
+            del method_cls.process_weights_after_loading
+        else:
+            method_cls.process_weights_after_loading = orig_pw
+        method_cls.apply = orig_apply
+
+    return restore

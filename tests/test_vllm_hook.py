@@ -93,3 +93,50 @@ def test_hook_runs_the_gpu_modules(mode):
         assert y.shape == (2, 70, 512)
     finally:
         restore()
+
+
+class FakeMoEMethod:
+    """The two methods of a serving engine's fused-MoE method."""
+
+    def process_weights_after_loading(self, layer):
+        layer.seen = True
+
+    def apply(self, layer, x, topk_weights, topk_ids, shared_experts=None, shared_experts_input=None):
+        raise AssertionError("the engine's own MoE path must not run for a packed layer")
+
+
+@pytest.mark.gpu
+def test_moe_method_hook_from_mxfp4_expert_tensors():
+    """install_moe on a stand-in method class: gpt-oss-style MXFP4 expert tensors (interleaved gate / up rows, e8m0 per 32)
+    are dequantised, pruned and packed once; apply() equals a SparseMoE built by hand from the dequantised weights."""
+    import quadbit_b200 as qb
+    from oracle import fakequant as fq
+    torch.manual_seed(9)
+    E, H, I, T, topk = 4, 256, 128, 40, 2
+
+    class Layer:
+        pass
+
+    layer = Layer()
+    layer.w13_weight = torch.randint(0, 256, (E, 2 * I, H // 2), dtype=torch.int32).to(torch.uint8).cuda()
+    layer.w13_weight_scale = torch.randint(118, 124, (E, 2 * I, H // 32), dtype=torch.int32).to(torch.uint8).cuda()
+    layer.w2_weight = torch.randint(0, 256, (E, H, I // 2), dtype=torch.int32).to(torch.uint8).cuda()
+    layer.w2_weight_scale = torch.randint(118, 124, (E, H, I // 32), dtype=torch.int32).to(torch.uint8).cuda()
+    restore = vllm_hook.install_moe(FakeMoEMethod, fmt="mxfp4", act="gptoss")
+    try:
+        m = FakeMoEMethod()
+        m.process_weights_after_loading(layer)
+        assert layer.seen and isinstance(layer._qb_moe, qb.SparseMoE)
+        x = torch.randn(T, H).cuda().bfloat16()
+        idx, w = fq.route_topk(torch.randn(T, E), topk)
+        y = m.apply(layer, x, w.cuda(), idx.cuda())
+    finally:
+        restore()
+    gus, dns = [], []
+    for e in range(E):
+        w13 = fq.mxfp4_dequant(layer.w13_weight[e].cpu(), layer.w13_weight_scale[e].cpu())
+        gus.append(torch.cat([w13[0::2], w13[1::2]], 0).cuda())
+        dns.append(fq.mxfp4_dequant(layer.w2_weight[e].cpu(), layer.w2_weight_scale[e].cpu()).cuda())
+    ref = qb.SparseMoE(gus, dns, topk, act="gptoss").forward(x, idx.cuda(), w.cuda())
+    assert y.shape == (T, H) and torch.equal(y, ref)
+    assert FakeMoEMethod.apply is not None and vllm_hook.STATS["moe_calls"] >= 1
