@@ -175,7 +175,9 @@ long long qb_meta_native_bytes(int out, int K);
  * eblk != NULL); out_mode 0: bf16 C[out][tok], 1: bf16 C[tok][out], 2: fp32 raw accumulators
  * C[out][tok] (globals ignored), 3: bf16 C[tok][out] = (acc*gA*gB + bias[expert][f]) * row_w[t].
  * splits > 1 splits K across CTAs through the fp32 workspace Cf[tok][out]. bn = token tile
- * (16..256, 0 = auto). Asynchronous on `stream`; qb_status() reports device-side errors. */
+ * (16..256, 0 = auto). In grouped mode eblk[b] is the expert of token block b (128 rows); a negative entry marks
+ * an unused block of a fixed-capacity routing: it is skipped and its output rows are left unwritten.
+ * Asynchronous on `stream`; qb_status() reports device-side errors. */
 int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
             const void* gB, void* C, void* Cf, const void* eblk, const void* bias, const void* row_w, int a_rows, int out,
             int tok, int K, int sparse, int out_mode, int splits, int bn, void* stream);
