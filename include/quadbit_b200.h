@@ -140,6 +140,13 @@ int dense_nvfp4_mm(const void* A, const void* B, const void* SFA, const void* SF
  * single-level recipe. sf_ref and/or sf_atoms receive the scales (either may be NULL). */
 int qb_quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,
                     void* stream);
+/* Fixed-capacity MoE routing in one launch (the reference builds it with torch ops: route_fixed_cap,
+ * harness/qb_vllm_plugin/qb_sm120_plugin.py:1271-1315): assign int64 [n] expert id of every routed slot (outside [0, e):
+ * not routed), r_cap >= n + 127*e and a multiple of 128. Writes src int64 [r_cap] (slot of every padded row, -1 =
+ * padding), pos int64 [n] (padded row of every slot, or -1) and eblk int32 [r_cap/128] (expert of every 128-row block,
+ * -1 = unused capacity, which qb_gemm skips). Expert segments are padded to 128 rows and packed in expert order; the
+ * row order inside a segment is not deterministic. No host read, graph-capturable. */
+int qb_moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, void* stream);
 /* The gather of routed MoE rows fused into their quantiser (the reference gathers with torch indexing and then
  * calls quantize_act_nvfp4_2lvl, harness/fused_moe.py:437-442, harness/qb_vllm_plugin/qb_sm120_plugin.py:2430-2441):
  * output row r = quantised x[src[r]], x bf16 [.][H] zero-padded to K (H % 8 == 0, H <= K), src int64 [rows],

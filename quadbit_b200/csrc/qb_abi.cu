@@ -356,6 +356,9 @@ int sparse_moe_gu_swiglu(const void* A, const void* B, const void* scaleA, const
     if (!rc && rows > 0) rc = qb::swiglu_quant_ex(cgu, Hwords, scaleH, nullptr, nullptr, rows, Ih, 1, act, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);
 }
+int qb_moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, void* stream) {
+    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream);
+}
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream) {
     int rc = qb::moe_route(assign, const_cast<void*>(poff), counter, src, N, E, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);

@@ -84,6 +84,59 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
     return (int)cudaGetLastError();
 }
 
+// Fixed-capacity routing in one launch of one CTA: histogram of the expert ids in shared memory, padded prefix,
+// then every routed slot takes the next free row of its expert's segment. Outputs: src[r_cap] (routed slot of every
+// padded row, -1 = padding), pos[n] (padded row of every slot, -1 for a slot without a valid expert), eblk[r_cap/128]
+// (expert of every 128-row block, -1 = unused capacity). The order of the rows inside an expert's segment follows
+// the atomics and may differ from run to run; rows are computed independently, so the layer's output does not.
+// Replaces the sort-based torch routing (harness/qb_vllm_plugin/qb_sm120_plugin.py:1271-1315) for graph capture.
+__global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap,
+                                                                long long* __restrict__ src, long long* __restrict__ pos,
+                                                                int* __restrict__ eblk) {
+    extern __shared__ int sm[];
+    int* counts = sm;
+    int* poff = sm + e;
+    int* cursor = sm + 2 * e;
+    __shared__ int total;
+    for (int i = threadIdx.x; i < e; i += blockDim.x) { counts[i] = 0; cursor[i] = 0; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const long long ex = assign[i];
+        if (ex >= 0 && ex < e) atomicAdd(&counts[(int)ex], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0;
+        for (int x = 0; x < e; x++) { poff[x] = off; off += (counts[x] + 127) / 128 * 128; }
+        total = off;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < r_cap; i += blockDim.x) src[i] = -1;
+    for (int b = total / 128 + threadIdx.x; b < r_cap / 128; b += blockDim.x) eblk[b] = -1;
+    for (int x = threadIdx.x; x < e; x += blockDim.x) {
+        const int b0 = poff[x] / 128, b1 = b0 + (counts[x] + 127) / 128;
+        for (int b = b0; b < b1; b++) eblk[b] = x;
+    }
+    __syncthreads();          // the -1 fill of src is complete (same CTA) before slots are written
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const long long ex = assign[i];
+        long long dst = -1;
+        if (ex >= 0 && ex < e) {
+            dst = poff[(int)ex] + atomicAdd(&cursor[(int)ex], 1);
+            src[dst] = i;
+        }
+        pos[i] = dst;
+    }
+}
+
+int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st) {
+    if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % 128 || (long long)r_cap < (long long)n + (long long)e * 127) return QB_ERR_ARG;
+    if (!assign || !src || !pos || !eblk) return QB_ERR_ARG;
+    moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
+                                                                         (long long*)pos, (int*)eblk);
+    return (int)cudaGetLastError();
+}
+
 int moe_route(const void* assign, void* poff, void* counter, void* src, int n, int e, cudaStream_t st) {
     if (n < 0 || e <= 0 || !poff || !counter) return QB_ERR_ARG;
     int rc = (int)cudaMemsetAsync(counter, 0, (size_t)e * sizeof(int), st);

@@ -109,6 +109,21 @@ def build_routing_fixed(assign: torch.Tensor, e: int):
     return src, eblk.contiguous(), r_cap, pos
 
 
+def route_fixed_kernel(lib, assign: torch.Tensor, e: int):
+    """`build_routing_fixed` as one kernel launch (qb_moe_route_fixed): same segments, capacity and expert-block table;
+    the order of the rows inside an expert's segment follows the kernel's atomics."""
+    dev = assign.device
+    n = assign.numel()
+    r_cap = fixed_capacity(n, e)
+    assign = assign.long().contiguous()
+    src = torch.empty((r_cap,), dtype=torch.long, device=dev)
+    pos = torch.empty((n,), dtype=torch.long, device=dev)
+    eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
+    check(lib.qb_moe_route_fixed(assign.data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, e, r_cap, _stream()),
+          "qb_moe_route_fixed")
+    return src, eblk, r_cap, pos
+
+
 def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None):
     """Quantise routed rows and run the grouped GEMM: [r_pad, mpe] bf16 (token-major);
     with bias / row_w the epilogue computes (acc + bias[expert]) * row_w[row]."""
@@ -192,7 +207,7 @@ class SparseMoE:
         lib = self.lib
         dev = rows_in.device
         if self.fixed_capacity:
-            src, eblk, r_pad, pos = build_routing_fixed(assign.long(), self.e1 - self.e0)
+            src, eblk, r_pad, pos = route_fixed_kernel(lib, assign, self.e1 - self.e0)
         else:
             src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
         if row_of is not None:

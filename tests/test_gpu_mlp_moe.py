@@ -280,3 +280,24 @@ def test_moe_fixed_capacity_routing_equals_exact_and_captures_in_a_graph():
         torch.cuda.synchronize()
         assert torch.equal(out, exact.forward(x2, idx2.cuda(), w2.cuda()))
         assert exact.lib.qb_status(0) == 0
+
+
+def test_route_fixed_kernel_matches_torch_routing_up_to_row_order():
+    import quadbit_b200 as qb
+    import quadbit_b200.moe as qmoe
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(29)
+    for n, e in ((1, 1), (300, 8), (5000, 128), (40000, 64)):
+        assign = torch.randint(0, e, (n,), device="cuda")
+        if e > 4:
+            assign[assign == 3] = 2                                  # an expert without rows
+        src, eblk, r_cap, pos = qmoe.route_fixed_kernel(lib, assign, e)
+        tsrc, teblk, tcap, tpos = qmoe.build_routing_fixed(assign, e)
+        assert r_cap == tcap and torch.equal(eblk, teblk)
+        # padding in the same rows (segment tails), every slot placed exactly once, in a block of its own expert
+        assert torch.equal(src < 0, tsrc < 0)
+        valid = src >= 0
+        assert torch.equal(torch.sort(src[valid]).values, torch.arange(n, device="cuda"))
+        assert torch.equal(pos[src[valid]], torch.nonzero(valid).squeeze(1))
+        assert torch.equal(assign[src[valid]].int(), eblk[torch.nonzero(valid).squeeze(1) // 128])
+        assert int(valid.sum()) == n and lib.qb_status(0) == 0
