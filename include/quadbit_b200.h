@@ -147,6 +147,11 @@ int qb_quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, v
  * -1 = unused capacity, which qb_gemm skips). Expert segments are padded to 128 rows and packed in expert order; the
  * row order inside a segment is not deterministic. No host read, graph-capturable. */
 int qb_moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, void* stream);
+/* Same, with the per-row bookkeeping of a top-k layer done in the same launch: src holds slot / div (div = top-k gives the
+ * token row of every padded row), rw fp32 [r_cap] = w_in[slot] for routed rows and 0 for padding (w_in fp32 [n], both or
+ * neither), inverse int32 [n] = pos as moe_combine_topk reads it (may be NULL). */
+int qb_moe_route_fixed_ex(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, int div, const void* w_in,
+                          void* rw, void* inverse, void* stream);
 /* The gather of routed MoE rows fused into their quantiser (the reference gathers with torch indexing and then
  * calls quantize_act_nvfp4_2lvl, harness/fused_moe.py:437-442, harness/qb_vllm_plugin/qb_sm120_plugin.py:2430-2441):
  * output row r = quantised x[src[r]], x bf16 [.][H] zero-padded to K (H % 8 == 0, H <= K), src int64 [rows],

@@ -39,6 +39,7 @@ _SIGS = {
     # native
     "qb_quantize_act": ([P] * 5 + [I] * 3 + [P], I),
     "qb_moe_route_fixed": ([P] * 4 + [I] * 3 + [P], I),
+    "qb_moe_route_fixed_ex": ([P] * 4 + [I] * 4 + [P] * 4, I),
     "qb_gather_quantize_act": ([P] * 6 + [I] * 4 + [P], I),
     "qb_swiglu_quant_act": ([P] * 6 + [I] * 4 + [P], I),
     "qb_compress_2to4": ([P, I] + [P] * 6 + [I] * 2 + [P], I),

@@ -359,6 +359,10 @@ int sparse_moe_gu_swiglu(const void* A, const void* B, const void* scaleA, const
 int qb_moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, void* stream) {
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream);
 }
+int qb_moe_route_fixed_ex(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, int div, const void* w_in,
+                          void* rw, void* inverse, void* stream) {
+    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse);
+}
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream) {
     int rc = qb::moe_route(assign, const_cast<void*>(poff), counter, src, N, E, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);

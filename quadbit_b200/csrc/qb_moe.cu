@@ -92,7 +92,10 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
 // Replaces the sort-based torch routing (harness/qb_vllm_plugin/qb_sm120_plugin.py:1271-1315) for graph capture.
 __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap,
                                                                 long long* __restrict__ src, long long* __restrict__ pos,
-                                                                int* __restrict__ eblk) {
+                                                                int* __restrict__ eblk, int div, const float* __restrict__ w_in,
+                                                                float* __restrict__ rw, int* __restrict__ inverse) {
+    // optional extras that the layer would otherwise do with a dozen small kernels: src holds slot / div (the token row
+    // of a slot when div = top-k), rw[row] = w_in[slot] (0 for padding rows), inverse[slot] = row as int32
     extern __shared__ int sm[];
     int* counts = sm;
     int* poff = sm + e;
@@ -111,7 +114,10 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
         total = off;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < r_cap; i += blockDim.x) src[i] = -1;
+    for (int i = threadIdx.x; i < r_cap; i += blockDim.x) {
+        src[i] = -1;
+        if (rw) rw[i] = 0.f;
+    }
     for (int b = total / 128 + threadIdx.x; b < r_cap / 128; b += blockDim.x) eblk[b] = -1;
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
         const int b0 = poff[x] / 128, b1 = b0 + (counts[x] + 127) / 128;
@@ -123,17 +129,20 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
         long long dst = -1;
         if (ex >= 0 && ex < e) {
             dst = poff[(int)ex] + atomicAdd(&cursor[(int)ex], 1);
-            src[dst] = i;
+            src[dst] = i / div;
+            if (rw) rw[dst] = w_in[i];
         }
         pos[i] = dst;
+        if (inverse) inverse[i] = (int)dst;
     }
 }
 
-int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st) {
+int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div,
+                    const void* w_in, void* rw, void* inverse) {
     if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % 128 || (long long)r_cap < (long long)n + (long long)e * 127) return QB_ERR_ARG;
-    if (!assign || !src || !pos || !eblk) return QB_ERR_ARG;
+    if (!assign || !src || !pos || !eblk || div < 1 || ((rw != nullptr) != (w_in != nullptr))) return QB_ERR_ARG;
     moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
-                                                                         (long long*)pos, (int*)eblk);
+                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse);
     return (int)cudaGetLastError();
 }
 

@@ -197,22 +197,13 @@ class SparseMoE:
         # from the device; `forward` then issues no host read and can be captured in a CUDA graph
         self.fixed_capacity = fixed_capacity
 
-    def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
-        """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
-        returns (d [r_pad, mpe_dn] bf16 = expert(row) * weight, pos [n] = padded row of routed row i).
-        Routed row i is rows_in[i], or rows_in[row_of[i]] when row_of is given (tokens are then not copied
-        once per routed slot before the gather).
-        Four kernels between the routing and the result: gather + pad + quantise, grouped gate/up GEMM,
-        SwiGLU + quantise, grouped down GEMM with the routing weight in its epilogue."""
+    def _run_padded(self, x: torch.Tensor, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor) -> torch.Tensor:
+        """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
+        padding), eblk = expert of every 128-row block, rw [r_pad] = routing weight of every row. Returns
+        d [r_pad, mpe_dn] bf16 = expert(row) * weight."""
         lib = self.lib
-        dev = rows_in.device
-        if self.fixed_capacity:
-            src, eblk, r_pad, pos = route_fixed_kernel(lib, assign, self.e1 - self.e0)
-        else:
-            src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
-        if row_of is not None:
-            src = torch.where(src >= 0, row_of[src.clamp_min(0)], src)
-        x = rows_in.to(torch.bfloat16).contiguous()
+        dev = x.device
+        x = x.to(torch.bfloat16).contiguous()
         if self.H % 8:                       # the fused gather reads 16-byte chunks
             x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
         Bb = torch.empty((r_pad, self.Hp // 2), dtype=torch.uint8, device=dev)
@@ -226,10 +217,24 @@ class SparseMoE:
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
+        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)  # [r_pad, mpe_dn]
+
+    def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
+        """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
+        returns (d [r_pad, mpe_dn] bf16 = expert(row) * weight, pos [n] = padded row of routed row i).
+        Routed row i is rows_in[i], or rows_in[row_of[i]] when row_of is given (tokens are then not copied
+        once per routed slot before the gather). Four kernels between the routing and the result: gather + pad +
+        quantise, grouped gate/up GEMM, SwiGLU + quantise, grouped down GEMM with the routing weight in its epilogue."""
+        dev = rows_in.device
+        if self.fixed_capacity:
+            src, eblk, r_pad, pos = route_fixed_kernel(self.lib, assign, self.e1 - self.e0)
+        else:
+            src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
+        if row_of is not None:
+            src = torch.where(src >= 0, row_of[src.clamp_min(0)], src)
         rw = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
         rw[pos] = row_w.float()
-        d = seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)  # [r_pad, mpe_dn]
-        return d, pos
+        return self._run_padded(rows_in, src, eblk, r_pad, rw), pos
 
     def expert_rows(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
         """rows_in [n,H] bf16, assign [n] local expert ids, row_w [n] routing weights -> [n,H] bf16 =
@@ -247,6 +252,21 @@ class SparseMoE:
         T = x.shape[0]
         dev = x.device
         assign_g = topk_idx.reshape(-1).long()
+        if self.e0 == 0 and self.e1 == self.E_total and self.fixed_capacity:
+            # routing, token row of every padded row, routing weight of every row and the combine table in one launch
+            n, e = assign_g.numel(), self.E
+            r_cap = fixed_capacity(n, e)
+            src = torch.empty((r_cap,), dtype=torch.long, device=dev)
+            pos = torch.empty((n,), dtype=torch.long, device=dev)
+            eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
+            rw = torch.empty((r_cap,), dtype=torch.float32, device=dev)
+            inverse = torch.empty((n,), dtype=torch.int32, device=dev)
+            w_in = topk_w.reshape(-1).float().contiguous()
+            check(self.lib.qb_moe_route_fixed_ex(assign_g.contiguous().data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, e,
+                                                 r_cap, self.topk, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(), _stream()),
+                  "qb_moe_route_fixed_ex")
+            d = self._run_padded(x, src, eblk, r_cap, rw)
+            return combine(self.lib, d, inverse, T, self.H, self.topk)
         if self.e0 == 0 and self.e1 == self.E_total:
             slots = torch.arange(assign_g.numel(), device=dev)
         else:
