@@ -215,7 +215,8 @@ int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sf
 long long qb_gemm_decode_ws_bytes(int out, int tok, int K);
 /* Split-K GEMM without a caller workspace (no counterpart in the reference library, whose
  * split-K entry sparse_down_sk_2lvl always takes the workspace Cf from the caller). Same
- * operands and meaning as qb_gemm with splits > 1, out_mode 0 or 1, plain (not grouped) mode;
+ * operands and meaning as qb_gemm with splits > 1, out_mode 0 or 1, plain (not grouped) mode
+ * (`sparse` carries the same two bits: bit 0 = 2:4-sparse A, bit 1 = A in the tiled layout);
  * the fp32 partial sums go to an 8 MiB array built into the library instead of a Cf argument.
  * It exists for callers that cannot allocate: an engine whose memory pool already owns the
  * whole GPU, code inside CUDA-graph capture, a hook that only receives inputs and outputs.
@@ -260,14 +261,6 @@ int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void
  * u64[SM count] of SM clock cycles; status_word: i32, non-zero if a bounded wait expired.
  * bn = 128 or 256. Time it with events around the call. */
 int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, void* status_word, void* stream);
-/* Barrier round-trip probe (no reference counterpart): one cluster of two CTAs plays ping-pong
- * `iters` times; cycles_out[0] = leader's cycles, cycles_out[1] = iters. mode 0: two warps of one
- * CTA through shared::cta mbarriers; 1: the two CTAs through mbarrier.arrive.shared::cluster;
- * 2: tcgen05.commit multicast to the peer and a remote arrive back; 3: mode 0 with the warp-wide
- * wait; 4: one thread, arrive then a try_wait that succeeds at once; 5: the same on two barriers with
- * the two try_waits back to back; 6+n: mode 0 with n (<= 14) more warps polling an incomplete barrier.
- * Bounded waits; asynchronous on `stream`. */
-int qb_sync_probe(int mode, int iters, void* cycles_out, void* status_word, void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

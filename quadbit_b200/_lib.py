@@ -67,7 +67,6 @@ _SIGS = {
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),
-    "qb_sync_probe": ([I] * 2 + [P] * 3, I),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),
     "qb_version": ([], ctypes.c_char_p),
@@ -82,8 +81,7 @@ def load(flavour: str = "sparse_fp4") -> ctypes.CDLL:
     if flavour not in build_so.FLAVOURS:
         raise ValueError(f"unknown library flavour {flavour!r}")
     path = build_so.so_path(flavour)
-    if not path.exists():
-        build_so.build()
+    build_so.build()                 # recompiles only what is older than its sources
     lib = ctypes.CDLL(str(path))
     for name, (argtypes, restype) in _SIGS.items():
         fn = getattr(lib, name)          # AttributeError if the symbol is missing

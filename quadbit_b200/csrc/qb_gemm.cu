@@ -34,7 +34,6 @@
 // and frees its TMEM.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "qb_common.cuh"
@@ -43,7 +42,6 @@
 namespace qb {
 
 __device__ int g_status = 0;
-unsigned long long* g_prof_ptr = nullptr;   // experiment counters (QB_PROF)
 
 struct KParams {
     const uint8_t* sfa;
@@ -63,9 +61,7 @@ struct KParams {
     int b_box_bytes;                     // bytes one B TMA box delivers (box rows * 128)
     int out_mode;
     int a_tiled;                         // A in 128-row x 256-K tiles: TMA row coordinate = tile * 128, column 0
-    int dbg;                             // experiment switches (QB_DEBUG_SKIP), 0 in normal use
     int* sk_counters;                    // split-K finished in the kernel: 4 arrival counters per output tile (zero between calls)
-    unsigned long long* prof;            // optional per-CTA cycle counters [grid][8]
 };
 
 template <bool SPARSE, int BN>
@@ -101,18 +97,7 @@ struct Cfg {
     static constexpr int CH = (BN % 32 == 0) ? 32 : 8;   // epilogue column chunk
 };
 
-// cycle counters of the roles are compiled in only for experiments: the reads sit on the serial paths
-#ifdef QB_PROFILE
-#define QB_CLK() clock64()
-#else
-#define QB_CLK() 0ll
-#endif
-#ifndef QB_BACKOFF
-#define QB_BACKOFF 64
-#endif
-#ifndef QB_BACKOFF_SF
-#define QB_BACKOFF_SF 32
-#endif
+constexpr uint32_t QB_BACKOFF = 64, QB_BACKOFF_SF = 32;   // ns a role with slack sleeps between polls
 constexpr int NPROD1 = 4;                      // producer warps of the single-CTA kernel (warp 0 and warps 6..8)
 constexpr int NTHREADS1 = (6 + NPROD1 - 1 + 4) * 32;  // + four scale-factor warps (9..12)
 enum { SITE_PROD = 1, SITE_MMA_FULL = 2, SITE_MMA_ACC = 3, SITE_EPI = 4, SITE_SF1 = 9 };
@@ -223,7 +208,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
-            long long c_wait_acc = 0, c_wait_full = 0, c_issue = 0, c_t0 = QB_CLK();
             for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
                 if (tile_skipped(tile)) continue;
                 const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
@@ -231,14 +215,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int n0 = n * BN;
                 const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
                 const uint32_t sfb_coloff = (uint32_t)((n0 & 127) >> 5);
-                long long ca = QB_CLK();
                 if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-                c_wait_acc += QB_CLK() - ca;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 bool ok = true;
                 for (int kb = kb0; kb < kb1;) {
-                    long long cf = QB_CLK();
                     // two K blocks per poll when the later one is ready too (a poll costs 100-200 cycles
                     // even on a completed barrier; the scale-factor warps signal in ring order)
                     int s1 = stage + 1;
@@ -249,8 +230,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         nb = 1;
                         if (!mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL)) { ok = false; break; }
                     }
-                    long long cg = QB_CLK();
-                    c_wait_full += cg - cf;
                     tc_fence_after();
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
@@ -272,15 +251,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     kb += nb;
                     stage += nb;
                     if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
-                    c_issue += QB_CLK() - cg;
                 }
                 if (!ok) break;
                 tc_commit(accf_bar(acc));
                 if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
-            }
-            if (p.prof) {
-                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_full; o[3] = c_issue;
             }
         }
         __syncwarp();
@@ -348,7 +322,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
         int acc = 0;
         uint32_t acc_phase = 0;
-        long long c_wait_accf = 0, c_epi = 0;
         for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
             if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
@@ -366,17 +339,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int col = n0 + c * C::CH + (lane % C::CH);
                 gbv[c] = (p.gB && col < p.tok) ? __ldg(p.gB + col) : 1.f;
             }
-            long long cw = QB_CLK();
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
-            long long cx = QB_CLK();
-            c_wait_accf += cx - cw;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += C::CH) {
-#ifdef QB_EXPERIMENT
-                if (p.dbg & 8) break;
-#endif
                 uint32_t r[C::CH];
                 if constexpr (C::CH == 32) tc_ld_32x32(t_acc + c0, r); else tc_ld_32x8(t_acc + c0, r);
                 tc_wait_ld();
@@ -490,10 +457,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     }
                 }
             }
-            c_epi += QB_CLK() - cx;
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (p.prof && warp == 2 && lane == 0) { p.prof[(size_t)blockIdx.x * 8 + 5] = c_wait_accf; p.prof[(size_t)blockIdx.x * 8 + 6] = c_epi; }
     }
 
     // teardown: every role has left its loop (all waits are bounded)
@@ -592,8 +557,6 @@ struct KParams2 {
     const __nv_bfloat16* bias;           // out_mode 3: per-expert bias [E][out_f] (may be null)
     const float* row_w;                  // out_mode 3: weight of every routed row [tok] (may be null)
     int bias_ld;                         // features per bias row (the rest of out_f is padding without bias)
-    int dbg;
-    unsigned long long* prof;
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
@@ -686,7 +649,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const bool isA = warp == W_PROD_A;
         int stage = 0;
         uint32_t phase = 0;
-        long long c_pw = 0, c_pb = 0, c_pn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile / p.num_m2;
@@ -694,7 +656,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
-                const long long q0 = QB_CLK();
                 int s1 = stage + 1;
                 uint32_t ph1 = phase;
                 if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
@@ -703,17 +664,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     nb = 1;
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD)) { ok = false; break; }
                 }
-                const long long q1 = QB_CLK();
-                c_pw += q1 - q0; c_pn += nb;
                 if (lane == 0) {
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
                         const uint32_t fb = mapa_shared(full_bar(s), 0);
-#ifdef QB_EXPERIMENT
-                        const bool skip = (p.dbg & (isA ? 4 : 2)) && kb >= 2;
-#else
                         constexpr bool skip = false;
-#endif
                         if (rank == 0) mbar_expect_tx(full_bar(s), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
                         if (!skip) {
                             if (isA) {
@@ -728,11 +683,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 kb += nb;
                 stage += nb;
                 if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
-                c_pb += QB_CLK() - q1;
             }
             if (!ok) break;
         }
-        if (p.prof && isA && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[0] = c_pw; o[1] = c_pb; o[2] = c_pn; }
     } else {
         // ------------------------------------------------------------ sideband producers (both CTAs)
         const bool isW = warp == W_SIDE_W;               // weight side: scale factors of A and metadata
@@ -756,9 +709,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     for (int u = 0; u < nb; u++) {
                         const int j = u ? j1 : slot;
                         const uint32_t fb = sbf_bar(j);
-#ifdef QB_EXPERIMENT
-                        if ((p.dbg & 32) && kb >= 2) { mbar_expect_tx(fb, 0u); } else
-#endif
                         if (isW) {
                             mbar_expect_tx(fb, (uint32_t)(C::SFA_BYTES + C::META_BYTES));
                             tma_load_2d(sideSFA(j), &tmSFA, fb, 0, rb_a * atoms_per_rb + (kb + u) * C::MMAS);
@@ -788,19 +738,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
             int stage = 0, acc = 0, tslot = 0;
             uint32_t phase = 0, acc_phase = 0;
-            long long c_wait_acc = 0, c_wait_sf = 0, c_issue = 0, c_iters = 0, c_t0 = QB_CLK();
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
                 if (tile_skipped(tile)) continue;
                 // a 192-token tile starts 0 or 64 rows into a 128-row scale-factor atom: 0 or 2 columns in
                 const uint32_t sfb_coloff = (uint32_t)((((tile / p.num_m2) * BN) & 127) >> 5);
-                long long ca = QB_CLK();
                 if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
-                c_wait_acc += QB_CLK() - ca;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 bool ok = true;
                 for (int kb = 0; kb < p.kblocks;) {
-                    long long cf = QB_CLK();
                     int s1 = stage + 1;
                     uint32_t ph1 = phase;
                     if (s1 == C::STAGES) { s1 = 0; ph1 ^= 1; }
@@ -814,8 +760,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             (!mbar_wait_thread(full_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_FULL) ||
                              !mbar_wait_thread(sfr_bar(stage), phase, &abort_flag, &g_status, SITE_MMA_SF))) { ok = false; break; }
                     }
-                    long long cg = QB_CLK();
-                    c_wait_sf += cg - cf; c_iters++;
                     tc_fence_after();
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
@@ -824,9 +768,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         if (++tslot == C::NSLOT) tslot = 0;
 #pragma unroll
                         for (int i = 0; i < C::MMAS; i++) {
-#ifdef QB_EXPERIMENT
-                            if ((p.dbg & 8) && kb >= 2) break;
-#endif
                             const uint64_t adesc = make_smem_desc(stageA(s) + i * 32, SPARSE ? 512 : 1024, 16, SPARSE ? 4 : 2);
                             const uint64_t bdesc = make_smem_desc(stageB(s) + i * C::B_KSTEP, 1024, 16, 2);
                             const uint32_t accum = (kb + u > 0 || i > 0) ? 1u : 0u;
@@ -840,15 +781,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     kb += nb;
                     stage += nb;
                     if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
-                    c_issue += QB_CLK() - cg;
                 }
                 if (!ok) break;
                 tc_commit_pair(accf_bar(acc), 3);
                 if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
-            }
-            if (p.prof) {
-                unsigned long long* o = p.prof + (size_t)blockIdx.x * 8;
-                o[0] = QB_CLK() - c_t0; o[1] = c_wait_acc; o[2] = c_wait_sf; o[3] = c_issue; o[4] = c_iters;
             }
         }
         __syncwarp();
@@ -862,12 +798,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // completed, which the empty barrier of THAT block's stage signals (completions come in ring order).
         int stage = 0, slot = 0, tslot = 0;
         uint32_t sphase = 0, it = 0;
-        long long c_sw = 0, c_sb = 0, c_sn = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
-                const long long f0 = QB_CLK();
                 int s1 = stage + 1, j1 = slot + 1, t1 = tslot + 1;
                 uint32_t sph1 = sphase;
                 if (s1 == C::STAGES) s1 = 0;
@@ -889,12 +823,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     if (it >= (uint32_t)C::NSLOT &&
                         !mbar_wait(done_bar(it - C::NSLOT), done_par(it - C::NSLOT), &abort_flag, &g_status, SITE_SF_SLOT)) { ok = false; break; }
                 }
-                const long long f1 = QB_CLK();
-                c_sw += f1 - f0; c_sn += nb;
                 tc_fence_after();
-#ifdef QB_EXPERIMENT
-                if (!((p.dbg & 1) && kb >= 2))
-#endif
                 {
                     for (int u = 0; u < nb; u++) {
                         const int j = u ? j1 : slot, ts = u ? t1 : tslot;
@@ -951,11 +880,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 if (slot >= C::NSB) { slot -= C::NSB; sphase ^= 1; }
                 tslot += nb;
                 if (tslot >= C::NSLOT) tslot -= C::NSLOT;
-                c_sb += QB_CLK() - f1;
             }
             if (!ok) break;
         }
-        if (p.prof && warp == 4 && lane == 0) { unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8; o[3] = c_sw; o[4] = c_sb; o[5] = c_sn; }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own rows)
         // Eight warps: warps 8-11 drain the first half of the tile's columns, warps 12-15 the second half;
@@ -968,7 +895,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t stg_s = epi0 + ew * (16 * C::EPI_PITCH);
         int acc = 0;
         uint32_t acc_phase = 0;
-        long long c_wait_accf = 0, c_epi = 0, c_ph1 = 0;
         constexpr int HCOLS = BN / 2;          // columns per warp
         constexpr int NCH = HCOLS / 16;        // chunks of 16 columns
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -998,22 +924,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(bh[e]); bias8[2 * e] = f.x; bias8[2 * e + 1] = f.y; }
             }
-            long long cw = QB_CLK();
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
-            long long cx = QB_CLK();
-            c_wait_accf += cx - cw;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN + half * HCOLS) + ((uint32_t)(q * 32) << 16);
             const uint32_t acce_leader = mapa_shared(acce_bar(acc), 0);
-#ifdef QB_EXPERIMENT
-            if (p.dbg & 16) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(acce_leader);
-                if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
-                continue;
-            }
-#endif
             uint32_t ra[16], rb[16];
             if constexpr (C::ACC_STAGES != 1) tc_ld_32x16(t_acc, ra);
             auto emit = [&](const uint32_t (&r)[16], int c) {
@@ -1082,7 +996,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acce_leader);
-                c_ph1 += QB_CLK() - cx;
 #pragma unroll
                 for (int c = 0; c < NCH; c++) emit(held[c], c);
                 acc_phase ^= 1;
@@ -1105,12 +1018,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
             if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
-            c_epi += QB_CLK() - cx;
-        }
-        if (p.prof && warp == 8 && lane == 0) {
-            unsigned long long* o = p.prof + 4096 + (size_t)blockIdx.x * 8;
-            o[6] = c_wait_accf; o[7] = c_epi;
-            p.prof[6144 + blockIdx.x] = c_ph1;
         }
     }
 
@@ -1281,12 +1188,6 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
-    kp.prof = g_prof_ptr;
-#ifdef QB_EXPERIMENT
-    { const char* e = getenv("QB_DEBUG_SKIP"); kp.dbg = e ? atoi(e) : 0; }
-#else
-    kp.dbg = 0;
-#endif
     nvfp4_gemm_pair_kernel<SPARSE, BN><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
     return (int)cudaGetLastError();
 }
@@ -1346,16 +1247,6 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     kp.splits = splits;
     kp.sfb_rowblocks = (a.tok + 127) / 128;
     kp.out_mode = a.out_mode;
-    {
-        static int dbg = -1;
-#ifdef QB_EXPERIMENT   // load / copy / epilogue skipping switches used while locating bottlenecks; results are wrong when set
-        if (dbg < 0) { const char* e = getenv("QB_DEBUG_SKIP"); dbg = e ? atoi(e) : 0; }
-#else
-        dbg = 0;
-#endif
-        kp.dbg = dbg;
-        kp.prof = g_prof_ptr;
-    }
     const bool slab = splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
     if (!slab) kp.sk_counters = nullptr;
     if (splits > 1 && !slab) {
@@ -1403,14 +1294,8 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
     }
     *splits = best_s;
     *bn = b;
-#ifdef QB_EXPERIMENT
-    { const char* e = getenv("QB_DECODE_SPLITS"); if (e && atoi(e) > 0 && atoi(e) <= kb) *splits = atoi(e); }
-#endif
 }
 
-#ifdef QB_EXPERIMENT
-extern "C" void qb_debug_set_prof(void* p) { g_prof_ptr = (unsigned long long*)p; }
-#endif
 
 int read_status(cudaStream_t st) {
     int rc = (int)cudaStreamSynchronize(st);

@@ -51,6 +51,7 @@ int qb_gemm_splitk_static(const void* A, const void* B, const void* sfa, const v
                           int splits, void* stream) {
     if (out <= 0 || tok < 0 || K <= 0) return QB_ERR_ARG;
     if (out_mode != 0 && out_mode != 1) return QB_ERR_ARG;
+    if (sparse < 0 || sparse > 3) return QB_ERR_ARG;   // bit 0: 2:4-sparse A, bit 1: A in the tiled layout (as qb_gemm)
     if ((long long)out * (long long)tok > (long long)QB_STATIC_WS_FLOATS) return QB_ERR_TOO_LARGE;
     if (tok == 0) return QB_OK;
     float* ws = nullptr;
@@ -59,7 +60,7 @@ int qb_gemm_splitk_static(const void* A, const void* B, const void* sfa, const v
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
     g.C = C; g.Cf = ws; g.eblk = nullptr; g.bias = nullptr; g.row_w = nullptr;
-    g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode;
+    g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse & 1; g.a_tiled = (sparse >> 1) & 1; g.out_mode = out_mode;
     g.splits = splits < 2 ? 2 : splits;   // always the workspace path; it is zeroed on the stream first
     g.bn = 0;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);

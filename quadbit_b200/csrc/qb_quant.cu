@@ -428,78 +428,103 @@ int norm_quant(const void* x, const void* res, const void* wt, void* hout, void*
     return (int)cudaGetLastError();
 }
 
-// SwiGLU quantisers over the reference's feature-major operands g, u [hidden][batch] (two separate
-// GEMM outputs): fused_swiglu_quant / fused_swiglu_quant_2lvl, cuda/sparse_fp4_lib.cu:794-894.
-// One thread per (token, 32-feature block), tokens fastest so the strided reads coalesce.
-template <bool TWO_LEVEL, bool AMAX_ONLY, int BLOCK = 32>
-__global__ void swiglu_fm_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u, uint32_t* __restrict__ Hwords,
-                                 uint8_t* __restrict__ scaleH, float* __restrict__ gH, int batch, int hidden) {
-    constexpr int P = 128 / BLOCK;     // scales per 128 features
-    const int hb = hidden / BLOCK;
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (long long)batch * hb) return;
-    const int hblock = (int)(t / batch), b = (int)(t % batch);
-    const long long base = (long long)(hblock * BLOCK) * batch + b;
-    float val[BLOCK], amax = 0.f;
+// SwiGLU quantisers over feature-major operands gate, up [hidden][batch] (the two halves of a feature-major
+// gate/up GEMM output): the compatibility symbols fused_swiglu_quant / fused_swiglu_quant_2lvl
+// (cuda/sparse_fp4_lib.cu:794-894) and swiglu_nvfp4 (cuda/dense_nvfp4_fast_lib.cu:258-278).
+// grid = (token pairs, scale blocks). A thread owns one scale block of TWO adjacent tokens: every load is one
+// 32-bit word holding feature f of both tokens, so a warp reads 128 contiguous bytes per feature row, and the
+// block's BLOCK features are walked once with both tokens' running maxima in registers. PASS 0 only records the
+// per-token maximum of |h| (two-level, first pass), PASS 1 quantises.
+template <bool TWO_LEVEL, int PASS, int BLOCK>
+__global__ void __launch_bounds__(128) swiglu_fmajor_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                                             uint32_t* __restrict__ Hwords, uint8_t* __restrict__ scaleH,
+                                                             float* __restrict__ tok_amax, int batch, int hidden) {
+    constexpr int PER128 = 128 / BLOCK;
+    const int t0 = 2 * (blockIdx.x * blockDim.x + threadIdx.x);     // first of this thread's two tokens
+    const int sblk = blockIdx.y;                                     // scale block along the hidden axis
+    if (t0 >= batch) return;
+    const bool pair = t0 + 1 < batch && (batch & 1) == 0;            // word loads need an even row pitch
+    const int ntok = (t0 + 1 < batch) ? 2 : 1;
+    float hv[2][BLOCK];
+    float mx[2] = {0.f, 0.f};
+    const size_t row0 = (size_t)sblk * BLOCK;
 #pragma unroll
-    for (int i = 0; i < BLOCK; i++) {
-        float gv = __bfloat162float(g[base + (long long)i * batch]);
-        float uv = __bfloat162float(u[base + (long long)i * batch]);
-        float h = (gv / (1.f + __expf(-gv))) * uv;
-        val[i] = h;
-        amax = fmaxf(amax, fabsf(h));
+    for (int f = 0; f < BLOCK; f++) {
+        const size_t at = (row0 + f) * (size_t)batch + t0;
+        float2 g2, u2;
+        if (pair) {
+            g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + at));
+            u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(up + at));
+        } else {
+            g2.x = __bfloat162float(gate[at]); u2.x = __bfloat162float(up[at]);
+            g2.y = ntok == 2 ? __bfloat162float(gate[at + 1]) : 0.f;
+            u2.y = ntok == 2 ? __bfloat162float(up[at + 1]) : 0.f;
+        }
+        hv[0][f] = swiglu_h<1>(g2.x, u2.x);
+        hv[1][f] = swiglu_h<1>(g2.y, u2.y);
+        mx[0] = fmaxf(mx[0], fabsf(hv[0][f]));
+        mx[1] = fmaxf(mx[1], fabsf(hv[1][f]));
     }
-    if (AMAX_ONLY) { atomicMax(reinterpret_cast<int*>(gH) + b, __float_as_int(amax)); return; }
-    const float gl = TWO_LEVEL ? fmaxf(__fdiv_rn(gH[b], 2688.f), 1e-30f) : 1.f;
-    const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(amax, 6.f), gl)) : enc_ue4m3(__fdiv_rn(amax, 6.f));
-    scaleH[((long long)(hblock / P) * batch + b) * P + (hblock % P)] = (uint8_t)code;
-    const float sg = fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f);
-    uint32_t w[BLOCK / 8];
-    const Fp4Divider dv(sg);
 #pragma unroll
-    for (int i = 0; i < BLOCK / 8; i++) {
-        float f8[8];
+    for (int k = 0; k < 2; k++) {
+        if (k >= ntok) break;
+        const int t = t0 + k;
+        if (PASS == 0) {      // |h| >= 0, so the integer order of the bit patterns is the float order
+            atomicMax(reinterpret_cast<int*>(tok_amax) + t, __float_as_int(mx[k]));
+            continue;
+        }
+        const float glob = TWO_LEVEL ? fmaxf(__fdiv_rn(tok_amax[t], 2688.f), 1e-30f) : 1.f;
+        const float want = __fdiv_rn(mx[k], 6.f);
+        const uint32_t code = enc_ue4m3(TWO_LEVEL ? __fdiv_rn(want, glob) : want);
+        scaleH[((size_t)(sblk / PER128) * batch + t) * PER128 + (sblk % PER128)] = (uint8_t)code;
+        const float dq = TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), glob) : dec_ue4m3(code);
+        const Fp4Divider dv(fmaxf(dq, 1e-30f));
+        uint32_t* dst = Hwords + (size_t)t * (hidden / 8) + (size_t)sblk * (BLOCK / 8);
 #pragma unroll
-        for (int e = 0; e < 8; e++) f8[e] = val[8 * i + e];
-        w[i] = dv.pack8(f8);
+        for (int w = 0; w < BLOCK / 8; w++) {
+            float f8[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f8[e] = hv[k][8 * w + e];
+            dst[w] = dv.pack8(f8);
+        }
     }
-    uint32_t* dst = Hwords + (long long)b * (hidden / 8) + hblock * (BLOCK / 8);
-    if constexpr (BLOCK == 32) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-    else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
 }
-__global__ void swiglu_fm_finalize(float* gH, int batch) {
-    int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < batch) gH[b] = fmaxf(__fdiv_rn(gH[b], 2688.f), 1e-30f);
+__global__ void amax_to_global_kernel(float* tok_amax, int batch) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < batch) tok_amax[t] = fmaxf(__fdiv_rn(tok_amax[t], 2688.f), 1e-30f);
+}
+
+template <bool TWO_LEVEL, int PASS, int BLOCK>
+static void launch_swiglu_fmajor(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st) {
+    const dim3 grid((unsigned)((batch + 255) / 256), (unsigned)(hidden / BLOCK));
+    swiglu_fmajor_kernel<TWO_LEVEL, PASS, BLOCK><<<grid, 128, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb,
+                                                                     (uint8_t*)scaleH, (float*)gH, batch, hidden);
 }
 
 int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st) {
     if (batch < 0 || hidden <= 0 || hidden % 128) return QB_ERR_ARG;
     if (batch == 0) return QB_OK;
-    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 15)) return QB_ERR_ARG;
-    long long total = (long long)batch * (hidden / 32);
-    int blocks = (int)((total + 255) / 256);
+    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 3) || ((uintptr_t)g & 3) || ((uintptr_t)u & 3)) return QB_ERR_ARG;
     if (gH) {
+        // two-level: per-token maximum first (gH holds the raw maximum while the second pass reads it), then the codes,
+        // then gH becomes the global the GEMM multiplies by
         int rc = (int)cudaMemsetAsync(gH, 0, (size_t)batch * sizeof(float), st);
         if (rc) return rc;
-        swiglu_fm_kernel<true, true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, nullptr, nullptr, (float*)gH, batch, hidden);
-        // quantise against amax/2688 (read raw amax), then turn gH into the global the GEMM multiplies by
-        swiglu_fm_kernel<true, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, (float*)gH, batch, hidden);
-        swiglu_fm_finalize<<<(batch + 255) / 256, 256, 0, st>>>((float*)gH, batch);
+        launch_swiglu_fmajor<true, 0, 32>(g, u, nullptr, nullptr, gH, batch, hidden, st);
+        launch_swiglu_fmajor<true, 1, 32>(g, u, Hb, scaleH, gH, batch, hidden, st);
+        amax_to_global_kernel<<<(batch + 255) / 256, 256, 0, st>>>((float*)gH, batch);
     } else {
-        swiglu_fm_kernel<false, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, nullptr, batch, hidden);
+        launch_swiglu_fmajor<false, 1, 32>(g, u, Hb, scaleH, nullptr, batch, hidden, st);
     }
     return (int)cudaGetLastError();
 }
 
-// per-16 single-level flavour of the feature-major SwiGLU quantiser: swiglu_nvfp4,
-// cuda/dense_nvfp4_fast_lib.cu:258-278
+// per-16 single-level flavour (swiglu_nvfp4 of the dense library)
 int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st) {
     if (batch < 0 || hidden <= 0 || hidden % 128) return QB_ERR_ARG;
     if (batch == 0) return QB_OK;
-    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 7)) return QB_ERR_ARG;
-    long long total = (long long)batch * (hidden / 16);
-    int blocks = (int)((total + 255) / 256);
-    swiglu_fm_kernel<false, false, 16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (uint32_t*)Hb, (uint8_t*)scaleH, nullptr, batch, hidden);
+    if (!g || !u || !Hb || !scaleH || ((uintptr_t)Hb & 3) || ((uintptr_t)g & 3) || ((uintptr_t)u & 3)) return QB_ERR_ARG;
+    launch_swiglu_fmajor<false, 1, 16>(g, u, Hb, scaleH, nullptr, batch, hidden, st);
     return (int)cudaGetLastError();
 }
 

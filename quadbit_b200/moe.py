@@ -171,7 +171,8 @@ class SparseMoE:
     [e0, e1) for expert parallelism; slots of other experts are skipped."""
 
     def __init__(self, w_gate_up: list[torch.Tensor], w_down: list[torch.Tensor], topk: int, act: str = "silu",
-                 expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None, fixed_capacity: bool = False):
+                 expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None, fixed_capacity: bool = False,
+                 b_gate_up: list[torch.Tensor] | None = None, b_down: list[torch.Tensor] | None = None):
         self.lib = lib = load("sparse_fp4")
         self.E = len(w_gate_up)
         self.topk, self.act = topk, act
@@ -191,6 +192,21 @@ class SparseMoE:
             gus.append(pack(lib, g))
             dns.append(pack(lib, d))
         self.w_gu, self.w_dn = stack(gus), stack(dns)
+        # optional expert biases (gpt-oss: w13_bias [2I] gate then up, w2_bias [H]); applied in the epilogues of the
+        # grouped GEMMs: gate/up + bias before SwiGLU, (down + bias) * routing weight (the reference's gu_bias / bias,
+        # harness/qb_vllm_plugin/qb_sm120_plugin.py:2192-2225,2397-2400). Rows are padded like the weights.
+        self.b_gu = self.b_dn = None
+        if b_gate_up is not None:
+            b = w_gate_up[0].new_zeros((self.E, self.mpe_gu), dtype=torch.bfloat16)
+            for e, be in enumerate(b_gate_up):
+                b[e, : self.I] = be[: self.I].to(torch.bfloat16)
+                b[e, self.Ip: self.Ip + self.I] = be[self.I:].to(torch.bfloat16)
+            self.b_gu = b.contiguous()
+        if b_down is not None:
+            b = w_down[0].new_zeros((self.E, self.mpe_dn), dtype=torch.bfloat16)
+            for e, be in enumerate(b_down):
+                b[e, : self.H] = be.to(torch.bfloat16)
+            self.b_dn = b.contiguous()
         self.e0, self.e1 = expert_range if expert_range else (0, self.E)
         self.E_total = n_experts_total or self.E
         # fixed_capacity: route into the worst-case number of padded rows instead of reading the exact count back
@@ -211,13 +227,13 @@ class SparseMoE:
         gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
                                          x.shape[1], 32, _stream()), "qb_gather_quantize_act")
-        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk)          # [r_pad, 2*Ip]: gate | up
+        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
-        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, row_w=rw)  # [r_pad, mpe_dn]
+        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw)  # [r_pad, mpe_dn]
 
     def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
         """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
@@ -232,9 +248,10 @@ class SparseMoE:
             src, eblk, r_pad, pos = build_routing(assign.long(), self.e1 - self.e0, with_pos=True)
         if row_of is not None:
             src = torch.where(src >= 0, row_of[src.clamp_min(0)], src)
-        rw = torch.zeros((r_pad,), dtype=torch.float32, device=dev)
-        rw[pos] = row_w.float()
-        return self._run_padded(rows_in, src, eblk, r_pad, rw), pos
+        rw = torch.zeros((r_pad + 1,), dtype=torch.float32, device=dev)
+        # an expert id outside the layer's range has no row (pos = -1, fixed-capacity routing): its weight goes to a spare slot
+        rw[torch.where(pos >= 0, pos, torch.full_like(pos, r_pad))] = row_w.float()
+        return self._run_padded(rows_in, src, eblk, r_pad, rw[:r_pad]), pos
 
     def expert_rows(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor) -> torch.Tensor:
         """rows_in [n,H] bf16, assign [n] local expert ids, row_w [n] routing weights -> [n,H] bf16 =
@@ -244,7 +261,8 @@ class SparseMoE:
         if rows_in.shape[0] == 0:
             return torch.zeros((0, self.H), dtype=torch.bfloat16, device=rows_in.device)
         d, pos = self._expert_rows_padded(rows_in, assign, row_w)
-        return torch.index_select(d[:, : self.H], 0, pos)          # one pass: gathers the H valid features of each row
+        out = torch.index_select(d[:, : self.H], 0, pos.clamp_min(0))          # one pass: gathers the H valid features of each row
+        return out * (pos >= 0).unsqueeze(1).to(out.dtype)                    # an id outside the expert range contributes nothing
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
         """x [T,H] bf16, topk_idx [T,topk] global expert ids, topk_w [T,topk] -> [T,H] bf16
@@ -299,119 +317,3 @@ def load_sparse_moe():
                            seg_bw=lambda x, w, mpe, in_f, eblk, row_w, bias=None: seg_gemm(lib, x, w, mpe, in_f, eblk, bias, row_w),
                            build_routing=build_routing, combine=lambda d, inv, t, H, topk: combine(lib, d, inv, t, H, topk),
                            pad_w=pad_w, swiglu=swiglu)
-
-
-def load_sparse_moe_reference_layout():
-    """The plugin's `_load_sparse_moe()` namespace with its own signatures and the reference's tensor layouts
-    (harness/qb_vllm_plugin/qb_sm120_plugin.py:1124-1368): every helper binds the reference-named entry point of the
-    library, so code written against that namespace runs unchanged. `pack` is the CUDA compressor emitting the
-    reference layout (Ac, meta [K/128,out,2] i32, scaleA [K/128,out,4] u8, gA); `load_sparse_moe()` above is the
-    native-layout variant the modules of this package use."""
-    lib = load("sparse_fp4")
-
-    def _st():
-        return torch.cuda.current_stream().cuda_stream
-
-    def pack_ref(w, colnorm=None):
-        w = w.contiguous()
-        if w.dtype not in (torch.float32, torch.bfloat16):
-            w = w.float()
-        out_f, in_f = w.shape
-        dev = w.device
-        ks = in_f // 128
-        ac = torch.empty((out_f, in_f // 4), dtype=torch.uint8, device=dev)
-        meta = torch.empty((ks, out_f, 2), dtype=torch.int32, device=dev)
-        scale_a = torch.empty((ks, out_f, 4), dtype=torch.uint8, device=dev)
-        ga = torch.empty((out_f,), dtype=torch.float32, device=dev)
-        if colnorm is not None:
-            colnorm = colnorm.to(device=dev, dtype=torch.float32).contiguous()
-            if not bool((colnorm != 0).any()):
-                colnorm = None
-        check(lib.qb_compress_2to4_colnorm(w.data_ptr(), 1 if w.dtype == torch.bfloat16 else 0, _ptr(colnorm), ac.data_ptr(),
-                                           meta.data_ptr(), 0, scale_a.data_ptr(), 0, ga.data_ptr(), out_f, in_f, _st()),
-              "qb_compress_2to4_colnorm")
-        return ac, meta, scale_a, ga
-
-    def stack_ref(packs):
-        return (torch.cat([p[0] for p in packs], 0).contiguous(), torch.cat([p[1] for p in packs], 1).contiguous(),
-                torch.cat([p[2] for p in packs], 1).contiguous(), torch.cat([p[3] for p in packs], 0).contiguous())
-
-    def quant_into(x, bb, sb, gb):
-        r, in_f = x.shape
-        lib.quantize_act_nvfp4_2lvl_s(x.data_ptr(), bb.data_ptr(), sb.data_ptr(), gb.data_ptr(), r, in_f, _st())
-
-    def quant_act_ref(x):
-        r, in_f = x.shape
-        x = x.to(torch.bfloat16).contiguous()
-        bb = torch.empty((r, in_f // 2), dtype=torch.uint8, device=x.device)
-        sb = torch.empty((in_f // 128, r, 4), dtype=torch.uint8, device=x.device)
-        gb = torch.empty((r,), dtype=torch.float32, device=x.device)
-        quant_into(x, bb, sb, gb)
-        return bb, sb, gb
-
-    def seg_into(w, bb, sb, gb, c, mpe, in_f, eblk):
-        ac, meta, scale_a, ga = w
-        check(lib.sparse_moe_mm_2lvl(ac.data_ptr(), bb.data_ptr(), scale_a.data_ptr(), sb.data_ptr(), meta.data_ptr(), c.data_ptr(),
-                                     ac.shape[0], mpe, c.shape[0], in_f, ga.data_ptr(), gb.data_ptr(), eblk.data_ptr(), 1, _st()),
-              "sparse_moe_mm_2lvl")
-
-    def seg_gemm_ref(x, w, mpe, in_f, eblk):
-        bb, sb, gb = quant_act_ref(x)
-        c = torch.empty((x.shape[0], mpe), dtype=torch.bfloat16, device=x.device)
-        seg_into(w, bb, sb, gb, c, mpe, in_f, eblk)
-        return c
-
-    def route_fixed_cap(assign, e, cap, valid=None):
-        """Every expert gets `cap` rows (a multiple of BN); slots beyond an expert's capacity are dropped and counted."""
-        assign = assign.to(torch.long)
-        r = assign.shape[0]
-        dev = assign.device
-        a, nb = (assign, e) if valid is None else (torch.where(valid, assign.clamp(0, e - 1), torch.full_like(assign, e)), e + 1)
-        order = torch.argsort(a, stable=True)
-        sa = a[order]
-        counts = torch.zeros(nb, dtype=torch.long, device=dev).scatter_add_(0, a, torch.ones_like(a))
-        within = torch.arange(r, device=dev) - (torch.cumsum(counts, 0) - counts)[sa]
-        keep = (within < cap) & (sa < e)
-        dest = torch.where(keep, sa * cap + within, torch.full_like(sa, e * cap))
-        src = torch.full((e * cap + 1,), -1, dtype=torch.long, device=dev)
-        src.scatter_(0, dest, order)
-        eblk = (torch.arange(e * cap // BN, device=dev) // (cap // BN)).to(torch.int32)
-        dropped = (r if valid is None else valid.sum()) - keep.sum()
-        return src[: e * cap], eblk, dropped
-
-    def gu_swiglu(w, bb, sb, gb, hw, sh, mpe, r, in_f, eblk, gu_bias, ih, act=0):
-        ac, meta, sa, ga = w
-        check(lib.sparse_moe_gu_swiglu(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), ac.shape[0], mpe, r,
-                                       in_f, ga.data_ptr(), gb.data_ptr(), eblk.data_ptr(), _ptr(gu_bias), hw.data_ptr(), sh.data_ptr(),
-                                       ih, act, _st()), "sparse_moe_gu_swiglu")
-
-    def down_scatter(w, bb, sb, out, mpe, r, in_f, eblk, sc_tok, sc_w, bias, hout):
-        ac, meta, sa, ga = w
-        check(lib.sparse_moe_mm_2lvl_scatter(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), ac.shape[0],
-                                             mpe, r, in_f, ga.data_ptr(), 0, eblk.data_ptr(), sc_tok.data_ptr(), sc_w.data_ptr(),
-                                             _ptr(bias), out.data_ptr(), hout, _st()), "sparse_moe_mm_2lvl_scatter")
-
-    def seg_bw(w, bb, sb, c, mpe, r, in_f, eblk, sc_w, bias, hout):
-        ac, meta, sa, ga = w
-        check(lib.sparse_moe_mm_2lvl_bw(ac.data_ptr(), bb.data_ptr(), sa.data_ptr(), sb.data_ptr(), meta.data_ptr(), c.data_ptr(),
-                                        ac.shape[0], mpe, r, in_f, ga.data_ptr(), 0, eblk.data_ptr(), sc_w.data_ptr(), _ptr(bias), hout,
-                                        _st()), "sparse_moe_mm_2lvl_bw")
-
-    def route(assign, e, rmax):
-        ai = assign.to(torch.int32)
-        counts = torch.zeros(e, dtype=torch.long, device=ai.device).scatter_add_(0, assign.long(), torch.ones_like(assign, dtype=torch.long))
-        padc = ((counts + BN - 1) // BN) * BN
-        ends = torch.cumsum(padc, 0)
-        poff = (ends - padc).to(torch.int64)
-        src = torch.full((rmax,), -1, dtype=torch.int32, device=ai.device)
-        counter = torch.empty(e, dtype=torch.int32, device=ai.device)
-        check(lib.moe_route(ai.data_ptr(), poff.data_ptr(), counter.data_ptr(), src.data_ptr(), ai.numel(), e, _st()), "moe_route")
-        eblk = torch.bucketize(torch.arange(rmax // BN, device=ai.device) * BN, ends, right=True).clamp_max_(e - 1).to(torch.int32)
-        return src.long(), eblk, rmax
-
-    def combine_ref(dbuf, inverse, y, t, hout, topk, mpe):
-        check(lib.moe_combine_topk(dbuf.data_ptr(), inverse.data_ptr(), y.data_ptr(), t, hout, topk, mpe, _st()), "moe_combine_topk")
-
-    return SimpleNamespace(lib=lib, pack=pack_ref, stack=stack_ref, quant_act=quant_act_ref, seg_gemm=seg_gemm_ref,
-                           build_routing=build_routing, quant_into=quant_into, seg_into=seg_into, route_fixed_cap=route_fixed_cap,
-                           gu_swiglu=gu_swiglu, down_scatter=down_scatter, seg_bw=seg_bw, combine=combine_ref, route=route)

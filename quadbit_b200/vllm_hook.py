@@ -83,7 +83,7 @@ def install_vllm(mode: str = "sparse", method: str = "vllm.model_executor.layers
 
 
 def install_moe(method_cls, fmt: str = "mxfp4", act: str = "gptoss", fixed_capacity: bool = True,
-                select: Callable[[object], bool] | None = None):
+                select: Callable[[object], bool] | None = None, release: bool = False):
     """Patch a fused-MoE method class the way the reference patches `GptOssMxfp4MoEMethod`
     (harness/qb_vllm_plugin/qb_sm120_plugin.py:2086-2498): after the engine's own
     `process_weights_after_loading(layer)`, the expert tensors of the layer are dequantised on the GPU, pruned 2:4 and
@@ -92,8 +92,11 @@ def install_moe(method_cls, fmt: str = "mxfp4", act: str = "gptoss", fixed_capac
     fmt "mxfp4": `layer.w13_weight` [E, 2I, H/2] u8 + `layer.w13_weight_scale` [E, 2I, H/32] e8m0 with gate / up rows
     interleaved, `layer.w2_weight` [E, H, I/2] + `layer.w2_weight_scale` [E, H, I/32] (gpt-oss checkpoints);
     fmt "bf16": `layer.w13_weight` [E, 2I, H] (gate rows then up rows) and `layer.w2_weight` [E, H, I] as they are.
-    Biases are not taken here (the reference keeps them for its own epilogues); layers that `select` rejects stay on
-    the engine's path. Returns a function that restores the original methods."""
+    `layer.w13_bias` [E, 2I] (same row order as the weight) and `layer.w2_bias` [E, H], when present, are applied in the
+    epilogues of the grouped GEMMs as the reference does (qb_sm120_plugin.py:2192-2225, 2397-2400). An `expert_map`
+    (expert-parallel engines passing local ids) is not supported and raises. The engine's expert tensors are released
+    after packing when `release=True`. Layers that `select` rejects stay on the engine's path. Returns a function that
+    restores the original methods."""
     if fmt not in ("mxfp4", "bf16"):
         raise ValueError(f"fmt {fmt!r}")
     from . import checkpoint as ck
@@ -123,7 +126,24 @@ def install_moe(method_cls, fmt: str = "mxfp4", act: str = "gptoss", fixed_capac
             else:
                 gus.append(w13[e].to(torch.bfloat16))
                 dns.append(w2[e].to(torch.bfloat16))
-        layer._qb_moe = SparseMoE(gus, dns, topk=1, act=act, fixed_capacity=fixed_capacity)
+        b13 = getattr(layer, "w13_bias", None)
+        b2 = getattr(layer, "w2_bias", None)
+        bgu = bdn = None
+        if b13 is not None:
+            b13 = getattr(b13, "data", b13)
+            if fmt == "mxfp4":      # interleaved like the weight rows: gate = even, up = odd
+                bgu = [torch.cat([b13[e][0::2], b13[e][1::2]], 0) for e in range(n_e)]
+            else:
+                bgu = [b13[e] for e in range(n_e)]
+        if b2 is not None:
+            b2 = getattr(b2, "data", b2)
+            bdn = [b2[e] for e in range(n_e)]
+        layer._qb_moe = SparseMoE(gus, dns, topk=1, act=act, fixed_capacity=fixed_capacity, b_gate_up=bgu, b_down=bdn)
+        if release:                  # the packed copy replaces the engine's expert tensors
+            for name in ("w13_weight", "w2_weight", "w13_weight_scale", "w2_weight_scale"):
+                t = getattr(layer, name, None)
+                if t is not None:
+                    getattr(t, "data", t).set_(torch.empty(0, dtype=getattr(t, "data", t).dtype, device=getattr(t, "data", t).device))
         STATS["moe_layers"] += 1
         return None
 
@@ -131,6 +151,9 @@ def install_moe(method_cls, fmt: str = "mxfp4", act: str = "gptoss", fixed_capac
         moe = getattr(layer, "_qb_moe", None)
         if moe is None:
             return orig_apply(self, layer, x, topk_weights, topk_ids, *args, **kw)
+        if kw.get("expert_map") is not None:
+            raise NotImplementedError("install_moe: expert_map (engine-side expert parallelism) is not supported; "
+                                      "use SparseMoE(expert_range=...) / forward_ep")
         STATS["moe_calls"] += 1
         moe.topk = topk_ids.shape[1]
         y = moe.forward(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16), topk_ids, topk_weights)

@@ -3,6 +3,7 @@ import pytest
 import torch
 
 from oracle import fakequant as fq
+from tests._parity import assert_codes_explained
 
 pytestmark = pytest.mark.gpu
 
@@ -18,8 +19,8 @@ def rel(y, ref):
 
 
 def test_swiglu_quant_kernel_against_oracle():
-    """One-pass SwiGLU + two-level quantiser: globals exact up to exp rounding, codes match the
-    oracle on all but boundary cases, dequantised values at the FP4 quantisation floor."""
+    """One-pass SwiGLU + two-level quantiser: globals exact up to exp rounding, every code that differs from
+    the oracle's sits within 1e-5 of a rounding boundary, dequantised values at the FP4 quantisation floor."""
     import quadbit_b200 as qb
     lib = qb.load("sparse_fp4")
     torch.manual_seed(0)
@@ -35,9 +36,7 @@ def test_swiglu_quant_kernel_against_oracle():
         assert lib.qb_swiglu_quant(d.data_ptr(), Hb.data_ptr(), sref.data_ptr(), atoms.data_ptr(), gH.data_ptr(), tok, I, S()) == 0
         assert lib.qb_status(S()) == 0
         deq = fq.unpack_act(Hb.cpu(), sref.cpu(), gH.cpu(), 32)
-        eB, eS, eg = fq.act_quant_2lvl(h, 32, round_bf16=False)
-        torch.testing.assert_close(gH.cpu(), eg, rtol=1e-5, atol=0)
-        assert (Hb.cpu() != eB).float().mean().item() < 5e-3      # exp() rounding moves a few boundary cases
+        assert_codes_explained(h, Hb, sref, gH, 32)                # exp() rounding moves boundary cases only
         assert ((deq - h).norm() / h.norm()).item() < 0.12           # FP4 floor
         mask = fq.sf_to_atoms(torch.ones(I // 128, tok, 4, dtype=torch.uint8)).view(-1).bool()
         assert torch.equal(atoms.cpu()[mask], fq.sf_to_atoms(sref.cpu()).view(-1)[mask])

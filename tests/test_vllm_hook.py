@@ -140,3 +140,54 @@ def test_moe_method_hook_from_mxfp4_expert_tensors():
     ref = qb.SparseMoE(gus, dns, topk, act="gptoss").forward(x, idx.cuda(), w.cuda())
     assert y.shape == (T, H) and torch.equal(y, ref)
     assert FakeMoEMethod.apply is not None and vllm_hook.STATS["moe_calls"] >= 1
+
+
+@pytest.mark.gpu
+def test_moe_method_hook_applies_expert_biases():
+    """gpt-oss layers carry w13_bias / w2_bias: the hook hands them to the epilogues of the grouped GEMMs
+    (gate/up + bias before the clamped SwiGLU, (down + bias) * routing weight). Checked against a per-expert loop of the
+    CPU oracle with the same bf16 roundings."""
+    from oracle import fakequant as fq
+    torch.manual_seed(10)
+    E, H, I, T, topk = 4, 256, 128, 48, 2
+
+    class Layer:
+        pass
+
+    layer = Layer()
+    w13 = (torch.randn(E, 2 * I, H) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I) * 0.05).to(torch.bfloat16)
+    b13 = (torch.randn(E, 2 * I) * 0.3).to(torch.bfloat16)
+    b2 = (torch.randn(E, H) * 0.3).to(torch.bfloat16)
+    layer.w13_weight, layer.w2_weight, layer.w13_bias, layer.w2_bias = w13.cuda(), w2.cuda(), b13.cuda(), b2.cuda()
+    restore = vllm_hook.install_moe(FakeMoEMethod, fmt="bf16", act="gptoss")
+    try:
+        m = FakeMoEMethod()
+        m.process_weights_after_loading(layer)
+        x = torch.randn(T, H).to(torch.bfloat16)
+        idx, w = fq.route_topk(torch.randn(T, E), topk)
+        y = m.apply(layer, x.cuda(), w.cuda(), idx.cuda()).float().cpu()
+        with pytest.raises(NotImplementedError):
+            m.apply(layer, x.cuda(), w.cuda(), idx.cuda(), expert_map=torch.arange(E))
+    finally:
+        restore()
+    ref = torch.zeros(T, H)
+    for e in range(E):
+        sel = idx == e
+        toks = torch.nonzero(sel.any(1)).squeeze(1)
+        if toks.numel() == 0:
+            continue
+        gu = (fq.linear_sparse(x[toks].float(), w13[e].float()) + b13[e].float()).to(torch.bfloat16).float()
+        g, u = gu[:, :I].clamp(max=7.0), gu[:, I:].clamp(-7.0, 7.0)
+        h = (g * torch.sigmoid(1.702 * g)) * (u + 1.0)
+        d = F_linear_2lvl(fq, h, w2[e].float())
+        wt = (w * sel)[toks].sum(1, keepdim=True)
+        ref[toks] += ((d + b2[e].float()) * wt).to(torch.bfloat16).float()
+    assert ((y - ref).norm() / ref.norm()).item() < 0.03
+    bias_effect = (b2.float().abs().mean() / ref.abs().mean()).item()
+    assert bias_effect > 0.05           # the biases are large enough that leaving them out would fail the bound above
+
+
+def F_linear_2lvl(fq, h, w):
+    """Down projection of the layer: h is quantised in fp32 (no bf16 rounding) by the SwiGLU quantiser."""
+    return torch.nn.functional.linear(fq.act_dequant_2lvl(h, 32, round_bf16=False), fq.sparse_fp4_dequant_2lvl(w))
