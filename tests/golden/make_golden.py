@@ -154,6 +154,11 @@ def main(ref_root: str) -> None:
                ck_mx=mx["_mxfp4_dequant"](cw, cs8).view(torch.int16).numpy(),
                ck_nv=nv["_dequant_nvfp4_expert"](cw, cs4.view(torch.float8_e4m3fn), torch.tensor(s2)).view(torch.int16).numpy())
 
+    # single-level per-32 activation fake-quant, the torch twin of the legacy quant_act kernel ("kernel-MATCHED STE":
+    # bf16 pre-round + no-denormal scale encode, harness/probe_ste_kernel.py:98-103); reuses x, draws nothing
+    ps = lift(ref / "harness/probe_ste_kernel.py", tables | {"q_fp4", "enc_ue4m3_t", "act_fp4_dequant_km"})
+    out["ax_deq32_1lvl"] = ps["act_fp4_dequant_km"](x).numpy()
+
     dst = Path(__file__).with_name("ref_fakequant.npz")
     np.savez_compressed(dst, **out)
     print(f"wrote {dst} ({dst.stat().st_size/1024:.0f} KiB, {len(out)} arrays)")

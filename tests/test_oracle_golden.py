@@ -72,6 +72,14 @@ def test_act_fake_quant_bit_exact():
         assert torch.equal(fq.unpack_act(Bb, sc, g, blk), t(ref))
 
 
+def test_single_level_act_fake_quant_bit_exact():
+    """act_quant_1lvl (per-32) against the reference's kernel-matched single-level fake-quant
+    (act_fp4_dequant_km, harness/probe_ste_kernel.py:98-103)."""
+    x = t("ax")
+    Bb, sc = fq.act_quant_1lvl(x, 32)
+    assert torch.equal(fq.unpack_act(Bb, sc, None, 32), t("ax_deq32_1lvl"))
+
+
 def test_dense_pack_bit_exact():
     W = t("dw")
     Ab, SFA, gA = fq.nvfp4_pack(W)
