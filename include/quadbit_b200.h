@@ -249,10 +249,11 @@ int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms,
                         int interleaved, int act, void* stream);
 /* fused_mlp_2lvl on native layouts (weights from qb_compress_2to4; sfb_x / sfb_h are scale-atom
  * scratch of qb_sf_atoms_bytes(tok, H | I, 32) bytes; Cf may be NULL or an fp32 [tok][dn_out]
- * workspace for a split-K down projection). Four launches, no synchronisation, no allocation. */
+ * workspace for a split-K down projection; flags bit 0: gu_A / dn_A are in the tiled layout of
+ * qb_tile_weights). Four launches, no synchronisation, no allocation. */
 int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
-                 void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits,
+                 void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits, int flags,
                  void* stream);
 /* Issue-only throughput probe of the block-scaled FP4 MMA (analogue of the reference's
  * cuda/mma_peak.cu): every SM runs `kblocks` K blocks of 256 (dense: 4 MMAs of 128xbnx64,
@@ -261,6 +262,40 @@ int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void
  * u64[SM count] of SM clock cycles; status_word: i32, non-zero if a bounded wait expired.
  * bn = 128 or 256. Time it with events around the call. */
 int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, void* status_word, void* stream);
+/* ---- tensor parallelism over one NVSwitch box (one process per GPU). No counterpart in the reference library: its
+ * one distributed script computes, then calls all_reduce (harness/moe_dist.py:123,161-167).
+ * Peer buffers: qb_peer_alloc = cudaMalloc + zero fill (set-up time only); qb_peer_export writes the 64-byte CUDA IPC
+ * handle of an allocation, which another process of the same box turns into a pointer with qb_peer_open (close with
+ * qb_peer_close before the owner frees). Only plain loads / stores and system-scope flag words touch peer memory. */
+int qb_peer_alloc(void** ptr, long long bytes);
+int qb_peer_free(void* ptr);
+int qb_peer_export(void* ptr, void* handle64);
+int qb_peer_open(const void* handle64, void** ptr);
+int qb_peer_close(void* ptr);
+/* One-thread kernels on `stream`: signal writes `value` into word my_rank of each of the n flag arrays (after a
+ * system-scope fence; stream order puts it after the kernels it announces); wait returns when all n words of `flags`
+ * are >= value, or after 20 s with a status code (qb_peer_status). */
+int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, void* stream);
+int qb_peer_wait(const void* flags, int n, int value, void* stream);
+int qb_peer_status(void* stream);
+/* Row-parallel GEMM fused with the reduce-scatter of its partial result (replaces "GEMM, then all_reduce"): operands as
+ * qb_gemm (this rank's K slice), token-major bf16 output; token row t is stored by the epilogue into
+ * peer_out[t / tok_per_rank] + (t % tok_per_rank) * out (a pointer into the owner's memory, already offset to this rank's
+ * slot), and the last CTA to finish writes flag_value into word `rank` of every peer_flags[r]. done_counter: one int on
+ * this device, zero between calls. Prefill sizes only: out % 256 == 0, tok >= 128, tok_per_rank % 16 == 0. */
+int qb_gemm_rs(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA, const void* gB,
+               void* const* peer_out, void* const* peer_flags, void* done_counter, int out, int tok, int K, int sparse, int n_ranks,
+               int rank, int tok_per_rank, int flag_value, int bn, void* stream);
+/* Consumer of qb_gemm_rs fused with the next block's input: v = sum_i src_i (fp32, source order; src_i = src0 + i *
+ * src_stride elements, bf16 [tok][H]) + res; hout = bf16(v); y = rmsnorm(v) * wt; two-level NVFP4 quantiser of y.
+ * wait_flags (may be NULL): every CTA first waits until its nsrc words are >= wait_val. fan == 0: outputs go to
+ * Bbytes_v[0] / sf_atoms_v[0] / g_v[0] for the tok local rows. fan > 0: they go to `fan` gathered arrays of tok_total rows
+ * (one per rank, peer pointers) at rows row0 .. row0 + tok: the all-gather of the quantised activations is done by the
+ * stores. sig_n > 0: the last CTA writes sig_val into word sig_rank of every sig_flags[d] (done_counter as above). */
+int qb_reduce_norm_quant(const void* src0, long long src_stride, int nsrc, const void* res, const void* wt, void* hout,
+                         void* const* Bbytes_v, void* const* sf_atoms_v, void* const* g_v, int fan, int row0, int tok_total, int tok,
+                         int H, float eps, int block, const void* wait_flags, int wait_val, void* const* sig_flags, int sig_n,
+                         int sig_rank, int sig_val, void* done_counter, void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

@@ -6,3 +6,5 @@ from .linear import DenseNVLinear, QBSparse, QuadbitLinear, quantize_act  # noqa
 from .mlp import FusedSparseMLP, register_fused_mlp_op  # noqa: F401,E402
 from .moe import SparseMoE, load_sparse_moe  # noqa: F401,E402
 from . import vllm_hook  # noqa: F401,E402
+from .llama import LlamaConfig, LlamaPrefill  # noqa: F401,E402
+from .tp import PeerBuffer, TPContext  # noqa: F401,E402

@@ -59,13 +59,23 @@ _SIGS = {
     "fused_mlp_2lvl": ([P] * 17 + [I] * 5 + [P], I),
     "fused_mlp_2lvl_skdown": ([P] * 18 + [I] * 6 + [P], I),
     "qb_swiglu_quant": ([P] * 5 + [I] * 2 + [P], I),
-    "qb_fused_mlp": ([P] * 18 + [I] * 6 + [P], I),
+    "qb_fused_mlp": ([P] * 18 + [I] * 7 + [P], I),
     "qb_gemm_decode": ([P] * 9 + [I] * 5 + [P], I),
     "qb_tile_weights": ([P] * 2 + [I] * 3 + [P], I),
     "qb_tiled_weight_bytes": ([I] * 3, c_longlong),
     "qb_gemm_decode_ws_bytes": ([I] * 3, c_longlong),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
+    "qb_peer_alloc": ([P, c_longlong], I),
+    "qb_peer_free": ([P], I),
+    "qb_peer_export": ([P, P], I),
+    "qb_peer_open": ([P, P], I),
+    "qb_peer_close": ([P], I),
+    "qb_peer_signal": ([P, I, I, I, P], I),
+    "qb_peer_wait": ([P, I, I, P], I),
+    "qb_peer_status": ([P], I),
+    "qb_gemm_rs": ([P] * 10 + [I] * 9 + [P], I),
+    "qb_reduce_norm_quant": ([P, c_longlong, I] + [P] * 6 + [I] * 5 + [c_float, I, P, I, P, I, I, I, P, P], I),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),

@@ -114,7 +114,7 @@ int finish_sync(int rc, cudaStream_t st) {
 static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA,
                             const void* dn_A, const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x,
                             void* gBx, void* Cgu, void* Hb, void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I,
-                            int gu_out, int dn_out, int splits, cudaStream_t st) {
+                            int gu_out, int dn_out, int splits, cudaStream_t st, int a_tiled = 0) {
     if (tok < 0 || H <= 0 || I <= 0 || gu_out != 2 * I || dn_out <= 0) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     int rc = 0;
@@ -125,7 +125,7 @@ static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa,
     if (rc) return rc;
     qb::GemmArgs g{};
     g.A = gu_A; g.B = Bb; g.sfa = gu_sfa; g.sfb = sfb_x; g.meta = gu_meta; g.gA = (const float*)gu_gA; g.gB = (const float*)gBx;
-    g.C = Cgu; g.a_rows = gu_out; g.out_f = gu_out; g.tok = tok; g.K = H; g.sparse = 1; g.out_mode = 1; g.splits = 1;
+    g.C = Cgu; g.a_rows = gu_out; g.out_f = gu_out; g.tok = tok; g.K = H; g.sparse = 1; g.a_tiled = a_tiled; g.out_mode = 1; g.splits = 1;
     g.bn = 0;
     rc = qb::gemm_nvfp4(g, st);
     if (rc) return rc;
@@ -133,7 +133,7 @@ static int fused_mlp_native(const void* x, const void* gu_A, const void* gu_sfa,
     if (rc) return rc;
     qb::GemmArgs d{};
     d.A = dn_A; d.B = Hb; d.sfa = dn_sfa; d.sfb = sfb_h; d.meta = dn_meta; d.gA = (const float*)dn_gA; d.gB = (const float*)gH;
-    d.C = Cout; d.Cf = (float*)Cf; d.a_rows = dn_out; d.out_f = dn_out; d.tok = tok; d.K = I; d.sparse = 1; d.out_mode = 1;
+    d.C = Cout; d.Cf = (float*)Cf; d.a_rows = dn_out; d.out_f = dn_out; d.tok = tok; d.K = I; d.sparse = 1; d.a_tiled = a_tiled; d.out_mode = 1;
     d.splits = (Cf && splits > 1) ? splits : 1;
     d.bn = 0;
     return qb::gemm_nvfp4(d, st);
@@ -266,9 +266,10 @@ int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms,
 int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
                  void* sfb_h, void* gH, void* Cout, void* Cf, int tok, int H, int I, int gu_out, int dn_out, int splits,
-                 void* stream) {
+                 int flags, void* stream) {
+    if (flags & ~1) return QB_ERR_ARG;
     return fused_mlp_native(x, gu_A, gu_sfa, gu_meta, gu_gA, dn_A, dn_sfa, dn_meta, dn_gA, Bb, sfb_x, gBx, Cgu, Hb, sfb_h, gH, Cout,
-                            Cf, tok, H, I, gu_out, dn_out, splits, (cudaStream_t)stream);
+                            Cf, tok, H, I, gu_out, dn_out, splits, (cudaStream_t)stream, flags & 1);
 }
 int fused_mlp_2lvl(const void* x, const void* gu_Ac, const void* gu_scaleA, const void* gu_meta, const void* gu_gA,
                    const void* dn_Ac, const void* dn_scaleA, const void* dn_meta, const void* dn_gA, void* Bb, void* sBg, void* gBg,

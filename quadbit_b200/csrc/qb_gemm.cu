@@ -557,6 +557,12 @@ struct KParams2 {
     const __nv_bfloat16* bias;           // out_mode 3: per-expert bias [E][out_f] (may be null)
     const float* row_w;                  // out_mode 3: weight of every routed row [tok] (may be null)
     int bias_ld;                         // features per bias row (the rest of out_f is padding without bias)
+    // row-parallel GEMM + reduce-scatter by peer stores (out_mode 1): token row t goes to peer_out[t / tok_per_rank]
+    // at local row t % tok_per_rank; the last CTA publishes peer_val in word peer_rank of every rank's flags
+    int peer_n, peer_rank, tok_per_rank, peer_val;
+    __nv_bfloat16* peer_out[8];
+    int* peer_flags[8];
+    int* peer_done;
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
@@ -571,7 +577,7 @@ template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(640, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                       const __grid_constant__ CUtensorMap tmMETA, const KParams2 p) {
+                       const __grid_constant__ CUtensorMap tmMETA, const __grid_constant__ KParams2 p) {
     using C = Cfg2<SPARSE, BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
@@ -982,7 +988,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         val.z = pack_bf16x2(f[4], f[5]);
                         val.w = pack_bf16x2(f[6], f[7]);
                         const int col = n0 + c0 + trow;
-                        if (col < p.tok) stg_v4(Cp + (size_t)col * p.out_f, val);
+                        if (col < p.tok) {
+                            if (p.peer_n) {
+                                // the partial row goes straight into the memory of the rank that owns the token (a plain
+                                // 16-byte store over NVLink, or a local one for this rank's own range)
+                                const int owner = col / p.tok_per_rank;
+                                stg_v4(p.peer_out[owner] + (size_t)(col - owner * p.tok_per_rank) * p.out_f + (o0 + q * 32 + (lane & 3) * 8), val);
+                            } else {
+                                stg_v4(Cp + (size_t)col * p.out_f, val);
+                            }
+                        }
                     }
                     __syncwarp();
                 }
@@ -1027,6 +1042,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, C::TM_COLS);
+    }
+    if (p.peer_n && threadIdx.x == 0) {
+        // every store of this CTA is ordered before the cluster barrier above; the system-scope fence after it is
+        // cumulative, so when the last CTA of the grid publishes the flag, all partial rows have landed at their owners
+        __threadfence_system();
+        if (atomicAdd(p.peer_done, 1) == (int)gridDim.x - 1) {
+            atomicExch(p.peer_done, 0);
+            __threadfence_system();
+            for (int r = 0; r < p.peer_n; r++)
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flags[r] + p.peer_rank), "r"(p.peer_val) : "memory");
+        }
     }
 }
 
@@ -1185,6 +1211,8 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
     kp.a_tiled = a.a_tiled;
     kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w; kp.bias_ld = a.bias_ld > 0 ? a.bias_ld : a.out_f;
+    kp.peer_n = a.peer_n; kp.peer_rank = a.peer_rank; kp.tok_per_rank = a.tok_per_rank; kp.peer_val = a.peer_val; kp.peer_done = a.peer_done;
+    for (int r = 0; r < 8; r++) { kp.peer_out[r] = (__nv_bfloat16*)a.peer_out[r]; kp.peer_flags[r] = a.peer_flags[r]; }
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
@@ -1196,7 +1224,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     if (a.out_f <= 0 || a.tok < 0 || a.K <= 0 || a.a_rows <= 0) return QB_ERR_ARG;
     if (a.tok == 0) return QB_OK;
     if (a.out_f % 128 || a.K % 128 || a.a_rows % 128) return QB_ERR_ARG;
-    if (!a.A || !a.B || !a.sfa || !a.sfb || !a.C || (a.sparse && !a.meta)) return QB_ERR_ARG;
+    if (!a.A || !a.B || !a.sfa || !a.sfb || (!a.C && !a.peer_n) || (a.sparse && !a.meta)) return QB_ERR_ARG;
     if (((uintptr_t)a.A & 15) || ((uintptr_t)a.B & 15) || ((uintptr_t)a.sfa & 15) || ((uintptr_t)a.sfb & 15) ||
         ((uintptr_t)a.meta & 15) || ((uintptr_t)a.C & 15))
         return QB_ERR_ARG;
@@ -1209,6 +1237,17 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
 
     // CTA-pair kernel: plain bf16 GEMM, enough tokens to fill a 256-wide tile, out % 256 == 0.
     // bn == 512 requests it explicitly, bn == 0 (auto) picks it for prefill-sized problems.
+    if (a.peer_n) {
+        // fused reduce-scatter: prefill pair kernel only, token-major output, token ranges of 16-token granularity
+        if (a.peer_n < 2 || a.peer_n > 8 || a.peer_rank < 0 || a.peer_rank >= a.peer_n || a.out_mode != 1 || a.eblk || splits != 1 ||
+            a.out_f % 256 || a.tok < 128 || a.tok_per_rank <= 0 || a.tok_per_rank % 16 || (long long)a.tok_per_rank * a.peer_n < a.tok ||
+            !a.peer_done)
+            return QB_ERR_ARG;
+        for (int r = 0; r < a.peer_n; r++)
+            if (!a.peer_out[r] || ((uintptr_t)a.peer_out[r] & 15) || !a.peer_flags[r]) return QB_ERR_ARG;
+        if (a.bn == 384) return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
+        return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
+    }
     const bool pair_ok = !a.eblk && splits == 1 && (a.out_mode == 0 || a.out_mode == 1) && a.out_f % 256 == 0 && a.tok >= 128 &&
                          b_tail_ok(a.tok);
     if ((a.bn == 512 || a.bn == 384 || a.bn == 576) && !pair_ok) return QB_ERR_ARG;

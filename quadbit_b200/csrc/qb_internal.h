@@ -23,6 +23,31 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
 // RMSNorm (+ residual add) fused with the quantiser; res / hout / g may be null (g null = single level)
 int norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
                int tok, int H, float eps, int block, cudaStream_t st);
+// The tensor-parallel form of the fused residual add + RMSNorm + quantiser (two-level only): the norm input is the
+// fp32 sum, in source order, of nsrc <= 8 bf16 sources [tok][H] (src0 + i * src_stride elements) plus the residual;
+// see NormTP in qb_quant.cu for wait_flags / fan / sig. With fan == 0 the outputs are Bbytes[0] / sf_atoms[0] / g[0]
+// for this rank's tok rows; with fan > 0 they are `fan` full gathered arrays and this rank's rows start at row0.
+struct ReduceNormArgs {
+    const void* src0;
+    long long src_stride;      // elements between sources (a multiple of 8)
+    int nsrc;
+    const void* res;           // residual [tok][H] bf16 or null
+    const void* wt;
+    void* hout;                // new residual (required with res)
+    void* Bbytes[8];
+    void* sf_atoms[8];
+    void* g[8];
+    int fan, row0, tok_total;
+    int tok, H, block;
+    float eps;
+    const int* wait_flags;
+    int wait_val;
+    int sig_n, sig_rank, sig_val;
+    int* sig_flags[8];
+    int* done;
+};
+int reduce_norm_quant(const ReduceNormArgs& a, cudaStream_t st);
+int quant_status_read_clear();
 // SwiGLU quantiser over feature-major g, u [hidden][batch]; gH null = single level
 int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st);
 int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st);
@@ -68,6 +93,17 @@ struct GemmArgs {
                            // 3: bf16 C[tok][out] = (acc*gA*gB + bias)*row_w
     int splits;            // K splits (>1 uses Cf + a convert pass)
     int bn;                // token tile (0 = choose)
+    // Row-parallel GEMM fused with the reduce-scatter of its partial result (prefill pair kernel, out_mode 1 only):
+    // with peer_n > 0 the epilogue stores token row t into peer_out[t / tok_per_rank] (a pointer into the memory of
+    // the rank that owns that token range, already offset to this rank's slot) at local row t % tok_per_rank, and
+    // the last CTA to finish publishes peer_val in flag word `peer_rank` of every rank's flag array. C is unused.
+    int peer_n;
+    int peer_rank;
+    int tok_per_rank;
+    int peer_val;
+    void* peer_out[8];
+    int* peer_flags[8];
+    int* peer_done;        // arrival counter of this device's CTAs, zero between calls
 };
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);
 int gemm_init_attrs();

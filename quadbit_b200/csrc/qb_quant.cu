@@ -287,12 +287,48 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
 // per BLOCK without passing through bf16. Replaces rmsnorm_quant_k / add_rmsnorm_quant_k
 // (cuda/sparse_fp4_lib.cu:902-1011, single-level per-32) and, with TWO_LEVEL, also emits the
 // per-token global so the following GEMM runs two-level. One CTA per row, row kept in registers.
+// Tensor-parallel extras of the norm kernel (all off when nsrc == 1, fan == 0, wait_flags == null):
+//   nsrc > 1   x is the first of nsrc bf16 sources [tok][H], src_stride uint4 apart: the partial results that the ranks'
+//              row-parallel GEMMs stored into this rank's slots; they are summed in fp32 in source order (the reduction
+//              half of a reduce-scatter), then the residual is added;
+//   wait_flags every CTA first waits, bounded, until the nsrc words are >= wait_val (each source rank's "my partials
+//              have landed"); on expiry the status word gets QB_ERR_TIMEOUT and the kernel goes on (wrong data, no hang);
+//   fan > 0    packed bytes, scale atoms and globals go to `fan` destinations (the full-size arrays of every rank, rows
+//              offset by row0): the all-gather of the quantised activations done by the stores themselves;
+//   sig_n > 0  the last CTA to finish writes sig_val into word sig_rank of every rank's flag array.
+struct NormTP {
+    long long src_stride;
+    int nsrc;
+    const int* wait_flags;
+    int wait_val;
+    int fan;
+    int row0;
+    int tok_total;              // rows of the gathered arrays (for the scale layouts)
+    uint32_t* Bwords[8];
+    uint8_t* sf_atoms[8];
+    float* g[8];
+    int sig_n, sig_rank, sig_val;
+    int* sig_flags[8];
+    int* done;
+    int* status;
+};
+__device__ int g_quant_status = 0;
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 template <int BLOCK, int NJ, bool ADD, bool TWO_LEVEL>
 __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
                                                           const uint4* __restrict__ wt, uint4* __restrict__ hout,
                                                           uint32_t* __restrict__ Bwords, uint8_t* __restrict__ sf_ref,
                                                           uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok, int H,
-                                                          float eps) {
+                                                          float eps, const NormTP tp) {
     // every lane owns whole scale blocks (BLOCK values, NJ per lane), like quant_act_kernel
     constexpr int CPB = BLOCK / 8, P = 128 / BLOCK;
     const int row = blockIdx.x;
@@ -300,6 +336,20 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
     const int nblocks = H / BLOCK;       // a multiple of 4 (H % 128 == 0)
     const int lane = threadIdx.x & 31;
     __shared__ float red[32];
+    if (tp.wait_flags) {
+        if ((int)threadIdx.x < tp.nsrc) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t it = 0;
+            while (ld_acquire_sys(tp.wait_flags + threadIdx.x) < tp.wait_val) {
+                __nanosleep(200);
+                if ((++it & 255u) == 0 && globaltimer_ns() - t0 > 20000000000ull) {      // 20 s
+                    atomicCAS(tp.status, 0, QB_ERR_TIMEOUT * 100 + 20);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
     float v[NJ][BLOCK];
     float ss = 0.f;
 #pragma unroll
@@ -309,14 +359,28 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
         for (int k = 0; k < CPB; k++) {
             const size_t c = (size_t)blk * CPB + k;
             uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-            if (blk < nblocks) { a = __ldg(x + (size_t)row * nchunks + c); if (ADD) b = __ldg(res + (size_t)row * nchunks + c); }
+            // sources written by other GPUs are read past the non-coherent path (ld.global, not ld.global.nc)
+            if (blk < nblocks) {
+                a = tp.nsrc > 1 ? __ldcg(x + (size_t)row * nchunks + c) : __ldg(x + (size_t)row * nchunks + c);
+                if (ADD) b = __ldg(res + (size_t)row * nchunks + c);
+            }
             const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
             const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+            float2 acc4[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc4[i] = __bfloat1622float2(ah[i]);
+            for (int sidx = 1; sidx < tp.nsrc; sidx++) {
+                uint4 e = make_uint4(0, 0, 0, 0);
+                if (blk < nblocks) e = __ldcg(x + (size_t)sidx * tp.src_stride + (size_t)row * nchunks + c);
+                const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&e);
+#pragma unroll
+                for (int i = 0; i < 4; i++) { const float2 t2 = __bfloat1622float2(eh[i]); acc4[i].x = __fadd_rn(acc4[i].x, t2.x); acc4[i].y = __fadd_rn(acc4[i].y, t2.y); }
+            }
             uint4 o;
             __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                float2 f = __bfloat1622float2(ah[i]);
+                float2 f = acc4[i];
                 if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); f.x = __fadd_rn(f.x, r2.x); f.y = __fadd_rn(f.y, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
                 v[j][8 * k + 2 * i] = f.x; v[j][8 * k + 2 * i + 1] = f.y;
                 ss += f.x * f.x + f.y * f.y;
@@ -364,7 +428,10 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
         float r = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
         r = warp_max(r);
         gl = fmaxf(__fdiv_rn(r, 2688.f), 1e-30f);
-        if (threadIdx.x == 0) g_out[row] = gl;
+        if (threadIdx.x == 0) {
+            if (tp.fan) { for (int d = 0; d < tp.fan; d++) tp.g[d][tp.row0 + row] = gl; }
+            else g_out[row] = gl;
+        }
     }
     const bool wide = (reinterpret_cast<uintptr_t>(Bwords) & 15) == 0;
 #pragma unroll
@@ -385,21 +452,66 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
 #pragma unroll
         for (int i = 0; i < 4; i++) sw |= __shfl_sync(0xffffffffu, code, base + i) << (8 * i);
         if (blk < nblocks) {
-            uint32_t* dst = Bwords + (size_t)row * nchunks + (size_t)blk * CPB;
-            if (wide) {
-                if constexpr (CPB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+            if (tp.fan) {
+                // every destination is the full gathered array of one rank; this rank's rows start at row0 there
+                const size_t grow = (size_t)(tp.row0 + row);
+                const size_t aoff = sf_atom_offset(tp.row0 + row, blk, kpad256(H) / BLOCK / 4);
+                for (int d = 0; d < tp.fan; d++) {
+                    uint32_t* dst = tp.Bwords[d] + grow * nchunks + (size_t)blk * CPB;
+                    if constexpr (CPB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                    if ((lane & 3) == 0) *reinterpret_cast<uint32_t*>(tp.sf_atoms[d] + aoff) = sw;
+                }
             } else {
+                uint32_t* dst = Bwords + (size_t)row * nchunks + (size_t)blk * CPB;
+                if (wide) {
+                    if constexpr (CPB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < CPB; k++) dst[k] = w[k];
-            }
-            if ((lane & 3) == 0) {
-                const int jcol = blk;
-                if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
-                if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(H) / BLOCK / 4)) = sw;
+                    for (int k = 0; k < CPB; k++) dst[k] = w[k];
+                }
+                if ((lane & 3) == 0) {
+                    const int jcol = blk;
+                    if (sf_ref) *reinterpret_cast<uint32_t*>(sf_ref + ((size_t)(jcol / P) * tok + row) * P + (jcol % P)) = sw;
+                    if (sf_atoms) *reinterpret_cast<uint32_t*>(sf_atoms + sf_atom_offset(row, jcol, kpad256(H) / BLOCK / 4)) = sw;
+                }
             }
         }
     }
+    if (tp.sig_n) {
+        // publish "my rows have landed everywhere": every thread's stores are ordered before the CTA barrier, the
+        // system-scope fence of thread 0 after it is cumulative, and the last CTA of the grid writes the flags
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            if (atomicAdd(tp.done, 1) == (int)gridDim.x - 1) {
+                atomicExch(tp.done, 0);
+                __threadfence_system();
+                for (int d = 0; d < tp.sig_n; d++) st_release_sys(tp.sig_flags[d] + tp.sig_rank, tp.sig_val);
+            }
+        }
+    }
+}
+
+static int norm_quant_launch(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms,
+                             void* g, int tok, int H, float eps, int block, const NormTP& tp, cudaStream_t st) {
+    const int nblocks = H / block;
+    int threads = (nblocks + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    const int nj = (nblocks + threads - 1) / threads;
+    if (nj > 4) return QB_ERR_UNSUPPORTED;     // H <= 32768 (per-16) / 65536 (per-32)
+#define QB_LN3(B, NJ, ADD, TL)                                                                                                   \
+    norm_quant_kernel<B, NJ, ADD, TL><<<tok, threads, 0, st>>>((const uint4*)x, (const uint4*)res, (const uint4*)wt, (uint4*)hout, \
+                                                               (uint32_t*)Bbytes, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)g, tok, H, eps, tp)
+#define QB_LN2(B, NJ) do { if (res) { if (g) QB_LN3(B, NJ, true, true); else QB_LN3(B, NJ, true, false); } \
+                           else { if (g) QB_LN3(B, NJ, false, true); else QB_LN3(B, NJ, false, false); } } while (0)
+#define QB_LN1(B) do { if (nj <= 1) QB_LN2(B, 1); else if (nj <= 2) QB_LN2(B, 2); else QB_LN2(B, 4); } while (0)
+    if (block == 32) QB_LN1(32); else QB_LN1(16);
+#undef QB_LN1
+#undef QB_LN2
+#undef QB_LN3
+    return (int)cudaGetLastError();
 }
 
 int norm_quant(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms, void* g,
@@ -410,22 +522,49 @@ int norm_quant(const void* x, const void* res, const void* wt, void* hout, void*
     if (((uintptr_t)x & 15) || ((uintptr_t)res & 15) || ((uintptr_t)wt & 15) || ((uintptr_t)hout & 15) || ((uintptr_t)Bbytes & 3) ||
         ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3))
         return QB_ERR_ARG;
-    const int nblocks = H / block;
-    int threads = (nblocks + 31) / 32 * 32;
-    if (threads > 512) threads = 512;
-    const int nj = (nblocks + threads - 1) / threads;
-    if (nj > 4) return QB_ERR_UNSUPPORTED;     // H <= 32768 (per-16) / 65536 (per-32)
-#define QB_LN3(B, NJ, ADD, TL)                                                                                                   \
-    norm_quant_kernel<B, NJ, ADD, TL><<<tok, threads, 0, st>>>((const uint4*)x, (const uint4*)res, (const uint4*)wt, (uint4*)hout, \
-                                                               (uint32_t*)Bbytes, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)g, tok, H, eps)
-#define QB_LN2(B, NJ) do { if (res) { if (g) QB_LN3(B, NJ, true, true); else QB_LN3(B, NJ, true, false); } \
-                           else { if (g) QB_LN3(B, NJ, false, true); else QB_LN3(B, NJ, false, false); } } while (0)
-#define QB_LN1(B) do { if (nj <= 1) QB_LN2(B, 1); else if (nj <= 2) QB_LN2(B, 2); else QB_LN2(B, 4); } while (0)
-    if (block == 32) QB_LN1(32); else QB_LN1(16);
-#undef QB_LN1
-#undef QB_LN2
-#undef QB_LN3
-    return (int)cudaGetLastError();
+    NormTP tp{};
+    tp.nsrc = 1;
+    return norm_quant_launch(x, res, wt, hout, Bbytes, sf_ref, sf_atoms, g, tok, H, eps, block, tp, st);
+}
+
+int reduce_norm_quant(const ReduceNormArgs& a, cudaStream_t st) {
+    if (a.tok < 0 || a.H <= 0 || a.H % 128 != 0 || (a.block != 16 && a.block != 32)) return QB_ERR_ARG;
+    if (a.nsrc < 1 || a.nsrc > 8 || a.fan < 0 || a.fan > 8 || a.sig_n < 0 || a.sig_n > 8) return QB_ERR_ARG;
+    if (a.tok == 0) return QB_OK;
+    if (!a.src0 || !a.wt) return QB_ERR_ARG;
+    if (((uintptr_t)a.src0 & 15) || ((uintptr_t)a.res & 15) || ((uintptr_t)a.wt & 15) || ((uintptr_t)a.hout & 15) || (a.src_stride & 7))
+        return QB_ERR_ARG;
+    if (a.res && !a.hout) return QB_ERR_ARG;
+    if (a.sig_n && !a.done) return QB_ERR_ARG;
+    NormTP tp{};
+    tp.src_stride = a.src_stride / 8;          // in 16-byte units
+    tp.nsrc = a.nsrc;
+    tp.wait_flags = a.wait_flags;
+    tp.wait_val = a.wait_val;
+    tp.fan = a.fan;
+    tp.row0 = a.row0;
+    tp.tok_total = a.tok_total;
+    tp.sig_n = a.sig_n; tp.sig_rank = a.sig_rank; tp.sig_val = a.sig_val; tp.done = a.done;
+    if (cudaGetSymbolAddress((void**)&tp.status, g_quant_status) != cudaSuccess) return QB_ERR_DRIVER;
+    void* Bb0 = a.Bbytes[0];
+    void* sf0 = a.sf_atoms[0];
+    void* g0 = a.g[0];
+    if (!Bb0 || !sf0 || !g0) return QB_ERR_ARG;
+    for (int d = 0; d < 8; d++) {
+        const bool used = d < (a.fan ? a.fan : 1);
+        if (used && (!a.Bbytes[d] || !a.sf_atoms[d] || !a.g[d] || ((uintptr_t)a.Bbytes[d] & 15) || ((uintptr_t)a.sf_atoms[d] & 3))) return QB_ERR_ARG;
+        tp.Bwords[d] = (uint32_t*)a.Bbytes[d]; tp.sf_atoms[d] = (uint8_t*)a.sf_atoms[d]; tp.g[d] = (float*)a.g[d];
+        tp.sig_flags[d] = d < a.sig_n ? a.sig_flags[d] : nullptr;
+        if (d < a.sig_n && !a.sig_flags[d]) return QB_ERR_ARG;
+    }
+    return norm_quant_launch(a.src0, a.res, a.wt, a.hout, Bb0, nullptr, sf0, g0, a.tok, a.H, a.eps, a.block, tp, st);
+}
+
+int quant_status_read_clear() {
+    int h = 0;
+    if (cudaMemcpyFromSymbol(&h, g_quant_status, sizeof(int)) != cudaSuccess) return QB_ERR_DRIVER;
+    if (h) { int z = 0; cudaMemcpyToSymbol(g_quant_status, &z, sizeof(int)); }
+    return h;
 }
 
 // SwiGLU quantisers over feature-major operands gate, up [hidden][batch] (the two halves of a feature-major

@@ -109,7 +109,9 @@ class QuadbitLinear:
         check(lib.qb_compress_2to4_colnorm(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, _ptr(colnorm), self.Ac.data_ptr(),
                                            _ptr(self.meta), self.meta_native.data_ptr(), _ptr(self.scaleA), self.sfa.data_ptr(),
                                            self.gA.data_ptr(), out_f, in_f, _stream()), "qb_compress_2to4_colnorm")
-        self.At = tile_weights(lib, self.Ac, out_f, in_f, 1)      # what the GEMMs read; Ac stays as the reference attribute
+        self.At = tile_weights(lib, self.Ac, out_f, in_f, 1)      # what the GEMMs read
+        if not keep_ref_layout:
+            self.Ac = None           # the row-major copy is a reference attribute only: one packed copy per layer
 
     def pack_act(self, x: torch.Tensor):
         """x [tok,in] -> (Bbytes, scaleB atoms, gB)."""
@@ -168,8 +170,9 @@ class DenseNVLinear(torch.nn.Module):
         SFA = torch.empty((in_f // 128, out_f, 8), dtype=torch.uint8, device=dev) if keep_ref_layout else None
         check(lib.qb_pack_dense(W.data_ptr(), 1 if W.dtype == torch.bfloat16 else 0, Ab.data_ptr(), _ptr(SFA), sfa.data_ptr(),
                                 gA.data_ptr(), out_f, in_f, _stream()), "qb_pack_dense")
-        self.register_buffer("Ab", Ab)
         self.register_buffer("At", tile_weights(lib, Ab, out_f, in_f, 0))   # what the GEMMs read
+        if keep_ref_layout:
+            self.register_buffer("Ab", Ab)
         self.register_buffer("gA", gA)
         self.register_buffer("sfa", sfa)
         if SFA is not None:

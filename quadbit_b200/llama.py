@@ -1,0 +1,347 @@
+"""Llama-architecture prefill forward on the NVFP4 kernels, tensor-parallel over the GPUs of one box.
+
+What the reference assembles for its end-to-end runs, here as one module: attention projections on the dense two-level
+NVFP4 GEMM (harness/dense_e2e.py:99-113), the SwiGLU MLP on the 2:4-sparse GEMM with the fused-MLP arithmetic
+(harness/quadbit_serve.py:394-462), RMSNorm fused with the quantiser in front of both (cuda/sparse_fp4_lib.cu:902-1011),
+attention math in bf16 (harness/real_model.py:181-188). Embedding, RoPE, attention and the final norm / logits are plain
+torch (host layer); every linear, quantiser and norm in the layer stack is a kernel of this library.
+
+Tensor parallelism (world = number of GPUs, one process each) with the residual stream sharded by tokens:
+
+    N1   reduce(down partials of the previous layer) + residual + RMSNorm + per-16 quantise of this rank's token rows,
+         the packed rows stored into EVERY rank's gathered array                      (qb_reduce_norm_quant)
+    QKV  dense GEMM on all tokens, this rank's heads: column-parallel, no exchange      (qb_gemm)
+    attention over this rank's heads (torch SDPA), per-16 quantise of its output        (qb_quantize_act)
+    O    dense GEMM over this rank's K slice, partial rows stored into the owner's slot (qb_gemm_rs)
+    N2   reduce(o_proj partials) + residual + RMSNorm + per-32 quantise, stored to all  (qb_reduce_norm_quant)
+    GU   2:4-sparse GEMM, this rank's gate and up rows, column-parallel                 (qb_gemm)
+    SwiGLU + per-32 quantise of the local intermediate slice                            (qb_swiglu_quant)
+    D    2:4-sparse GEMM over this rank's K slice, partial rows stored into the owners  (qb_gemm_rs)
+
+so per layer the NVLink carries two reduce-scatters of bf16 partials (issued by GEMM epilogues, overlapping the MMAs) and
+two all-gathers of QUANTISED activations (0.56 bytes per value instead of 2), and no NCCL call. `comm="nccl"` runs the
+same arithmetic with all_to_all_single / all_gather_into_tensor in place of the peer stores (the baseline the fused
+form is measured against, and the fallback when peer mapping is unavailable). The row-parallel GEMMs quantise each
+rank's K slice on its own (per-slice token global), the partials are bf16 and are summed in rank order: see
+oracle/llama_ref.py for the arithmetic this is tested against."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from ._lib import check, load
+from .linear import DenseNVLinear, QuadbitLinear, _stream
+from .tp import TPContext, ptr_array
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 14336
+    rms_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    vocab: int = 128256
+
+
+def random_layer(cfg: LlamaConfig, seed: int, li: int, device) -> dict:
+    """One layer of random-init weights ~ N(0, 0.02) in bf16 (norm weights 1 + small noise), from a generator seeded by
+    (seed, layer): any rank generates the same full matrices and slices its shard."""
+    H, hd, I = cfg.hidden, cfg.head_dim, cfg.intermediate
+    g = torch.Generator(device=device).manual_seed(seed * 1000003 + li + 1)
+    r = lambda *s: (torch.randn(*s, device=device, generator=g) * 0.02).to(torch.bfloat16)
+    n = lambda: (1 + 0.05 * torch.randn(H, device=device, generator=g)).to(torch.bfloat16)
+    return dict(wq=r(cfg.n_heads * hd, H), wk=r(cfg.n_kv_heads * hd, H), wv=r(cfg.n_kv_heads * hd, H), wo=r(H, cfg.n_heads * hd),
+                w_gate=r(I, H), w_up=r(I, H), w_down=r(H, I), norm_attn=n(), norm_mlp=n())
+
+
+def random_weights(cfg: LlamaConfig, seed: int, device) -> dict:
+    """Random-init model: embedding, lm_head, final norm and a per-layer generator (layers are built and packed one at a
+    time, so the bf16 matrices of only one layer exist at once)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    H = cfg.hidden
+    return dict(embed=(torch.randn(cfg.vocab, H, device=device, generator=g) * 0.02).to(torch.bfloat16),
+                lm_head=(torch.randn(cfg.vocab, H, device=device, generator=g) * 0.02).to(torch.bfloat16),
+                norm_f=(1 + 0.05 * torch.randn(H, device=device, generator=g)).to(torch.bfloat16),
+                layers=lambda li: random_layer(cfg, seed, li, device))
+
+
+def shard_layer(L: dict, cfg: LlamaConfig, rank: int, world: int) -> dict:
+    """This rank's slices of one layer's bf16 weights: heads (q, k, v rows; o_proj columns) and intermediate features
+    (gate, up rows; down columns)."""
+    hd = cfg.head_dim
+    hq, hk, isl = cfg.n_heads // world * hd, cfg.n_kv_heads // world * hd, cfg.intermediate // world
+    qkv = torch.cat([L["wq"][rank * hq:(rank + 1) * hq], L["wk"][rank * hk:(rank + 1) * hk], L["wv"][rank * hk:(rank + 1) * hk]], 0)
+    gu = torch.cat([L["w_gate"][rank * isl:(rank + 1) * isl], L["w_up"][rank * isl:(rank + 1) * isl]], 0)
+    return dict(qkv=qkv.contiguous(), wo=L["wo"][:, rank * hq:(rank + 1) * hq].contiguous(), gate_up=gu.contiguous(),
+                down=L["w_down"][:, rank * isl:(rank + 1) * isl].contiguous(), norm_attn=L["norm_attn"], norm_mlp=L["norm_mlp"])
+
+
+class _Layer:
+    def __init__(self, W: dict):
+        self.qkv = DenseNVLinear(W["qkv"], keep_ref_layout=False)
+        self.wo = DenseNVLinear(W["wo"], keep_ref_layout=False)
+        self.gu = QuadbitLinear(W["gate_up"], keep_ref_layout=False)
+        self.dn = QuadbitLinear(W["down"], keep_ref_layout=False)
+        self.norm_attn = W["norm_attn"].to(torch.bfloat16).contiguous()
+        self.norm_mlp = W["norm_mlp"].to(torch.bfloat16).contiguous()
+
+
+class LlamaPrefill:
+    """One rank of the model. `weights`: dict as oracle-side `make_weights` builds it (embed, lm_head, norm_f, layers =
+    list of per-layer dicts or a callable layer index -> dict, so full-size layers can be generated and packed one at a
+    time). `ctx`: a TPContext for world > 1 with comm="peer"."""
+
+    def __init__(self, cfg: LlamaConfig, weights: dict, rank: int = 0, world: int = 1, group=None, comm: str = "peer",
+                 ctx: TPContext | None = None, device=None):
+        assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.intermediate % (128 * world) == 0
+        assert comm in ("peer", "nccl")
+        self.cfg, self.rank, self.world, self.group, self.comm = cfg, rank, world, group, comm
+        self.lib = load("sparse_fp4")
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.embed = weights["embed"].to(self.device)
+        self.lm_head = weights["lm_head"].to(self.device)
+        self.norm_f = weights["norm_f"].to(self.device)
+        layers = weights["layers"]
+        n = cfg.n_layers
+        self.layers = []
+        for li in range(n):
+            L = layers(li) if callable(layers) else layers[li]
+            self.layers.append(_Layer(shard_layer({k: v.to(self.device) for k, v in L.items()}, cfg, rank, world)))
+        self.ctx = ctx
+        self._rope = {}
+        self.timings = None
+        self._marks = []
+
+    # ------------------------------------------------------------------ pieces
+    def _rope_tables(self, S: int):
+        if S not in self._rope:
+            hd = self.cfg.head_dim
+            inv = 1.0 / (self.cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=self.device) / hd))
+            ang = torch.outer(torch.arange(S, dtype=torch.float32, device=self.device), inv)
+            self._rope[S] = (torch.cos(ang).to(torch.bfloat16)[None, :, None, :], torch.sin(ang).to(torch.bfloat16)[None, :, None, :])
+        return self._rope[S]
+
+    @staticmethod
+    def _apply_rope(x, cos, sin):
+        h = x.shape[-1] // 2
+        x1, x2 = x[..., :h], x[..., h:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+    def _attention(self, qkv: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """qkv [T, (hq + 2 hk) * hd] bf16 of this rank's heads -> [T, hq * hd] bf16 (RoPE, causal GQA attention)."""
+        cfg = self.cfg
+        hd, hq, hk = cfg.head_dim, cfg.n_heads // self.world, cfg.n_kv_heads // self.world
+        q = qkv[:, : hq * hd].view(B, S, hq, hd)
+        k = qkv[:, hq * hd:(hq + hk) * hd].view(B, S, hk, hd)
+        v = qkv[:, (hq + hk) * hd:].view(B, S, hk, hd)
+        cos, sin = self._rope_tables(S)
+        q, k = self._apply_rope(q, cos, sin), self._apply_rope(k, cos, sin)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True)
+        return o.transpose(1, 2).reshape(B * S, hq * hd)
+
+    def _gemm(self, lin, Bb: int, sfb: int, gB: int, tok: int, out: torch.Tensor):
+        dense = isinstance(lin, DenseNVLinear)
+        out_f, in_f = (lin.out, lin.inn) if dense else (lin.out_f, lin.in_f)
+        check(self.lib.qb_gemm(lin.At.data_ptr(), Bb, lin.sfa.data_ptr(), sfb, 0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(),
+                               gB, out.data_ptr(), 0, 0, 0, 0, out_f, out_f, tok, in_f, 2 if dense else 3, 1, 1, 0, _stream()), "qb_gemm")
+
+    def _row_parallel(self, lin, q, tok: int, k: int) -> torch.Tensor | None:
+        """Row-parallel GEMM on the quantised local K slice q = (Bb, atoms, g). world 1: returns [tok, out]. Otherwise the
+        partial rows go to the owners' slots (set k) and None is returned."""
+        dense = isinstance(lin, DenseNVLinear)
+        out_f, in_f = (lin.out, lin.inn) if dense else (lin.out_f, lin.in_f)
+        Bb, sfb, gB = q
+        if self.world == 1:
+            out = torch.empty((tok, out_f), dtype=torch.bfloat16, device=self.device)
+            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), tok, out)
+            return out
+        ctx = self.ctx
+        if self.comm == "nccl":
+            import torch.distributed as dist
+            part = torch.empty((tok, out_f), dtype=torch.bfloat16, device=self.device)
+            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), tok, part)
+            dist.all_to_all_single(ctx.slots_view(k), part.view(self.world, ctx.Tl, out_f), group=self.group)
+            return None
+        val = ctx.next_value(ctx.FLAG_SLOT[k])
+        check(self.lib.qb_gemm_rs(lin.At.data_ptr(), Bb.data_ptr(), lin.sfa.data_ptr(), sfb.data_ptr(),
+                                  0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(), gB.data_ptr(), ctx.slot_out_ptrs(k),
+                                  ctx.flag_ptrs(ctx.FLAG_SLOT[k]), ctx.done[k:].data_ptr(), out_f, tok, in_f, 2 if dense else 3, self.world,
+                                  self.rank, ctx.Tl, val, 0, _stream()), "qb_gemm_rs")
+        return None
+
+    def _norm_quant(self, src, k, res, wt, block: int, T: int):
+        """Fused reduce + residual add + RMSNorm + quantiser of this rank's rows. src: bf16 [Tl, H] tensor (world 1, or the
+        embedding rows of the first layer) or None = this rank's slots `k`. Returns (new residual or None, (Bb ptr, atoms
+        ptr, g ptr) of the quantised activations of ALL T tokens as the following column-parallel GEMM reads them)."""
+        lib, H, W = self.lib, self.cfg.hidden, self.world
+        Tl = T // W
+        hout = torch.empty((Tl, H), dtype=torch.bfloat16, device=self.device) if res is not None else None
+        hp = hout.data_ptr() if hout is not None else 0
+        rp = res.data_ptr() if res is not None else 0
+        if W == 1:
+            Bb = torch.empty((T, H // 2), dtype=torch.uint8, device=self.device)
+            sf = torch.empty(lib.qb_sf_atoms_bytes(T, H, block), dtype=torch.uint8, device=self.device)
+            g = torch.empty((T,), dtype=torch.float32, device=self.device)
+            check(lib.qb_reduce_norm_quant(src.data_ptr(), 0, 1, rp, wt.data_ptr(), hp, ptr_array([Bb.data_ptr()]), ptr_array([sf.data_ptr()]),
+                                           ptr_array([g.data_ptr()]), 0, 0, T, T, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, _stream()),
+                  "qb_reduce_norm_quant")
+            self._keep = (Bb, sf, g)
+            return hout, (Bb.data_ptr(), sf.data_ptr(), g.data_ptr())
+        ctx = self.ctx
+        if src is None:
+            s0, stride, nsrc = ctx.slots_view(k).data_ptr(), Tl * H, W
+        else:
+            s0, stride, nsrc = src.data_ptr(), 0, 1
+        if self.comm == "nccl":
+            import torch.distributed as dist
+            Bl = torch.empty((Tl, H // 2), dtype=torch.uint8, device=self.device)
+            sl = torch.empty(lib.qb_sf_atoms_bytes(Tl, H, block), dtype=torch.uint8, device=self.device)
+            gl = torch.empty((Tl,), dtype=torch.float32, device=self.device)
+            check(lib.qb_reduce_norm_quant(s0, stride, nsrc, rp, wt.data_ptr(), hp, ptr_array([Bl.data_ptr()]), ptr_array([sl.data_ptr()]),
+                                           ptr_array([gl.data_ptr()]), 0, 0, Tl, Tl, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, _stream()),
+                  "qb_reduce_norm_quant")
+            Bb = torch.empty((T, H // 2), dtype=torch.uint8, device=self.device)
+            sf = torch.empty(lib.qb_sf_atoms_bytes(T, H, block), dtype=torch.uint8, device=self.device)
+            g = torch.empty((T,), dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(Bb, Bl, group=self.group)
+            dist.all_gather_into_tensor(sf, sl, group=self.group)        # atoms are 128-row-block major: rank chunks concatenate
+            dist.all_gather_into_tensor(g, gl, group=self.group)
+            self._keep = (Bb, sf, g)
+            return hout, (Bb.data_ptr(), sf.data_ptr(), g.data_ptr())
+        fw = ctx.FLAG_GATHER[block]
+        val = ctx.next_value(fw)
+        wait_ptr, wait_val = (ctx.flag_own(ctx.FLAG_SLOT[k]), ctx.counter[ctx.FLAG_SLOT[k]]) if src is None else (0, 0)
+        Bv, Sv, Gv = ctx.gathered_ptrs(block)
+        check(lib.qb_reduce_norm_quant(s0, stride, nsrc, rp, wt.data_ptr(), hp, Bv, Sv, Gv, W, self.rank * Tl, T, Tl, H, self.cfg.rms_eps,
+                                       block, wait_ptr, wait_val, ctx.flag_ptrs(fw), W, self.rank, val, ctx.done[2 + (block == 32):].data_ptr(),
+                                       _stream()), "qb_reduce_norm_quant")
+        return hout, ("gathered", block, val)
+
+    def _resolve(self, q, block: int):
+        """Pointers of the gathered activations; with peer stores, first wait until every rank's rows have landed."""
+        if isinstance(q[0], str):
+            ctx = self.ctx
+            check(self.lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), self.world, q[2], _stream()), "qb_peer_wait")
+            return ctx.gathered_own(block)
+        return q
+
+    # ------------------------------------------------------------------ forward
+    def forward_steps(self, ids: torch.Tensor):
+        """Generator over the forward: yields after every kernel that other ranks wait for (so that a single process can
+        drive several emulated ranks in lock step); the last value is (hidden_local [T/world, H] bf16, logits [B, vocab])."""
+        cfg, lib, W = self.cfg, self.lib, self.world
+        B, S = ids.shape
+        T, H, I = B * S, cfg.hidden, cfg.intermediate // W
+        Tl = T // W
+        r0 = self.rank * Tl
+        self._mark("start")
+        x = self.embed[ids.reshape(-1)[r0:r0 + Tl].to(self.device)]                # residual stream, this rank's rows
+        res, q16 = self._norm_quant(x, None, None, self.layers[0].norm_attn, 16, T)
+        self._mark("embed+norm_quant")
+        yield None
+        for li, L in enumerate(self.layers):
+            Bb, sf, g = self._resolve(q16, 16)
+            qkv = torch.empty((T, L.qkv.out), dtype=torch.bfloat16, device=self.device)
+            self._gemm(L.qkv, Bb, sf, g, T, qkv)
+            self._mark("qkv_gemm")
+            attn = self._attention(qkv, B, S)
+            self._mark("rope+attention")
+            aq = self._quantize(attn, 16)
+            self._mark("act_quant")
+            o = self._row_parallel(L.wo, aq, T, 0)
+            self._mark("o_proj_gemm")
+            yield None
+            x, q32 = self._norm_quant(o, 0, x, L.norm_mlp, 32, T)
+            self._mark("reduce+norm_quant")
+            yield None
+            Bb, sf, g = self._resolve(q32, 32)
+            cgu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=self.device)
+            self._gemm(L.gu, Bb, sf, g, T, cgu)
+            self._mark("gate_up_gemm")
+            Hb = torch.empty((T, I // 2), dtype=torch.uint8, device=self.device)
+            sfh = torch.empty(lib.qb_sf_atoms_bytes(T, I, 32), dtype=torch.uint8, device=self.device)
+            gH = torch.empty((T,), dtype=torch.float32, device=self.device)
+            check(lib.qb_swiglu_quant(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), T, I, _stream()), "qb_swiglu_quant")
+            self._mark("swiglu_quant")
+            d = self._row_parallel(L.dn, (Hb, sfh, gH), T, 1)
+            self._mark("down_gemm")
+            yield None
+            if li + 1 < len(self.layers):
+                x, q16 = self._norm_quant(d, 1, x, self.layers[li + 1].norm_attn, 16, T)
+                self._mark("reduce+norm_quant")
+                yield None
+        # final: sum of the last partials + residual -> bf16 -> RMSNorm -> logits of the last token of every sequence
+        if W == 1:
+            v = (d.float() + x.float())
+        else:
+            ctx = self.ctx
+            if self.comm == "peer":
+                check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_SLOT[1]), W, ctx.counter[ctx.FLAG_SLOT[1]], _stream()), "qb_peer_wait")
+            sl = ctx.slots_view(1).float()
+            v = sl[0]
+            for s in range(1, W):
+                v = v + sl[s]
+            v = v + x.float()
+        xf = v.to(torch.bfloat16).float()
+        hid = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * self.norm_f.float()).to(torch.bfloat16)
+        last = torch.zeros((B, H), dtype=torch.float32, device=self.device)
+        pos = torch.arange(B, device=self.device) * S + (S - 1)
+        mine = (pos >= r0) & (pos < r0 + Tl)
+        last[mine] = hid[(pos[mine] - r0)].float()
+        if W > 1 and self.group is not False and torch.distributed.is_initialized():
+            torch.distributed.all_reduce(last, group=self.group)
+        self._last_rows = last
+        logits = (last.to(torch.bfloat16) @ self.lm_head.t()).float()
+        self._mark("final_norm+logits")
+        yield hid, logits
+
+    def _mark(self, name: str):
+        """With `self.timings` set to a dict, the device time between consecutive marks is added to timings[name]
+        (events are resolved by `finish_timings`)."""
+        if self.timings is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._marks.append((name, ev))
+
+    def finish_timings(self):
+        torch.cuda.synchronize()
+        for (_, e0), (name, e1) in zip(self._marks[:-1], self._marks[1:]):
+            self.timings[name] = self.timings.get(name, 0.0) + e0.elapsed_time(e1)
+        self._marks = []
+        return self.timings
+
+    def _quantize(self, x: torch.Tensor, block: int):
+        lib = self.lib
+        tok, K = x.shape
+        Bb = torch.empty((tok, K // 2), dtype=torch.uint8, device=self.device)
+        sf = (torch.zeros if K % 256 else torch.empty)(lib.qb_sf_atoms_bytes(tok, K, block), dtype=torch.uint8, device=self.device)
+        g = torch.empty((tok,), dtype=torch.float32, device=self.device)
+        check(lib.qb_quantize_act(x.data_ptr(), Bb.data_ptr(), 0, sf.data_ptr(), g.data_ptr(), tok, K, block, _stream()), "qb_quantize_act")
+        return Bb, sf, g
+
+    def forward(self, ids: torch.Tensor):
+        out = None
+        for out in self.forward_steps(ids):
+            pass
+        return out
+
+    __call__ = forward
+
+
+def forward_emulated(models, ids: torch.Tensor):
+    """Drive `world` ranks that share one GPU in lock step (see tp.TPContext.emulated). Returns the list of per-rank
+    (hidden_local, logits); the last-token rows are summed here in place of the all-reduce."""
+    gens = [m.forward_steps(ids) for m in models]
+    outs = [None] * len(models)
+    for step in zip(*gens):
+        outs = list(step)
+    last = sum(m._last_rows for m in models)
+    return [(o[0], (last.to(torch.bfloat16) @ m.lm_head.t()).float()) for o, m in zip(outs, models)]

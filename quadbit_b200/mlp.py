@@ -46,10 +46,10 @@ class FusedSparseMLP:
         splits = self.sk_splits if (tok <= self.sk_max_tok and self.sk_splits > 1) else 1
         Cf = torch.empty((tok, self.out_f), dtype=torch.float32, device=dev) if splits > 1 else None
         gu, dn = self.gu, self.dn
-        check(lib.qb_fused_mlp(x2.data_ptr(), gu.Ac.data_ptr(), gu.sfa.data_ptr(), gu.meta_native.data_ptr(), gu.gA.data_ptr(),
-                               dn.Ac.data_ptr(), dn.sfa.data_ptr(), dn.meta_native.data_ptr(), dn.gA.data_ptr(), Bb.data_ptr(),
+        check(lib.qb_fused_mlp(x2.data_ptr(), gu.At.data_ptr(), gu.sfa.data_ptr(), gu.meta_native.data_ptr(), gu.gA.data_ptr(),
+                               dn.At.data_ptr(), dn.sfa.data_ptr(), dn.meta_native.data_ptr(), dn.gA.data_ptr(), Bb.data_ptr(),
                                sfx.data_ptr(), gBx.data_ptr(), Cgu.data_ptr(), Hb.data_ptr(), sfh.data_ptr(), gH.data_ptr(),
-                               Cout.data_ptr(), _ptr(Cf), tok, H, I, 2 * I, self.out_f, splits, _stream()), "qb_fused_mlp")
+                               Cout.data_ptr(), _ptr(Cf), tok, H, I, 2 * I, self.out_f, splits, 1, _stream()), "qb_fused_mlp")
         return Cout.reshape(*lead, self.out_f)
 
     __call__ = forward
