@@ -299,6 +299,15 @@ def run_tp_set(torch, qb, lib, dev, rank, world, dist, args, comm):
     full = {b: (torch.empty((TOK, H // 2), dtype=torch.uint8, device=dev), torch.empty(lib.qb_sf_atoms_bytes(TOK, H, b), dtype=torch.uint8, device=dev),
                 torch.empty((TOK,), dtype=torch.float32, device=dev)) for b in (16, 32)}
 
+    # Flag values come from a device word (the step count, bumped by the first node of every step on every rank), so the
+    # peer-store step has fixed kernel arguments and is replayed from one CUDA graph: a rank issues one launch per step.
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    ep = epoch.data_ptr()
+    slot_out = {k: ctx.slot_out_ptrs(k) for k in (0, 1)}
+    slot_flags = {k: ctx.flag_ptrs(ctx.FLAG_SLOT[k]) for k in (0, 1)}
+    gat = {b: ctx.gathered_ptrs(b) for b in (16, 32)}
+    gat_flags = {b: ctx.flag_ptrs(ctx.FLAG_GATHER[b]) for b in (16, 32)}
+
     def col_gemm(name, q):
         m = mods[name]
         rc = lib.qb_gemm(m.At.data_ptr(), q[0], m.sfa.data_ptr(), q[1], m.meta_native.data_ptr(), m.gA.data_ptr(), q[2], outs[name].data_ptr(),
@@ -315,10 +324,9 @@ def run_tp_set(torch, qb, lib, dev, rank, world, dist, args, comm):
             assert rc == 0, rc
             dist.all_to_all_single(ctx.slots_view(k), part[name].view(world, Tl, H))
         else:
-            val = ctx.next_value(ctx.FLAG_SLOT[k])
             rc = lib.qb_gemm_rs(m.At.data_ptr(), Bb.data_ptr(), m.sfa.data_ptr(), sf.data_ptr(), m.meta_native.data_ptr(), m.gA.data_ptr(),
-                                g.data_ptr(), ctx.slot_out_ptrs(k), ctx.flag_ptrs(ctx.FLAG_SLOT[k]), ctx.done[k:].data_ptr(), m.out_f, TOK, m.in_f,
-                                3, world, rank, Tl, val, 0, S())
+                                g.data_ptr(), slot_out[k], slot_flags[k], ctx.done[k:].data_ptr(), m.out_f, TOK, m.in_f,
+                                3, world, rank, Tl, 0, ep, 0, S())
             assert rc == 0, rc
         launches[0] += 1
 
@@ -327,50 +335,82 @@ def run_tp_set(torch, qb, lib, dev, rank, world, dist, args, comm):
         if comm == "nccl":
             Bl, sl, gl = loc[block]
             rc = lib.qb_reduce_norm_quant(s0, Tl * H, world, res.data_ptr(), wnorm.data_ptr(), hout.data_ptr(), ptr_array([Bl.data_ptr()]),
-                                          ptr_array([sl.data_ptr()]), ptr_array([gl.data_ptr()]), 0, 0, Tl, Tl, H, 1e-5, block, 0, 0, None, 0, 0, 0, 0, S())
+                                          ptr_array([sl.data_ptr()]), ptr_array([gl.data_ptr()]), 0, 0, Tl, Tl, H, 1e-5, block, 0, 0, None, 0, 0, 0, 0, 0,
+                                          S())
             assert rc == 0, rc
             for dst, src in zip(full[block], loc[block]):
                 dist.all_gather_into_tensor(dst, src)
             launches[0] += 1
             return tuple(t.data_ptr() for t in full[block])
-        fw = ctx.FLAG_GATHER[block]
-        val = ctx.next_value(fw)
-        Bv, Sv, Gv = ctx.gathered_ptrs(block)
+        Bv, Sv, Gv = gat[block]
         rc = lib.qb_reduce_norm_quant(s0, Tl * H, world, res.data_ptr(), wnorm.data_ptr(), hout.data_ptr(), Bv, Sv, Gv, world, rank * Tl, TOK, Tl, H,
-                                      1e-5, block, ctx.flag_own(ctx.FLAG_SLOT[k]), ctx.counter[ctx.FLAG_SLOT[k]], ctx.flag_ptrs(fw), world, rank, val,
-                                      ctx.done[2 + (block == 32):].data_ptr(), S())
+                                      1e-5, block, ctx.flag_own(ctx.FLAG_SLOT[k]), 0, gat_flags[block], world, rank, 0,
+                                      ctx.done[2 + (block == 32):].data_ptr(), ep, S())
         assert rc == 0, rc
         launches[0] += 1
-        return ("gathered", block, val)
+        return ("gathered", block)
 
     def resolve(q, block):
         if isinstance(q[0], str):
-            rc = lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), world, q[2], S())
+            rc = lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), world, 0, ep, S())
             assert rc == 0, rc
             launches[0] += 1
             return ctx.gathered_own(block)
         return q
 
-    state = {"q16": None}
-
-    def step():
-        q16 = state["q16"]
-        if q16 is None:            # first step: a reduce over (zero) slots produces the first gathered activations
-            row_gemm("down", 1)
-            q16 = reduce_gather(1, 16)
-        col_gemm("qkv", resolve(q16, 16))
+    def step_body(q16):
+        """One step; with peer stores every flag of the step carries the step count read from `epoch`. The per-16 gathered
+        activations that the qkv GEMM reads were produced by the LAST reduce of the previous step (flag value = step - 1
+        there), so the first wait of a step runs before the bump."""
+        if comm == "peer":
+            q16r = resolve(q16, 16)
+            rc = lib.qb_epoch_add(ep, 1, S())
+            assert rc == 0, rc
+            launches[0] += 1
+        else:
+            q16r = q16
+        col_gemm("qkv", q16r)
         row_gemm("o_proj", 0)
         q32 = reduce_gather(0, 32)
         q = resolve(q32, 32)
         col_gemm("gate", q)
         col_gemm("up", q)
         row_gemm("down", 1)
-        state["q16"] = reduce_gather(1, 16)
+        return reduce_gather(1, 16)
+
+    # prologue (eager): a reduce over the zero-filled slots produces the first gathered per-16 activations at epoch 0
+    state = {"q16": reduce_gather(1, 16)}
+    torch.cuda.synchronize()
+    dist.barrier()               # every rank's first rows have landed everywhere before any rank's first step reads them
+    graph = None
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            state["q16"] = step_body(state["q16"])
 
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     dist.barrier()
+    timing = "eager"
+    if comm == "peer":
+        # capture one step on a side stream; all ranks replay the same graph the same number of times
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g_ = torch.cuda.CUDAGraph()
+        launches[0] = 0
+        with torch.cuda.graph(g_, stream=side):
+            step_body(state["q16"])
+        graph = g_
+        per_step = launches[0]
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        timing = "one CUDA graph replay per step"
     launches[0] = 0
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) as cs:
@@ -383,6 +423,8 @@ def run_tp_set(torch, qb, lib, dev, rank, world, dist, args, comm):
     tt = torch.tensor([t], device=dev)
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     t = float(tt.item())
+    if graph is not None:
+        launches[0] = per_step * args.steps
     stt = torch.tensor([lib.qb_status(0) or lib.qb_peer_status(0)], device=dev)
     dist.all_reduce(stt, op=dist.ReduceOp.MAX)          # every rank sees the worst status and raises at the same point
     n_launch = launches[0]
@@ -390,7 +432,7 @@ def run_tp_set(torch, qb, lib, dev, rank, world, dist, args, comm):
     ctx.close()
     if int(stt.item()):
         raise RuntimeError(f"device status {int(stt.item())}")
-    return t, n_launch, cs.summary()
+    return t, n_launch, dict(cs.summary(), timing=timing)
 
 
 def run_tp(torch, qb, lib, dev, rank, world, dist, args, peaks):

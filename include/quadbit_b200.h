@@ -274,9 +274,13 @@ int qb_peer_open(const void* handle64, void** ptr);
 int qb_peer_close(void* ptr);
 /* One-thread kernels on `stream`: signal writes `value` into word my_rank of each of the n flag arrays (after a
  * system-scope fence; stream order puts it after the kernels it announces); wait returns when all n words of `flags`
- * are >= value, or after 20 s with a status code (qb_peer_status). */
+ * are >= value (or >= *value_ptr when that is not NULL), or after 20 s with a status code (qb_peer_status). */
 int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, void* stream);
-int qb_peer_wait(const void* flags, int n, int value, void* stream);
+int qb_peer_wait(const void* flags, int n, int value, const void* value_ptr, void* stream);
+/* *epoch += delta by one thread on `stream`. The entries here that take a `value_ptr` read their flag value(s) from that
+ * device word when the kernel runs instead of from the argument, so a captured CUDA graph can be replayed: every replay
+ * first bumps the word, on every rank. */
+int qb_epoch_add(void* epoch, int delta, void* stream);
 int qb_peer_status(void* stream);
 /* Row-parallel GEMM fused with the reduce-scatter of its partial result (replaces "GEMM, then all_reduce"): operands as
  * qb_gemm (this rank's K slice), token-major bf16 output; token row t is stored by the epilogue into
@@ -285,7 +289,7 @@ int qb_peer_status(void* stream);
  * this device, zero between calls. Prefill sizes only: out % 256 == 0, tok >= 128, tok_per_rank % 16 == 0. */
 int qb_gemm_rs(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA, const void* gB,
                void* const* peer_out, void* const* peer_flags, void* done_counter, int out, int tok, int K, int sparse, int n_ranks,
-               int rank, int tok_per_rank, int flag_value, int bn, void* stream);
+               int rank, int tok_per_rank, int flag_value, const void* value_ptr, int bn, void* stream);
 /* Consumer of qb_gemm_rs fused with the next block's input: v = sum_i src_i (fp32, source order; src_i = src0 + i *
  * src_stride elements, bf16 [tok][H]) + res; hout = bf16(v); y = rmsnorm(v) * wt; two-level NVFP4 quantiser of y.
  * wait_flags (may be NULL): every CTA first waits until its nsrc words are >= wait_val. fan == 0: outputs go to
@@ -295,7 +299,12 @@ int qb_gemm_rs(const void* A, const void* B, const void* sfa, const void* sfb, c
 int qb_reduce_norm_quant(const void* src0, long long src_stride, int nsrc, const void* res, const void* wt, void* hout,
                          void* const* Bbytes_v, void* const* sf_atoms_v, void* const* g_v, int fan, int row0, int tok_total, int tok,
                          int H, float eps, int block, const void* wait_flags, int wait_val, void* const* sig_flags, int sig_n,
-                         int sig_rank, int sig_val, void* done_counter, void* stream);
+                         int sig_rank, int sig_val, void* done_counter, const void* value_ptr, void* stream);
+/* Rotary position embedding in place on a token-major bf16 matrix x [tok][row_stride] whose first n_heads * 128 columns
+ * are heads of 128 values (the q and k heads of a QKV GEMM output): rotate-half convention, position = row % seq,
+ * cos_sin fp32 [seq][128] = cos[0:64] | sin[0:64]; fp32 arithmetic, one rounding to bf16. No reference counterpart (the
+ * reference leaves RoPE to the framework, harness/real_model.py:181-188). */
+int qb_rope_inplace(void* x, const void* cos_sin, int tok, int seq, long long row_stride, int n_heads, void* stream);
 /* Synchronise `stream`, return and clear the device status word (0 = no error). */
 int qb_status(void* stream);
 /* Error code of the last void-returning entry point on this thread. */

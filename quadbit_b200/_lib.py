@@ -72,10 +72,12 @@ _SIGS = {
     "qb_peer_open": ([P, P], I),
     "qb_peer_close": ([P], I),
     "qb_peer_signal": ([P, I, I, I, P], I),
-    "qb_peer_wait": ([P, I, I, P], I),
+    "qb_peer_wait": ([P, I, I, P, P], I),
+    "qb_epoch_add": ([P, I, P], I),
     "qb_peer_status": ([P], I),
-    "qb_gemm_rs": ([P] * 10 + [I] * 9 + [P], I),
-    "qb_reduce_norm_quant": ([P, c_longlong, I] + [P] * 6 + [I] * 5 + [c_float, I, P, I, P, I, I, I, P, P], I),
+    "qb_gemm_rs": ([P] * 10 + [I] * 8 + [P, I, P], I),
+    "qb_reduce_norm_quant": ([P, c_longlong, I] + [P] * 6 + [I] * 5 + [c_float, I, P, I, P, I, I, I, P, P, P], I),
+    "qb_rope_inplace": ([P, P, I, I, c_longlong, I, P], I),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),
     "qb_status": ([P], I),
     "qb_last_error": ([], I),

@@ -563,6 +563,7 @@ struct KParams2 {
     __nv_bfloat16* peer_out[8];
     int* peer_flags[8];
     int* peer_done;
+    const int* peer_val_ptr;
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
@@ -1050,8 +1051,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (atomicAdd(p.peer_done, 1) == (int)gridDim.x - 1) {
             atomicExch(p.peer_done, 0);
             __threadfence_system();
+            const int val = p.peer_val_ptr ? *p.peer_val_ptr : p.peer_val;
             for (int r = 0; r < p.peer_n; r++)
-                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flags[r] + p.peer_rank), "r"(p.peer_val) : "memory");
+                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flags[r] + p.peer_rank), "r"(val) : "memory");
         }
     }
 }
@@ -1211,7 +1213,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.num_m2 = a.out_f / 256; kp.num_n = (a.tok + BN - 1) / BN; kp.kblocks = kblocks; kp.out_mode = a.out_mode;
     kp.a_tiled = a.a_tiled;
     kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w; kp.bias_ld = a.bias_ld > 0 ? a.bias_ld : a.out_f;
-    kp.peer_n = a.peer_n; kp.peer_rank = a.peer_rank; kp.tok_per_rank = a.tok_per_rank; kp.peer_val = a.peer_val; kp.peer_done = a.peer_done;
+    kp.peer_n = a.peer_n; kp.peer_rank = a.peer_rank; kp.tok_per_rank = a.tok_per_rank; kp.peer_val = a.peer_val; kp.peer_done = a.peer_done; kp.peer_val_ptr = a.peer_val_ptr;
     for (int r = 0; r < 8; r++) { kp.peer_out[r] = (__nv_bfloat16*)a.peer_out[r]; kp.peer_flags[r] = a.peer_flags[r]; }
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;

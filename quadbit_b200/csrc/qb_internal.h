@@ -45,6 +45,7 @@ struct ReduceNormArgs {
     int sig_n, sig_rank, sig_val;
     int* sig_flags[8];
     int* done;
+    const int* val_ptr;        // non-null: wait_val and sig_val are both read from this device word when the kernel runs
 };
 int reduce_norm_quant(const ReduceNormArgs& a, cudaStream_t st);
 int quant_status_read_clear();
@@ -104,6 +105,7 @@ struct GemmArgs {
     void* peer_out[8];
     int* peer_flags[8];
     int* peer_done;        // arrival counter of this device's CTAs, zero between calls
+    const int* peer_val_ptr;   // non-null: the flag value is read from this device word when the kernel runs (graph replay)
 };
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);
 int gemm_init_attrs();

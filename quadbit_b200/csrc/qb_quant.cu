@@ -311,6 +311,7 @@ struct NormTP {
     int* sig_flags[8];
     int* done;
     int* status;
+    const int* val_ptr;
 };
 __device__ int g_quant_status = 0;
 
@@ -340,7 +341,8 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
         if ((int)threadIdx.x < tp.nsrc) {
             const uint64_t t0 = globaltimer_ns();
             uint32_t it = 0;
-            while (ld_acquire_sys(tp.wait_flags + threadIdx.x) < tp.wait_val) {
+            const int want = tp.val_ptr ? *tp.val_ptr : tp.wait_val;
+            while (ld_acquire_sys(tp.wait_flags + threadIdx.x) < want) {
                 __nanosleep(200);
                 if ((++it & 255u) == 0 && globaltimer_ns() - t0 > 20000000000ull) {      // 20 s
                     atomicCAS(tp.status, 0, QB_ERR_TIMEOUT * 100 + 20);
@@ -488,10 +490,25 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
             if (atomicAdd(tp.done, 1) == (int)gridDim.x - 1) {
                 atomicExch(tp.done, 0);
                 __threadfence_system();
-                for (int d = 0; d < tp.sig_n; d++) st_release_sys(tp.sig_flags[d] + tp.sig_rank, tp.sig_val);
+                const int val = tp.val_ptr ? *tp.val_ptr : tp.sig_val;
+                for (int d = 0; d < tp.sig_n; d++) st_release_sys(tp.sig_flags[d] + tp.sig_rank, val);
             }
         }
     }
+}
+
+// device address of the status word, looked up once per device (a host-side query; cached so that calls under stream
+// capture make no runtime query)
+static int* quant_status_ptr() {
+    static int* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_quant_status) != cudaSuccess) return nullptr;
+        cache[dev] = p;
+    }
+    return cache[dev];
 }
 
 static int norm_quant_launch(const void* x, const void* res, const void* wt, void* hout, void* Bbytes, void* sf_ref, void* sf_atoms,
@@ -544,8 +561,9 @@ int reduce_norm_quant(const ReduceNormArgs& a, cudaStream_t st) {
     tp.fan = a.fan;
     tp.row0 = a.row0;
     tp.tok_total = a.tok_total;
-    tp.sig_n = a.sig_n; tp.sig_rank = a.sig_rank; tp.sig_val = a.sig_val; tp.done = a.done;
-    if (cudaGetSymbolAddress((void**)&tp.status, g_quant_status) != cudaSuccess) return QB_ERR_DRIVER;
+    tp.sig_n = a.sig_n; tp.sig_rank = a.sig_rank; tp.sig_val = a.sig_val; tp.done = a.done; tp.val_ptr = a.val_ptr;
+    tp.status = quant_status_ptr();
+    if (!tp.status) return QB_ERR_DRIVER;
     void* Bb0 = a.Bbytes[0];
     void* sf0 = a.sf_atoms[0];
     void* g0 = a.g[0];

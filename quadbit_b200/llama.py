@@ -118,31 +118,30 @@ class LlamaPrefill:
         self._rope = {}
         self.timings = None
         self._marks = []
+        self.capture = None          # set to a dict to keep the intermediate tensors of the LAST layer run (tests)
 
     # ------------------------------------------------------------------ pieces
-    def _rope_tables(self, S: int):
+    def _rope_table(self, S: int) -> torch.Tensor:
+        """fp32 [S, 128] = cos | sin of pos * theta^(-2i/128); computed on the host so that every device (and the CPU
+        oracle) uses the same bits."""
         if S not in self._rope:
             hd = self.cfg.head_dim
-            inv = 1.0 / (self.cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=self.device) / hd))
-            ang = torch.outer(torch.arange(S, dtype=torch.float32, device=self.device), inv)
-            self._rope[S] = (torch.cos(ang).to(torch.bfloat16)[None, :, None, :], torch.sin(ang).to(torch.bfloat16)[None, :, None, :])
+            inv = 1.0 / (self.cfg.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+            ang = torch.outer(torch.arange(S, dtype=torch.float32), inv)
+            self._rope[S] = torch.cat([torch.cos(ang), torch.sin(ang)], 1).contiguous().to(self.device)
         return self._rope[S]
 
-    @staticmethod
-    def _apply_rope(x, cos, sin):
-        h = x.shape[-1] // 2
-        x1, x2 = x[..., :h], x[..., h:]
-        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
-
     def _attention(self, qkv: torch.Tensor, B: int, S: int) -> torch.Tensor:
-        """qkv [T, (hq + 2 hk) * hd] bf16 of this rank's heads -> [T, hq * hd] bf16 (RoPE, causal GQA attention)."""
+        """qkv [T, (hq + 2 hk) * hd] bf16 of this rank's heads -> [T, hq * hd] bf16: RoPE in place on the q and k heads
+        (qb_rope_inplace), then causal GQA attention in bf16 (torch SDPA)."""
         cfg = self.cfg
         hd, hq, hk = cfg.head_dim, cfg.n_heads // self.world, cfg.n_kv_heads // self.world
+        assert hd == 128
+        check(self.lib.qb_rope_inplace(qkv.data_ptr(), self._rope_table(S).data_ptr(), B * S, S, qkv.shape[1], hq + hk, _stream()),
+              "qb_rope_inplace")
         q = qkv[:, : hq * hd].view(B, S, hq, hd)
         k = qkv[:, hq * hd:(hq + hk) * hd].view(B, S, hk, hd)
         v = qkv[:, (hq + hk) * hd:].view(B, S, hk, hd)
-        cos, sin = self._rope_tables(S)
-        q, k = self._apply_rope(q, cos, sin), self._apply_rope(k, cos, sin)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True)
         return o.transpose(1, 2).reshape(B * S, hq * hd)
 
@@ -173,7 +172,7 @@ class LlamaPrefill:
         check(self.lib.qb_gemm_rs(lin.At.data_ptr(), Bb.data_ptr(), lin.sfa.data_ptr(), sfb.data_ptr(),
                                   0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(), gB.data_ptr(), ctx.slot_out_ptrs(k),
                                   ctx.flag_ptrs(ctx.FLAG_SLOT[k]), ctx.done[k:].data_ptr(), out_f, tok, in_f, 2 if dense else 3, self.world,
-                                  self.rank, ctx.Tl, val, 0, _stream()), "qb_gemm_rs")
+                                  self.rank, ctx.Tl, val, 0, 0, _stream()), "qb_gemm_rs")
         return None
 
     def _norm_quant(self, src, k, res, wt, block: int, T: int):
@@ -190,7 +189,7 @@ class LlamaPrefill:
             sf = torch.empty(lib.qb_sf_atoms_bytes(T, H, block), dtype=torch.uint8, device=self.device)
             g = torch.empty((T,), dtype=torch.float32, device=self.device)
             check(lib.qb_reduce_norm_quant(src.data_ptr(), 0, 1, rp, wt.data_ptr(), hp, ptr_array([Bb.data_ptr()]), ptr_array([sf.data_ptr()]),
-                                           ptr_array([g.data_ptr()]), 0, 0, T, T, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, _stream()),
+                                           ptr_array([g.data_ptr()]), 0, 0, T, T, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, 0, _stream()),
                   "qb_reduce_norm_quant")
             self._keep = (Bb, sf, g)
             return hout, (Bb.data_ptr(), sf.data_ptr(), g.data_ptr())
@@ -205,7 +204,7 @@ class LlamaPrefill:
             sl = torch.empty(lib.qb_sf_atoms_bytes(Tl, H, block), dtype=torch.uint8, device=self.device)
             gl = torch.empty((Tl,), dtype=torch.float32, device=self.device)
             check(lib.qb_reduce_norm_quant(s0, stride, nsrc, rp, wt.data_ptr(), hp, ptr_array([Bl.data_ptr()]), ptr_array([sl.data_ptr()]),
-                                           ptr_array([gl.data_ptr()]), 0, 0, Tl, Tl, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, _stream()),
+                                           ptr_array([gl.data_ptr()]), 0, 0, Tl, Tl, H, self.cfg.rms_eps, block, 0, 0, None, 0, 0, 0, 0, 0, _stream()),
                   "qb_reduce_norm_quant")
             Bb = torch.empty((T, H // 2), dtype=torch.uint8, device=self.device)
             sf = torch.empty(lib.qb_sf_atoms_bytes(T, H, block), dtype=torch.uint8, device=self.device)
@@ -221,14 +220,14 @@ class LlamaPrefill:
         Bv, Sv, Gv = ctx.gathered_ptrs(block)
         check(lib.qb_reduce_norm_quant(s0, stride, nsrc, rp, wt.data_ptr(), hp, Bv, Sv, Gv, W, self.rank * Tl, T, Tl, H, self.cfg.rms_eps,
                                        block, wait_ptr, wait_val, ctx.flag_ptrs(fw), W, self.rank, val, ctx.done[2 + (block == 32):].data_ptr(),
-                                       _stream()), "qb_reduce_norm_quant")
+                                       0, _stream()), "qb_reduce_norm_quant")
         return hout, ("gathered", block, val)
 
     def _resolve(self, q, block: int):
         """Pointers of the gathered activations; with peer stores, first wait until every rank's rows have landed."""
         if isinstance(q[0], str):
             ctx = self.ctx
-            check(self.lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), self.world, q[2], _stream()), "qb_peer_wait")
+            check(self.lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), self.world, q[2], 0, _stream()), "qb_peer_wait")
             return ctx.gathered_own(block)
         return q
 
@@ -248,23 +247,34 @@ class LlamaPrefill:
         yield None
         for li, L in enumerate(self.layers):
             Bb, sf, g = self._resolve(q16, 16)
+            self._cap_gathered("q16", (Bb, sf, g), 16, T)
+            self._cap("x_attn_in", x)
             qkv = torch.empty((T, L.qkv.out), dtype=torch.bfloat16, device=self.device)
             self._gemm(L.qkv, Bb, sf, g, T, qkv)
             self._mark("qkv_gemm")
+            self._cap("qkv", qkv)
             attn = self._attention(qkv, B, S)
             self._mark("rope+attention")
+            self._cap("attn", attn)
             aq = self._quantize(attn, 16)
             self._mark("act_quant")
             o = self._row_parallel(L.wo, aq, T, 0)
             self._mark("o_proj_gemm")
             yield None
+            if self.capture is not None:
+                if W > 1 and self.comm == "peer":          # test aid: the partials must have landed before they are copied
+                    check(lib.qb_peer_wait(self.ctx.flag_own(0), W, self.ctx.counter[0], 0, _stream()), "qb_peer_wait")
+                self._cap("o_parts", o.unsqueeze(0) if W == 1 else self.ctx.slots_view(0))
             x, q32 = self._norm_quant(o, 0, x, L.norm_mlp, 32, T)
             self._mark("reduce+norm_quant")
             yield None
+            self._cap("x_mlp_in", x)
             Bb, sf, g = self._resolve(q32, 32)
+            self._cap_gathered("q32", (Bb, sf, g), 32, T)
             cgu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=self.device)
             self._gemm(L.gu, Bb, sf, g, T, cgu)
             self._mark("gate_up_gemm")
+            self._cap("cgu", cgu)
             Hb = torch.empty((T, I // 2), dtype=torch.uint8, device=self.device)
             sfh = torch.empty(lib.qb_sf_atoms_bytes(T, I, 32), dtype=torch.uint8, device=self.device)
             gH = torch.empty((T,), dtype=torch.float32, device=self.device)
@@ -273,6 +283,10 @@ class LlamaPrefill:
             d = self._row_parallel(L.dn, (Hb, sfh, gH), T, 1)
             self._mark("down_gemm")
             yield None
+            if self.capture is not None:
+                if W > 1 and self.comm == "peer":
+                    check(lib.qb_peer_wait(self.ctx.flag_own(1), W, self.ctx.counter[1], 0, _stream()), "qb_peer_wait")
+                self._cap("d_parts", d.unsqueeze(0) if W == 1 else self.ctx.slots_view(1))
             if li + 1 < len(self.layers):
                 x, q16 = self._norm_quant(d, 1, x, self.layers[li + 1].norm_attn, 16, T)
                 self._mark("reduce+norm_quant")
@@ -283,7 +297,7 @@ class LlamaPrefill:
         else:
             ctx = self.ctx
             if self.comm == "peer":
-                check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_SLOT[1]), W, ctx.counter[ctx.FLAG_SLOT[1]], _stream()), "qb_peer_wait")
+                check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_SLOT[1]), W, ctx.counter[ctx.FLAG_SLOT[1]], 0, _stream()), "qb_peer_wait")
             sl = ctx.slots_view(1).float()
             v = sl[0]
             for s in range(1, W):
@@ -317,6 +331,20 @@ class LlamaPrefill:
             self.timings[name] = self.timings.get(name, 0.0) + e0.elapsed_time(e1)
         self._marks = []
         return self.timings
+
+    def _cap(self, name: str, t):
+        if self.capture is not None:
+            self.capture[name] = t.clone() if isinstance(t, torch.Tensor) else t
+
+    def _cap_gathered(self, name: str, q, block: int, T: int):
+        """Copy of the quantised activations a column-parallel GEMM is about to read: (Bbytes, atoms, g)."""
+        if self.capture is None:
+            return
+        from .tp import view_u8
+        H = self.cfg.hidden
+        nb, ns = T * H // 2, self.lib.qb_sf_atoms_bytes(T, H, block)
+        self.capture[name] = (view_u8(q[0], nb, self.device).clone().view(T, H // 2), view_u8(q[1], ns, self.device).clone(),
+                              view_u8(q[2], T * 4, self.device).clone().view(torch.float32))
 
     def _quantize(self, x: torch.Tensor, block: int):
         lib = self.lib

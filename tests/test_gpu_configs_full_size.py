@@ -117,14 +117,17 @@ def test_moe_layer_config4_full_size():
     sample = torch.linspace(0, T - 1, 12).round().long()
     ref = torch.zeros(len(sample), H)
     seen = set()
+    Hp = (H + 127) // 128 * 128                      # the layer zero-pads the hidden and intermediate sizes to 128 (2880 -> 2944)
+    pad_k = lambda w: torch.nn.functional.pad(w.float().cpu(), (0, Hp - w.shape[1]))
     for i, t in enumerate(sample.tolist()):
+        xt = torch.nn.functional.pad(x[t:t + 1].float(), (0, Hp - H))
         for k in range(topk):
             e = int(idx[t, k])
             seen.add(e)
-            gu = fq.linear_sparse(x[t:t + 1].float(), wgu[e].float().cpu()).to(torch.bfloat16).float()
+            gu = fq.linear_sparse(xt, pad_k(wgu[e])).to(torch.bfloat16).float()
             gt, up = gu[:, :I].clamp(max=7.0), gu[:, I:].clamp(-7.0, 7.0)
-            h = (gt * torch.sigmoid(1.702 * gt)) * (up + 1.0)
-            d = torch.nn.functional.linear(fq.act_dequant_2lvl(h, 32, round_bf16=False), fq.sparse_fp4_dequant_2lvl(wdn[e].float().cpu()))
+            h = torch.nn.functional.pad((gt * torch.sigmoid(1.702 * gt)) * (up + 1.0), (0, Hp - I))
+            d = torch.nn.functional.linear(fq.act_dequant_2lvl(h, 32, round_bf16=False), fq.sparse_fp4_dequant_2lvl(pad_k(wdn[e])))
             ref[i] += (d * w[t, k]).to(torch.bfloat16).float()[0]
     assert max(seen) - min(seen) > E // 2            # the sampled rows reach experts over the whole range
     got = y[sample.cuda()].float().cpu()
