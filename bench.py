@@ -199,7 +199,7 @@ def model_flops(cfg, B, S):
     return lin, attn
 
 
-def run_model(torch, qb, dev, rank, world, dist, args, comm="peer", layers=32, batch=16, seq=2048, steps=3, ctx=None):
+def run_model(torch, qb, dev, rank, world, dist, args, comm="peer", layers=32, batch=16, seq=2048, steps=3, ctx=None, fuse_swiglu=False):
     """One rank of the tensor-parallel prefill forward; returns the result dict on every rank (times are max over ranks)."""
     from quadbit_b200.llama import LlamaConfig, LlamaPrefill, random_weights
     from quadbit_b200.tp import TPContext
@@ -209,7 +209,7 @@ def run_model(torch, qb, dev, rank, world, dist, args, comm="peer", layers=32, b
     if world > 1 and ctx is None:
         own_ctx = ctx = TPContext(T, cfg.hidden, rank, world)
         dist.barrier()
-    model = LlamaPrefill(cfg, random_weights(cfg, 2, dev), rank=rank, world=world, comm=comm, ctx=ctx)
+    model = LlamaPrefill(cfg, random_weights(cfg, 2, dev), rank=rank, world=world, comm=comm, ctx=ctx, fuse_swiglu=fuse_swiglu)
     ids = torch.randint(0, cfg.vocab, (batch, seq), generator=torch.Generator().manual_seed(2))
     ids_d = ids.to(dev)
     for _ in range(2):
@@ -597,6 +597,7 @@ def run_gpu(args):
         wgu = [(torch.randn(2 * Hh, Hh, device=dev, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(e0, e1)]
         wdn = [(torch.randn(Hh, Hh, device=dev, generator=gen) * 0.02).to(torch.bfloat16) for _ in range(e0, e1)]
         moe = qb.SparseMoE(wgu, wdn, topk, act="gptoss", expert_range=(e0, e1), n_experts_total=E)
+        moe_f = qb.SparseMoE(wgu, wdn, topk, act="gptoss", fixed_capacity=True, fused_gu=True) if world == 1 else None
         del wgu, wdn
         g2 = torch.Generator(device="cpu").manual_seed(3)
         xs = torch.randn(T, Hh, generator=g2).to(torch.bfloat16)
@@ -643,6 +644,22 @@ def run_gpu(args):
             same = bool(torch.equal(y_graph, moe.forward(x_l, i_l, w_l)))
             graph = {"ms_per_step": tg * 1e3, "tokens_per_s": T / tg, "useful_tflops": fl / tg / 1e12, "equals_eager": same,
                      "what": "SparseMoE.forward with fixed-capacity routing replayed from one CUDA graph"}
+            # the same with SwiGLU + quantiser fused into the epilogue of the grouped gate/up GEMM (single-level h)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    moe_f.forward(x_l, i_l, w_l)
+            torch.cuda.current_stream().wait_stream(side)
+            cgf = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cgf):
+                y_f = moe_f.forward(x_l, i_l, w_l)
+            for _ in range(3):
+                cgf.replay()
+            tf_ = ev_time(cgf.replay, min(args.steps, 50))
+            relf = float(((y_f.float() - y_graph.float()).norm() / y_graph.float().norm()).item())
+            graph["fused_gate_up"] = {"ms_per_step": tf_ * 1e3, "tokens_per_s": T / tf_, "useful_tflops": fl / tf_ / 1e12,
+                                      "rel_l2_vs_two_level": relf,
+                                      "what": "SwiGLU + single-level per-32 quantiser in the epilogue of the grouped gate/up GEMM (qb_gemm_swiglu)"}
         if rank == 0:
             print(json.dumps({"metric": "MoE layer tokens/s (2:4-sparse NVFP4 experts, expert parallel)", "value": T / t, "unit": "tokens/s",
                               "n_gpus": world, "steps": min(args.steps, 50), "warmup": max(args.warmup, 3), "ms_per_step": t * 1e3,
@@ -842,6 +859,34 @@ def run_gpu(args):
                                        "routing weight in the epilogue; SwiGLU, gather and combine not included"}
         del w_gu, w_dn, rows, hrows
 
+        # ---- what one rank of the tensor-parallel step computes, kernel by kernel on this GPU (no exchange: slots are local):
+        #      the compute-side floor of `bench.py --gpus W`, to set beside its measured step time and its NVLink floor
+        from quadbit_b200.tp import ptr_array
+        tp_floor = {}
+        for Wn in (2, 4, 8):
+            ks = {}
+            for (name, n, k, par) in SHAPES:
+                n_l, k_l = (n // Wn, k) if par == "col" else (n, k // Wn)
+                lin = qb.QuadbitLinear((torch.randn(n_l, k_l, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
+                xq = qb.quantize_act(lib, torch.randn(TOK, k_l, device=dev).to(torch.bfloat16), 32, True)
+                ks[name] = ev_time(lambda: lin.run(xq[0], xq[1], TOK, xq[2], out_t=True), 10, 3) * 1e6
+                del lin, xq
+            Tl = TOK // Wn
+            slots = torch.randn(Wn, Tl, 4096, device=dev).to(torch.bfloat16)
+            resd = torch.randn(Tl, 4096, device=dev).to(torch.bfloat16)
+            hout = torch.empty_like(resd)
+            wn = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+            Bl = torch.empty((Tl, 2048), dtype=torch.uint8, device=dev)
+            sl = torch.empty(lib.qb_sf_atoms_bytes(Tl, 4096, 32), dtype=torch.uint8, device=dev)
+            gl = torch.empty(Tl, device=dev)
+            pa = (ptr_array([Bl.data_ptr()]), ptr_array([sl.data_ptr()]), ptr_array([gl.data_ptr()]))
+            ks["reduce_norm_quant"] = ev_time(lambda: lib.qb_reduce_norm_quant(slots.data_ptr(), Tl * 4096, Wn, resd.data_ptr(), wn.data_ptr(), hout.data_ptr(),
+                                                                                 pa[0], pa[1], pa[2], 0, 0, Tl, Tl, 4096, 1e-5, 32, 0, 0, None, 0, 0, 0, 0, 0,
+                                                                                 torch.cuda.current_stream().cuda_stream), 10, 3) * 1e6
+            ks["sum_us"] = sum(v for kk, v in ks.items() if kk != "reduce_norm_quant") + 2 * ks["reduce_norm_quant"]
+            tp_floor[f"tp{Wn}"] = ks
+        line["tp_rank_kernels_us"] = tp_floor
+
         # ---- end to end through the module API with host buffers (H2D + quantise + GEMM + D2H)
         hx = [torch.randn(TOK, L["k"]).to(torch.bfloat16).pin_memory() for L in layers]
         hy = [torch.empty((TOK, L["n"]), dtype=torch.bfloat16).pin_memory() for L in layers]
@@ -936,6 +981,11 @@ def run_gpu(args):
             try:
                 torch.cuda.empty_cache()
                 line["model"] = run_model(torch, qb, dev, 0, 1, None, args)
+                torch.cuda.empty_cache()
+                mf = run_model(torch, qb, dev, 0, 1, None, args, fuse_swiglu=True)
+                line["model"]["fused_swiglu_epilogue"] = {k: mf[k] for k in ("tokens_per_s", "ms_per_forward", "ms_per_layer_breakdown_rank0")}
+                line["model"]["fused_swiglu_epilogue"]["what"] = ("SwiGLU + single-level quantiser of h in the gate/up GEMM epilogue (different "
+                                                                    "arithmetic for h than the default, which matches the reference's fused_mlp_2lvl)")
             except Exception as e:
                 line["model"] = {"unavailable": f"{type(e).__name__}: {e}"}
     elif rank == 0:

@@ -262,6 +262,40 @@ int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void
  * u64[SM count] of SM clock cycles; status_word: i32, non-zero if a bounded wait expired.
  * bn = 128 or 256. Time it with events around the call. */
 int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, void* status_word, void* stream);
+/* Gate/up GEMM with SwiGLU + single-level per-32 quantiser in its epilogue, native layouts (what sparse_moe_gu_swiglu,
+ * cuda/sparse_fp4_lib.cu:1679-1875, does on the reference's layouts): operands as qb_gemm, A's rows are (gate, up) pairs
+ * (row 2i = gate feature i, row 2i + 1 = up feature i, `out` rows per expert), optional grouped mode (eblk, a_rows = experts
+ * * out) and bf16 bias [experts][out] added before the activation. h = act(gate, up) is formed from the fp32 accumulators
+ * and quantised with one UE4M3 scale per 32 features (no global): Hb[tok][out/4] packed codes, scale codes as 128x4 atoms
+ * (sf_atoms) and / or [out/256][tok][4] (sf_ref). act 0: clamped gpt-oss SwiGLU, 1: silu(g) * u. out % 256 == 0,
+ * tok >= 128 (grouped: tok % 128 == 0). */
+int qb_gemm_swiglu(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA, const void* gB,
+                   const void* eblk, const void* bias, void* Hb, void* sf_atoms, void* sf_ref, int a_rows, int out, int tok, int K,
+                   int sparse, int act, void* stream);
+/* ---- unit-scale FP4 entries of the reference's kernel-only benchmark libraries: C[M,N] bf16 = A[M,K] @ B[N,K]^T on raw
+ * E2M1 codes (two per byte, low nibble = even k), every block scale 1.0. N % 128 == 0, K % 128 == 0, any M.
+ * cuda/dense_fp4_lib.cu:125, cuda/dense_sk_lib.cu:147 (Cf: fp32 [M*N] workspace, used when splits > 1),
+ * cuda/dense_decode_lib.cu:116-168 (qb_encode_map returns a host handle for one operand, freed by qb_free_map; the
+ * _cached entries take two of them; _async does not synchronise and reports through qb_last_error),
+ * cuda/sparse_sk_lib.cu:199 (single-level 2:4-sparse split-K on reference layouts, C[M][N], A = the sparse weight). */
+int dense_fp4_mm(const void* A, const void* B, void* C, int M, int N, int K);
+int dense_fp4_mm_sk(const void* A, const void* B, void* C, void* Cf, int M, int N, int K, int splits);
+int qb_decode_tn(int N);
+int dense_fp4_decode(const void* A, const void* B, void* C, int M, int N, int K);
+void* qb_encode_map(const void* ptr, int rows, int K, int boxrows);
+void qb_free_map(void* m);
+int dense_fp4_decode_cached(const void* mapA, const void* mapB, void* C, int M, int N, int K);
+void dense_fp4_decode_cached_async(const void* mapA, const void* mapB, void* C, int M, int N, int K);
+int sparse_fp4_mm_sk(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, void* Cf, int M,
+                     int N, int Klog, int splits);
+/* Register a weight's reference-layout scale factors [K/128][rows][4 or 8] (and metadata [K/128][rows][2] i32 when sparse):
+ * the layouts the tensor-core kernels read are made once and every later call of a reference-named GEMM entry with the
+ * same pointers uses them instead of re-laying the weight (the reference consumes its layouts as they are,
+ * cuda/sparse_fp4_lib.cu:1029-1046, so its callers pay no such step). Two device allocations per weight, made here and
+ * kept until qb_forget_weight(scaleA); the registered arrays must not change meanwhile. Unregistered weights keep
+ * working (re-laid per call). */
+int qb_register_weight(const void* scaleA, const void* meta, int rows, int K, int sparse, void* stream);
+int qb_forget_weight(const void* scaleA);
 /* ---- tensor parallelism over one NVSwitch box (one process per GPU). No counterpart in the reference library: its
  * one distributed script computes, then calls all_reduce (harness/moe_dist.py:123,161-167).
  * Peer buffers: qb_peer_alloc = cudaMalloc + zero fill (set-up time only); qb_peer_export writes the 64-byte CUDA IPC

@@ -77,6 +77,18 @@ _SIGS = {
     "qb_peer_status": ([P], I),
     "qb_gemm_rs": ([P] * 10 + [I] * 8 + [P, I, P], I),
     "qb_reduce_norm_quant": ([P, c_longlong, I] + [P] * 6 + [I] * 5 + [c_float, I, P, I, P, I, I, I, P, P, P], I),
+    "qb_gemm_swiglu": ([P] * 12 + [I] * 6 + [P], I),
+    "dense_fp4_mm": ([P] * 3 + [I] * 3, I),
+    "dense_fp4_mm_sk": ([P] * 4 + [I] * 4, I),
+    "qb_decode_tn": ([I], I),
+    "dense_fp4_decode": ([P] * 3 + [I] * 3, I),
+    "qb_encode_map": ([P, I, I, I], P),
+    "qb_free_map": ([P], None),
+    "dense_fp4_decode_cached": ([P] * 3 + [I] * 3, I),
+    "dense_fp4_decode_cached_async": ([P] * 3 + [I] * 3, None),
+    "sparse_fp4_mm_sk": ([P] * 7 + [I] * 4, I),
+    "qb_register_weight": ([P, P, I, I, I, P], I),
+    "qb_forget_weight": ([P], I),
     "qb_rope_inplace": ([P, P, I, I, c_longlong, I, P], I),
     "qb_mma_peak": ([I] * 4 + [P] * 3, I),
     "qb_status": ([P], I),

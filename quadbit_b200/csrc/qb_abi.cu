@@ -7,7 +7,10 @@
 // weight buffer in place is safe). The scratch buffer is the one device allocation the
 // library makes; it grows on demand under a mutex, so the first call at a new size must
 // happen outside CUDA-graph capture. The native qb_* entry points allocate nothing.
+#include <stdlib.h>
+
 #include <mutex>
+#include <vector>
 
 #include "../../include/quadbit_b200.h"
 #include "qb_common.cuh"
@@ -56,20 +59,47 @@ size_t sf_atoms_bytes(int rows, int K, int block) {
 }
 size_t meta_native_bytes(int out_f, int K) { return (size_t)((out_f + 127) / 128) * (size_t)(qb::kpad256(K) / 256) * 2048; }
 
+// Weights registered with qb_register_weight: their scale factors / metadata were re-laid once into buffers the library
+// owns, and the reference-named entry points that are handed the same reference-layout pointers use those instead of
+// re-laying the weight on every call. Keyed by the scale pointer; the caller says when the weight goes away.
+struct PreparedWeight {
+    const void* scaleA;
+    const void* meta;
+    int rows, K, sparse, dev;
+    void* sfa_native;
+    void* meta_native;
+};
+std::mutex g_prepared_mu;
+std::vector<PreparedWeight> g_prepared;
+
+bool prepared_lookup(const void* scaleA, const void* meta, int rows, int K, int sparse, PreparedWeight* out) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(g_prepared_mu);
+    for (const PreparedWeight& w : g_prepared)
+        if (w.scaleA == scaleA && w.meta == meta && w.rows == rows && w.K == K && w.sparse == sparse && w.dev == dev) {
+            *out = w;
+            return true;
+        }
+    return false;
+}
+
 // GEMM on reference-layout operands: re-layout into scratch, then run the native kernel.
 int ref_gemm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, float* Cf,
              int a_rows, int out_f, int tok, int K, const void* gA, const void* gB, const int* eblk, const void* bias,
              const float* row_w, int sparse, int out_mode, int splits, cudaStream_t st, size_t extra_bytes = 0,
-             void** extra = nullptr, int bias_ld = 0) {
+             void** extra = nullptr, int bias_ld = 0, void* h_bytes = nullptr, void* h_sf_ref = nullptr, int act = 0) {
     // extra_bytes / extra: a further region of the scratch buffer for the caller (an intermediate the
     // reference keeps in shared memory); with it, a null C means "write the GEMM output there"
     if (a_rows <= 0 || out_f <= 0 || tok < 0 || K <= 0 || K % 128 || a_rows % 128) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!scaleA || !scaleB || (sparse && !meta)) return QB_ERR_ARG;
     const int block = sparse ? 32 : 16;
-    size_t n_sfa = align256(sf_atoms_bytes(a_rows, K, block));
+    PreparedWeight pw{};
+    const bool cached = prepared_lookup(scaleA, meta, a_rows, K, sparse, &pw);
+    size_t n_sfa = cached ? 0 : align256(sf_atoms_bytes(a_rows, K, block));
     size_t n_sfb = align256(sf_atoms_bytes(tok, K, block));
-    size_t n_meta = sparse ? align256(meta_native_bytes(a_rows, K)) : 0;
+    size_t n_meta = (sparse && !cached) ? align256(meta_native_bytes(a_rows, K)) : 0;
     void* base = nullptr;
     int rc = scratch_get(n_sfa + n_sfb + n_meta + extra_bytes, &base);
     if (rc) return rc;
@@ -84,19 +114,28 @@ int ref_gemm(const void* A, const void* B, const void* scaleA, const void* scale
         rc = (int)cudaMemsetAsync(base, 0, n_sfa + n_sfb + n_meta, st);
         if (rc) return rc;
     }
-    rc = qb::relayout_sf(scaleA, p_sfa, a_rows, K, block, st);
-    if (rc) return rc;
+    if (!cached) {
+        rc = qb::relayout_sf(scaleA, p_sfa, a_rows, K, block, st);
+        if (rc) return rc;
+    } else {
+        p_sfa = (uint8_t*)pw.sfa_native;
+    }
     rc = qb::relayout_sf(scaleB, p_sfb, tok, K, block, st);
     if (rc) return rc;
     if (sparse) {
-        rc = qb::relayout_meta(meta, p_meta, a_rows, K, st);
-        if (rc) return rc;
+        if (!cached) {
+            rc = qb::relayout_meta(meta, p_meta, a_rows, K, st);
+            if (rc) return rc;
+        } else {
+            p_meta = (uint8_t*)pw.meta_native;
+        }
     }
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = p_sfa; g.sfb = p_sfb; g.meta = sparse ? p_meta : nullptr;
     g.gA = (const float*)gA; g.gB = (const float*)gB; g.C = C; g.Cf = Cf; g.eblk = eblk; g.bias = bias; g.row_w = row_w; g.bias_ld = bias_ld;
     g.a_rows = a_rows; g.out_f = out_f; g.tok = tok; g.K = K; g.sparse = sparse; g.out_mode = out_mode;
     g.splits = splits; g.bn = 0;
+    g.h_bytes = h_bytes; g.h_sf_ref = h_sf_ref; g.h_feats = out_f / 2; g.act = act;
     return qb::gemm_nvfp4(g, st);
 }
 
@@ -288,6 +327,128 @@ int fused_mlp_2lvl_skdown(const void* x, const void* gu_Ac, const void* gu_scale
                          Iw, gu_out, dn_out, splits, (cudaStream_t)stream);
 }
 
+// ------------------------------------------------------------------ unit-scale FP4 entries of the reference's benchmark libraries
+// C[M,N] = A[M,K] @ B[N,K]^T on raw E2M1 codes (every block scale 1.0, no globals): the reference's dense_fp4_lib /
+// dense_sk_lib / dense_decode_lib use unit ue8m0 scales for its kernel-only comparisons. Here B plays the weight (the
+// tensor-core A operand, rows = N) and A the tokens, so the token-major output of the native GEMM is C[M][N] as it is;
+// the scale-factor atoms of both operands are filled with the UE4M3 code of 1.0 (0x38) in the scratch buffer.
+static int unit_scale_gemm(const void* A, const void* B, void* C, void* Cf, int M, int N, int K, int splits, bool decode, cudaStream_t st) {
+    if (M < 0 || N <= 0 || K <= 0 || K % 128 || N % 128) return QB_ERR_ARG;
+    if (M == 0) return QB_OK;
+    if (!A || !B || !C) return QB_ERR_ARG;
+    const size_t n_w = align256(sf_atoms_bytes(N, K, 16)), n_x = align256(sf_atoms_bytes(M, K, 16));
+    size_t n_ws = 0;
+    int sp = splits < 1 ? 1 : splits, bn = 0;
+    if (decode && M <= 256) {
+        qb::decode_plan(N, M, K, &sp, &bn);
+        if (sp > 1) n_ws = align256((size_t)qb_gemm_decode_ws_bytes(N, M, K));
+    }
+    void* base = nullptr;
+    int rc = scratch_get(n_w + n_x + n_ws, &base);
+    if (rc) return rc;
+    uint8_t* sfw = (uint8_t*)base;
+    uint8_t* sfx = sfw + n_w;
+    if ((rc = (int)cudaMemsetAsync(base, 0x38, n_w + n_x, st))) return rc;
+    qb::GemmArgs g{};
+    g.A = B; g.B = A; g.sfa = sfw; g.sfb = sfx; g.C = C; g.a_rows = N; g.out_f = N; g.tok = M; g.K = K; g.sparse = 0; g.out_mode = 1;
+    g.splits = sp; g.bn = bn;
+    if (decode && sp > 1) {
+        // in-kernel split-K finish: counters + sums must be zero on entry (the scratch is shared, so zero it every call)
+        uint8_t* ws = sfx + n_x;
+        if ((rc = (int)cudaMemsetAsync(ws, 0, n_ws, st))) return rc;
+        g.sk_counters = ws;
+        g.Cf = (float*)(ws + decode_counter_bytes(N, M));
+    } else if (sp > 1) {
+        if (!Cf) return QB_ERR_ARG;
+        g.Cf = (float*)Cf;
+    }
+    return qb::gemm_nvfp4(g, st);
+}
+
+struct MapHandle {          // what qb_encode_map hands out in place of the reference's host-side CUtensorMap
+    const void* ptr;
+    int rows, K, boxrows;
+};
+
+/* cuda/dense_fp4_lib.cu:125 */
+int dense_fp4_mm(const void* A, const void* B, void* C, int M, int N, int K) {
+    return finish_sync(unit_scale_gemm(A, B, C, nullptr, M, N, K, 1, false, 0), 0);
+}
+/* cuda/dense_sk_lib.cu:147 — Cf: caller workspace of M*N floats (unused when splits == 1) */
+int dense_fp4_mm_sk(const void* A, const void* B, void* C, void* Cf, int M, int N, int K, int splits) {
+    return finish_sync(unit_scale_gemm(A, B, C, Cf, M, N, K, splits, false, 0), 0);
+}
+/* cuda/dense_decode_lib.cu:116 — the reference's token-tile width for N (kept as its callers pass it back) */
+int qb_decode_tn(int N) { return (N >= 8192 ? 8 : 4) * 8; }
+/* cuda/dense_decode_lib.cu:143 */
+int dense_fp4_decode(const void* A, const void* B, void* C, int M, int N, int K) {
+    return finish_sync(unit_scale_gemm(A, B, C, nullptr, M, N, K, 1, true, 0), 0);
+}
+/* cuda/dense_decode_lib.cu:153-158 — a reusable handle for one operand (the reference caches a tensor map; here the
+ * pointer and shape, the maps are encoded per launch) */
+void* qb_encode_map(const void* ptr, int rows, int K, int boxrows) {
+    MapHandle* h = (MapHandle*)malloc(sizeof(MapHandle));
+    if (h) { h->ptr = ptr; h->rows = rows; h->K = K; h->boxrows = boxrows; }
+    return h;
+}
+void qb_free_map(void* m) { free(m); }
+/* cuda/dense_decode_lib.cu:160,166 */
+int dense_fp4_decode_cached(const void* mapA, const void* mapB, void* C, int M, int N, int K) {
+    if (!mapA || !mapB) return QB_ERR_ARG;
+    return finish_sync(unit_scale_gemm(((const MapHandle*)mapA)->ptr, ((const MapHandle*)mapB)->ptr, C, nullptr, M, N, K, 1, true, 0), 0);
+}
+void dense_fp4_decode_cached_async(const void* mapA, const void* mapB, void* C, int M, int N, int K) {
+    t_last_error = (!mapA || !mapB) ? QB_ERR_ARG
+                                    : unit_scale_gemm(((const MapHandle*)mapA)->ptr, ((const MapHandle*)mapB)->ptr, C, nullptr, M, N, K, 1, true, 0);
+}
+/* cuda/sparse_sk_lib.cu:199 — single-level 2:4-sparse split-K GEMM on reference layouts, C[M][N], A = sparse weight */
+int sparse_fp4_mm_sk(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, void* Cf, int M,
+                     int N, int Klog, int splits) {
+    if (splits > 1 && !Cf) return QB_ERR_ARG;
+    return finish_sync(ref_gemm(A, B, scaleA, scaleB, meta, C, (float*)Cf, M, M, N, Klog, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0,
+                                splits < 1 ? 1 : splits, 0), 0);
+}
+
+/* Register a weight's reference-layout scale factors (and 2:4 metadata, sparse only) so that the reference-named GEMM
+ * entry points stop re-laying them on every call: the native copies are made once here (two allocations the library
+ * keeps until qb_forget_weight). The contents must not change while registered. */
+int qb_register_weight(const void* scaleA, const void* meta, int rows, int K, int sparse, void* stream) {
+    if (!scaleA || rows <= 0 || K <= 0 || K % 128 || rows % 128 || (sparse && !meta) || (sparse != 0 && sparse != 1)) return QB_ERR_ARG;
+    PreparedWeight w{};
+    if (prepared_lookup(scaleA, sparse ? meta : nullptr, rows, K, sparse, &w)) return QB_OK;
+    const int block = sparse ? 32 : 16;
+    const size_t n_sfa = sf_atoms_bytes(rows, K, block), n_meta = sparse ? meta_native_bytes(rows, K) : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    w.scaleA = scaleA; w.meta = sparse ? meta : nullptr; w.rows = rows; w.K = K; w.sparse = sparse;
+    cudaGetDevice(&w.dev);
+    int rc = (int)cudaMalloc(&w.sfa_native, n_sfa);
+    if (rc) return rc;
+    if (sparse && (rc = (int)cudaMalloc(&w.meta_native, n_meta))) { cudaFree(w.sfa_native); return rc; }
+    if (K % 256) {
+        cudaMemsetAsync(w.sfa_native, 0, n_sfa, st);
+        if (sparse) cudaMemsetAsync(w.meta_native, 0, n_meta, st);
+    }
+    rc = qb::relayout_sf(scaleA, w.sfa_native, rows, K, block, st);
+    if (!rc && sparse) rc = qb::relayout_meta(meta, w.meta_native, rows, K, st);
+    if (rc) { cudaFree(w.sfa_native); if (w.meta_native) cudaFree(w.meta_native); return rc; }
+    std::lock_guard<std::mutex> lk(g_prepared_mu);
+    g_prepared.push_back(w);
+    return QB_OK;
+}
+/* Drop a registration (by its scale pointer) and free its native copies; synchronises the device first. */
+int qb_forget_weight(const void* scaleA) {
+    std::lock_guard<std::mutex> lk(g_prepared_mu);
+    for (size_t i = 0; i < g_prepared.size(); i++)
+        if (g_prepared[i].scaleA == scaleA) {
+            cudaDeviceSynchronize();
+            cudaFree(g_prepared[i].sfa_native);
+            if (g_prepared[i].meta_native) cudaFree(g_prepared[i].meta_native);
+            g_prepared.erase(g_prepared.begin() + i);
+            return QB_OK;
+        }
+    return QB_ERR_ARG;
+}
+
 // ------------------------------------------------------------------ reference symbols
 int sparse_fp4_mm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C, int out,
                   int tok, int K) {
@@ -351,11 +512,30 @@ int sparse_moe_gu_swiglu(const void* A, const void* B, const void* scaleA, const
                          int rows, int K, const void* gA, const void* gB, const void* eblk, const void* guBias, void* Hwords,
                          void* scaleH, int Ih, int act, void* stream) {
     if (rows % 128 || !eblk || !Hwords || !scaleH || Ih * 2 != Mpe || Ih % 128) return QB_ERR_ARG;
+    if (Mpe % 256 == 0 && rows >= 128) {
+        // one launch: SwiGLU + quantiser in the epilogue of the grouped GEMM (the reference's fused kernel)
+        int rc = ref_gemm(A, B, scaleA, scaleB, meta, nullptr, nullptr, Mtot, Mpe, rows, K, gA, gB, (const int*)eblk, guBias, nullptr, 1, 4, 1,
+                          (cudaStream_t)stream, 0, nullptr, 0, Hwords, scaleH, act);
+        return stream ? rc : finish_sync(rc, 0);
+    }
     void* cgu = nullptr;
     int rc = ref_gemm(A, B, scaleA, scaleB, meta, nullptr, nullptr, Mtot, Mpe, rows, K, gA, gB, (const int*)eblk, guBias, nullptr,
                       1, guBias ? 3 : 1, 1, (cudaStream_t)stream, align256((size_t)rows * Mpe * 2), &cgu);
     if (!rc && rows > 0) rc = qb::swiglu_quant_ex(cgu, Hwords, scaleH, nullptr, nullptr, rows, Ih, 1, act, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);
+}
+/* Native form of the fused gate/up GEMM: operands as qb_gemm (plain or grouped with eblk / bias), A's rows are (gate, up)
+ * pairs; writes Hb[tok][out/4] and the scale codes of h (atoms and / or reference layout). */
+int qb_gemm_swiglu(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA, const void* gB,
+                   const void* eblk, const void* bias, void* Hb, void* sf_atoms, void* sf_ref, int a_rows, int out, int tok, int K,
+                   int sparse, int act, void* stream) {
+    if (sparse < 0 || sparse > 3) return QB_ERR_ARG;
+    qb::GemmArgs g{};
+    g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
+    g.eblk = (const int*)eblk; g.bias = bias; g.a_rows = a_rows; g.out_f = out; g.tok = tok; g.K = K;
+    g.sparse = sparse & 1; g.a_tiled = (sparse >> 1) & 1; g.out_mode = 4; g.splits = 1;
+    g.h_bytes = Hb; g.h_sf_atoms = sf_atoms; g.h_sf_ref = sf_ref; g.h_feats = out / 2; g.act = act;
+    return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
 int qb_moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, void* stream) {
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream);

@@ -142,9 +142,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    // launched as a programmatic dependent: barrier set-up, the tensor-memory allocation and the descriptor
-    // prefetch above ran beside the tail of the activation quantiser; its outputs are read only from here on
-    griddep_wait();
+    // Launched as a programmatic dependent: barrier set-up, the tensor-memory allocation and the descriptor prefetch above
+    // ran beside the tail of the kernel in front (the activation quantiser). Everything that kernel writes (packed
+    // activations, their scale factors and globals, routing tables) is read only after griddep_wait(); the weights are
+    // constants, so the producers stream the first ring of weight tiles BEFORE they wait (below).
+    griddep_launch_dependents();
+    const bool is_producer = warp == 0 || (warp >= 6 && warp < 9);
+    const bool prefetch_weights = p.eblk == nullptr;        // grouped mode reads its expert table first
+    if (!(is_producer && prefetch_weights)) griddep_wait();
 
     const int tiles_mn = p.num_m * p.num_n;
     const int total_tiles = tiles_mn * p.splits;
@@ -154,7 +159,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int kb_per_split = (p.kblocks + p.splits - 1) / p.splits;
     const int atoms_per_rb = p.kblocks * C::MMAS;   // scale atoms per 128-row block along K
 
-    if (warp == 0 || (warp >= 6 && warp < 9)) {
+    if (is_producer) {
         // ------------------------------------------------------------ producers
         // Four warps take the K blocks round-robin: one thread needs ~90 cycles to issue one bulk load
         // (measured) and a stage takes 5-6 of them, so one producer cannot keep a thin-token stream fed.
@@ -162,40 +167,57 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // empty barrier aliases; with in-order consumption that holds iff producers <= stages.
         constexpr int NP = C::STAGES < NPROD1 ? C::STAGES : NPROD1;
         const int pw = warp == 0 ? 0 : warp - 5;
-        int stage = 0;
-        uint32_t phase = 0;
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag && pw < NP; tile += gridDim.x) {
-            if (tile_skipped(tile)) continue;
-            const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
-            const int m = mn % p.num_m, n = mn / p.num_m;
-            const int n0 = n * BN;
-            const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m * 128;
-            const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
-            const int rb0 = n0 >> 7;
-            const int nsfb = min(C::NB128, p.sfb_rowblocks - rb0);
-            const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
-            for (int kb = kb0; kb < kb1; kb++, it++) {
-                if ((int)(it % NP) == pw) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) break;
-                    if (lane == 0) {
-                        const uint32_t fb = full_bar(stage);
-                        mbar_expect_tx(fb, tx);
-                        if (p.a_tiled) tma_load_2d(stageA(stage), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb) * 128);
-                        else tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
-                        tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0);
-                        bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512,
-                                  C::SFA_BYTES, fb);
-                        for (int i = 0; i < nsfb; i++)
-                            bulk_load(stageSFB(stage) + i * C::MMAS * 512,
-                                      p.sfb + ((size_t)(rb0 + i) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::MMAS * 512, fb);
-                        if (SPARSE)
-                            bulk_load(stageMETA(stage), p.meta + ((size_t)(a_row0 >> 7) * p.kblocks + kb) * 2048, 2048, fb);
-                    }
-                    __syncwarp();
-                }
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        // what: 0 = the whole stage, 1 = byte count + weight side (tile of A, its scale factors, metadata),
+        //       2 = activation side only (the byte count was announced with the weight side)
+        auto issue = [&](int what, int stage, int kb, int a_row0, int n0, int rb0, int nsfb, uint32_t tx) {
+            const uint32_t fb = full_bar(stage);
+            if (what != 2) {
+                mbar_expect_tx(fb, tx);
+                if (p.a_tiled) tma_load_2d(stageA(stage), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb) * 128);
+                else tma_load_2d(stageA(stage), &tmA, fb, kb * C::A_ROW, a_row0);
+                bulk_load(stageSFA(stage), p.sfa + ((size_t)(a_row0 >> 7) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::SFA_BYTES, fb);
+                if (SPARSE) bulk_load(stageMETA(stage), p.meta + ((size_t)(a_row0 >> 7) * p.kblocks + kb) * 2048, 2048, fb);
             }
+            if (what != 1) {
+                tma_load_2d(stageB(stage), &tmB, fb, kb * 128, n0);
+                for (int i = 0; i < nsfb; i++)
+                    bulk_load(stageSFB(stage) + i * C::MMAS * 512,
+                              p.sfb + ((size_t)(rb0 + i) * atoms_per_rb + (size_t)kb * C::MMAS) * 512, C::MMAS * 512, fb);
+            }
+        };
+        // pass 0 (only when weights are prefetched): the weight side of the first ring revolution, no waits (fresh ring);
+        // then griddep_wait; pass 1: everything else, in the same order
+        for (int pass = prefetch_weights ? 0 : 1; pass < 2; pass++) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t it = 0;
+            bool stop = false;
+            for (int tile = blockIdx.x; tile < total_tiles && !abort_flag && pw < NP && !stop; tile += gridDim.x) {
+                if (pass == 1 && tile_skipped(tile)) continue;
+                const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
+                const int m = mn % p.num_m, n = mn / p.num_m;
+                const int n0 = n * BN;
+                const int a_row0 = ((pass == 1 && p.eblk) ? p.eblk[n] * p.out_f : 0) + m * 128;
+                const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
+                const int rb0 = n0 >> 7;
+                const int nsfb = min(C::NB128, p.sfb_rowblocks - rb0);
+                const uint32_t tx = C::A_BYTES + (uint32_t)p.b_box_bytes + C::SFA_BYTES + (uint32_t)nsfb * C::MMAS * 512 + C::META_BYTES;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    if (pass == 0 && it >= (uint32_t)C::STAGES) { stop = true; break; }
+                    if ((int)(it % NP) == pw) {
+                        if (pass == 0) {
+                            if (lane == 0) issue(1, stage, kb, a_row0, n0, rb0, nsfb, tx);
+                        } else {
+                            const bool prefetched = prefetch_weights && it < (uint32_t)C::STAGES;
+                            if (!prefetched && !mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, &g_status, SITE_PROD, QB_BACKOFF)) { stop = true; break; }
+                            if (lane == 0) issue(prefetched ? 2 : 0, stage, kb, a_row0, n0, rb0, nsfb, tx);
+                        }
+                        __syncwarp();
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (pass == 0) griddep_wait();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -564,6 +586,15 @@ struct KParams2 {
     int* peer_flags[8];
     int* peer_done;
     const int* peer_val_ptr;
+    int peer_bpo;                        // token tiles per owner (0 = natural tile order)
+    // out_mode 4: the weight rows are (gate, up) pairs (row 2i = gate feature i, 2i + 1 = up feature i); the epilogue forms
+    // h = SwiGLU(gate, up) from the fp32 accumulators (+ bias), quantises h single-level per 32 features and writes packed
+    // codes h_bytes[tok][h_feats / 2] and UE4M3 scale codes (128x4 atoms and / or the reference layout [h_feats/128][tok][4])
+    uint8_t* h_bytes;
+    uint8_t* h_sf_atoms;
+    uint8_t* h_sf_ref;
+    int h_feats;
+    int act;
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
@@ -583,6 +614,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
     __shared__ uint32_t tmem_base_slot;
+    __shared__ float hmax_xch[8][2][16];      // out_mode 4: block maxima exchanged between partner epilogue warps
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t side0 = smem0 + C::STAGES * C::STAGE_BYTES;
@@ -636,6 +668,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t tmem_base = tmem_base_slot;
 
     const int total_tiles = p.num_m2 * p.num_n;
+    // Token tile of a work item. With the reduce-scatter epilogue the token tiles are visited owner by owner in a rotation
+    // that starts behind this rank: at any moment the ranks store into different owners and every rank's local and remote
+    // tiles alternate, so the NVLink traffic is spread over the whole kernel instead of arriving in one burst per owner.
+    auto tile_n = [&](int tile) {
+        const int i = tile / p.num_m2;
+        if (p.peer_bpo == 0) return i;
+        int owner = p.peer_rank + 1 + i % p.peer_n;
+        if (owner >= p.peer_n) owner -= p.peer_n;
+        return owner * p.peer_bpo + i / p.peer_n;
+    };
     // grouped mode: a 128-token block with expert id < 0 is unused capacity of a fixed-capacity routing; every
     // role of both CTAs skips its tiles (same test everywhere, so the ring and accumulator counters stay in step)
     auto tile_skipped = [&](int tile) { return p.eblk != nullptr && p.eblk[tile / p.num_m2] < 0; };
@@ -658,7 +700,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
-            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int m2 = tile % p.num_m2, n = tile_n(tile);
             const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
@@ -700,7 +742,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
-            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int m2 = tile % p.num_m2, n = tile_n(tile);
             const int rb_a = ((p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
@@ -748,7 +790,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
                 if (tile_skipped(tile)) continue;
                 // a 192-token tile starts 0 or 64 rows into a 128-row scale-factor atom: 0 or 2 columns in
-                const uint32_t sfb_coloff = (uint32_t)((((tile / p.num_m2) * BN) & 127) >> 5);
+                const uint32_t sfb_coloff = (uint32_t)(((tile_n(tile) * BN) & 127) >> 5);
                 if (!mbar_wait_thread(acce_bar(acc), acc_phase ^ 1, &abort_flag, &g_status, SITE_MMA_ACC)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -906,7 +948,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         constexpr int NCH = HCOLS / 16;        // chunks of 16 columns
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
-            const int m2 = tile % p.num_m2, n = tile / p.num_m2;
+            const int m2 = tile % p.num_m2, n = tile_n(tile);
             const int n0 = n * BN + half * HCOLS;          // first token column of this warp
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
@@ -925,7 +967,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
             for (int e = 0; e < 8; e++) bias8[e] = 0.f;
             const int f8 = o0 + q * 32 + (lane & 3) * 8;       // bias rows hold bias_ld (a multiple of 8) valid features
-            if (p.out_mode == 3 && p.bias && f8 + 8 <= p.bias_ld) {
+            if ((p.out_mode == 3 || p.out_mode == 4) && p.bias && f8 + 8 <= p.bias_ld) {
                 const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + (size_t)(p.eblk ? p.eblk[n] : 0) * p.bias_ld + f8));
                 const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
@@ -969,6 +1011,62 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     for (int j = 0; j < 16; j++) sts_u32(stg_s + j * C::EPI_PITCH + lane * 4, __float_as_uint(__uint_as_float(r[j]) * ga));
                     __syncwarp();
                     __nv_bfloat16* Cp = reinterpret_cast<__nv_bfloat16*>(p.C) + o0 + q * 32 + (lane & 3) * 8;
+                    if (p.out_mode == 4) {
+                        // SwiGLU + single-level per-32 quantiser in the epilogue (the reference's fused gate/up GEMM,
+                        // cuda/sparse_fp4_lib.cu:1679-1868). After the transpose a lane holds 8 consecutive rows of one token
+                        // = 4 (gate, up) pairs; the 4 lanes of a token hold this warp's 16 h features, and the partner warp
+                        // (lane quadrant q ^ 1) holds the other 16 of the 32-feature scale block.
+                        float hv[2][4], bm[2];
+#pragma unroll
+                        for (int it = 0; it < 2; it++) {
+                            const int trow = (it * 32 + lane) >> 2;
+                            const float gt = __shfl_sync(0xffffffffu, gbl, trow);
+                            const uint4 lo = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32);
+                            const uint4 hi = lds_v4(stg_s + trow * C::EPI_PITCH + (lane & 3) * 32 + 16);
+                            const float f[8] = {__uint_as_float(lo.x) * gt + bias8[0], __uint_as_float(lo.y) * gt + bias8[1],
+                                                __uint_as_float(lo.z) * gt + bias8[2], __uint_as_float(lo.w) * gt + bias8[3],
+                                                __uint_as_float(hi.x) * gt + bias8[4], __uint_as_float(hi.y) * gt + bias8[5],
+                                                __uint_as_float(hi.z) * gt + bias8[6], __uint_as_float(hi.w) * gt + bias8[7]};
+                            float m = 0.f;
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                hv[it][k] = p.act == 0 ? swiglu_h<0>(f[2 * k], f[2 * k + 1]) : swiglu_h<1>(f[2 * k], f[2 * k + 1]);
+                                m = fmaxf(m, fabsf(hv[it][k]));
+                            }
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                            bm[it] = m;
+                            if ((lane & 3) == 0) hmax_xch[ew][c & 1][trow] = m;
+                        }
+                        // the two buffers alternate by chunk: a warp rewrites a buffer only after the barrier of the chunk in
+                        // between, which its partner reaches after it has read that buffer
+                        named_bar_sync(1 + (ew >> 1), 64);
+                        const int blk32 = ((o0 >> 1) + q * 16) >> 5;          // scale block of these features within the row of h
+#pragma unroll
+                        for (int it = 0; it < 2; it++) {
+                            const int trow = (it * 32 + lane) >> 2;
+                            const float blockmax = fmaxf(bm[it], hmax_xch[ew ^ 1][c & 1][trow]);
+                            // h is only defined up to the accumulation order of the tensor core, so the quotient by the
+                            // block scale is one multiply by its reciprocal and the hardware E2M1 conversion (a tenth of
+                            // the instructions of the exact-quotient path of the stand-alone quantisers)
+                            const uint32_t code = enc_ue4m3_bits(__fdiv_rn(blockmax, 6.f));
+                            const uint32_t w = pack4_e2m1_rcp(hv[it], code ? __frcp_rn(dec_ue4m3(code)) : 0.f);
+                            const int base = lane & ~3;
+                            const uint32_t w1 = __shfl_sync(0xffffffffu, w, base + 1), w2 = __shfl_sync(0xffffffffu, w, base + 2),
+                                           w3 = __shfl_sync(0xffffffffu, w, base + 3);
+                            const int col = n0 + c0 + trow;
+                            if ((lane & 3) == 0 && col < p.tok) {
+                                uint8_t* dst = p.h_bytes + (size_t)col * (p.h_feats >> 1) + (((o0 >> 1) + q * 16) >> 1);
+                                *reinterpret_cast<uint2*>(dst) = make_uint2(w | (w1 << 16), w2 | (w3 << 16));
+                                if ((q & 1) == 0) {
+                                    if (p.h_sf_atoms) p.h_sf_atoms[sf_atom_offset(col, blk32, kpad256(p.h_feats) / 128)] = (uint8_t)code;
+                                    if (p.h_sf_ref) p.h_sf_ref[((size_t)(blk32 >> 2) * p.tok + col) * 4 + (blk32 & 3)] = (uint8_t)code;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        return;
+                    }
 #pragma unroll
                     for (int it = 0; it < 2; it++) {
                         const int trow = (it * 32 + lane) >> 2;
@@ -1214,7 +1312,9 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.a_tiled = a.a_tiled;
     kp.eblk = a.eblk; kp.bias = (const __nv_bfloat16*)a.bias; kp.row_w = a.row_w; kp.bias_ld = a.bias_ld > 0 ? a.bias_ld : a.out_f;
     kp.peer_n = a.peer_n; kp.peer_rank = a.peer_rank; kp.tok_per_rank = a.tok_per_rank; kp.peer_val = a.peer_val; kp.peer_done = a.peer_done; kp.peer_val_ptr = a.peer_val_ptr;
+    kp.peer_bpo = (a.peer_n && a.tok_per_rank % BN == 0 && kp.num_n == (a.tok_per_rank / BN) * a.peer_n) ? a.tok_per_rank / BN : 0;
     for (int r = 0; r < 8; r++) { kp.peer_out[r] = (__nv_bfloat16*)a.peer_out[r]; kp.peer_flags[r] = a.peer_flags[r]; }
+    kp.h_bytes = (uint8_t*)a.h_bytes; kp.h_sf_atoms = (uint8_t*)a.h_sf_atoms; kp.h_sf_ref = (uint8_t*)a.h_sf_ref; kp.h_feats = a.h_feats; kp.act = a.act;
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
@@ -1226,11 +1326,11 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     if (a.out_f <= 0 || a.tok < 0 || a.K <= 0 || a.a_rows <= 0) return QB_ERR_ARG;
     if (a.tok == 0) return QB_OK;
     if (a.out_f % 128 || a.K % 128 || a.a_rows % 128) return QB_ERR_ARG;
-    if (!a.A || !a.B || !a.sfa || !a.sfb || (!a.C && !a.peer_n) || (a.sparse && !a.meta)) return QB_ERR_ARG;
+    if (!a.A || !a.B || !a.sfa || !a.sfb || (!a.C && !a.peer_n && a.out_mode != 4) || (a.sparse && !a.meta)) return QB_ERR_ARG;
     if (((uintptr_t)a.A & 15) || ((uintptr_t)a.B & 15) || ((uintptr_t)a.sfa & 15) || ((uintptr_t)a.sfb & 15) ||
         ((uintptr_t)a.meta & 15) || ((uintptr_t)a.C & 15))
         return QB_ERR_ARG;
-    if (a.out_mode < 0 || a.out_mode > 3) return QB_ERR_ARG;
+    if (a.out_mode < 0 || a.out_mode > 4) return QB_ERR_ARG;
     int splits = a.splits < 1 ? 1 : a.splits;
     if (splits > 1 && (!a.Cf || a.eblk || a.out_mode > 1)) return QB_ERR_ARG;
     if (a.eblk && a.a_rows % a.out_f) return QB_ERR_ARG;
@@ -1239,6 +1339,15 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
 
     // CTA-pair kernel: plain bf16 GEMM, enough tokens to fill a 256-wide tile, out % 256 == 0.
     // bn == 512 requests it explicitly, bn == 0 (auto) picks it for prefill-sized problems.
+    if (a.out_mode == 4) {
+        // fused SwiGLU + quantiser epilogue: pair kernel only (plain or grouped), out = interleaved (gate, up) rows
+        if (splits != 1 || a.peer_n || a.out_f % 256 || a.tok < 128 || !a.h_bytes || (!a.h_sf_atoms && !a.h_sf_ref) ||
+            a.h_feats != a.out_f / 2 || ((uintptr_t)a.h_bytes & 7) || (a.act != 0 && a.act != 1) || (a.eblk && a.tok % 128) ||
+            (((uintptr_t)a.bias & 15) != 0) || (a.bias_ld > 0 && a.bias_ld % 8))
+            return QB_ERR_ARG;
+        if (a.eblk || a.tok < 512) return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
+        return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
+    }
     if (a.peer_n) {
         // fused reduce-scatter: prefill pair kernel only, token-major output, token ranges of 16-token granularity
         if (a.peer_n < 2 || a.peer_n > 8 || a.peer_rank < 0 || a.peer_rank >= a.peer_n || a.out_mode != 1 || a.eblk || splits != 1 ||

@@ -92,6 +92,7 @@ struct GemmArgs {
     int a_tiled;           // 1 = A is in the tiled layout [rows/128][Kp/256][128][64 or 128 B] (see tile_weights)
     int out_mode;          // 0: bf16 C[out][tok]  1: bf16 C[tok][out]  2: fp32 raw accumulators C[out][tok]
                            // 3: bf16 C[tok][out] = (acc*gA*gB + bias)*row_w
+                           // 4: no C; h = SwiGLU(acc*gA*gB + bias) quantised single-level (see h_bytes)
     int splits;            // K splits (>1 uses Cf + a convert pass)
     int bn;                // token tile (0 = choose)
     // Row-parallel GEMM fused with the reduce-scatter of its partial result (prefill pair kernel, out_mode 1 only):
@@ -105,6 +106,12 @@ struct GemmArgs {
     void* peer_out[8];
     int* peer_flags[8];
     int* peer_done;        // arrival counter of this device's CTAs, zero between calls
+    // out_mode 4 (pair kernel): SwiGLU + single-level per-32 quantiser of h in the epilogue; A's rows are (gate, up) pairs
+    void* h_bytes;         // packed E2M1 codes of h [tok][h_feats / 2]
+    void* h_sf_atoms;      // UE4M3 scale codes of h as 128x4 atoms (may be null if h_sf_ref is given)
+    void* h_sf_ref;        // ... and / or in the reference layout [h_feats/128][tok][4]
+    int h_feats;           // features of h per row = out_f / 2
+    int act;               // 0 = clamped gpt-oss SwiGLU, 1 = silu(g) * u
     const int* peer_val_ptr;   // non-null: the flag value is read from this device word when the kernel runs (graph replay)
 };
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);

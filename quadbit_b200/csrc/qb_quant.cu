@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
     constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
     griddep_launch_dependents();     // a thin-token GEMM that follows may set itself up while this grid runs
+    griddep_wait();                  // launched as a programmatic dependent itself: x may come from the kernel in front
     const int row = blockIdx.x;
     const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
@@ -135,15 +136,6 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 // them; TWO_LEVEL = false is the single-level quantiser (no per-token global) that the reference's fused MoE
 // GEMM1 epilogue applies (matmul_sp_moe_gu_swiglu, cuda/sparse_fp4_lib.cu:1828-1866); act 0 is the clamped
 // gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1), act 1 the plain silu(g) * u.
-template <int ACT>
-__device__ __forceinline__ float swiglu_h(float g, float u) {
-    if (ACT == 0) {
-        g = fminf(g, 7.f);
-        u = fmaxf(fminf(u, 7.f), -7.f);
-        return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
-    }
-    return __fdividef(g, 1.f + __expf(-g)) * u;
-}
 template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
 __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
                                                             uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
@@ -692,16 +684,27 @@ static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atom
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
     const int nj = (nblocks + threads - 1) / threads;
-#define QB_LQ(NJ)                                                                                                 \
-    quant_act_kernel<BLOCK, NJ, TWO_LEVEL><<<tok, threads, 0, st>>>((const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
-                                                                    (uint8_t*)sf_atoms, g, tok, K, src, h8)
+    // programmatic dependent launch: the grid may become resident while the kernel in front drains (it waits for that
+    // kernel's results with griddepcontrol.wait before its first load), which hides the launch latency between the
+    // kernels of a decode step
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tok);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define QB_LQ(NJ)                                                                                                          \
+    return (int)cudaLaunchKernelEx(&cfg, quant_act_kernel<BLOCK, NJ, TWO_LEVEL>, (const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
+                                   (uint8_t*)sf_atoms, g, tok, K, src, h8)
     if (nj <= 1) QB_LQ(1);
     else if (nj <= 2) QB_LQ(2);
     else if (nj <= 4) QB_LQ(4);
     else if (nj <= 8) QB_LQ(8);
-    else return QB_ERR_UNSUPPORTED;
+    return QB_ERR_UNSUPPORTED;
 #undef QB_LQ
-    return (int)cudaGetLastError();
 }
 
 int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int block,

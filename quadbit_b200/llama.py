@@ -84,10 +84,14 @@ def shard_layer(L: dict, cfg: LlamaConfig, rank: int, world: int) -> dict:
 
 
 class _Layer:
-    def __init__(self, W: dict):
+    def __init__(self, W: dict, interleave_gu: bool = False):
         self.qkv = DenseNVLinear(W["qkv"], keep_ref_layout=False)
         self.wo = DenseNVLinear(W["wo"], keep_ref_layout=False)
-        self.gu = QuadbitLinear(W["gate_up"], keep_ref_layout=False)
+        gu = W["gate_up"]
+        if interleave_gu:            # rows as (gate, up) pairs for the fused SwiGLU epilogue
+            half = gu.shape[0] // 2
+            gu = torch.stack([gu[:half], gu[half:]], 1).reshape(gu.shape[0], gu.shape[1]).contiguous()
+        self.gu = QuadbitLinear(gu, keep_ref_layout=False)
         self.dn = QuadbitLinear(W["down"], keep_ref_layout=False)
         self.norm_attn = W["norm_attn"].to(torch.bfloat16).contiguous()
         self.norm_mlp = W["norm_mlp"].to(torch.bfloat16).contiguous()
@@ -96,10 +100,14 @@ class _Layer:
 class LlamaPrefill:
     """One rank of the model. `weights`: dict as oracle-side `make_weights` builds it (embed, lm_head, norm_f, layers =
     list of per-layer dicts or a callable layer index -> dict, so full-size layers can be generated and packed one at a
-    time). `ctx`: a TPContext for world > 1 with comm="peer"."""
+    time). `ctx`: a TPContext for world > 1 with comm="peer". fuse_swiglu: SwiGLU and the quantiser of its result run in the
+    epilogue of the gate/up GEMM (qb_gemm_swiglu): the [tokens, 2 * intermediate] bf16 round trip and one kernel per layer
+    disappear, at the price of a different arithmetic for h (formed from the fp32 accumulators, quantised with one scale per
+    32 features and no per-token global, as the reference's fused MoE GEMM does) - off by default, the default matches the
+    reference's fused_mlp_2lvl."""
 
     def __init__(self, cfg: LlamaConfig, weights: dict, rank: int = 0, world: int = 1, group=None, comm: str = "peer",
-                 ctx: TPContext | None = None, device=None):
+                 ctx: TPContext | None = None, device=None, fuse_swiglu: bool = False):
         assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.intermediate % (128 * world) == 0
         assert comm in ("peer", "nccl")
         self.cfg, self.rank, self.world, self.group, self.comm = cfg, rank, world, group, comm
@@ -113,7 +121,8 @@ class LlamaPrefill:
         self.layers = []
         for li in range(n):
             L = layers(li) if callable(layers) else layers[li]
-            self.layers.append(_Layer(shard_layer({k: v.to(self.device) for k, v in L.items()}, cfg, rank, world)))
+            self.layers.append(_Layer(shard_layer({k: v.to(self.device) for k, v in L.items()}, cfg, rank, world), fuse_swiglu))
+        self.fuse_swiglu = fuse_swiglu
         self.ctx = ctx
         self._rope = {}
         self.timings = None
@@ -157,20 +166,21 @@ class LlamaPrefill:
         dense = isinstance(lin, DenseNVLinear)
         out_f, in_f = (lin.out, lin.inn) if dense else (lin.out_f, lin.in_f)
         Bb, sfb, gB = q
+        gp = gB.data_ptr() if gB is not None else 0
         if self.world == 1:
             out = torch.empty((tok, out_f), dtype=torch.bfloat16, device=self.device)
-            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), tok, out)
+            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gp, tok, out)
             return out
         ctx = self.ctx
         if self.comm == "nccl":
             import torch.distributed as dist
             part = torch.empty((tok, out_f), dtype=torch.bfloat16, device=self.device)
-            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), tok, part)
+            self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gp, tok, part)
             dist.all_to_all_single(ctx.slots_view(k), part.view(self.world, ctx.Tl, out_f), group=self.group)
             return None
         val = ctx.next_value(ctx.FLAG_SLOT[k])
         check(self.lib.qb_gemm_rs(lin.At.data_ptr(), Bb.data_ptr(), lin.sfa.data_ptr(), sfb.data_ptr(),
-                                  0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(), gB.data_ptr(), ctx.slot_out_ptrs(k),
+                                  0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(), gp, ctx.slot_out_ptrs(k),
                                   ctx.flag_ptrs(ctx.FLAG_SLOT[k]), ctx.done[k:].data_ptr(), out_f, tok, in_f, 2 if dense else 3, self.world,
                                   self.rank, ctx.Tl, val, 0, 0, _stream()), "qb_gemm_rs")
         return None
@@ -271,15 +281,21 @@ class LlamaPrefill:
             self._cap("x_mlp_in", x)
             Bb, sf, g = self._resolve(q32, 32)
             self._cap_gathered("q32", (Bb, sf, g), 32, T)
-            cgu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=self.device)
-            self._gemm(L.gu, Bb, sf, g, T, cgu)
-            self._mark("gate_up_gemm")
-            self._cap("cgu", cgu)
             Hb = torch.empty((T, I // 2), dtype=torch.uint8, device=self.device)
             sfh = torch.empty(lib.qb_sf_atoms_bytes(T, I, 32), dtype=torch.uint8, device=self.device)
-            gH = torch.empty((T,), dtype=torch.float32, device=self.device)
-            check(lib.qb_swiglu_quant(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), T, I, _stream()), "qb_swiglu_quant")
-            self._mark("swiglu_quant")
+            if self.fuse_swiglu:
+                gH = None
+                check(lib.qb_gemm_swiglu(L.gu.At.data_ptr(), Bb, L.gu.sfa.data_ptr(), sf, L.gu.meta_native.data_ptr(), L.gu.gA.data_ptr(), g, 0, 0,
+                                         Hb.data_ptr(), sfh.data_ptr(), 0, 2 * I, 2 * I, T, H, 3, 1, _stream()), "qb_gemm_swiglu")
+                self._mark("gate_up_gemm")
+            else:
+                cgu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=self.device)
+                self._gemm(L.gu, Bb, sf, g, T, cgu)
+                self._mark("gate_up_gemm")
+                self._cap("cgu", cgu)
+                gH = torch.empty((T,), dtype=torch.float32, device=self.device)
+                check(lib.qb_swiglu_quant(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), T, I, _stream()), "qb_swiglu_quant")
+                self._mark("swiglu_quant")
             d = self._row_parallel(L.dn, (Hb, sfh, gH), T, 1)
             self._mark("down_gemm")
             yield None

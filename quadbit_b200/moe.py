@@ -144,7 +144,7 @@ def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bia
     r = Bb.shape[0]
     C = torch.empty((r, mpe), dtype=torch.bfloat16, device=Bb.device)
     mode = 3 if (bias is not None or row_w is not None) else 1
-    check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
+    check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), _ptr(gB),
                       C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
                       _stream()), "qb_gemm(grouped)")
     return C
@@ -172,7 +172,7 @@ class SparseMoE:
 
     def __init__(self, w_gate_up: list[torch.Tensor], w_down: list[torch.Tensor], topk: int, act: str = "silu",
                  expert_range: tuple[int, int] | None = None, n_experts_total: int | None = None, fixed_capacity: bool = False,
-                 b_gate_up: list[torch.Tensor] | None = None, b_down: list[torch.Tensor] | None = None):
+                 b_gate_up: list[torch.Tensor] | None = None, b_down: list[torch.Tensor] | None = None, fused_gu: bool = False):
         self.lib = lib = load("sparse_fp4")
         self.E = len(w_gate_up)
         self.topk, self.act = topk, act
@@ -182,11 +182,20 @@ class SparseMoE:
         self.Ip = (self.I + 127) // 128 * 128
         self.mpe_gu = (2 * self.Ip + 255) // 256 * 256       # multiples of 256: the grouped GEMM then runs on the CTA-pair kernel
         self.mpe_dn = (self.H + 255) // 256 * 256
+        # fused_gu: SwiGLU + single-level per-32 quantiser of h run in the epilogue of the gate/up GEMM (qb_gemm_swiglu, the
+        # reference's fused GEMM1, cuda/sparse_fp4_lib.cu:1679-1868): the gate/up rows are stored as (gate, up) pairs, the bf16
+        # [rows, 2*Ip] intermediate and the SwiGLU kernel disappear, and h carries no per-row global (as in the reference's
+        # MoE path). Without it h is quantised two-level by a separate kernel.
+        self.fused_gu = fused_gu
         gus, dns = [], []
         for wg, wd in zip(w_gate_up, w_down):
-            g = wg.new_zeros(self.mpe_gu, self.Hp)                 # gate rows [0,I), up rows [Ip, Ip+I)
-            g[: self.I, : self.H] = wg[: self.I]
-            g[self.Ip: self.Ip + self.I, : self.H] = wg[self.I:]
+            g = wg.new_zeros(self.mpe_gu, self.Hp)
+            if fused_gu:                                           # row 2i = gate i, row 2i + 1 = up i
+                g[0: 2 * self.I: 2, : self.H] = wg[: self.I]
+                g[1: 2 * self.I: 2, : self.H] = wg[self.I:]
+            else:                                                  # gate rows [0,I), up rows [Ip, Ip+I)
+                g[: self.I, : self.H] = wg[: self.I]
+                g[self.Ip: self.Ip + self.I, : self.H] = wg[self.I:]
             d = wd.new_zeros(self.mpe_dn, self.Ip)
             d[: self.H, : self.I] = wd
             gus.append(pack(lib, g))
@@ -199,8 +208,12 @@ class SparseMoE:
         if b_gate_up is not None:
             b = w_gate_up[0].new_zeros((self.E, self.mpe_gu), dtype=torch.bfloat16)
             for e, be in enumerate(b_gate_up):
-                b[e, : self.I] = be[: self.I].to(torch.bfloat16)
-                b[e, self.Ip: self.Ip + self.I] = be[self.I:].to(torch.bfloat16)
+                if fused_gu:
+                    b[e, 0: 2 * self.I: 2] = be[: self.I].to(torch.bfloat16)
+                    b[e, 1: 2 * self.I: 2] = be[self.I:].to(torch.bfloat16)
+                else:
+                    b[e, : self.I] = be[: self.I].to(torch.bfloat16)
+                    b[e, self.Ip: self.Ip + self.I] = be[self.I:].to(torch.bfloat16)
             self.b_gu = b.contiguous()
         if b_down is not None:
             b = w_down[0].new_zeros((self.E, self.mpe_dn), dtype=torch.bfloat16)
@@ -227,9 +240,16 @@ class SparseMoE:
         gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
                                          x.shape[1], 32, _stream()), "qb_gather_quantize_act")
-        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
+        if self.fused_gu:
+            Ac, meta, sfa, gA = self.w_gu
+            assert self.mpe_gu == 2 * self.Ip
+            check(lib.qb_gemm_swiglu(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
+                                     eblk.data_ptr(), _ptr(self.b_gu), Hb.data_ptr(), sfh.data_ptr(), 0, Ac.shape[0], self.mpe_gu, r_pad, self.Hp,
+                                     1, 0 if self.act == "gptoss" else 1, _stream()), "qb_gemm_swiglu")
+            return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw)
+        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")

@@ -10,7 +10,7 @@ import pytest
 from quadbit_b200 import _lib, build_so
 
 HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "quadbit_b200.h")
-DECL = re.compile(r"^\s*(?:const\s+char\s*\*|long\s+long|int|void)\s+(\w+)\s*\(([^;{]*)\)\s*;", re.M | re.S)
+DECL = re.compile(r"^\s*(?:const\s+char\s*\*|long\s+long|int|void\s*\*|void)\s*(\w+)\s*\(([^;{]*)\)\s*;", re.M | re.S)
 
 
 def declared():

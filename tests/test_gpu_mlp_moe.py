@@ -166,6 +166,44 @@ def test_moe_layer_matches_per_expert_reference(H, I, E, topk, T):
     assert rel(parts[0] + parts[1], ref) < 0.03
 
 
+@pytest.mark.parametrize("act", ["silu", "gptoss"])
+def test_moe_layer_fused_gate_up_epilogue(act):
+    """SparseMoE(fused_gu=True): SwiGLU + single-level quantiser of h in the epilogue of the grouped gate/up GEMM (the
+    reference's fused GEMM1 arithmetic: h from the fp32 accumulators, one UE4M3 scale per 32 features, no per-row global),
+    against a per-expert loop of the oracle with that arithmetic."""
+    import quadbit_b200 as qb
+    torch.manual_seed(31)
+    H, I, E, topk, T = 256, 384, 4, 2, 200
+    wgu = [torch.randn(2 * I, H) * 0.5 for _ in range(E)]         # large enough that h sits well inside the UE4M3 range
+    wdn = [torch.randn(H, I) * 0.05 for _ in range(E)]
+    x = torch.randn(T, H)
+    idx, w = fq.route_topk(torch.randn(T, E), topk)
+    moe = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk, act=act, fused_gu=True)
+    for fixed in (False, True):
+        moe.fixed_capacity = fixed
+        y = moe.forward(x.cuda().bfloat16(), idx.cuda(), w.cuda())
+        assert moe.lib.qb_status(0) == 0
+        ref = torch.zeros(T, H)
+        for e in range(E):
+            sel = idx == e
+            toks = torch.nonzero(sel.any(1)).squeeze(1)
+            if toks.numel() == 0:
+                continue
+            gu = fq.linear_sparse(x[toks], wgu[e])
+            g, u = gu[:, :I], gu[:, I:]
+            if act == "gptoss":
+                g, u = g.clamp(max=7.0), u.clamp(-7.0, 7.0)
+                h = (g * torch.sigmoid(1.702 * g)) * (u + 1.0)
+            else:
+                h = torch.nn.functional.silu(g) * u
+            hq = fq.unpack_act(*fq.act_quant_1lvl(h, 32, round_bf16=False), None, 32)
+            d = torch.nn.functional.linear(hq, fq.sparse_fp4_dequant_2lvl(wdn[e]))
+            wt = (w * sel)[toks].sum(1, keepdim=True)
+            ref[toks] += (d * wt).to(torch.bfloat16).float()
+        cos = torch.nn.functional.cosine_similarity(y.float().cpu().flatten(), ref.flatten(), dim=0).item()
+        assert cos > 0.999 and rel(y, ref) < 0.03, (fixed, cos, rel(y, ref))
+
+
 def test_build_routing_matches_reference_helper():
     import quadbit_b200.moe as moe
     torch.manual_seed(1)

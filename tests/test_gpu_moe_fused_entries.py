@@ -122,7 +122,10 @@ def test_gate_up_swiglu_entry_matches_unfused_path(lib, act):
     gu = Cgu.float().cpu()
     ref_gu = fq.moe_seg_linear(rows, eblk, Ws) + bias.float()[eblk.long().repeat_interleave(128)]
     assert ((gu - ref_gu).abs() / (ref_gu.abs() + 1.0)).max().item() < 6e-3
-    g, u = gu[:, 0::2], gu[:, 1::2]
+    # the fused entry forms h from the fp32 accumulators (no bf16 rounding of gate / up in between), as the reference's
+    # fused kernel does: the oracle is the fp32 fake-quant linear; codes may differ where the accumulation order of the
+    # tensor core moves a quotient across a boundary (relative distance <= 2e-4)
+    g, u = ref_gu[:, 0::2], ref_gu[:, 1::2]
     if act == 0:
         g = g.clamp(max=7.0)
         u = u.clamp(-7.0, 7.0)
@@ -132,9 +135,52 @@ def test_gate_up_swiglu_entry_matches_unfused_path(lib, act):
     eB, eS = fq.act_quant_1lvl(h, 32, round_bf16=False)
     want = fq.unpack_act(eB, eS, None, 32)
     deq = fq.unpack_act(Hw.cpu(), sH.cpu(), None, 32)
-    assert_codes_explained(h, Hw, sH, None, 32)
+    assert_codes_explained(h, Hw, sH, None, 32, tol=2e-4, max_scale_flips=5e-3)
     # single-level scales bottom out at 2^-9, so small h quantise coarsely: compare with the oracle's own error
     assert ((deq - h).norm() / h.norm()).item() < 1.02 * ((want - h).norm() / h.norm()).item() + 1e-3
+
+
+@pytest.mark.parametrize("tok,grouped", [(256, False), (640, False), (384, True)])
+def test_native_fused_gate_up_swiglu_epilogue(lib, tok, grouped):
+    """qb_gemm_swiglu: gate/up GEMM (interleaved rows) with SwiGLU + single-level per-32 quantiser in the epilogue, plain
+    (the 128- and 256-token tiles of the CTA-pair kernel) and grouped, scale codes in both layouts."""
+    import quadbit_b200.moe as qmoe
+    torch.manual_seed(tok)
+    Ih, K, E = 256, 512, 3 if grouped else 1
+    out_f = 2 * Ih
+    Ws = [torch.randn(out_f, K) * 0.05 for _ in range(E)]          # rows: (gate_0, up_0, gate_1, up_1, ...)
+    x = torch.randn(tok, K)
+    bias = (torch.randn(E, out_f) * 0.2).to(torch.bfloat16)
+    packs = [qmoe.pack(lib, w.cuda()) for w in Ws]
+    Ac, meta, sfa, gA = qmoe.stack(packs)
+    import quadbit_b200 as qb
+    Bb, sfb, gB = qb.quantize_act(lib, x.cuda().bfloat16(), 32, True)
+    eblk = torch.tensor([i % E for i in range(tok // 128)], dtype=torch.int32) if grouped else None
+    Hb = torch.zeros((tok, Ih // 2), dtype=torch.uint8, device="cuda")
+    atoms = torch.zeros(lib.qb_sf_atoms_bytes(tok, Ih, 32), dtype=torch.uint8, device="cuda")
+    sref = torch.zeros((Ih // 128, tok, 4), dtype=torch.uint8, device="cuda")
+    for act in (1, 0):
+        rc = lib.qb_gemm_swiglu(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
+                                eblk.cuda().data_ptr() if grouped else 0, bias.cuda().data_ptr(), Hb.data_ptr(), atoms.data_ptr(), sref.data_ptr(),
+                                E * out_f, out_f, tok, K, 1, act, S())
+        assert rc == 0 and lib.qb_status(S()) == 0
+        xq = fq.act_dequant_2lvl(x, 32)
+        gu = torch.empty(tok, out_f)
+        for b in range(tok // 128):
+            e = int(eblk[b]) if grouped else 0
+            gu[b * 128:(b + 1) * 128] = torch.nn.functional.linear(xq[b * 128:(b + 1) * 128], fq.sparse_fp4_dequant_2lvl(Ws[e])) + bias[e].float()
+        g, u = gu[:, 0::2], gu[:, 1::2]
+        if act == 0:
+            g, u = g.clamp(max=7.0), u.clamp(-7.0, 7.0)
+            h = (g / (1.0 + torch.exp(-1.702 * g))) * (u + 1.0)
+        else:
+            h = (g / (1.0 + torch.exp(-g))) * u
+        assert_codes_explained(h, Hb, sref, None, 32, tol=2e-4, max_scale_flips=5e-3)
+        mask = fq.sf_to_atoms(torch.ones(Ih // 128, tok, 4, dtype=torch.uint8)).view(-1).bool()
+        assert torch.equal(atoms.cpu()[mask], fq.sf_to_atoms(sref.cpu()).view(-1)[mask])
+    d = torch.zeros(16, dtype=torch.uint8, device="cuda").data_ptr()
+    assert lib.qb_gemm_swiglu(d, d, d, d, d, 0, 0, 0, 0, d, d, 0, 384, 384, 256, 512, 1, 1, S()) == 1001        # out % 256
+    assert lib.qb_gemm_swiglu(d, d, d, d, d, 0, 0, 0, 0, d, d, 0, 512, 512, 64, 512, 1, 1, S()) == 1001         # tok < 128
 
 
 def test_dense_library_glue_per16():
