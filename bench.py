@@ -212,15 +212,18 @@ def run_model(torch, qb, dev, rank, world, dist, args, comm="peer", layers=32, b
     model = LlamaPrefill(cfg, random_weights(cfg, 2, dev), rank=rank, world=world, comm=comm, ctx=ctx, fuse_swiglu=fuse_swiglu)
     ids = torch.randint(0, cfg.vocab, (batch, seq), generator=torch.Generator().manual_seed(2))
     ids_d = ids.to(dev)
+    # the layer stack is replayed from one CUDA graph (captured by the first call after two eager runs)
+    graphed = not args.eager_model and comm != "nccl"
+    run = model.forward_graphed if graphed else model.forward
     for _ in range(2):
-        model(ids_d)
+        run(ids_d)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(steps):
-        hid, logits = model(ids_d)
+        hid, logits = run(ids_d)
     b.record()
     torch.cuda.synchronize()
     t = a.elapsed_time(b) / steps * 1e-3
@@ -242,12 +245,13 @@ def run_model(torch, qb, dev, rank, world, dist, args, comm="peer", layers=32, b
     lin, attn = model_flops(cfg, batch, seq)
     out = {"workload": MODEL_WORKLOAD if layers == 32 else MODEL_WORKLOAD.replace("32 layers", f"{layers} layers"),
            "tokens_per_s": T / t, "ms_per_forward": t * 1e3, "layers": layers, "tokens": T,
+           "timing": "eager launches" if not graphed else "layer stack replayed from one CUDA graph; embedding lookup, logits of the last tokens eager",
            "parallelism": "single" if world == 1 else f"tp{world}, {comm}: " + (
                "reduce-scatter by peer stores from the GEMM epilogues, all-gather of quantised activations by peer stores from the fused "
                "reduce+norm+quantise kernel, no NCCL call in the layer stack" if comm == "peer" else
                "NCCL all_to_all_single of bf16 partials + all_gather_into_tensor of quantised activations"),
            "linear_tflops": lin / t / 1e12, "attention_tflops_bf16": attn / t / 1e12,
-           "ms_per_layer_breakdown_rank0": {k: v / layers for k, v in br.items() if k not in ("embed+norm_quant", "final_norm+logits")},
+           "ms_per_layer_breakdown_rank0": {k: v / layers for k, v in br.items() if k not in ("embed+norm_quant", "final_norm")},
            "logits_finite": bool(torch.isfinite(logits).all())}
     if world > 1:
         # NVLink floor per layer: two reduce-scatters of bf16 partials and two all-gathers of quantised rows per rank
@@ -1014,6 +1018,7 @@ def main():
     ap.add_argument("--model", action="store_true", help="only the Llama-architecture prefill forward of configs[3] (tokens/s)")
     ap.add_argument("--layers", type=int, default=32, help="with --model: number of layers (32 = configs[3])")
     ap.add_argument("--no-model", action="store_true", help="skip the configs[3] forward in the default run")
+    ap.add_argument("--eager-model", action="store_true", help="run the model forward eagerly instead of replaying its CUDA graph")
     ap.add_argument("--ep", action="store_true", help="instead of the GEMM set: the gpt-oss-120b-shaped MoE layer with the experts split over "
                                                       "the ranks and all-to-all dispatch / combine (strong scaling, 8192 tokens in total)")
     ap.add_argument("--dense", action="store_true", help="with --only: the dense NVFP4 GEMM instead of the 2:4-sparse one")

@@ -127,6 +127,8 @@ class LlamaPrefill:
         self._rope = {}
         self.timings = None
         self._marks = []
+        self._last_idx = {}
+        self._graph = self._graph_key = self._graph_out = self._ids_static = None
         self.capture = None          # set to a dict to keep the intermediate tensors of the LAST layer run (tests)
 
     # ------------------------------------------------------------------ pieces
@@ -178,11 +180,10 @@ class LlamaPrefill:
             self._gemm(lin, Bb.data_ptr(), sfb.data_ptr(), gp, tok, part)
             dist.all_to_all_single(ctx.slots_view(k), part.view(self.world, ctx.Tl, out_f), group=self.group)
             return None
-        val = ctx.next_value(ctx.FLAG_SLOT[k])
         check(self.lib.qb_gemm_rs(lin.At.data_ptr(), Bb.data_ptr(), lin.sfa.data_ptr(), sfb.data_ptr(),
                                   0 if dense else lin.meta_native.data_ptr(), lin.gA.data_ptr(), gp, ctx.slot_out_ptrs(k),
                                   ctx.flag_ptrs(ctx.FLAG_SLOT[k]), ctx.done[k:].data_ptr(), out_f, tok, in_f, 2 if dense else 3, self.world,
-                                  self.rank, ctx.Tl, val, 0, 0, _stream()), "qb_gemm_rs")
+                                  self.rank, ctx.Tl, 0, ctx.epoch.data_ptr(), 0, _stream()), "qb_gemm_rs")
         return None
 
     def _norm_quant(self, src, k, res, wt, block: int, T: int):
@@ -225,19 +226,18 @@ class LlamaPrefill:
             self._keep = (Bb, sf, g)
             return hout, (Bb.data_ptr(), sf.data_ptr(), g.data_ptr())
         fw = ctx.FLAG_GATHER[block]
-        val = ctx.next_value(fw)
-        wait_ptr, wait_val = (ctx.flag_own(ctx.FLAG_SLOT[k]), ctx.counter[ctx.FLAG_SLOT[k]]) if src is None else (0, 0)
+        wait_ptr = ctx.flag_own(ctx.FLAG_SLOT[k]) if src is None else 0
         Bv, Sv, Gv = ctx.gathered_ptrs(block)
         check(lib.qb_reduce_norm_quant(s0, stride, nsrc, rp, wt.data_ptr(), hp, Bv, Sv, Gv, W, self.rank * Tl, T, Tl, H, self.cfg.rms_eps,
-                                       block, wait_ptr, wait_val, ctx.flag_ptrs(fw), W, self.rank, val, ctx.done[2 + (block == 32):].data_ptr(),
-                                       0, _stream()), "qb_reduce_norm_quant")
-        return hout, ("gathered", block, val)
+                                       block, wait_ptr, 0, ctx.flag_ptrs(fw), W, self.rank, 0, ctx.done[2 + (block == 32):].data_ptr(),
+                                       ctx.epoch.data_ptr(), _stream()), "qb_reduce_norm_quant")
+        return hout, ("gathered", block)
 
     def _resolve(self, q, block: int):
         """Pointers of the gathered activations; with peer stores, first wait until every rank's rows have landed."""
         if isinstance(q[0], str):
             ctx = self.ctx
-            check(self.lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), self.world, q[2], 0, _stream()), "qb_peer_wait")
+            check(self.lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_GATHER[block]), self.world, 0, ctx.epoch.data_ptr(), _stream()), "qb_peer_wait")
             return ctx.gathered_own(block)
         return q
 
@@ -251,12 +251,14 @@ class LlamaPrefill:
         Tl = T // W
         r0 = self.rank * Tl
         self._mark("start")
-        x = self.embed[ids.reshape(-1)[r0:r0 + Tl].to(self.device)]                # residual stream, this rank's rows
+        x = self.embed[ids.reshape(-1)[r0:r0 + Tl]]                                # residual stream, this rank's rows (ids on the device)
         res, q16 = self._norm_quant(x, None, None, self.layers[0].norm_attn, 16, T)
         self._mark("embed+norm_quant")
         yield None
         for li, L in enumerate(self.layers):
             Bb, sf, g = self._resolve(q16, 16)
+            if W > 1 and self.comm == "peer":
+                self.ctx.bump(_stream())         # every flag written in this layer carries the new epoch
             self._cap_gathered("q16", (Bb, sf, g), 16, T)
             self._cap("x_attn_in", x)
             qkv = torch.empty((T, L.qkv.out), dtype=torch.bfloat16, device=self.device)
@@ -273,7 +275,7 @@ class LlamaPrefill:
             yield None
             if self.capture is not None:
                 if W > 1 and self.comm == "peer":          # test aid: the partials must have landed before they are copied
-                    check(lib.qb_peer_wait(self.ctx.flag_own(0), W, self.ctx.counter[0], 0, _stream()), "qb_peer_wait")
+                    check(lib.qb_peer_wait(self.ctx.flag_own(0), W, 0, self.ctx.epoch.data_ptr(), _stream()), "qb_peer_wait")
                 self._cap("o_parts", o.unsqueeze(0) if W == 1 else self.ctx.slots_view(0))
             x, q32 = self._norm_quant(o, 0, x, L.norm_mlp, 32, T)
             self._mark("reduce+norm_quant")
@@ -301,7 +303,7 @@ class LlamaPrefill:
             yield None
             if self.capture is not None:
                 if W > 1 and self.comm == "peer":
-                    check(lib.qb_peer_wait(self.ctx.flag_own(1), W, self.ctx.counter[1], 0, _stream()), "qb_peer_wait")
+                    check(lib.qb_peer_wait(self.ctx.flag_own(1), W, 0, self.ctx.epoch.data_ptr(), _stream()), "qb_peer_wait")
                 self._cap("d_parts", d.unsqueeze(0) if W == 1 else self.ctx.slots_view(1))
             if li + 1 < len(self.layers):
                 x, q16 = self._norm_quant(d, 1, x, self.layers[li + 1].norm_attn, 16, T)
@@ -313,7 +315,7 @@ class LlamaPrefill:
         else:
             ctx = self.ctx
             if self.comm == "peer":
-                check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_SLOT[1]), W, ctx.counter[ctx.FLAG_SLOT[1]], 0, _stream()), "qb_peer_wait")
+                check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_SLOT[1]), W, 0, ctx.epoch.data_ptr(), _stream()), "qb_peer_wait")
             sl = ctx.slots_view(1).float()
             v = sl[0]
             for s in range(1, W):
@@ -321,16 +323,29 @@ class LlamaPrefill:
             v = v + x.float()
         xf = v.to(torch.bfloat16).float()
         hid = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * self.norm_f.float()).to(torch.bfloat16)
+        # rows of the last token of every sequence that this rank owns (static index tensors, cached per shape)
+        src_idx, dst_idx = self._last_index(B, S, r0, Tl)
         last = torch.zeros((B, H), dtype=torch.float32, device=self.device)
-        pos = torch.arange(B, device=self.device) * S + (S - 1)
-        mine = (pos >= r0) & (pos < r0 + Tl)
-        last[mine] = hid[(pos[mine] - r0)].float()
-        if W > 1 and self.group is not False and torch.distributed.is_initialized():
-            torch.distributed.all_reduce(last, group=self.group)
+        if src_idx.numel():
+            last.index_copy_(0, dst_idx, hid.index_select(0, src_idx).float())
         self._last_rows = last
-        logits = (last.to(torch.bfloat16) @ self.lm_head.t()).float()
-        self._mark("final_norm+logits")
-        yield hid, logits
+        self._mark("final_norm")
+        yield hid, last
+
+    def _last_index(self, B: int, S: int, r0: int, Tl: int):
+        key = (B, S, r0, Tl)
+        if key not in self._last_idx:
+            own = [(b * S + S - 1 - r0, b) for b in range(B) if r0 <= b * S + S - 1 < r0 + Tl]
+            self._last_idx[key] = (torch.tensor([o[0] for o in own], dtype=torch.long, device=self.device),
+                                   torch.tensor([o[1] for o in own], dtype=torch.long, device=self.device))
+        return self._last_idx[key]
+
+    def _finish(self, hid: torch.Tensor, last: torch.Tensor):
+        """Sum the last-token rows over the ranks (every rank filled the ones it owns) and take the logits."""
+        if self.world > 1 and torch.distributed.is_initialized():
+            last = last.clone()
+            torch.distributed.all_reduce(last, group=self.group)
+        return hid, (last.to(torch.bfloat16) @ self.lm_head.t()).float()
 
     def _mark(self, name: str):
         """With `self.timings` set to a dict, the device time between consecutive marks is added to timings[name]
@@ -373,19 +388,44 @@ class LlamaPrefill:
 
     def forward(self, ids: torch.Tensor):
         out = None
-        for out in self.forward_steps(ids):
+        for out in self.forward_steps(ids.to(self.device)):
             pass
-        return out
+        return self._finish(*out)
 
     __call__ = forward
+
+    def forward_graphed(self, ids: torch.Tensor):
+        """`forward` with the whole layer stack replayed from one CUDA graph (captured on the first call for a shape, after
+        two eager warm-up runs). The cross-GPU flag values are read from the device epoch when the kernels run, so the
+        captured arguments stay valid; every rank must make the same sequence of calls."""
+        key = tuple(ids.shape)
+        if self._graph is None or self._graph_key != key:
+            self._graph = None
+            self._ids_static = ids.to(self.device).clone()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    for out in self.forward_steps(self._ids_static):
+                        pass
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for out in self.forward_steps(self._ids_static):
+                    pass
+            self._graph, self._graph_key, self._graph_out = g, key, out
+        self._ids_static.copy_(ids.to(self.device))
+        self._graph.replay()
+        return self._finish(*self._graph_out)
 
 
 def forward_emulated(models, ids: torch.Tensor):
     """Drive `world` ranks that share one GPU in lock step (see tp.TPContext.emulated). Returns the list of per-rank
     (hidden_local, logits); the last-token rows are summed here in place of the all-reduce."""
-    gens = [m.forward_steps(ids) for m in models]
+    gens = [m.forward_steps(ids.to(m.device)) for m in models]
     outs = [None] * len(models)
     for step in zip(*gens):
         outs = list(step)
-    last = sum(m._last_rows for m in models)
+    last = sum(o[1] for o in outs)
     return [(o[0], (last.to(torch.bfloat16) @ m.lm_head.t()).float()) for o, m in zip(outs, models)]

@@ -99,7 +99,7 @@ class TPContext:
     gathered[b]   quantised activations of all T tokens on every rank (b = 16 dense / 32 sparse input): packed bytes
                   [T][H/2], scale atoms, globals [T]; every rank stores its rows into all copies.
     flags         four arrays of `world` ints on every rank (slots 0 / 1 landed, gathered 16 / 32 landed), written with
-                  monotonically increasing values: the op count of the model, equal on all ranks.
+                  the value of `epoch`, a device counter that every rank bumps once per layer (equal on all ranks).
     """
 
     FLAG_SLOT = (0, 1)
@@ -126,7 +126,10 @@ class TPContext:
             self.bufs = [PeerBuffer(n, rank, world, group, self.device) for n in sizes]
         self.sizes = sizes
         self.done = torch.zeros(16, dtype=torch.int32, device=self.device)
-        self.counter = [0, 0, 0, 0]
+        # Flag values are the "epoch", a device word every rank bumps at the same points of its stream (qb_epoch_add): the
+        # kernels read it when they run, so their arguments never change and a whole forward can be replayed from a CUDA
+        # graph. It starts at 1: the flag words start at 0 and the first wait must not pass on that.
+        self.epoch = torch.ones(1, dtype=torch.int32, device=self.device)
 
     @staticmethod
     def emulated(T: int, H: int, world: int, device):
@@ -171,9 +174,8 @@ class TPContext:
     def flag_own(self, which: int) -> int:
         return self.bufs[4].ptrs[self.rank] + which * 64
 
-    def next_value(self, which: int) -> int:
-        self.counter[which] += 1
-        return self.counter[which]
+    def bump(self, stream: int):
+        check(self.lib.qb_epoch_add(self.epoch.data_ptr(), 1, stream), "qb_epoch_add")
 
     def close(self):
         for b in self.bufs:

@@ -166,6 +166,9 @@ def test_forward_end_to_end_one_gpu():
     assert rel < 0.25 and cos > 0.97, (rel, cos)
     hid2, _ = model(ids)
     assert torch.equal(hid, hid2)                 # a second call reuses nothing stale
+    for _ in range(2):                            # the CUDA-graph replay gives the same bits
+        hid3, logits3 = model.forward_graphed(ids)
+        assert torch.equal(hid, hid3) and torch.equal(logits, logits3)
 
 
 def test_tensor_parallel_data_path_two_ranks_on_one_gpu():
@@ -220,6 +223,10 @@ def _tp_worker(rank, world, port, ret):
         model = LlamaPrefill(cfg, w, rank=rank, world=world, comm=comm, ctx=ctx)
         for _ in range(2):
             hid, logits = model(ids)
+        if comm == "peer":                      # replayed from a CUDA graph: same bits, flags keep counting
+            for _ in range(2):
+                hid_g, logits_g = model.forward_graphed(ids)
+            assert torch.equal(hid_g, hid) and torch.equal(logits_g, logits)
         torch.cuda.synchronize()
         assert model.lib.qb_status(0) == 0 and model.lib.qb_peer_status(0) == 0
         res[comm] = (hid.cpu(), logits.cpu())
