@@ -611,7 +611,43 @@ def run_gpu(args):
         tl = T // world
         mine = slice(rank * tl, (rank + 1) * tl)
         x_l, i_l, w_l = xs[mine].to(dev), ti[mine].to(dev), tw[mine].to(dev)
-        step_ep = lambda: moe.forward_ep(x_l, i_l, w_l)
+        # N > 1: expert parallelism by peer loads (`SparseMoE.forward_ep_peer`: routing tables replicated by stores, token rows
+        # pulled by the gather + quantise kernel, expert outputs pulled by the combine; no NCCL call, no host read), replayed
+        # from one CUDA graph per rank; `--ep-comm nccl` times the all-to-all form instead. N = 1: the all-to-all form
+        # degenerates to sort -> experts -> unsort (the graph-replayed one-rank layer follows below).
+        peer = world > 1 and args.ep_comm == "peer"
+        ep_note = None
+        nccl_t = None
+        if world > 1:
+            # the NCCL all-to-all form, as the baseline beside the peer form
+            for _ in range(3):
+                moe.forward_ep(x_l, i_l, w_l)
+            torch.cuda.synchronize()
+            dist.barrier()
+            nccl_t = ev_time(lambda: moe.forward_ep(x_l, i_l, w_l), min(args.steps, 30))
+            tt = torch.tensor([nccl_t], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            nccl_t = float(tt.item())
+        if peer:
+            try:
+                ectx = moe.make_ep_context(T, rank, world)
+            except RuntimeError as e:        # raised on every rank at the same point
+                peer, ep_note = False, f"peer form unavailable ({e})"
+        if peer:
+            dist.barrier()
+            for _ in range(3):
+                moe.forward_ep_peer(x_l, i_l, w_l, ectx)
+            torch.cuda.synchronize()
+            dist.barrier()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph, stream=side):
+                y_ep = moe.forward_ep_peer(x_l, i_l, w_l, ectx)
+            torch.cuda.current_stream().wait_stream(side)
+            step_ep = gph.replay
+        else:
+            step_ep = lambda: moe.forward_ep(x_l, i_l, w_l)
         for _ in range(max(args.warmup, 3)):
             step_ep()
         torch.cuda.synchronize()
@@ -624,6 +660,10 @@ def run_gpu(args):
             tt = torch.tensor([t], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             t = float(tt.item())
+            stt = torch.tensor([lib.qb_status(0) or lib.qb_peer_status(0)], device=dev)
+            dist.all_reduce(stt, op=dist.ReduceOp.MAX)
+            if int(stt.item()):
+                raise RuntimeError(f"device status {int(stt.item())}")
             dist.barrier()
         if lib.qb_status(0):
             raise RuntimeError("device status")
@@ -670,9 +710,13 @@ def run_gpu(args):
                               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic",
                               "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate, bf16 out)",
                               "config": {"workload": "gpt-oss-120b-shaped MoE layer: hidden 2880, 128 experts, intermediate 2880, top-4, "
-                                                     "8192 tokens in total", "parallelism": f"ep{world}: {E // world} experts and {tl} tokens per rank, "
-                                                     "all-to-all dispatch and combine of bf16 rows"},
-                              "useful_tflops": fl / t / 1e12, "cuda_graph": graph, "clocks": cs.summary()}), flush=True)
+                                                     "8192 tokens in total", "parallelism": f"ep{world}: {E // world} experts and {tl} tokens per rank, " + (
+                                                         "routing replicated by peer stores, token rows pulled by the gather + quantise kernel, expert "
+                                                         "outputs pulled by the combine, one CUDA graph replay per step" if peer else
+                                                         "all-to-all dispatch and combine of bf16 rows (NCCL)"), "note": ep_note},
+                              "useful_tflops": fl / t / 1e12, "cuda_graph": graph,
+                              "nccl_baseline": None if nccl_t is None else {"ms_per_step": nccl_t * 1e3, "tokens_per_s": T / nccl_t},
+                              "clocks": cs.summary()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -1015,6 +1059,7 @@ def main():
                     "scaling) instead of the default tensor-parallel sharding")
     ap.add_argument("--tp-comm", default="both", choices=["peer", "nccl", "both"], help="tensor-parallel exchange: peer stores from the "
                     "kernels, NCCL calls beside them, or both (peer is the reported value, nccl goes to nccl_baseline)")
+    ap.add_argument("--ep-comm", default="peer", choices=["peer", "nccl"], help="with --ep at N > 1: peer loads from the kernels or NCCL all-to-all")
     ap.add_argument("--model", action="store_true", help="only the Llama-architecture prefill forward of configs[3] (tokens/s)")
     ap.add_argument("--layers", type=int, default=32, help="with --model: number of layers (32 = configs[3])")
     ap.add_argument("--no-model", action="store_true", help="skip the configs[3] forward in the default run")

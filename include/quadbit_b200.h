@@ -46,7 +46,12 @@ extern "C" {
 
 /* ------------------------------------------------------------------ reference symbols */
 
-/* cuda/sparse_fp4_lib.cu:1042 — single-level 2:4-sparse GEMM, C[out][tok] bf16; synchronises. */
+/* The reference-named GEMM entries below take the reference's tensor layouts and re-lay scale factors / metadata into ONE
+ * per-device scratch buffer of the library (grown with cudaMalloc when a larger problem arrives: make the first call of a
+ * size outside graph capture). Calls on one device must therefore be stream-ordered with each other: two of them running
+ * at once on different streams or threads overwrite each other's re-laid operands. qb_register_weight removes the
+ * per-call weight re-layout; the native qb_* entries use no scratch at all.
+ * cuda/sparse_fp4_lib.cu:1042 — single-level 2:4-sparse GEMM, C[out][tok] bf16; synchronises. */
 int sparse_fp4_mm(const void* A, const void* B, const void* scaleA, const void* scaleB, const void* meta, void* C,
                   int out, int tok, int K);
 /* cuda/sparse_fp4_lib.cu:1110 — two-level: C[out][tok] = gA[out]*gB[tok]*sum; synchronises. */
@@ -308,14 +313,34 @@ int qb_peer_open(const void* handle64, void** ptr);
 int qb_peer_close(void* ptr);
 /* One-thread kernels on `stream`: signal writes `value` into word my_rank of each of the n flag arrays (after a
  * system-scope fence; stream order puts it after the kernels it announces); wait returns when all n words of `flags`
- * are >= value (or >= *value_ptr when that is not NULL), or after 20 s with a status code (qb_peer_status). */
-int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, void* stream);
+ * are >= value (or >= *value_ptr when that is not NULL; signal takes its value the same way), or after 20 s with a status
+ * code (qb_peer_status). */
+int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, const void* value_ptr, void* stream);
 int qb_peer_wait(const void* flags, int n, int value, const void* value_ptr, void* stream);
 /* *epoch += delta by one thread on `stream`. The entries here that take a `value_ptr` read their flag value(s) from that
  * device word when the kernel runs instead of from the argument, so a captured CUDA graph can be replayed: every replay
  * first bumps the word, on every rank. */
 int qb_epoch_add(void* epoch, int delta, void* stream);
 int qb_peer_status(void* stream);
+/* ---- expert parallelism by peer loads (no counterpart in the reference library; its script all-reduces partial outputs,
+ * harness/moe_dist.py:161-167, its plugin dispatches with torch indexing, harness/qb_vllm_plugin/qb_sm120_plugin.py:2430-2441).
+ * qb_ep_publish: copy this rank's token rows x (x_bytes, 16-byte multiple) into its peer-visible buffer x_pub and store its
+ *   routing (idx i64, w f32, n_slots entries) into the replicated tables assign_all[r] / w_all[r] of every rank at slot0; the
+ *   last CTA writes *value_ptr into word `rank` of every flags[r] (done_counter: one int, zero between calls).
+ * qb_moe_route_fixed_range: qb_moe_route_fixed_ex for a rank that owns experts [e_base, e_base + e) of a global id space.
+ * qb_gather_quantize_act_peer: qb_gather_quantize_act whose source rows are numbered over n_peers buffers of rows_per_peer
+ *   rows each (pointers into the ranks' x_pub): the dispatch is done by the loads of the quantiser.
+ * qb_ep_combine: y[t][f] = sum_k d_owner[inverse_owner[(t0 + t) * topk + k]][f] for this rank's t_local tokens, the rows read
+ *   from the rank that owns the slot's expert (owner = idx / experts_per_rank; dbuf[r], inverse[r]: peer pointers). */
+int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx, const void* w, int n_slots, int slot0,
+                  void* const* assign_all, void* const* w_all, int world, int rank, void* const* flags, const void* value_ptr,
+                  void* done_counter, void* stream);
+int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
+                             const void* w_in, void* rw, void* inverse, void* stream);
+int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
+                                void* g, int rows, int K, int H, int block, void* stream);
+int qb_ep_combine(void* const* dbuf, void* const* inverse, const void* idx, void* y, int t_local, int t0, int H, int topk, int Mpe,
+                  int experts_per_rank, int world, void* stream);
 /* Row-parallel GEMM fused with the reduce-scatter of its partial result (replaces "GEMM, then all_reduce"): operands as
  * qb_gemm (this rank's K slice), token-major bf16 output; token row t is stored by the epilogue into
  * peer_out[t / tok_per_rank] + (t % tok_per_rank) * out (a pointer into the owner's memory, already offset to this rank's

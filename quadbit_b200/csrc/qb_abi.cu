@@ -544,6 +544,17 @@ int qb_moe_route_fixed_ex(const void* assign, void* src, void* pos, void* eblk, 
                           void* rw, void* inverse, void* stream) {
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse);
 }
+int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
+                             const void* w_in, void* rw, void* inverse, void* stream) {
+    if (e_base < 0) return QB_ERR_ARG;
+    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base);
+}
+int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
+                                void* g, int rows, int K, int H, int block, void* stream) {
+    if (!x_peers) return QB_ERR_ARG;
+    return qb::gather_quantize_act(nullptr, src, Bbytes, nullptr, sf_atoms, g, rows, K, H, block, (cudaStream_t)stream,
+                                   (const void* const*)x_peers, n_peers, rows_per_peer);
+}
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream) {
     int rc = qb::moe_route(assign, const_cast<void*>(poff), counter, src, N, E, (cudaStream_t)stream);
     return stream ? rc : finish_sync(rc, 0);

@@ -93,7 +93,7 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
 __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap,
                                                                 long long* __restrict__ src, long long* __restrict__ pos,
                                                                 int* __restrict__ eblk, int div, const float* __restrict__ w_in,
-                                                                float* __restrict__ rw, int* __restrict__ inverse) {
+                                                                float* __restrict__ rw, int* __restrict__ inverse, int e_base) {
     // optional extras that the layer would otherwise do with a dozen small kernels: src holds slot / div (the token row
     // of a slot when div = top-k), rw[row] = w_in[slot] (0 for padding rows), inverse[slot] = row as int32
     extern __shared__ int sm[];
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
     for (int i = threadIdx.x; i < e; i += blockDim.x) { counts[i] = 0; cursor[i] = 0; }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const long long ex = assign[i];
+        const long long ex = assign[i] - e_base;           // expert ids are global; this rank owns [e_base, e_base + e)
         if (ex >= 0 && ex < e) atomicAdd(&counts[(int)ex], 1);
     }
     __syncthreads();
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
     }
     __syncthreads();          // the -1 fill of src is complete (same CTA) before slots are written
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const long long ex = assign[i];
+        const long long ex = assign[i] - e_base;
         long long dst = -1;
         if (ex >= 0 && ex < e) {
             dst = poff[(int)ex] + atomicAdd(&cursor[(int)ex], 1);
@@ -138,11 +138,11 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
 }
 
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div,
-                    const void* w_in, void* rw, void* inverse) {
+                    const void* w_in, void* rw, void* inverse, int e_base) {
     if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % 128 || (long long)r_cap < (long long)n + (long long)e * 127) return QB_ERR_ARG;
     if (!assign || !src || !pos || !eblk || div < 1 || ((rw != nullptr) != (w_in != nullptr))) return QB_ERR_ARG;
     moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
-                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse);
+                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base);
     return (int)cudaGetLastError();
 }
 

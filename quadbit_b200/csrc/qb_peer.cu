@@ -15,10 +15,12 @@
 
 namespace {
 
-__global__ void peer_signal_kernel(int* f0, int* f1, int* f2, int* f3, int* f4, int* f5, int* f6, int* f7, int n, int rank, int value) {
+__global__ void peer_signal_kernel(int* f0, int* f1, int* f2, int* f3, int* f4, int* f5, int* f6, int* f7, int n, int rank, int value,
+                                   const int* value_ptr) {
     // stream order puts this after the kernels whose reads / writes it announces; one thread, one flag word per rank
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         int* f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+        if (value_ptr) value = *value_ptr;
         __threadfence_system();
         for (int r = 0; r < n; r++) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f[r] + rank), "r"(value) : "memory");
     }
@@ -93,14 +95,14 @@ int qb_peer_open(const void* handle64, void** ptr) {
 
 int qb_peer_close(void* ptr) { return ptr ? (int)cudaIpcCloseMemHandle(ptr) : QB_OK; }
 
-int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, void* stream) {
+int qb_peer_signal(void* const* flag_arrays, int n, int my_rank, int value, const void* value_ptr, void* stream) {
     if (!flag_arrays || n < 1 || n > 8 || my_rank < 0 || my_rank >= n) return QB_ERR_ARG;
     int* f[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     for (int r = 0; r < n; r++) {
         if (!flag_arrays[r]) return QB_ERR_ARG;
         f[r] = (int*)flag_arrays[r];
     }
-    peer_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], n, my_rank, value);
+    peer_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], n, my_rank, value, (const int*)value_ptr);
     return (int)cudaGetLastError();
 }
 

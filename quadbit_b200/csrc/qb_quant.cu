@@ -22,11 +22,17 @@ namespace qb {
 // reciprocal of the divider) runs once per block and lane: with the 8-values-per-lane mapping it ran in
 // all BLOCK/8 lanes of a block, and the kernel was issue-bound (ncu: 92 % issue-active, 59 warp
 // instructions per value) at a fifth of the HBM rate.
+struct GatherPeers {
+    const uint4* p[8];
+    long long rows_per;
+    int n;
+};
+
 template <int BLOCK, int NJ, bool TWO_LEVEL>
 __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
                                                           uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
                                                           float* __restrict__ g_out, int tok, int K,
-                                                          const long long* __restrict__ src, int h8) {
+                                                          const long long* __restrict__ src, int h8, const GatherPeers peers) {
     // src != nullptr: row `row` of the output quantises source row src[row] of x [.][h8 * 8] zero-padded to K
     // (src < 0: an all-zero row) — the gather of routed MoE rows fused into their quantiser
     constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
@@ -37,7 +43,15 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
     const long long srow = src ? src[row] : (long long)row;
-    const uint4* xr = x + (size_t)(srow < 0 ? 0 : srow) * h8;
+    // peers.n > 0: source rows are numbered over all ranks (rows_per rows each) and read from the rank that holds them
+    // (plain loads from peer-mapped memory: the dispatch of an expert-parallel layer folded into the gather)
+    const uint4* xr;
+    if (peers.n > 0 && srow >= 0) {
+        const int owner = (int)(srow / peers.rows_per);
+        xr = peers.p[owner] + (size_t)(srow - (long long)owner * peers.rows_per) * h8;
+    } else {
+        xr = x + (size_t)(srow < 0 ? 0 : srow) * h8;
+    }
     if (srow < 0) {
         // padding row: what the full path makes of an all-zero row (codes 0, scale codes 0, global 1e-30), without the passes
         for (int b = threadIdx.x; b < nblocks; b += blockDim.x) {
@@ -63,7 +77,7 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 #pragma unroll
         for (int k = 0; k < CPB; k++) {
             v[j][k] = make_uint4(0, 0, 0, 0);
-            if (b < nblocks && b * CPB + k < h8 && srow >= 0) v[j][k] = __ldg(xr + (size_t)b * CPB + k);
+            if (b < nblocks && b * CPB + k < h8 && srow >= 0) v[j][k] = peers.n > 0 ? __ldcg(xr + (size_t)b * CPB + k) : __ldg(xr + (size_t)b * CPB + k);
             m = fmaxf(m, absmax8_bf16(v[j][k]));
         }
         bmax[j] = m;
@@ -679,7 +693,7 @@ int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* s
 
 template <int BLOCK, bool TWO_LEVEL>
 static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, float* g, int tok, int K,
-                        cudaStream_t st, const long long* src, int h8) {
+                        cudaStream_t st, const long long* src, int h8, const GatherPeers& peers) {
     const int nblocks = K / BLOCK;
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
@@ -698,7 +712,7 @@ static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atom
     cfg.numAttrs = 1;
 #define QB_LQ(NJ)                                                                                                          \
     return (int)cudaLaunchKernelEx(&cfg, quant_act_kernel<BLOCK, NJ, TWO_LEVEL>, (const uint4*)x, (uint32_t*)Bbytes, (uint8_t*)sf_ref, \
-                                   (uint8_t*)sf_atoms, g, tok, K, src, h8)
+                                   (uint8_t*)sf_atoms, g, tok, K, src, h8, peers)
     if (nj <= 1) QB_LQ(1);
     else if (nj <= 2) QB_LQ(2);
     else if (nj <= 4) QB_LQ(4);
@@ -715,19 +729,30 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
 // src == nullptr: plain quantiser of x [tok][K]. Otherwise output row r = quantised x[src[r]] (x rows of H <= K values,
 // zero-padded to K; src[r] < 0 gives a zero row): gather + pad + quantise of routed MoE rows in one pass.
 int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
-                        int block, cudaStream_t st) {
+                        int block, cudaStream_t st, const void* const* peer_x, int n_peers, long long rows_per_peer) {
     if (tok < 0 || K <= 0 || K % 128 != 0 || (block != 16 && block != 32) || H <= 0 || H > K || H % 8) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
-    if (!x || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
+    if ((!x && !peer_x) || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
     if (((uintptr_t)x & 15) || ((uintptr_t)Bbytes & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3) || ((uintptr_t)src & 7)) return QB_ERR_ARG;
     if (K > 65536) return QB_ERR_UNSUPPORTED;
+    GatherPeers peers{};
+    if (peer_x) {
+        if (n_peers < 1 || n_peers > 8 || rows_per_peer <= 0 || !src) return QB_ERR_ARG;
+        for (int r = 0; r < n_peers; r++) {
+            if (!peer_x[r] || ((uintptr_t)peer_x[r] & 15)) return QB_ERR_ARG;
+            peers.p[r] = (const uint4*)peer_x[r];
+        }
+        peers.n = n_peers;
+        peers.rows_per = rows_per_peer;
+        if (!x) x = peer_x[0];
+    }
     const long long* sp = (const long long*)src;
     const int h8 = H >> 3;
     if (block == 32)
-        return g ? launch_quant<32, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8)
-                 : launch_quant<32, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8);
-    return g ? launch_quant<16, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8)
-             : launch_quant<16, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8);
+        return g ? launch_quant<32, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8, peers)
+                 : launch_quant<32, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8, peers);
+    return g ? launch_quant<16, true>(x, Bbytes, sf_ref, sf_atoms, (float*)g, tok, K, st, sp, h8, peers)
+             : launch_quant<16, false>(x, Bbytes, sf_ref, sf_atoms, nullptr, tok, K, st, sp, h8, peers);
 }
 
 // ---- re-layout: reference step-major scales [K/128][rows][P] -> 128x4 atoms

@@ -138,11 +138,11 @@ def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tens
     return C
 
 
-def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None):
-    """Grouped GEMM on already quantised routed rows (Bb [r, in_f/2], scale atoms, gB [r])."""
+def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None, out=None):
+    """Grouped GEMM on already quantised routed rows (Bb [r, in_f/2], scale atoms, gB [r]); out: optional [r, mpe] bf16."""
     Ac, meta, sfa, gA = w
     r = Bb.shape[0]
-    C = torch.empty((r, mpe), dtype=torch.bfloat16, device=Bb.device)
+    C = out if out is not None else torch.empty((r, mpe), dtype=torch.bfloat16, device=Bb.device)
     mode = 3 if (bias is not None or row_w is not None) else 1
     check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), _ptr(gB),
                       C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
@@ -226,20 +226,27 @@ class SparseMoE:
         # from the device; `forward` then issues no host read and can be captured in a CUDA graph
         self.fixed_capacity = fixed_capacity
 
-    def _run_padded(self, x: torch.Tensor, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor) -> torch.Tensor:
+    def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None) -> torch.Tensor:
         """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
         padding), eblk = expert of every 128-row block, rw [r_pad] = routing weight of every row. Returns
         d [r_pad, mpe_dn] bf16 = expert(row) * weight."""
         lib = self.lib
-        dev = x.device
-        x = x.to(torch.bfloat16).contiguous()
-        if self.H % 8:                       # the fused gather reads 16-byte chunks
-            x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
+        dev = src.device
         Bb = torch.empty((r_pad, self.Hp // 2), dtype=torch.uint8, device=dev)
         sfb = sf_atoms_empty(lib, r_pad, self.Hp, 32, dev)
         gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
-        check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
-                                         x.shape[1], 32, _stream()), "qb_gather_quantize_act")
+        if peer_x is not None:
+            # src holds GLOBAL token rows; the rows are pulled from the ranks that hold them (peer_x = (pointer table, rows
+            # per rank, row width in elements, number of ranks))
+            xp, rows_per_rank, width, nr = peer_x
+            check(lib.qb_gather_quantize_act_peer(xp, nr, rows_per_rank, src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), r_pad,
+                                                  self.Hp, width, 32, _stream()), "qb_gather_quantize_act_peer")
+        else:
+            x = x.to(torch.bfloat16).contiguous()
+            if self.H % 8:                       # the fused gather reads 16-byte chunks
+                x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
+            check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
+                                             x.shape[1], 32, _stream()), "qb_gather_quantize_act")
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
         if self.fused_gu:
@@ -248,12 +255,12 @@ class SparseMoE:
             check(lib.qb_gemm_swiglu(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
                                      eblk.data_ptr(), _ptr(self.b_gu), Hb.data_ptr(), sfh.data_ptr(), 0, Ac.shape[0], self.mpe_gu, r_pad, self.Hp,
                                      1, 0 if self.act == "gptoss" else 1, _stream()), "qb_gemm_swiglu")
-            return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw)
+            return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)
         gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
-        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw)  # [r_pad, mpe_dn]
+        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)  # [r_pad, mpe_dn]
 
     def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
         """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
@@ -324,6 +331,69 @@ class SparseMoE:
         from . import dist as qd
         return qd.ep_moe(x, topk_idx, topk_w, self.E_total, self.expert_rows,
                          lambda d, inverse, T: combine(self.lib, d, inverse, T, self.H, self.topk), group)
+
+    # ------------------------------------------------------------------ expert parallelism by peer loads
+    def ep_capacity(self, T: int) -> int:
+        """Routed rows a rank must be able to hold when all T * topk slots could land on its experts."""
+        return fixed_capacity(T * self.topk, self.e1 - self.e0)
+
+    def make_ep_context(self, T: int, rank: int, world: int, group=None, emulate=None):
+        from .tp import EPContext
+        width = self.Hp if self.H % 8 else self.H
+        if emulate is not None:
+            return emulate
+        return EPContext(T, width, self.topk, self.mpe_dn, self.ep_capacity(T), rank, world, group)
+
+    def forward_ep_peer_steps(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, ctx):
+        """Expert-parallel layer without a collective library and without a host read (a generator that yields where
+        other ranks are waited for, so that one process can drive emulated ranks; the last value is y [T_local, H]).
+
+        This rank holds experts [e0, e1) and tokens x [T_local, H]. (1) Every rank copies its tokens into a peer-visible
+        buffer and stores its routing (expert ids, weights) into the replicated tables of all ranks. (2) Every rank routes
+        ALL slots onto its own experts with the one-kernel fixed-capacity routing, pulls the token rows it needs from
+        their home ranks inside the fused gather + quantise kernel, and runs its experts. (3) Every rank combines the
+        top-k rows of its own tokens, reading them from the experts' owners. Flags carry the device epoch, so the whole
+        layer has fixed kernel arguments (CUDA-graph replay). Equals `forward` of a 1-rank layer."""
+        lib, W, rank = self.lib, ctx.world, ctx.rank
+        T, Tl, topk = ctx.T, ctx.Tl, self.topk
+        dev = x.device
+        epr = self.e1 - self.e0
+        assert x.shape[0] == Tl and self.E_total == epr * W and self.e0 == rank * epr
+        x = x.to(torch.bfloat16).contiguous()
+        if self.H % 8:
+            x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
+        idx = topk_idx.reshape(-1).long().contiguous()
+        w = topk_w.reshape(-1).float().contiguous()
+        n = T * topk
+        ep = ctx.epoch.data_ptr()
+        ctx.bump(_stream())
+        check(lib.qb_ep_publish(x.data_ptr(), ctx.own(0), x.numel() * 2, idx.data_ptr(), w.data_ptr(), Tl * topk, rank * Tl * topk,
+                                ctx.ptrs(1), ctx.ptrs(1, ctx.off_w), W, rank, ctx.flag_ptrs(ctx.FLAG_PUBLISHED), ep, ctx.done.data_ptr(),
+                                _stream()), "qb_ep_publish")
+        yield None
+        check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_PUBLISHED), W, 0, ep, _stream()), "qb_peer_wait")
+        r_cap = ctx.r_cap
+        src = torch.empty((r_cap,), dtype=torch.long, device=dev)
+        pos = torch.empty((n,), dtype=torch.long, device=dev)
+        eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
+        rw = torch.empty((r_cap,), dtype=torch.float32, device=dev)
+        check(lib.qb_moe_route_fixed_range(ctx.own(1), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, self.e0, epr, r_cap, topk,
+                                           ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), _stream()), "qb_moe_route_fixed_range")
+        d_out = ctx.own_tensor(2)[: r_cap * self.mpe_dn * 2].view(torch.bfloat16).view(r_cap, self.mpe_dn)
+        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out)
+        check(lib.qb_peer_signal(ctx.flag_ptrs(ctx.FLAG_OUTPUT), W, rank, 0, ep, _stream()), "qb_peer_signal")
+        yield None
+        check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_OUTPUT), W, 0, ep, _stream()), "qb_peer_wait")
+        y = torch.empty((Tl, self.H), dtype=torch.bfloat16, device=dev)
+        check(lib.qb_ep_combine(ctx.ptrs(2), ctx.ptrs(3), idx.data_ptr(), y.data_ptr(), Tl, rank * Tl, self.H, topk, self.mpe_dn, epr, W,
+                                _stream()), "qb_ep_combine")
+        yield y
+
+    def forward_ep_peer(self, x, topk_idx, topk_w, ctx):
+        y = None
+        for y in self.forward_ep_peer_steps(x, topk_idx, topk_w, ctx):
+            pass
+        return y
 
     __call__ = forward
 

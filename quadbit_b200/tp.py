@@ -181,3 +181,62 @@ class TPContext:
         for b in self.bufs:
             if isinstance(b, PeerBuffer):
                 b.close()
+
+
+class EPContext:
+    """Peer buffers of one expert-parallel MoE layer instance: `T` tokens in total (T / world per rank, rows of `x_width`
+    bf16 values as the gather reads them), `topk` slots per token, `r_cap` routed rows of capacity and `mpe_dn` output
+    features per routed row on every rank.
+
+    x_pub     this rank's token rows, readable by every rank (the owner of an expert pulls the rows it needs);
+    tables    the routing of ALL tokens, replicated on every rank by peer stores: expert ids [T*topk] i64, weights f32;
+    d         weighted expert outputs of this rank's experts [r_cap][mpe_dn] bf16, read by the tokens' home ranks;
+    inverse   row of every slot in `d` (-1 for slots of other ranks' experts) [T*topk] i32, read by the home ranks;
+    flags     two arrays of `world` ints (tables published, outputs ready), values = the device epoch."""
+
+    FLAG_PUBLISHED, FLAG_OUTPUT = 0, 1
+
+    def __init__(self, T: int, x_width: int, topk: int, mpe_dn: int, r_cap: int, rank: int, world: int, group=None, device=None,
+                 emulate=None):
+        self.lib = load("sparse_fp4")
+        assert T % world == 0
+        self.T, self.Tl, self.topk, self.rank, self.world = T, T // world, topk, rank, world
+        self.x_width, self.mpe_dn, self.r_cap = x_width, mpe_dn, r_cap
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        n = T * topk
+        self.off_w = _align(n * 8)
+        self.sizes = [_align(self.Tl * x_width * 2), self.off_w + _align(n * 4), _align(r_cap * mpe_dn * 2), _align(n * 4), 4096]
+        self.bufs = emulate if emulate is not None else [PeerBuffer(b, rank, world, group, self.device) for b in self.sizes]
+        self.done = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.epoch = torch.ones(1, dtype=torch.int32, device=self.device)
+
+    @staticmethod
+    def emulated(T, x_width, topk, mpe_dn, r_cap, world, device):
+        probe = [_align(T // world * x_width * 2), _align(T * topk * 8) + _align(T * topk * 4), _align(r_cap * mpe_dn * 2),
+                 _align(T * topk * 4), 4096]
+        shared = [_EmulatedPeers(b, world, device) for b in probe]
+        return [EPContext(T, x_width, topk, mpe_dn, r_cap, r, world, device=device, emulate=shared) for r in range(world)]
+
+    def ptrs(self, k: int, off: int = 0):
+        return ptr_array([p + off for p in self.bufs[k].ptrs])
+
+    def own(self, k: int, off: int = 0) -> int:
+        return self.bufs[k].ptrs[self.rank] + off
+
+    def own_tensor(self, k: int) -> torch.Tensor:
+        b = self.bufs[k]
+        return b.tensors[self.rank] if isinstance(b, _EmulatedPeers) else b.tensor
+
+    def flag_ptrs(self, which: int):
+        return self.ptrs(4, which * 64)
+
+    def flag_own(self, which: int) -> int:
+        return self.own(4, which * 64)
+
+    def bump(self, stream: int):
+        check(self.lib.qb_epoch_add(self.epoch.data_ptr(), 1, stream), "qb_epoch_add")
+
+    def close(self):
+        for b in self.bufs:
+            if isinstance(b, PeerBuffer):
+                b.close()

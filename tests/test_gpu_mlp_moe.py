@@ -230,6 +230,77 @@ def test_moe_forward_ep_single_rank_equals_forward():
     assert torch.equal(y, y_ep)
 
 
+def _ep_problem(seed=23):
+    torch.manual_seed(seed)
+    H, I, E, topk, T = 256, 256, 4, 2, 256
+    wgu = [torch.randn(2 * I, H) * 0.05 for _ in range(E)]
+    wdn = [torch.randn(H, I) * 0.05 for _ in range(E)]
+    x = torch.randn(T, H).to(torch.bfloat16)
+    idx, w = fq.route_topk(torch.randn(T, E), topk)
+    return H, I, E, topk, T, wgu, wdn, x, idx, w
+
+
+def test_moe_expert_parallel_by_peer_loads_two_ranks_on_one_gpu():
+    """forward_ep_peer with both ranks in this process (buffers are plain allocations, ranks driven in lock step so that a
+    waiting kernel always follows its producers): routing tables replicated by stores, token rows pulled by the fused
+    gather + quantise, expert outputs pulled by the combine. Must equal the 1-rank layer bit for bit, twice in a row."""
+    import quadbit_b200 as qb
+    from quadbit_b200.tp import EPContext
+    H, I, E, topk, T, wgu, wdn, x, idx, w = _ep_problem()
+    full = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk, fixed_capacity=True)
+    y_ref = full.forward(x.cuda(), idx.cuda(), w.cuda())
+    world, Tl = 2, T // 2
+    moes = [qb.SparseMoE([t.cuda() for t in wgu[r * 2:(r + 1) * 2]], [t.cuda() for t in wdn[r * 2:(r + 1) * 2]], topk,
+                         expert_range=(r * 2, (r + 1) * 2), n_experts_total=E) for r in range(world)]
+    ctxs = EPContext.emulated(T, H, topk, moes[0].mpe_dn, moes[0].ep_capacity(T), world, torch.device("cuda"))
+    for it in range(2):
+        gens = [m.forward_ep_peer_steps(x[r * Tl:(r + 1) * Tl].cuda(), idx[r * Tl:(r + 1) * Tl].cuda(), w[r * Tl:(r + 1) * Tl].cuda(), ctxs[r])
+                for r, m in enumerate(moes)]
+        outs = None
+        for step in zip(*gens):
+            outs = step
+        assert full.lib.qb_status(0) == 0 and full.lib.qb_peer_status(0) == 0
+        y = torch.cat(list(outs), 0)
+        assert torch.equal(y, y_ref), it
+
+
+def _ep_peer_gpu_worker(rank, world, port, ret):
+    import os
+    import torch.distributed as dist
+    import quadbit_b200 as qb
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    H, I, E, topk, T, wgu, wdn, x, idx, w = _ep_problem()
+    epr, Tl = E // world, T // world
+    moe = qb.SparseMoE([t.cuda() for t in wgu[rank * epr:(rank + 1) * epr]], [t.cuda() for t in wdn[rank * epr:(rank + 1) * epr]], topk,
+                       expert_range=(rank * epr, (rank + 1) * epr), n_experts_total=E)
+    ctx = moe.make_ep_context(T, rank, world)
+    dist.barrier()
+    xs, ids, ws = x[rank * Tl:(rank + 1) * Tl].cuda(), idx[rank * Tl:(rank + 1) * Tl].cuda(), w[rank * Tl:(rank + 1) * Tl].cuda()
+    for _ in range(3):
+        y = moe.forward_ep_peer(xs, ids, ws, ctx)
+    torch.cuda.synchronize()
+    assert moe.lib.qb_status(0) == 0 and moe.lib.qb_peer_status(0) == 0
+    ret[rank] = y.cpu()
+    dist.barrier()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_moe_expert_parallel_by_peer_loads_two_gpus():
+    import torch.multiprocessing as mp
+    import quadbit_b200 as qb
+    H, I, E, topk, T, wgu, wdn, x, idx, w = _ep_problem()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_ep_peer_gpu_worker, args=(2, 29541, ret), nprocs=2, join=True)
+    full = qb.SparseMoE([t.cuda() for t in wgu], [t.cuda() for t in wdn], topk, fixed_capacity=True)
+    y_ref = full.forward(x.cuda(), idx.cuda(), w.cuda()).cpu()
+    assert torch.equal(torch.cat([ret[0], ret[1]], 0), y_ref)
+
+
 def _ep_gpu_worker(rank, world, port, ret):
     import os
     import torch.distributed as dist
