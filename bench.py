@@ -550,7 +550,7 @@ def run_gpu(args):
             Hb = torch.empty((rows, ih // 2), dtype=torch.uint8, device=dev)
             sfh = torch.zeros(lib.qb_sf_atoms_bytes(rows, ih, 32), dtype=torch.uint8, device=dev)
             gH = torch.empty(rows, device=dev)
-            fn = lambda: qb._lib.check(lib.qb_swiglu_quant_act(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), 0, rows, ih, 0, 0,
+            fn = lambda: qb._lib.check(lib.qb_swiglu_quant_act(cgu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), 0, 0, rows, ih, 0, 0,
                                                                 torch.cuda.current_stream().cuda_stream), "qb_swiglu_quant_act")
             algo = rows * (2 * ih * 2 + ih * (0.5 + 1 / 32) + 4)
             what = f"swiglu_quant_kernel<1,false,true,0> on [{rows},{2 * ih}] bf16"

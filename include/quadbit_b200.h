@@ -250,8 +250,8 @@ int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
  * harness/fused_moe.py:450-452), 1 = silu(g)*u; gH == NULL selects the single-level quantiser of the reference's
  * fused GEMM1 epilogue (cuda/sparse_fp4_lib.cu:1828-1866). row_src (int64 [tok], may be NULL): rows with row_src < 0
  * are padding of a routed batch, their input is not read and they quantise as all-zero rows. */
-int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, int tok, int I,
-                        int interleaved, int act, void* stream);
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, const void* n_rows_dev,
+                        int tok, int I, int interleaved, int act, void* stream);
 /* fused_mlp_2lvl on native layouts (weights from qb_compress_2to4; sfb_x / sfb_h are scale-atom
  * scratch of qb_sf_atoms_bytes(tok, H | I, 32) bytes; Cf may be NULL or an fp32 [tok][dn_out]
  * workspace for a split-K down projection; flags bit 0: gu_A / dn_A are in the tiled layout of
@@ -329,16 +329,17 @@ int qb_peer_status(void* stream);
  *   last CTA writes *value_ptr into word `rank` of every flags[r] (done_counter: one int, zero between calls).
  * qb_moe_route_fixed_range: qb_moe_route_fixed_ex for a rank that owns experts [e_base, e_base + e) of a global id space.
  * qb_gather_quantize_act_peer: qb_gather_quantize_act whose source rows are numbered over n_peers buffers of rows_per_peer
- *   rows each (pointers into the ranks' x_pub): the dispatch is done by the loads of the quantiser.
+ *   rows each (pointers into the ranks' x_pub): the dispatch is done by the loads of the quantiser. n_used (route) / n_rows_dev
+ *   (quantisers; may be NULL): one device int = padded rows in use; rows beyond it are unused capacity and are not touched.
  * qb_ep_combine: y[t][f] = sum_k d_owner[inverse_owner[(t0 + t) * topk + k]][f] for this rank's t_local tokens, the rows read
  *   from the rank that owns the slot's expert (owner = idx / experts_per_rank; dbuf[r], inverse[r]: peer pointers). */
 int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx, const void* w, int n_slots, int slot0,
                   void* const* assign_all, void* const* w_all, int world, int rank, void* const* flags, const void* value_ptr,
                   void* done_counter, void* stream);
 int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
-                             const void* w_in, void* rw, void* inverse, void* stream);
+                             const void* w_in, void* rw, void* inverse, void* n_used, void* stream);
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
-                                void* g, int rows, int K, int H, int block, void* stream);
+                                void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream);
 int qb_ep_combine(void* const* dbuf, void* const* inverse, const void* idx, void* y, int t_local, int t0, int H, int topk, int Mpe,
                   int experts_per_rank, int world, void* stream);
 /* Row-parallel GEMM fused with the reduce-scatter of its partial result (replaces "GEMM, then all_reduce"): operands as

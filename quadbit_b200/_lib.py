@@ -41,7 +41,7 @@ _SIGS = {
     "qb_moe_route_fixed": ([P] * 4 + [I] * 3 + [P], I),
     "qb_moe_route_fixed_ex": ([P] * 4 + [I] * 4 + [P] * 4, I),
     "qb_gather_quantize_act": ([P] * 6 + [I] * 4 + [P], I),
-    "qb_swiglu_quant_act": ([P] * 6 + [I] * 4 + [P], I),
+    "qb_swiglu_quant_act": ([P] * 7 + [I] * 4 + [P], I),
     "qb_compress_2to4": ([P, I] + [P] * 6 + [I] * 2 + [P], I),
     "qb_compress_2to4_colnorm": ([P, I] + [P] * 7 + [I] * 2 + [P], I),
     "qb_dequant_fp4_blocks": ([P] * 4 + [I] * 3 + [c_longlong, P], I),
@@ -73,8 +73,8 @@ _SIGS = {
     "qb_peer_close": ([P], I),
     "qb_peer_signal": ([P, I, I, I, P, P], I),
     "qb_ep_publish": ([P, P, c_longlong, P, P, I, I, P, P, I, I, P, P, P, P], I),
-    "qb_moe_route_fixed_range": ([P] * 4 + [I] * 5 + [P] * 4, I),
-    "qb_gather_quantize_act_peer": ([P, I, c_longlong] + [P] * 4 + [I] * 4 + [P], I),
+    "qb_moe_route_fixed_range": ([P] * 4 + [I] * 5 + [P] * 5, I),
+    "qb_gather_quantize_act_peer": ([P, I, c_longlong] + [P] * 4 + [I] * 4 + [P, P], I),
     "qb_ep_combine": ([P] * 4 + [I] * 7 + [P], I),
     "qb_peer_wait": ([P, I, I, P, P], I),
     "qb_epoch_add": ([P, I, P], I),

@@ -298,9 +298,9 @@ int qb_status(void* stream) { return qb::read_status((cudaStream_t)stream); }
 int qb_swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, void* stream) {
     return qb::swiglu_quant(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, (cudaStream_t)stream);
 }
-int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, int tok, int I,
-                        int interleaved, int act, void* stream) {
-    return qb::swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, interleaved, act, (cudaStream_t)stream, row_src);
+int qb_swiglu_quant_act(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, const void* row_src, const void* n_rows_dev,
+                        int tok, int I, int interleaved, int act, void* stream) {
+    return qb::swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, interleaved, act, (cudaStream_t)stream, row_src, n_rows_dev);
 }
 int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void* gu_meta, const void* gu_gA, const void* dn_A,
                  const void* dn_sfa, const void* dn_meta, const void* dn_gA, void* Bb, void* sfb_x, void* gBx, void* Cgu, void* Hb,
@@ -545,15 +545,15 @@ int qb_moe_route_fixed_ex(const void* assign, void* src, void* pos, void* eblk, 
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse);
 }
 int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
-                             const void* w_in, void* rw, void* inverse, void* stream) {
+                             const void* w_in, void* rw, void* inverse, void* n_used, void* stream) {
     if (e_base < 0) return QB_ERR_ARG;
-    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base);
+    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base, n_used);
 }
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
-                                void* g, int rows, int K, int H, int block, void* stream) {
+                                void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream) {
     if (!x_peers) return QB_ERR_ARG;
     return qb::gather_quantize_act(nullptr, src, Bbytes, nullptr, sf_atoms, g, rows, K, H, block, (cudaStream_t)stream,
-                                   (const void* const*)x_peers, n_peers, rows_per_peer);
+                                   (const void* const*)x_peers, n_peers, rows_per_peer, n_rows_dev);
 }
 int moe_route(const void* assign, const void* poff, void* counter, void* src, int N, int E, void* stream) {
     int rc = qb::moe_route(assign, const_cast<void*>(poff), counter, src, N, E, (cudaStream_t)stream);

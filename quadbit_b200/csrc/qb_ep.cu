@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(256) ep_publish_kernel(const uint4* __restrict
             __threadfence_system();
             const int val = *value_ptr;
             for (int r = 0; r < world; r++)
-                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(reinterpret_cast<int*>(flags.p[r]) + rank), "r"(val) : "memory");
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(reinterpret_cast<int*>(flags.p[r]) + rank), "r"(val) : "memory");
         }
     }
 }

@@ -1150,8 +1150,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             atomicExch(p.peer_done, 0);
             __threadfence_system();
             const int val = p.peer_val_ptr ? *p.peer_val_ptr : p.peer_val;
+            // one system-scope fence orders every partial row before the flag words, which then go out as relaxed stores
+            // (a release store per rank would fence again each time: ~2 us apiece)
             for (int r = 0; r < p.peer_n; r++)
-                asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flags[r] + p.peer_rank), "r"(val) : "memory");
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p.peer_flags[r] + p.peer_rank), "r"(val) : "memory");
         }
     }
 }

@@ -12,13 +12,14 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
 // cgu: token-major gate/up GEMM output [tok][2*I] bf16 -> Hb[tok][I/2], per-32 scales, gH[tok]
 // peer_x != null: src holds row numbers over n_peers sources of rows_per_peer rows each (peer-mapped pointers)
 int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
-                        int block, cudaStream_t st, const void* const* peer_x = nullptr, int n_peers = 0, long long rows_per_peer = 0);
+                        int block, cudaStream_t st, const void* const* peer_x = nullptr, int n_peers = 0, long long rows_per_peer = 0,
+                        const void* n_rows_dev = nullptr);
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                    cudaStream_t st, const void* row_src = nullptr);
+                    cudaStream_t st, const void* row_src = nullptr, const void* n_rows_dev = nullptr);
 int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st);
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div = 1,
-                    const void* w_in = nullptr, void* rw = nullptr, void* inverse = nullptr, int e_base = 0);
+                    const void* w_in = nullptr, void* rw = nullptr, void* inverse = nullptr, int e_base = 0, void* n_used = nullptr);
 int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const void* sc_w, const void* bias, void* Out, int rows,
                     int Mpe, int Hout, cudaStream_t st);
 // RMSNorm (+ residual add) fused with the quantiser; res / hout / g may be null (g null = single level)

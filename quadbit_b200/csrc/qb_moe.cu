@@ -93,7 +93,8 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
 __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap,
                                                                 long long* __restrict__ src, long long* __restrict__ pos,
                                                                 int* __restrict__ eblk, int div, const float* __restrict__ w_in,
-                                                                float* __restrict__ rw, int* __restrict__ inverse, int e_base) {
+                                                                float* __restrict__ rw, int* __restrict__ inverse, int e_base,
+                                                                int* __restrict__ n_used) {
     // optional extras that the layer would otherwise do with a dozen small kernels: src holds slot / div (the token row
     // of a slot when div = top-k), rw[row] = w_in[slot] (0 for padding rows), inverse[slot] = row as int32
     extern __shared__ int sm[];
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
         int off = 0;
         for (int x = 0; x < e; x++) { poff[x] = off; off += (counts[x] + 127) / 128 * 128; }
         total = off;
+        if (n_used) *n_used = off;          // rows in use: kernels over the padded rows stop here instead of at r_cap
     }
     __syncthreads();
     for (int i = threadIdx.x; i < r_cap; i += blockDim.x) {
@@ -138,11 +140,11 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
 }
 
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div,
-                    const void* w_in, void* rw, void* inverse, int e_base) {
+                    const void* w_in, void* rw, void* inverse, int e_base, void* n_used) {
     if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % 128 || (long long)r_cap < (long long)n + (long long)e * 127) return QB_ERR_ARG;
     if (!assign || !src || !pos || !eblk || div < 1 || ((rw != nullptr) != (w_in != nullptr))) return QB_ERR_ARG;
     moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
-                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base);
+                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base, (int*)n_used);
     return (int)cudaGetLastError();
 }
 

@@ -22,7 +22,7 @@ __global__ void peer_signal_kernel(int* f0, int* f1, int* f2, int* f3, int* f4, 
         int* f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
         if (value_ptr) value = *value_ptr;
         __threadfence_system();
-        for (int r = 0; r < n; r++) asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f[r] + rank), "r"(value) : "memory");
+        for (int r = 0; r < n; r++) asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(f[r] + rank), "r"(value) : "memory");
     }
 }
 

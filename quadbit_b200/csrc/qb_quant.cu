@@ -26,20 +26,17 @@ struct GatherPeers {
     const uint4* p[8];
     long long rows_per;
     int n;
+    const int* n_rows;      // non-null: rows at and beyond *n_rows are unused capacity of a routed batch and are left alone
 };
 
 template <int BLOCK, int NJ, bool TWO_LEVEL>
-__global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
-                                                          uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                          float* __restrict__ g_out, int tok, int K,
-                                                          const long long* __restrict__ src, int h8, const GatherPeers peers) {
+__device__ __forceinline__ void quant_act_row(const int row, const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
+                                              uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok,
+                                              int K, const long long* __restrict__ src, int h8, const GatherPeers& peers) {
     // src != nullptr: row `row` of the output quantises source row src[row] of x [.][h8 * 8] zero-padded to K
     // (src < 0: an all-zero row) — the gather of routed MoE rows fused into their quantiser
     constexpr int CPB = BLOCK / 8;   // 16-byte input chunks (8 values) per scale block
     constexpr int P = 128 / BLOCK;   // scales per 128 K in the reference layout
-    griddep_launch_dependents();     // a thin-token GEMM that follows may set itself up while this grid runs
-    griddep_wait();                  // launched as a programmatic dependent itself: x may come from the kernel in front
-    const int row = blockIdx.x;
     const int nblocks = K / BLOCK;   // a multiple of 4 (K % 128 == 0)
     const int lane = threadIdx.x & 31;
     const long long srow = src ? src[row] : (long long)row;
@@ -138,6 +135,22 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
     }
 }
 
+// One CTA per row; with a rows-in-use limit (routed batches with fixed capacity) a bounded grid walks the rows instead, so that
+// unused capacity costs no CTA launches (34816 rows of capacity for ~4100 in use cost 47 us of empty CTAs otherwise).
+template <int BLOCK, int NJ, bool TWO_LEVEL>
+__global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict__ x, uint32_t* __restrict__ Bwords,
+                                                          uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
+                                                          float* __restrict__ g_out, int tok, int K,
+                                                          const long long* __restrict__ src, int h8, const GatherPeers peers) {
+    griddep_launch_dependents();     // a thin-token GEMM that follows may set itself up while this grid runs
+    griddep_wait();                  // launched as a programmatic dependent itself: x may come from the kernel in front
+    const int nrows = peers.n_rows ? min(tok, *peers.n_rows) : tok;
+    for (int row = blockIdx.x; row < nrows; row += gridDim.x) {
+        quant_act_row<BLOCK, NJ, TWO_LEVEL>(row, x, Bwords, sf_ref, sf_atoms, g_out, tok, K, src, h8, peers);
+        __syncthreads();             // the row's reduction scratch is reused by the next row
+    }
+}
+
 // SwiGLU + two-level per-32 quantiser for the fused MLP: reads the token-major gate/up GEMM
 // output Cgu[tok][2*I] (gate features 0..I-1, up features I..2I-1, bf16), forms
 // h = silu(g) * u in fp32 and quantises h exactly like an activation row (per-token global
@@ -151,10 +164,9 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 // GEMM1 epilogue applies (matmul_sp_moe_gu_swiglu, cuda/sparse_fp4_lib.cu:1828-1866); act 0 is the clamped
 // gpt-oss SwiGLU (alpha 1.702, limit 7, up + 1), act 1 the plain silu(g) * u.
 template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
-__global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
-                                                            uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
-                                                            float* __restrict__ g_out, int tok, int I, const long long* __restrict__ row_src) {
-    const int row = blockIdx.x;
+__device__ __forceinline__ void swiglu_quant_row(const int row, const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
+                                                 uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok,
+                                                 int I, const long long* __restrict__ row_src) {
     const int nchunks = I >> 3;
     const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
     const int lane = threadIdx.x & 31;
@@ -259,13 +271,27 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
     }
 }
 
+// one CTA per row, or a bounded grid walking the rows in use when a routed batch has unused capacity (n_rows)
+template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
+__global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
+                                                            uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms,
+                                                            float* __restrict__ g_out, int tok, int I, const long long* __restrict__ row_src,
+                                                            const int* __restrict__ n_rows) {
+    const int nrows = n_rows ? min(tok, *n_rows) : tok;
+    for (int row = blockIdx.x; row < nrows; row += gridDim.x) {
+        swiglu_quant_row<NJ, INTERLEAVED, TWO_LEVEL, ACT>(row, cgu, Hwords, sf_ref, sf_atoms, g_out, tok, I, row_src);
+        __syncthreads();
+    }
+}
+
+
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st) {
     return swiglu_quant_ex(cgu, Hb, sf_ref, sf_atoms, gH, tok, I, 0, 1, st, nullptr);
 }
 
 // interleaved: row layout [g0,u0,g1,u1,...]; gH == nullptr selects the single-level quantiser
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
-                    cudaStream_t st, const void* row_src) {
+                    cudaStream_t st, const void* row_src, const void* n_rows_dev) {
     if (tok < 0 || I <= 0 || I % 128 != 0 || (act != 0 && act != 1)) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!cgu || !Hb || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
@@ -274,7 +300,7 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
     int threads = (nblocks + 31) / 32 * 32;
     if (threads > 512) threads = 512;
     const int nj = (nblocks + threads - 1) / threads;
-#define QB_LS4(NJ, IL, TL, ACT) swiglu_quant_kernel<NJ, IL, TL, ACT><<<tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I, (const long long*)row_src)
+#define QB_LS4(NJ, IL, TL, ACT) swiglu_quant_kernel<NJ, IL, TL, ACT><<<(n_rows_dev && tok > 148 * 16) ? 148 * 16 : tok, threads, 0, st>>>((const uint4*)cgu, (uint32_t*)Hb, (uint8_t*)sf_ref, (uint8_t*)sf_atoms, (float*)gH, tok, I, (const long long*)row_src, (const int*)n_rows_dev)
 #define QB_LS3(NJ, IL, TL) do { if (act == 0) QB_LS4(NJ, IL, TL, 0); else QB_LS4(NJ, IL, TL, 1); } while (0)
 #define QB_LS(NJ) do { if (interleaved) { if (gH) QB_LS3(NJ, true, true); else QB_LS3(NJ, true, false); } \
                        else { if (gH) QB_LS3(NJ, false, true); else QB_LS3(NJ, false, false); } } while (0)
@@ -326,8 +352,9 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// flag store after a __threadfence_system() (the fence orders the data before the flag; the store itself is relaxed)
+__device__ __forceinline__ void st_flag_sys(int* p, int v) {
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 template <int BLOCK, int NJ, bool ADD, bool TWO_LEVEL>
@@ -497,7 +524,7 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
                 atomicExch(tp.done, 0);
                 __threadfence_system();
                 const int val = tp.val_ptr ? *tp.val_ptr : tp.sig_val;
-                for (int d = 0; d < tp.sig_n; d++) st_release_sys(tp.sig_flags[d] + tp.sig_rank, val);
+                for (int d = 0; d < tp.sig_n; d++) st_flag_sys(tp.sig_flags[d] + tp.sig_rank, val);
             }
         }
     }
@@ -702,7 +729,7 @@ static int launch_quant(const void* x, void* Bbytes, void* sf_ref, void* sf_atom
     // kernel's results with griddepcontrol.wait before its first load), which hides the launch latency between the
     // kernels of a decode step
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)tok);
+    cfg.gridDim = dim3((unsigned)(peers.n_rows && tok > 148 * 16 ? 148 * 16 : tok));
     cfg.blockDim = dim3((unsigned)threads);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -729,13 +756,14 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
 // src == nullptr: plain quantiser of x [tok][K]. Otherwise output row r = quantised x[src[r]] (x rows of H <= K values,
 // zero-padded to K; src[r] < 0 gives a zero row): gather + pad + quantise of routed MoE rows in one pass.
 int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
-                        int block, cudaStream_t st, const void* const* peer_x, int n_peers, long long rows_per_peer) {
+                        int block, cudaStream_t st, const void* const* peer_x, int n_peers, long long rows_per_peer, const void* n_rows_dev) {
     if (tok < 0 || K <= 0 || K % 128 != 0 || (block != 16 && block != 32) || H <= 0 || H > K || H % 8) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if ((!x && !peer_x) || !Bbytes || (!sf_ref && !sf_atoms)) return QB_ERR_ARG;
     if (((uintptr_t)x & 15) || ((uintptr_t)Bbytes & 3) || ((uintptr_t)sf_ref & 3) || ((uintptr_t)sf_atoms & 3) || ((uintptr_t)src & 7)) return QB_ERR_ARG;
     if (K > 65536) return QB_ERR_UNSUPPORTED;
     GatherPeers peers{};
+    peers.n_rows = (const int*)n_rows_dev;
     if (peer_x) {
         if (n_peers < 1 || n_peers > 8 || rows_per_peer <= 0 || !src) return QB_ERR_ARG;
         for (int r = 0; r < n_peers; r++) {

@@ -226,12 +226,14 @@ class SparseMoE:
         # from the device; `forward` then issues no host read and can be captured in a CUDA graph
         self.fixed_capacity = fixed_capacity
 
-    def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None) -> torch.Tensor:
+    def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None,
+                    n_used=None) -> torch.Tensor:
         """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
         padding), eblk = expert of every 128-row block, rw [r_pad] = routing weight of every row. Returns
         d [r_pad, mpe_dn] bf16 = expert(row) * weight."""
         lib = self.lib
         dev = src.device
+        nu = n_used.data_ptr() if n_used is not None else 0       # device int: rows in use (fixed-capacity routing), else all
         Bb = torch.empty((r_pad, self.Hp // 2), dtype=torch.uint8, device=dev)
         sfb = sf_atoms_empty(lib, r_pad, self.Hp, 32, dev)
         gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
@@ -240,13 +242,14 @@ class SparseMoE:
             # per rank, row width in elements, number of ranks))
             xp, rows_per_rank, width, nr = peer_x
             check(lib.qb_gather_quantize_act_peer(xp, nr, rows_per_rank, src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), r_pad,
-                                                  self.Hp, width, 32, _stream()), "qb_gather_quantize_act_peer")
+                                                  self.Hp, width, 32, nu, _stream()), "qb_gather_quantize_act_peer")
         else:
             x = x.to(torch.bfloat16).contiguous()
             if self.H % 8:                       # the fused gather reads 16-byte chunks
                 x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
-            check(lib.qb_gather_quantize_act(x.data_ptr(), src.data_ptr(), Bb.data_ptr(), 0, sfb.data_ptr(), gB.data_ptr(), r_pad, self.Hp,
-                                             x.shape[1], 32, _stream()), "qb_gather_quantize_act")
+            from .tp import ptr_array
+            check(lib.qb_gather_quantize_act_peer(ptr_array([x.data_ptr()]), 1, max(x.shape[0], 1), src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(),
+                                                  gB.data_ptr(), r_pad, self.Hp, x.shape[1], 32, nu, _stream()), "qb_gather_quantize_act_peer")
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
         if self.fused_gu:
@@ -258,7 +261,7 @@ class SparseMoE:
             return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)
         gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
-        check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), r_pad, self.Ip, 0,
+        check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), nu, r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
         return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)  # [r_pad, mpe_dn]
 
@@ -307,10 +310,11 @@ class SparseMoE:
             rw = torch.empty((r_cap,), dtype=torch.float32, device=dev)
             inverse = torch.empty((n,), dtype=torch.int32, device=dev)
             w_in = topk_w.reshape(-1).float().contiguous()
-            check(self.lib.qb_moe_route_fixed_ex(assign_g.contiguous().data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, e,
-                                                 r_cap, self.topk, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(), _stream()),
-                  "qb_moe_route_fixed_ex")
-            d = self._run_padded(x, src, eblk, r_cap, rw)
+            n_used = torch.empty((1,), dtype=torch.int32, device=dev)
+            check(self.lib.qb_moe_route_fixed_range(assign_g.contiguous().data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, 0, e,
+                                                    r_cap, self.topk, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(), n_used.data_ptr(),
+                                                    _stream()), "qb_moe_route_fixed_range")
+            d = self._run_padded(x, src, eblk, r_cap, rw, n_used=n_used)
             return combine(self.lib, d, inverse, T, self.H, self.topk)
         if self.e0 == 0 and self.e1 == self.E_total:
             slots = torch.arange(assign_g.numel(), device=dev)
@@ -377,10 +381,12 @@ class SparseMoE:
         pos = torch.empty((n,), dtype=torch.long, device=dev)
         eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
         rw = torch.empty((r_cap,), dtype=torch.float32, device=dev)
+        n_used = torch.empty((1,), dtype=torch.int32, device=dev)
         check(lib.qb_moe_route_fixed_range(ctx.own(1), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, self.e0, epr, r_cap, topk,
-                                           ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), _stream()), "qb_moe_route_fixed_range")
+                                           ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), n_used.data_ptr(), _stream()),
+              "qb_moe_route_fixed_range")
         d_out = ctx.own_tensor(2)[: r_cap * self.mpe_dn * 2].view(torch.bfloat16).view(r_cap, self.mpe_dn)
-        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out)
+        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out, n_used=n_used)
         check(lib.qb_peer_signal(ctx.flag_ptrs(ctx.FLAG_OUTPUT), W, rank, 0, ep, _stream()), "qb_peer_signal")
         yield None
         check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_OUTPUT), W, 0, ep, _stream()), "qb_peer_wait")
