@@ -262,10 +262,14 @@ int qb_fused_mlp(const void* x, const void* gu_A, const void* gu_sfa, const void
                  void* stream);
 /* Issue-only throughput probe of the block-scaled FP4 MMA (analogue of the reference's
  * cuda/mma_peak.cu): every SM runs `kblocks` K blocks of 256 (dense: 4 MMAs of 128xbnx64,
- * sparse: 2 of 128xbnx128) on operands resident in shared memory. mode bit 0 issues the MMAs,
- * bit 1 the per-block scale-factor / metadata tcgen05.cp copies. cycles_per_sm: optional
- * u64[SM count] of SM clock cycles; status_word: i32, non-zero if a bounded wait expired.
- * bn = 128 or 256. Time it with events around the call. */
+ * sparse: 2 of 128xbnx128) on operands resident in shared memory. mode bits: 0 issue the MMAs (the pair form
+ * always does); 1 the per-block scale-factor / metadata tcgen05.cp copies (one-CTA form); 2 one commit per K block;
+ * 3 a tcgen05 fence per block (one-CTA form) or a wait for every block's completion (pair form); 4 the CTA-pair form
+ * (cta_group::2, M = 256); 5 the sparse A tile in 128-byte rows with the 128-byte swizzle instead of 64-byte rows;
+ * 6 a second warp streams 24 KB per K block from global memory into spare shared memory meanwhile.
+ * cycles_per_sm: optional u64[SM count] of SM clock cycles of the MMA loop (u64[2 x SM count] with bit 6: the second
+ * half receives the cycles of the streaming loop); status_word: i32, non-zero if a bounded wait expired.
+ * bn = 64, 128 or 256. Time it with events around the call. */
 int qb_mma_peak(int sparse, int bn, int kblocks, int mode, void* cycles_per_sm, void* status_word, void* stream);
 /* Gate/up GEMM with SwiGLU + single-level per-32 quantiser in its epilogue, native layouts (what sparse_moe_gu_swiglu,
  * cuda/sparse_fp4_lib.cu:1679-1875, does on the reference's layouts): operands as qb_gemm, A's rows are (gate, up) pairs
