@@ -192,7 +192,8 @@ long long qb_meta_native_bytes(int out, int K);
  * eblk != NULL); out_mode 0: bf16 C[out][tok], 1: bf16 C[tok][out], 2: fp32 raw accumulators
  * C[out][tok] (globals ignored), 3: bf16 C[tok][out] = (acc*gA*gB + bias[expert][f]) * row_w[t].
  * splits > 1 splits K across CTAs through the fp32 workspace Cf[tok][out]. bn = token tile
- * (16..256, 0 = auto). In grouped mode eblk[b] is the expert of token block b (128 rows); a negative entry marks
+ * (16..256, 0 = auto). In grouped mode the tile is 128 tokens, or 256 with bn = 256 when every expert's rows are padded to
+ * 256 (tok % 256 == 0; the two eblk entries of a tile are equal). In grouped mode eblk[b] is the expert of token block b (128 rows); a negative entry marks
  * an unused block of a fixed-capacity routing: it is skipped and its output rows are left unwritten.
  * Asynchronous on `stream`; qb_status() reports device-side errors. */
 int qb_gemm(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
@@ -331,7 +332,9 @@ int qb_peer_status(void* stream);
  * qb_ep_publish: copy this rank's token rows x (x_bytes, 16-byte multiple) into its peer-visible buffer x_pub and store its
  *   routing (idx i64, w f32, n_slots entries) into the replicated tables assign_all[r] / w_all[r] of every rank at slot0; the
  *   last CTA writes *value_ptr into word `rank` of every flags[r] (done_counter: one int, zero between calls).
- * qb_moe_route_fixed_range: qb_moe_route_fixed_ex for a rank that owns experts [e_base, e_base + e) of a global id space.
+ * qb_moe_route_fixed_range: qb_moe_route_fixed_ex for a rank that owns experts [e_base, e_base + e) of a global id space;
+ *   align = 128 or 256: rows every expert's segment is padded to (r_cap % align == 0, r_cap >= n + e * (align - 1)). With 256 the
+ *   grouped GEMM can be asked for 256-token tiles (qb_gemm with eblk and bn = 256: eblk keeps one entry per 128 rows).
  * qb_gather_quantize_act_peer: qb_gather_quantize_act whose source rows are numbered over n_peers buffers of rows_per_peer
  *   rows each (pointers into the ranks' x_pub): the dispatch is done by the loads of the quantiser. n_used (route) / n_rows_dev
  *   (quantisers; may be NULL): one device int = padded rows in use; rows beyond it are unused capacity and are not touched.
@@ -341,7 +344,7 @@ int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx
                   void* const* assign_all, void* const* w_all, int world, int rank, void* const* flags, const void* value_ptr,
                   void* done_counter, void* stream);
 int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
-                             const void* w_in, void* rw, void* inverse, void* n_used, void* stream);
+                             int align, const void* w_in, void* rw, void* inverse, void* n_used, void* stream);
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
                                 void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream);
 int qb_ep_combine(void* const* dbuf, void* const* inverse, const void* idx, void* y, int t_local, int t0, int H, int topk, int Mpe,

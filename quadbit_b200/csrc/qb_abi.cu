@@ -545,9 +545,9 @@ int qb_moe_route_fixed_ex(const void* assign, void* src, void* pos, void* eblk, 
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse);
 }
 int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
-                             const void* w_in, void* rw, void* inverse, void* n_used, void* stream) {
+                             int align, const void* w_in, void* rw, void* inverse, void* n_used, void* stream) {
     if (e_base < 0) return QB_ERR_ARG;
-    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base, n_used);
+    return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base, n_used, align);
 }
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
                                 void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream) {

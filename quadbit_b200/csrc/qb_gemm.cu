@@ -575,7 +575,8 @@ struct KParams2 {
     int num_m2, num_n, kblocks;
     int out_mode;
     int a_tiled;
-    const int* eblk;                     // grouped mode (BN == 128): expert of every 128-token block, null = plain GEMM
+    const int* eblk;                     // grouped mode: expert of every 128-token block (a 256-token tile reads the entry of its first
+                                         // block: the routing then pads every expert to 256 rows), null = plain GEMM
     const __nv_bfloat16* bias;           // out_mode 3: per-expert bias [E][out_f] (may be null)
     const float* row_w;                  // out_mode 3: weight of every routed row [tok] (may be null)
     int bias_ld;                         // features per bias row (the rest of out_f is padding without bias)
@@ -603,7 +604,7 @@ enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
 // service warpgroups hand most of theirs to the two epilogue warpgroups, which then hold a whole fp32
 // accumulator slice (128 words per thread).  640 * 96 = 128 * (40 + 64 + 40) + 256 * 168.
 enum { W_PROD_A = 0, W_PROD_B = 1, W_SIDE_W = 2, W_SIDE_B = 3, W_MMA = 16 };
-constexpr int REGS_PROD = 40, REGS_SF = 64, REGS_MMA = 40, REGS_EPI = 160;
+constexpr int REGS_PROD = 40, REGS_SF = 64, REGS_MMA = 40, REGS_EPI = 168;
 
 template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(640, 1)
@@ -680,7 +681,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     };
     // grouped mode: a 128-token block with expert id < 0 is unused capacity of a fixed-capacity routing; every
     // role of both CTAs skips its tiles (same test everywhere, so the ring and accumulator counters stay in step)
-    auto tile_skipped = [&](int tile) { return p.eblk != nullptr && p.eblk[tile / p.num_m2] < 0; };
+    auto tile_expert = [&](int n) { return p.eblk[n * (BN / 128)]; };
+    auto tile_skipped = [&](int tile) { return p.eblk != nullptr && tile_expert(tile / p.num_m2) < 0; };
     const int atoms_per_rb = p.kblocks * C::MMAS;
 
     // Every role below handles two K blocks per barrier poll whenever the later one is ready as well: a
@@ -701,7 +703,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile_n(tile);
-            const int a_row0 = (p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128;
+            const int a_row0 = (p.eblk ? tile_expert(n) * p.out_f : 0) + m2 * 256 + (int)rank * 128;
             const int b_row0 = n * BN + (int)rank * C::B_ROWS;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
@@ -717,14 +719,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     for (int u = 0; u < nb; u++) {
                         const int s = u ? s1 : stage;
                         const uint32_t fb = mapa_shared(full_bar(s), 0);
-                        constexpr bool skip = false;
-                        if (rank == 0) mbar_expect_tx(full_bar(s), skip ? 0u : 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
-                        if (!skip) {
-                            if (isA) {
-                                if (p.a_tiled) tma_load_2d_pair(stageA(s), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb + u) * 128);
-                                else tma_load_2d_pair(stageA(s), &tmA, fb, (kb + u) * C::A_ROW, a_row0);
-                            }
-                            else tma_load_2d_pair(stageB(s), &tmB, fb, (kb + u) * 128, b_row0);
+                        if (rank == 0) mbar_expect_tx(full_bar(s), 2u * (uint32_t)(isA ? C::A_BYTES : C::B_BYTES));
+                        if (isA) {
+                            if (p.a_tiled) tma_load_2d_pair(stageA(s), &tmA, fb, 0, ((a_row0 >> 7) * p.kblocks + kb + u) * 128);
+                            else tma_load_2d_pair(stageA(s), &tmA, fb, (kb + u) * C::A_ROW, a_row0);
+                        } else {
+                            tma_load_2d_pair(stageB(s), &tmB, fb, (kb + u) * 128, b_row0);
                         }
                     }
                 }
@@ -743,7 +743,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
             if (tile_skipped(tile)) continue;
             const int m2 = tile % p.num_m2, n = tile_n(tile);
-            const int rb_a = ((p.eblk ? p.eblk[n] * p.out_f : 0) + m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
+            const int rb_a = ((p.eblk ? tile_expert(n) * p.out_f : 0) + m2 * 256 + (int)rank * 128) >> 7, rb_b = (n * BN) >> 7;
             bool ok = true;
             for (int kb = 0; kb < p.kblocks;) {
                 int j1 = slot + 1;
@@ -952,7 +952,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int n0 = n * BN + half * HCOLS;          // first token column of this warp
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
-            const int a_base = p.eblk ? p.eblk[n] * p.out_f : 0;      // first row of this tile's expert in A / gA / bias
+            const int a_base = p.eblk ? tile_expert(n) * p.out_f : 0;      // first row of this tile's expert in A / gA / bias
             // per-tile constants first, so their latency hides behind the accumulator wait
             const float ga = p.gA ? __ldg(p.gA + a_base + o) : 1.f;
             float gbv[NCH], rwv[NCH];
@@ -968,7 +968,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             for (int e = 0; e < 8; e++) bias8[e] = 0.f;
             const int f8 = o0 + q * 32 + (lane & 3) * 8;       // bias rows hold bias_ld (a multiple of 8) valid features
             if ((p.out_mode == 3 || p.out_mode == 4) && p.bias && f8 + 8 <= p.bias_ld) {
-                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + (size_t)(p.eblk ? p.eblk[n] : 0) * p.bias_ld + f8));
+                const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + (size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + f8));
                 const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(bh[e]); bias8[2 * e] = f.x; bias8[2 * e + 1] = f.y; }
@@ -1102,6 +1102,81 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
             };
             if constexpr (C::ACC_STAGES == 1) {
+              if (p.out_mode == 1 || p.out_mode == 3) {
+                // Token-major bf16 output of the one-accumulator tile. The slice is read in the 16x256b shape: a thread then
+                // holds, for every group of 8 tokens, two adjacent tokens of four features (lanes t/4 + 8m), which is the
+                // fragment layout stmatrix stores transposed. Scale, round to bf16, store the four 8x8 matrices of a group
+                // transposed into a 512-byte shared-memory tile (token rows of 32 features, 16-byte chunks XOR-swizzled so
+                // that neither the stores nor the reads conflict), read 16 bytes per lane and store them token-major. Half
+                // the shared-memory traffic and a third fewer instructions than staging fp32, and no conversion after the
+                // shared-memory round trip.
+                uint32_t hf[4][32];                    // [16-lane half * 2 + 64-column half]
+                tc_ld_16x256b_x8(t_acc, hf[0]);
+                tc_ld_16x256b_x8(t_acc + 64, hf[1]);
+                tc_ld_16x256b_x8(t_acc + (16u << 16), hf[2]);
+                tc_ld_16x256b_x8(t_acc + (16u << 16) + 64, hf[3]);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acce_leader);
+                const int fr = o0 + q * 32 + (lane >> 2);              // this thread's features: fr + 8m
+                float ga4[4], bi4[4];
+#pragma unroll
+                for (int m = 0; m < 4; m++) {
+                    ga4[m] = p.gA ? __ldg(p.gA + a_base + fr + 8 * m) : 1.f;
+                    bi4[m] = (p.out_mode == 3 && p.bias && fr + 8 * m < p.bias_ld)
+                                 ? __bfloat162float(p.bias[(size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + fr + 8 * m]) : 0.f;
+                }
+                const uint32_t sbuf = epi0 + ew * 2048;               // four 512-byte tiles per warp
+                const int st_i = lane & 7, rd_i = lane >> 2;
+                const uint32_t st_off = (uint32_t)(st_i * 64 + (((lane >> 3) ^ ((st_i >> 1) & 3)) * 16));
+                const uint32_t rd_off = (uint32_t)(rd_i * 64 + (((lane & 3) ^ ((rd_i >> 1) & 3)) * 16));
+                const int fcol = o0 + q * 32 + (lane & 3) * 8;          // first of the 8 features this lane stores
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int j = jj * 4 + u, k = j & 7;
+                        const uint32_t* lo = hf[j >> 3];
+                        const uint32_t* hi = hf[2 + (j >> 3)];
+                        const int sl = 8 * (j & 1) + 2 * (lane & 3);  // gbv[c] holds the global of column 16c + (lane & 15)
+                        const float g0 = __shfl_sync(0xffffffffu, gbv[j >> 1], sl), g1 = __shfl_sync(0xffffffffu, gbv[j >> 1], sl + 1);
+                        float w0 = 1.f, w1 = 1.f;
+                        if (p.out_mode == 3) {
+                            w0 = __shfl_sync(0xffffffffu, rwv[j >> 1], sl);
+                            w1 = __shfl_sync(0xffffffffu, rwv[j >> 1], sl + 1);
+                        }
+                        const uint32_t v[4][2] = {{lo[4 * k], lo[4 * k + 1]}, {lo[4 * k + 2], lo[4 * k + 3]},
+                                                  {hi[4 * k], hi[4 * k + 1]}, {hi[4 * k + 2], hi[4 * k + 3]}};
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int m = 0; m < 4; m++) {
+                            float a = (__uint_as_float(v[m][0]) * ga4[m]) * g0, b = (__uint_as_float(v[m][1]) * ga4[m]) * g1;
+                            if (p.out_mode == 3) { a = (a + bi4[m]) * w0; b = (b + bi4[m]) * w1; }
+                            pk[m] = pack_bf16x2(a, b);
+                        }
+                        stmatrix_x4_trans(sbuf + u * 512 + st_off, pk[0], pk[1], pk[2], pk[3]);
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int col = n0 + 8 * (jj * 4 + u) + rd_i;
+                        const uint4 val = lds_v4(sbuf + u * 512 + rd_off);
+                        if (col < p.tok) {
+                            if (p.peer_n) {
+                                // the partial row goes straight into the memory of the rank that owns the token (a plain
+                                // 16-byte store over NVLink, or a local one for this rank's own range)
+                                const int owner = col / p.tok_per_rank;
+                                stg_v4(p.peer_out[owner] + (size_t)(col - owner * p.tok_per_rank) * p.out_f + fcol, val);
+                            } else {
+                                stg_v4(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)col * p.out_f + fcol, val);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+                acc_phase ^= 1;
+              } else {
                 // one accumulator: all loads first, then give it back, then the (slow) conversions and stores
                 uint32_t held[NCH][16];
 #pragma unroll
@@ -1113,6 +1188,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
                 for (int c = 0; c < NCH; c++) emit(held[c], c);
                 acc_phase ^= 1;
+              }
             } else {
 #pragma unroll
             for (int c = 0; c < NCH; c += 2) {
@@ -1375,6 +1451,14 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     if (pair_ok && a.bn == 384)                                     // 384: pair kernel, 128-token tile, two accumulators
         return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);
     // grouped (MoE) form on the pair kernel: one expert per 128-token block = per tile of the 128-token variant
+    // grouped, every expert's rows padded to 256 (bn == 256): 256-token tiles; the pair MMA takes as long for 128 tokens
+    // as for 256, so an expert with 129..256 rows costs one tile instead of two
+    if (a.eblk && a.bn == 256) {
+        if (splits != 1 || (a.out_mode != 1 && a.out_mode != 3) || a.out_f % 256 || a.tok < 256 || a.tok % 256 || (((uintptr_t)a.bias & 15) != 0) ||
+            (a.bias_ld > 0 && a.bias_ld % 8))
+            return QB_ERR_ARG;
+        return a.sparse ? launch_pair<true, 256>(a, st) : launch_pair<false, 256>(a, st);
+    }
     if (a.eblk && splits == 1 && (a.out_mode == 1 || a.out_mode == 3) && a.out_f % 256 == 0 && a.tok >= 128 && a.tok % 128 == 0 &&
         (a.bn == 0 || a.bn == 128) && (((uintptr_t)a.bias & 15) == 0) && (a.bias_ld <= 0 || a.bias_ld % 8 == 0))
         return a.sparse ? launch_pair<true, 128>(a, st) : launch_pair<false, 128>(a, st);

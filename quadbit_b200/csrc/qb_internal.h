@@ -19,7 +19,8 @@ int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, voi
                     cudaStream_t st, const void* row_src = nullptr, const void* n_rows_dev = nullptr);
 int swiglu_quant_feature_major16(const void* g, const void* u, void* Hb, void* scaleH, int batch, int hidden, cudaStream_t st);
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div = 1,
-                    const void* w_in = nullptr, void* rw = nullptr, void* inverse = nullptr, int e_base = 0, void* n_used = nullptr);
+                    const void* w_in = nullptr, void* rw = nullptr, void* inverse = nullptr, int e_base = 0, void* n_used = nullptr,
+                    int align = 128);
 int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const void* sc_w, const void* bias, void* Out, int rows,
                     int Mpe, int Hout, cudaStream_t st);
 // RMSNorm (+ residual add) fused with the quantiser; res / hout / g may be null (g null = single level)

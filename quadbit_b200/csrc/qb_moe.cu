@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
                                                                 long long* __restrict__ src, long long* __restrict__ pos,
                                                                 int* __restrict__ eblk, int div, const float* __restrict__ w_in,
                                                                 float* __restrict__ rw, int* __restrict__ inverse, int e_base,
-                                                                int* __restrict__ n_used) {
+                                                                int* __restrict__ n_used, int align) {
     // optional extras that the layer would otherwise do with a dozen small kernels: src holds slot / div (the token row
     // of a slot when div = top-k), rw[row] = w_in[slot] (0 for padding rows), inverse[slot] = row as int32
     extern __shared__ int sm[];
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
     __syncthreads();
     if (threadIdx.x == 0) {
         int off = 0;
-        for (int x = 0; x < e; x++) { poff[x] = off; off += (counts[x] + 127) / 128 * 128; }
+        for (int x = 0; x < e; x++) { poff[x] = off; off += (counts[x] + align - 1) / align * align; }     // align = 128 or 256 rows
         total = off;
         if (n_used) *n_used = off;          // rows in use: kernels over the padded rows stop here instead of at r_cap
     }
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
     }
     for (int b = total / 128 + threadIdx.x; b < r_cap / 128; b += blockDim.x) eblk[b] = -1;
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
-        const int b0 = poff[x] / 128, b1 = b0 + (counts[x] + 127) / 128;
+        const int b0 = poff[x] / 128, b1 = b0 + (counts[x] + align - 1) / align * (align / 128);
         for (int b = b0; b < b1; b++) eblk[b] = x;
     }
     __syncthreads();          // the -1 fill of src is complete (same CTA) before slots are written
@@ -140,11 +140,12 @@ __global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* 
 }
 
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div,
-                    const void* w_in, void* rw, void* inverse, int e_base, void* n_used) {
-    if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % 128 || (long long)r_cap < (long long)n + (long long)e * 127) return QB_ERR_ARG;
+                    const void* w_in, void* rw, void* inverse, int e_base, void* n_used, int align) {
+    if (align != 128 && align != 256) return QB_ERR_ARG;
+    if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % align || (long long)r_cap < (long long)n + (long long)e * (align - 1)) return QB_ERR_ARG;
     if (!assign || !src || !pos || !eblk || div < 1 || ((rw != nullptr) != (w_in != nullptr))) return QB_ERR_ARG;
     moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
-                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base, (int*)n_used);
+                                                                         (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base, (int*)n_used, align);
     return (int)cudaGetLastError();
 }
 

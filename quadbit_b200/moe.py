@@ -76,9 +76,9 @@ def build_routing(assign: torch.Tensor, e: int, with_pos: bool = False):
     return src, eblk.contiguous(), r_pad
 
 
-def fixed_capacity(n: int, e: int) -> int:
-    """Rows that always hold n routed slots of e experts with every segment padded to BN."""
-    return (n + e * (BN - 1) + BN - 1) // BN * BN
+def fixed_capacity(n: int, e: int, align: int = BN) -> int:
+    """Rows that always hold n routed slots of e experts with every segment padded to `align` rows."""
+    return (n + e * (align - 1) + align - 1) // align * align
 
 
 def build_routing_fixed(assign: torch.Tensor, e: int):
@@ -138,14 +138,15 @@ def seg_gemm(lib, x_rows: torch.Tensor, w, mpe: int, in_f: int, eblk: torch.Tens
     return C
 
 
-def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None, out=None):
-    """Grouped GEMM on already quantised routed rows (Bb [r, in_f/2], scale atoms, gB [r]); out: optional [r, mpe] bf16."""
+def seg_gemm_q(lib, Bb, sfb, gB, w, mpe: int, in_f: int, eblk: torch.Tensor, bias=None, row_w=None, out=None, tile: int = 128):
+    """Grouped GEMM on already quantised routed rows (Bb [r, in_f/2], scale atoms, gB [r]); out: optional [r, mpe] bf16.
+    tile = 256 needs every expert's rows padded to 256."""
     Ac, meta, sfa, gA = w
     r = Bb.shape[0]
     C = out if out is not None else torch.empty((r, mpe), dtype=torch.bfloat16, device=Bb.device)
     mode = 3 if (bias is not None or row_w is not None) else 1
     check(lib.qb_gemm(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), _ptr(gB),
-                      C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, 128,
+                      C.data_ptr(), 0, eblk.data_ptr(), _ptr(bias), _ptr(row_w), Ac.shape[0], mpe, r, in_f, 1, mode, 1, tile,
                       _stream()), "qb_gemm(grouped)")
     return C
 
@@ -225,9 +226,13 @@ class SparseMoE:
         # fixed_capacity: route into the worst-case number of padded rows instead of reading the exact count back
         # from the device; `forward` then issues no host read and can be captured in a CUDA graph
         self.fixed_capacity = fixed_capacity
+        # Rows every expert's segment is padded to in the one-kernel fixed-capacity routing. The CTA-pair MMA takes as long for
+        # a 128-token tile as for a 256-token one, so with segments padded to 256 an expert with 129..256 rows costs one
+        # tile instead of two (and 257..384 two instead of three); the padding rows cost the quantisers next to nothing.
+        self.row_align = 256
 
     def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None,
-                    n_used=None) -> torch.Tensor:
+                    n_used=None, tile: int = 128) -> torch.Tensor:
         """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
         padding), eblk = expert of every 128-row block, rw [r_pad] = routing weight of every row. Returns
         d [r_pad, mpe_dn] bf16 = expert(row) * weight."""
@@ -258,12 +263,12 @@ class SparseMoE:
             check(lib.qb_gemm_swiglu(Ac.data_ptr(), Bb.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), meta.data_ptr(), gA.data_ptr(), gB.data_ptr(),
                                      eblk.data_ptr(), _ptr(self.b_gu), Hb.data_ptr(), sfh.data_ptr(), 0, Ac.shape[0], self.mpe_gu, r_pad, self.Hp,
                                      1, 0 if self.act == "gptoss" else 1, _stream()), "qb_gemm_swiglu")
-            return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)
-        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu)   # [r_pad, 2*Ip]: gate | up
+            return seg_gemm_q(lib, Hb, sfh, None, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out, tile=tile)
+        gu = seg_gemm_q(lib, Bb, sfb, gB, self.w_gu, self.mpe_gu, self.Hp, eblk, bias=self.b_gu, tile=tile)   # [r_pad, 2*Ip]: gate | up
         gH = torch.empty((r_pad,), dtype=torch.float32, device=dev)
         check(lib.qb_swiglu_quant_act(gu.data_ptr(), Hb.data_ptr(), 0, sfh.data_ptr(), gH.data_ptr(), src.data_ptr(), nu, r_pad, self.Ip, 0,
                                       0 if self.act == "gptoss" else 1, _stream()), "qb_swiglu_quant_act")
-        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out)  # [r_pad, mpe_dn]
+        return seg_gemm_q(lib, Hb, sfh, gH, self.w_dn, self.mpe_dn, self.Ip, eblk, bias=self.b_dn, row_w=rw, out=d_out, tile=tile)  # [r_pad, mpe_dn]
 
     def _expert_rows_padded(self, rows_in: torch.Tensor, assign: torch.Tensor, row_w: torch.Tensor, row_of=None):
         """Routed rows through this layer's experts in the padded, expert-sorted row order of the grouped GEMM:
@@ -303,7 +308,8 @@ class SparseMoE:
         if self.e0 == 0 and self.e1 == self.E_total and self.fixed_capacity:
             # routing, token row of every padded row, routing weight of every row and the combine table in one launch
             n, e = assign_g.numel(), self.E
-            r_cap = fixed_capacity(n, e)
+            al = self.row_align
+            r_cap = fixed_capacity(n, e, al)
             src = torch.empty((r_cap,), dtype=torch.long, device=dev)
             pos = torch.empty((n,), dtype=torch.long, device=dev)
             eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
@@ -312,9 +318,9 @@ class SparseMoE:
             w_in = topk_w.reshape(-1).float().contiguous()
             n_used = torch.empty((1,), dtype=torch.int32, device=dev)
             check(self.lib.qb_moe_route_fixed_range(assign_g.contiguous().data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, 0, e,
-                                                    r_cap, self.topk, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(), n_used.data_ptr(),
-                                                    _stream()), "qb_moe_route_fixed_range")
-            d = self._run_padded(x, src, eblk, r_cap, rw, n_used=n_used)
+                                                    r_cap, self.topk, al, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(),
+                                                    n_used.data_ptr(), _stream()), "qb_moe_route_fixed_range")
+            d = self._run_padded(x, src, eblk, r_cap, rw, n_used=n_used, tile=al)
             return combine(self.lib, d, inverse, T, self.H, self.topk)
         if self.e0 == 0 and self.e1 == self.E_total:
             slots = torch.arange(assign_g.numel(), device=dev)
@@ -339,7 +345,7 @@ class SparseMoE:
     # ------------------------------------------------------------------ expert parallelism by peer loads
     def ep_capacity(self, T: int) -> int:
         """Routed rows a rank must be able to hold when all T * topk slots could land on its experts."""
-        return fixed_capacity(T * self.topk, self.e1 - self.e0)
+        return fixed_capacity(T * self.topk, self.e1 - self.e0, self.row_align)
 
     def make_ep_context(self, T: int, rank: int, world: int, group=None, emulate=None):
         from .tp import EPContext
@@ -382,11 +388,13 @@ class SparseMoE:
         eblk = torch.empty((r_cap // BN,), dtype=torch.int32, device=dev)
         rw = torch.empty((r_cap,), dtype=torch.float32, device=dev)
         n_used = torch.empty((1,), dtype=torch.int32, device=dev)
+        assert r_cap == self.ep_capacity(T)
         check(lib.qb_moe_route_fixed_range(ctx.own(1), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, self.e0, epr, r_cap, topk,
-                                           ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), n_used.data_ptr(), _stream()),
+                                           self.row_align, ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), n_used.data_ptr(), _stream()),
               "qb_moe_route_fixed_range")
         d_out = ctx.own_tensor(2)[: r_cap * self.mpe_dn * 2].view(torch.bfloat16).view(r_cap, self.mpe_dn)
-        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out, n_used=n_used)
+        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out, n_used=n_used,
+                         tile=self.row_align)
         check(lib.qb_peer_signal(ctx.flag_ptrs(ctx.FLAG_OUTPUT), W, rank, 0, ep, _stream()), "qb_peer_signal")
         yield None
         check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_OUTPUT), W, 0, ep, _stream()), "qb_peer_wait")
