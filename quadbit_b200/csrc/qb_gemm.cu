@@ -615,6 +615,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
     __shared__ uint32_t tmem_base_slot;
+    griddep_launch_dependents();
     __shared__ float hmax_xch[8][2][16];      // out_mode 4: block maxima exchanged between partner epilogue warps
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -669,6 +670,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t tmem_base = tmem_base_slot;
 
     const int total_tiles = p.num_m2 * p.num_n;
+    // Launched as a programmatic dependent: this grid may start while the kernel in front (an activation quantiser, the GEMM
+    // of another layer) is still running. What that kernel produces - activations, their scale factors and globals, the
+    // routing table of the grouped mode - is read only after griddep_wait(); barriers, tensor memory, tensor maps and the
+    // weight side of the first ring revolution (weights are constants) are set up / loaded before.
+    const bool dep_all = p.eblk != nullptr;
     // Token tile of a work item. With the reduce-scatter epilogue the token tiles are visited owner by owner in a rotation
     // that starts behind this rank: at any moment the ranks store into different owners and every rank's local and remote
     // tiles alternate, so the NVLink traffic is spread over the whole kernel instead of arriving in one burst per owner.
@@ -698,6 +704,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // leader's full barrier, whose two arrivals (with the byte count of the pair) come from the
         // leader's producers; a peer load that lands first only drives the pending count negative.
         const bool isA = warp == W_PROD_A;
+        if (!isA || dep_all) griddep_wait();             // activations (and the routing table) come from the kernel in front
         int stage = 0;
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -738,6 +745,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     } else {
         // ------------------------------------------------------------ sideband producers (both CTAs)
         const bool isW = warp == W_SIDE_W;               // weight side: scale factors of A and metadata
+        if (!isW || dep_all) griddep_wait();
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -785,6 +793,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // barrier wait and the MMAs it gates.
         if (warp == W_MMA && rank == 0 && lane == 0) {
             const uint32_t idesc = make_idesc_nvf4(BN, SPARSE, 256);
+            if (dep_all) griddep_wait();
             int stage = 0, acc = 0, tslot = 0;
             uint32_t phase = 0, acc_phase = 0;
             for (int tile = cluster_id; tile < total_tiles && !abort_flag; tile += num_clusters) {
@@ -842,6 +851,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // ------------------------------------------------------------ scale-factor warps (both CTAs)
         const int q = warp & 3;
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
+        if (dep_all) griddep_wait();
         // K block number `it` (counted over all tiles) uses operand stage it % STAGES, sideband slot it % NSB and
         // tensor-memory slot it % NSLOT. Its tensor-memory slot is free once the MMAs of K block it - NSLOT have
         // completed, which the empty barrier of THAT block's stage signals (completions come in ring order).
@@ -937,6 +947,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // Eight warps: warps 8-11 drain the first half of the tile's columns, warps 12-15 the second half;
         // a warp reads the TMEM lane quadrant (warp % 4) it is allowed to.
         reg_alloc<REGS_EPI>();
+        griddep_wait();                                  // token globals, routing weights; and nothing is stored before
         const int q = warp & 3;
         const int half = warp >= 12 ? 1 : 0;
         const int ew = warp - 8;
@@ -1396,8 +1407,17 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
-    nvfp4_gemm_pair_kernel<SPARSE, BN><<<nclusters * 2, C::THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(nclusters * 2));
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see griddep_wait() in the kernel
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<SPARSE, BN>, tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
 }
 
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
