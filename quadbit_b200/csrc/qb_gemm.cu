@@ -1162,8 +1162,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                         uint32_t pk[4];
 #pragma unroll
                         for (int m = 0; m < 4; m++) {
-                            float a = (__uint_as_float(v[m][0]) * ga4[m]) * g0, b = (__uint_as_float(v[m][1]) * ga4[m]) * g1;
-                            if (p.out_mode == 3) { a = (a + bi4[m]) * w0; b = (b + bi4[m]) * w1; }
+                            float a = __uint_as_float(v[m][0]), b = __uint_as_float(v[m][1]);     // two adjacent tokens of one feature
+                            mul_f32x2(a, b, ga4[m], ga4[m]);
+                            mul_f32x2(a, b, g0, g1);
+                            if (p.out_mode == 3) {
+                                add_f32x2(a, b, bi4[m], bi4[m]);
+                                mul_f32x2(a, b, w0, w1);
+                            }
                             pk[m] = pack_bf16x2(a, b);
                         }
                         stmatrix_x4_trans(sbuf + u * 512 + st_off, pk[0], pk[1], pk[2], pk[3]);
