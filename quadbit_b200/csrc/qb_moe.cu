@@ -84,59 +84,93 @@ int moe_scatter_add(const void* Cs, const void* eblk, const void* sc_tok, const 
     return (int)cudaGetLastError();
 }
 
-// Fixed-capacity routing in one launch of one CTA: histogram of the expert ids in shared memory, padded prefix,
-// then every routed slot takes the next free row of its expert's segment. Outputs: src[r_cap] (routed slot of every
-// padded row, -1 = padding), pos[n] (padded row of every slot, -1 for a slot without a valid expert), eblk[r_cap/128]
-// (expert of every 128-row block, -1 = unused capacity). The order of the rows inside an expert's segment follows
-// the atomics and may differ from run to run; rows are computed independently, so the layer's output does not.
+// Fixed-capacity routing in one launch of one cluster of eight CTAs: every CTA histograms its share of the slots in its
+// own shared memory, the CTAs read each other's counts through distributed shared memory (per expert: the total and the
+// number of slots that lower-ranked CTAs hold, which is where this CTA's rows start inside the expert's segment), every
+// CTA forms the padded prefix, and then each routed slot takes the next free row of its CTA's part of the segment.
+// Outputs: src[r_cap] (routed slot of every padded row, -1 = padding), pos[n] (padded row of every slot, -1 for a slot
+// without a valid expert), eblk[r_cap/128] (expert of every 128-row block, -1 = unused capacity). Padding rows and unused
+// capacity are filled by the CTAs in parallel with the scatter: they are disjoint from the rows the slots take, so nothing
+// has to be ordered between CTAs. The order of the rows inside an expert's segment follows the atomics and may differ from
+// run to run; rows are computed independently, so the layer's output does not.
 // Replaces the sort-based torch routing (harness/qb_vllm_plugin/qb_sm120_plugin.py:1271-1315) for graph capture.
-__global__ void __launch_bounds__(1024) moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap,
-                                                                long long* __restrict__ src, long long* __restrict__ pos,
-                                                                int* __restrict__ eblk, int div, const float* __restrict__ w_in,
-                                                                float* __restrict__ rw, int* __restrict__ inverse, int e_base,
-                                                                int* __restrict__ n_used, int align) {
+constexpr int ROUTE_CTAS = 8;
+__device__ __forceinline__ int ld_cluster_s32(uint32_t cluster_addr) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+__global__ void __cluster_dims__(ROUTE_CTAS, 1, 1) __launch_bounds__(1024)
+moe_route_fixed_kernel(const long long* __restrict__ assign, int n, int e, int r_cap, long long* __restrict__ src,
+                       long long* __restrict__ pos, int* __restrict__ eblk, int div, const float* __restrict__ w_in,
+                       float* __restrict__ rw, int* __restrict__ inverse, int e_base, int* __restrict__ n_used, int align) {
     // optional extras that the layer would otherwise do with a dozen small kernels: src holds slot / div (the token row
     // of a slot when div = top-k), rw[row] = w_in[slot] (0 for padding rows), inverse[slot] = row as int32
     extern __shared__ int sm[];
-    int* counts = sm;
-    int* poff = sm + e;
-    int* cursor = sm + 2 * e;
+    int* counts = sm;            // this CTA's slots per expert
+    int* poff = sm + e;          // first row of every expert's segment
+    int* cursor = sm + 2 * e;    // next free row of this CTA's part of the segment
+    int* tot = sm + 3 * e;       // slots per expert over all CTAs
     __shared__ int total;
-    for (int i = threadIdx.x; i < e; i += blockDim.x) { counts[i] = 0; cursor[i] = 0; }
+    const int rank = (int)cluster_ctarank();
+    const int i0 = (int)(((long long)n * rank) / ROUTE_CTAS), i1 = (int)(((long long)n * (rank + 1)) / ROUTE_CTAS);
+    for (int i = threadIdx.x; i < e; i += blockDim.x) counts[i] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const long long ex = assign[i] - e_base;           // expert ids are global; this rank owns [e_base, e_base + e)
         if (ex >= 0 && ex < e) atomicAdd(&counts[(int)ex], 1);
+    }
+    cluster_sync_all();
+    for (int x = threadIdx.x; x < e; x += blockDim.x) {
+        int t = 0, before = 0;
+        const uint32_t a = smem_u32(&counts[x]);
+        for (int r = 0; r < ROUTE_CTAS; r++) {
+            const int c = ld_cluster_s32(mapa_shared(a, (uint32_t)r));
+            if (r < rank) before += c;
+            t += c;
+        }
+        tot[x] = t;
+        cursor[x] = before;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         int off = 0;
-        for (int x = 0; x < e; x++) { poff[x] = off; off += (counts[x] + align - 1) / align * align; }     // align = 128 or 256 rows
+        for (int x = 0; x < e; x++) { poff[x] = off; off += (tot[x] + align - 1) / align * align; }     // align = 128 or 256 rows
         total = off;
-        if (n_used) *n_used = off;          // rows in use: kernels over the padded rows stop here instead of at r_cap
+        if (n_used && rank == 0) *n_used = off;          // rows in use: kernels over the padded rows stop here instead of at r_cap
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < r_cap; i += blockDim.x) {
-        src[i] = -1;
-        if (rw) rw[i] = 0.f;
+    // unused capacity behind the last segment, and its blocks
+    const int tail = r_cap - total;
+    for (int i = (int)(((long long)tail * rank) / ROUTE_CTAS) + threadIdx.x; i < (int)(((long long)tail * (rank + 1)) / ROUTE_CTAS); i += blockDim.x) {
+        src[total + i] = -1;
+        if (rw) rw[total + i] = 0.f;
     }
-    for (int b = total / 128 + threadIdx.x; b < r_cap / 128; b += blockDim.x) eblk[b] = -1;
-    for (int x = threadIdx.x; x < e; x += blockDim.x) {
-        const int b0 = poff[x] / 128, b1 = b0 + (counts[x] + align - 1) / align * (align / 128);
-        for (int b = b0; b < b1; b++) eblk[b] = x;
+    if (rank == 0)
+        for (int b = total / 128 + threadIdx.x; b < r_cap / 128; b += blockDim.x) eblk[b] = -1;
+    // the experts of this CTA (x = rank, rank + 8, ...): blocks of the segment and its padding rows
+    for (int x = rank; x < e; x += ROUTE_CTAS) {
+        const int seg = (tot[x] + align - 1) / align * align;
+        for (int b = threadIdx.x; b < seg / 128; b += blockDim.x) eblk[poff[x] / 128 + b] = x;
+        for (int i = tot[x] + threadIdx.x; i < seg; i += blockDim.x) {
+            src[poff[x] + i] = -1;
+            if (rw) rw[poff[x] + i] = 0.f;
+        }
     }
-    __syncthreads();          // the -1 fill of src is complete (same CTA) before slots are written
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int x = threadIdx.x; x < e; x += blockDim.x) cursor[x] += poff[x];
+    __syncthreads();
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const long long ex = assign[i] - e_base;
         long long dst = -1;
         if (ex >= 0 && ex < e) {
-            dst = poff[(int)ex] + atomicAdd(&cursor[(int)ex], 1);
+            dst = atomicAdd(&cursor[(int)ex], 1);
             src[dst] = i / div;
             if (rw) rw[dst] = w_in[i];
         }
         pos[i] = dst;
         if (inverse) inverse[i] = (int)dst;
     }
+    cluster_sync_all();          // no CTA leaves while its counts can still be read by the others
 }
 
 int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n, int e, int r_cap, cudaStream_t st, int div,
@@ -144,7 +178,12 @@ int moe_route_fixed(const void* assign, void* src, void* pos, void* eblk, int n,
     if (align != 128 && align != 256) return QB_ERR_ARG;
     if (n < 0 || e <= 0 || e > 4096 || r_cap <= 0 || r_cap % align || (long long)r_cap < (long long)n + (long long)e * (align - 1)) return QB_ERR_ARG;
     if (!assign || !src || !pos || !eblk || div < 1 || ((rw != nullptr) != (w_in != nullptr))) return QB_ERR_ARG;
-    moe_route_fixed_kernel<<<1, 1024, (size_t)3 * e * sizeof(int), st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
+    const size_t smem = (size_t)4 * e * sizeof(int);
+    if (smem > 48 * 1024) {
+        const int rc = (int)cudaFuncSetAttribute(moe_route_fixed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc) return rc;
+    }
+    moe_route_fixed_kernel<<<ROUTE_CTAS, 1024, smem, st>>>((const long long*)assign, n, e, r_cap, (long long*)src,
                                                                          (long long*)pos, (int*)eblk, div, (const float*)w_in, (float*)rw, (int*)inverse, e_base, (int*)n_used, align);
     return (int)cudaGetLastError();
 }

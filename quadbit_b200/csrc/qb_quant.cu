@@ -50,6 +50,10 @@ __device__ __forceinline__ void quant_act_row(const int row, const uint4* __rest
         xr = x + (size_t)(srow < 0 ? 0 : srow) * h8;
     }
     if (srow < 0) {
+        // With a rows-in-use limit (the fixed-capacity routing of the MoE layer) a padding row is left unwritten: the grouped
+        // GEMM computes its token column from whatever the buffers hold, every token column is independent of the others,
+        // and no one reads the result rows of padding (the combine follows the slot -> row table).
+        if (peers.n_rows) return;
         // padding row: what the full path makes of an all-zero row (codes 0, scale codes 0, global 1e-30), without the passes
         for (int b = threadIdx.x; b < nblocks; b += blockDim.x) {
             uint32_t* dst = Bwords + (size_t)row * (K >> 3) + (size_t)b * CPB;
@@ -166,13 +170,14 @@ __global__ void __launch_bounds__(1024) quant_act_kernel(const uint4* __restrict
 template <int NJ, bool INTERLEAVED, bool TWO_LEVEL, int ACT>
 __device__ __forceinline__ void swiglu_quant_row(const int row, const uint4* __restrict__ cgu, uint32_t* __restrict__ Hwords,
                                                  uint8_t* __restrict__ sf_ref, uint8_t* __restrict__ sf_atoms, float* __restrict__ g_out, int tok,
-                                                 int I, const long long* __restrict__ row_src) {
+                                                 int I, const long long* __restrict__ row_src, const bool skip_padding) {
     const int nchunks = I >> 3;
     const int nblocks = I >> 5;          // a multiple of 4 (I % 128 == 0)
     const int lane = threadIdx.x & 31;
     const uint4* gr = cgu + (size_t)row * (nchunks * 2);
     const uint4* ur = gr + nchunks;
     if (row_src && row_src[row] < 0) {
+        if (skip_padding) return;          // rows-in-use mode: padding rows stay unwritten (see quant_act_row)
         // padding row of a routed batch (its gate/up row may never have been written): zeros, as for an all-zero row
         for (int b = threadIdx.x; b < nblocks; b += blockDim.x) {
             uint32_t* dst = Hwords + (size_t)row * nchunks + (size_t)b * 4;
@@ -279,7 +284,7 @@ __global__ void __launch_bounds__(512) swiglu_quant_kernel(const uint4* __restri
                                                             const int* __restrict__ n_rows) {
     const int nrows = n_rows ? min(tok, *n_rows) : tok;
     for (int row = blockIdx.x; row < nrows; row += gridDim.x) {
-        swiglu_quant_row<NJ, INTERLEAVED, TWO_LEVEL, ACT>(row, cgu, Hwords, sf_ref, sf_atoms, g_out, tok, I, row_src);
+        swiglu_quant_row<NJ, INTERLEAVED, TWO_LEVEL, ACT>(row, cgu, Hwords, sf_ref, sf_atoms, g_out, tok, I, row_src, n_rows != nullptr);
         __syncthreads();
     }
 }
