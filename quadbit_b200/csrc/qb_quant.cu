@@ -250,14 +250,17 @@ __device__ __forceinline__ void swiglu_quant_row(const int row, const uint4* __r
     for (int j = 0; j < NJ; j++) {
         const int b = threadIdx.x + j * blockDim.x;
         const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax[j], 6.f));
-        const Fp4Divider dv(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
+        // h comes from exp / divide intrinsics and is only defined up to a few ulp, so the exact IEEE quotient of the
+        // activation quantiser buys nothing here: one multiply by the reciprocal of the scale and the hardware E2M1
+        // conversion; against the exact path a code can differ only where the quotient sits within an ulp or two of a
+        // rounding boundary (the parity test checks exactly that: every differing code lies on a boundary)
+        const float rs = __frcp_rn(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            float f8[8];
-#pragma unroll
-            for (int e = 0; e < 8; e++) f8[e] = h[j][8 * k + e];
-            w[k] = dv.pack8(f8);
+            const float lo4[4] = {h[j][8 * k], h[j][8 * k + 1], h[j][8 * k + 2], h[j][8 * k + 3]};
+            const float hi4[4] = {h[j][8 * k + 4], h[j][8 * k + 5], h[j][8 * k + 6], h[j][8 * k + 7]};
+            w[k] = pack4_e2m1_rcp(lo4, rs) | (pack4_e2m1_rcp(hi4, rs) << 16);
         }
         uint32_t sw = 0;
         const int base = lane & ~3;
