@@ -481,14 +481,15 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
     for (int j = 0; j < NJ; j++) {
         const int blk = threadIdx.x + j * blockDim.x;
         const uint32_t code = TWO_LEVEL ? enc_ue4m3(__fdiv_rn(__fdiv_rn(bmax[j], 6.f), gl)) : enc_ue4m3(__fdiv_rn(bmax[j], 6.f));
-        const Fp4Divider dv(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
+        // the normalised values come from rsqrtf and are only defined up to an ulp or two, so (as in the SwiGLU quantiser)
+        // the quotient is one multiply by the reciprocal of the scale and the hardware E2M1 conversion
+        const float rs = __frcp_rn(fmaxf(TWO_LEVEL ? __fmul_rn(dec_ue4m3(code), gl) : dec_ue4m3(code), 1e-30f));
         uint32_t w[CPB];
 #pragma unroll
         for (int k = 0; k < CPB; k++) {
-            float f8[8];
-#pragma unroll
-            for (int e = 0; e < 8; e++) f8[e] = v[j][8 * k + e];
-            w[k] = dv.pack8(f8);
+            const float lo4[4] = {v[j][8 * k], v[j][8 * k + 1], v[j][8 * k + 2], v[j][8 * k + 3]};
+            const float hi4[4] = {v[j][8 * k + 4], v[j][8 * k + 5], v[j][8 * k + 6], v[j][8 * k + 7]};
+            w[k] = pack4_e2m1_rcp(lo4, rs) | (pack4_e2m1_rcp(hi4, rs) << 16);
         }
         uint32_t sw = 0;
         const int base = lane & ~3;
