@@ -345,6 +345,16 @@ int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx
                   void* done_counter, void* stream);
 int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* eblk, int n, int e_base, int e, int r_cap, int div,
                              int align, const void* w_in, void* rw, void* inverse, void* n_used, void* stream);
+/* Dispatch of quantised rows. qb_quantize_rows: x[rows][H] bf16 (H % 8 == 0, zero-padded to K) -> codes Bbytes[rows][K/2], scales in
+ * the step-major layout sf_ref[K/128][rows][128/block], g[rows] (NULL = single level): each token quantised once.
+ * qb_gather_quantized: routed row r copies the quantised row of token src[r] (numbered over n_peers buffers of rows_per_peer rows,
+ * per-32 scales) into Bbytes[r], the 128x4 scale atoms of row r and g[r]; src[r] < 0 is a padding row (zeros, or left unwritten
+ * when n_rows_dev, the device count of rows in use, is given). Replaces gather + quantise of every routed row
+ * (harness/qb_vllm_plugin/qb_sm120_plugin.py:2430-2441): a token with top-k slots is quantised once, and over NVLink 0.53 bytes
+ * per value move instead of 2. */
+int qb_quantize_rows(const void* x, void* Bbytes, void* sf_ref, void* g, int rows, int K, int H, int block, void* stream);
+int qb_gather_quantized(void* const* q_codes, void* const* q_sf, void* const* q_g, int n_peers, long long rows_per_peer, const void* src,
+                        void* Bbytes, void* sf_atoms, void* g, int rows, int K, const void* n_rows_dev, void* stream);
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
                                 void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream);
 int qb_ep_combine(void* const* dbuf, void* const* inverse, const void* idx, void* y, int t_local, int t0, int H, int topk, int Mpe,

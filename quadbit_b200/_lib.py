@@ -74,6 +74,8 @@ _SIGS = {
     "qb_peer_signal": ([P, I, I, I, P, P], I),
     "qb_ep_publish": ([P, P, c_longlong, P, P, I, I, P, P, I, I, P, P, P, P], I),
     "qb_moe_route_fixed_range": ([P] * 4 + [I] * 6 + [P] * 5, I),
+    "qb_quantize_rows": ([P] * 4 + [I] * 4 + [P], I),
+    "qb_gather_quantized": ([P] * 3 + [I, c_longlong] + [P] * 4 + [I] * 2 + [P] * 2, I),
     "qb_gather_quantize_act_peer": ([P, I, c_longlong] + [P] * 4 + [I] * 4 + [P, P], I),
     "qb_ep_combine": ([P] * 4 + [I] * 7 + [P], I),
     "qb_peer_wait": ([P, I, I, P, P], I),

@@ -549,6 +549,15 @@ int qb_moe_route_fixed_range(const void* assign, void* src, void* pos, void* ebl
     if (e_base < 0) return QB_ERR_ARG;
     return qb::moe_route_fixed(assign, src, pos, eblk, n, e, r_cap, (cudaStream_t)stream, div, w_in, rw, inverse, e_base, n_used, align);
 }
+int qb_quantize_rows(const void* x, void* Bbytes, void* sf_ref, void* g, int rows, int K, int H, int block, void* stream) {
+    if (!x || !sf_ref) return QB_ERR_ARG;
+    return qb::gather_quantize_act(x, nullptr, Bbytes, sf_ref, nullptr, g, rows, K, H, block, (cudaStream_t)stream, nullptr, 0, 0, nullptr);
+}
+int qb_gather_quantized(void* const* q_codes, void* const* q_sf, void* const* q_g, int n_peers, long long rows_per_peer, const void* src,
+                        void* Bbytes, void* sf_atoms, void* g, int rows, int K, const void* n_rows_dev, void* stream) {
+    return qb::gather_quantized((const void* const*)q_codes, (const void* const*)q_sf, (const void* const*)q_g, n_peers, rows_per_peer, src,
+                                Bbytes, sf_atoms, g, rows, K, n_rows_dev, (cudaStream_t)stream);
+}
 int qb_gather_quantize_act_peer(void* const* x_peers, int n_peers, long long rows_per_peer, const void* src, void* Bbytes, void* sf_atoms,
                                 void* g, int rows, int K, int H, int block, const void* n_rows_dev, void* stream) {
     if (!x_peers) return QB_ERR_ARG;

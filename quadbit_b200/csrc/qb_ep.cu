@@ -89,10 +89,12 @@ extern "C" {
 int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx, const void* w, int n_slots, int slot0,
                   void* const* assign_all, void* const* w_all, int world, int rank, void* const* flags, const void* value_ptr,
                   void* done_counter, void* stream) {
-    if (!x || !x_pub || x_bytes <= 0 || (x_bytes & 15) || !idx || !w || n_slots <= 0 || slot0 < 0 || !assign_all || !w_all || !flags ||
-        world < 1 || world > 8 || rank < 0 || rank >= world || !value_ptr || !done_counter)
+    // x_bytes == 0: nothing to copy (the rank's rows were written into its peer-visible buffer by the kernel in front, e.g. the
+    // quantiser of qb_quantize_rows); the flag still orders them, because that kernel has completed when this one starts
+    if (x_bytes < 0 || (x_bytes & 15) || (x_bytes > 0 && (!x || !x_pub)) || !idx || !w || n_slots <= 0 || slot0 < 0 || !assign_all ||
+        !w_all || !flags || world < 1 || world > 8 || rank < 0 || rank >= world || !value_ptr || !done_counter)
         return QB_ERR_ARG;
-    if (((uintptr_t)x & 15) || ((uintptr_t)x_pub & 15)) return QB_ERR_ARG;
+    if (x_bytes > 0 && (((uintptr_t)x & 15) || ((uintptr_t)x_pub & 15))) return QB_ERR_ARG;
     PtrTable8 a{}, ww{}, f{};
     for (int r = 0; r < world; r++) {
         if (!assign_all[r] || !w_all[r] || !flags[r]) return QB_ERR_ARG;
@@ -100,6 +102,7 @@ int qb_ep_publish(const void* x, void* x_pub, long long x_bytes, const void* idx
     }
     const size_t chunks = (size_t)x_bytes / 16;
     unsigned blocks = (unsigned)((chunks + 255) / 256);
+    if (chunks == 0) blocks = (unsigned)((n_slots + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (blocks == 0) blocks = 1;
     ep_publish_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)x_pub, chunks, (const long long*)idx, (const float*)w,

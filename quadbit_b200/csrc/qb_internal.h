@@ -14,6 +14,9 @@ int quantize_act(const void* x, void* Bbytes, void* sf_ref, void* sf_atoms, void
 int gather_quantize_act(const void* x, const void* src, void* Bbytes, void* sf_ref, void* sf_atoms, void* g, int tok, int K, int H,
                         int block, cudaStream_t st, const void* const* peer_x = nullptr, int n_peers = 0, long long rows_per_peer = 0,
                         const void* n_rows_dev = nullptr);
+// routed rows copy their token's quantised row (codes, per-32 scales in the step-major layout, global) from n_peers buffers
+int gather_quantized(const void* const* q_codes, const void* const* q_sf, const void* const* q_g, int n_peers, long long rows_per_peer,
+                     const void* src, void* Bbytes, void* sf_atoms, void* g, int rows, int K, const void* n_rows_dev, cudaStream_t st);
 int swiglu_quant(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, cudaStream_t st);
 int swiglu_quant_ex(const void* cgu, void* Hb, void* sf_ref, void* sf_atoms, void* gH, int tok, int I, int interleaved, int act,
                     cudaStream_t st, const void* row_src = nullptr, const void* n_rows_dev = nullptr);

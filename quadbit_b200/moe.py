@@ -231,6 +231,25 @@ class SparseMoE:
         # tile instead of two (and 257..384 two instead of three); the padding rows cost the quantisers next to nothing.
         self.row_align = 256
 
+    def quantize_tokens(self, x: torch.Tensor, out=None):
+        """x [T, H] bf16 -> (codes [T, Hp/2] u8, scales [Hp/128, T, 4] u8, globals [T] f32): the layer's input quantiser
+        (two-level, per-32), hidden size zero-padded to Hp. `out`: optional (codes ptr, scales ptr, globals ptr) to write to."""
+        x = x.to(torch.bfloat16).contiguous()
+        if self.H % 8:                           # the quantiser reads 16-byte chunks
+            x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
+        T = x.shape[0]
+        if out is None:
+            Bq = torch.empty((T, self.Hp // 2), dtype=torch.uint8, device=x.device)
+            sq = torch.empty((self.Hp // 128, T, 4), dtype=torch.uint8, device=x.device)
+            gq = torch.empty((T,), dtype=torch.float32, device=x.device)
+            ptrs = (Bq.data_ptr(), sq.data_ptr(), gq.data_ptr())
+        else:
+            Bq = sq = gq = None
+            ptrs = out
+        if T:
+            check(self.lib.qb_quantize_rows(x.data_ptr(), ptrs[0], ptrs[1], ptrs[2], T, self.Hp, x.shape[1], 32, _stream()), "qb_quantize_rows")
+        return Bq, sq, gq
+
     def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None,
                     n_used=None, tile: int = 128) -> torch.Tensor:
         """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
@@ -242,19 +261,19 @@ class SparseMoE:
         Bb = torch.empty((r_pad, self.Hp // 2), dtype=torch.uint8, device=dev)
         sfb = sf_atoms_empty(lib, r_pad, self.Hp, 32, dev)
         gB = torch.empty((r_pad,), dtype=torch.float32, device=dev)
+        # Every token is quantised ONCE; its routed slots copy the packed row (codes, scales, global): a token with top-k
+        # slots is not quantised k times, and what moves (over NVLink, with peers) is 0.53 bytes per value instead of 2.
         if peer_x is not None:
-            # src holds GLOBAL token rows; the rows are pulled from the ranks that hold them (peer_x = (pointer table, rows
-            # per rank, row width in elements, number of ranks))
-            xp, rows_per_rank, width, nr = peer_x
-            check(lib.qb_gather_quantize_act_peer(xp, nr, rows_per_rank, src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), r_pad,
-                                                  self.Hp, width, 32, nu, _stream()), "qb_gather_quantize_act_peer")
+            # src holds GLOBAL token rows; the quantised rows are pulled from the ranks that hold them
+            # (peer_x = (code pointers, scale pointers, global pointers, rows per rank, number of ranks))
+            qc, qs, qg, rows_per_rank, nr = peer_x
         else:
-            x = x.to(torch.bfloat16).contiguous()
-            if self.H % 8:                       # the fused gather reads 16-byte chunks
-                x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
             from .tp import ptr_array
-            check(lib.qb_gather_quantize_act_peer(ptr_array([x.data_ptr()]), 1, max(x.shape[0], 1), src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(),
-                                                  gB.data_ptr(), r_pad, self.Hp, x.shape[1], 32, nu, _stream()), "qb_gather_quantize_act_peer")
+            rows_per_rank, nr = max(x.shape[0], 1), 1
+            Bq, sq, gq = self.quantize_tokens(x)
+            qc, qs, qg = ptr_array([Bq.data_ptr()]), ptr_array([sq.data_ptr()]), ptr_array([gq.data_ptr()])
+        check(lib.qb_gather_quantized(qc, qs, qg, nr, rows_per_rank, src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), r_pad,
+                                      self.Hp, nu, _stream()), "qb_gather_quantized")
         Hb = torch.empty((r_pad, self.Ip // 2), dtype=torch.uint8, device=dev)
         sfh = sf_atoms_empty(lib, r_pad, self.Ip, 32, dev)
         if self.fused_gu:
@@ -358,10 +377,10 @@ class SparseMoE:
         """Expert-parallel layer without a collective library and without a host read (a generator that yields where
         other ranks are waited for, so that one process can drive emulated ranks; the last value is y [T_local, H]).
 
-        This rank holds experts [e0, e1) and tokens x [T_local, H]. (1) Every rank copies its tokens into a peer-visible
-        buffer and stores its routing (expert ids, weights) into the replicated tables of all ranks. (2) Every rank routes
-        ALL slots onto its own experts with the one-kernel fixed-capacity routing, pulls the token rows it needs from
-        their home ranks inside the fused gather + quantise kernel, and runs its experts. (3) Every rank combines the
+        This rank holds experts [e0, e1) and tokens x [T_local, H]. (1) Every rank quantises its tokens once into a
+        peer-visible buffer and stores its routing (expert ids, weights) into the replicated tables of all ranks. (2) Every
+        rank routes ALL slots onto its own experts with the one-kernel fixed-capacity routing, pulls the QUANTISED rows it
+        needs from their home ranks (qb_gather_quantized), and runs its experts. (3) Every rank combines the
         top-k rows of its own tokens, reading them from the experts' owners. Flags carry the device epoch, so the whole
         layer has fixed kernel arguments (CUDA-graph replay). Equals `forward` of a 1-rank layer."""
         lib, W, rank = self.lib, ctx.world, ctx.rank
@@ -369,15 +388,17 @@ class SparseMoE:
         dev = x.device
         epr = self.e1 - self.e0
         assert x.shape[0] == Tl and self.E_total == epr * W and self.e0 == rank * epr
-        x = x.to(torch.bfloat16).contiguous()
-        if self.H % 8:
-            x = torch.nn.functional.pad(x, (0, self.Hp - self.H))
         idx = topk_idx.reshape(-1).long().contiguous()
         w = topk_w.reshape(-1).float().contiguous()
         n = T * topk
         ep = ctx.epoch.data_ptr()
         ctx.bump(_stream())
-        check(lib.qb_ep_publish(x.data_ptr(), ctx.own(0), x.numel() * 2, idx.data_ptr(), w.data_ptr(), Tl * topk, rank * Tl * topk,
+        # this rank's tokens, quantised once, straight into its peer-visible buffer: codes | scales | globals
+        off_sf = (Tl * (self.Hp // 2) + 255) // 256 * 256
+        off_g = off_sf + ((self.Hp // 128) * Tl * 4 + 255) // 256 * 256
+        assert off_g + Tl * 4 <= ctx.sizes[0]
+        self.quantize_tokens(x, out=(ctx.own(0), ctx.own(0, off_sf), ctx.own(0, off_g)))
+        check(lib.qb_ep_publish(0, 0, 0, idx.data_ptr(), w.data_ptr(), Tl * topk, rank * Tl * topk,
                                 ctx.ptrs(1), ctx.ptrs(1, ctx.off_w), W, rank, ctx.flag_ptrs(ctx.FLAG_PUBLISHED), ep, ctx.done.data_ptr(),
                                 _stream()), "qb_ep_publish")
         yield None
@@ -393,8 +414,8 @@ class SparseMoE:
                                            self.row_align, ctx.own(1, ctx.off_w), rw.data_ptr(), ctx.own(3), n_used.data_ptr(), _stream()),
               "qb_moe_route_fixed_range")
         d_out = ctx.own_tensor(2)[: r_cap * self.mpe_dn * 2].view(torch.bfloat16).view(r_cap, self.mpe_dn)
-        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), Tl, ctx.x_width, W), d_out=d_out, n_used=n_used,
-                         tile=self.row_align)
+        self._run_padded(None, src, eblk, r_cap, rw, peer_x=(ctx.ptrs(0), ctx.ptrs(0, off_sf), ctx.ptrs(0, off_g), Tl, W), d_out=d_out,
+                         n_used=n_used, tile=self.row_align)
         check(lib.qb_peer_signal(ctx.flag_ptrs(ctx.FLAG_OUTPUT), W, rank, 0, ep, _stream()), "qb_peer_signal")
         yield None
         check(lib.qb_peer_wait(ctx.flag_own(ctx.FLAG_OUTPUT), W, 0, ep, _stream()), "qb_peer_wait")
