@@ -596,6 +596,7 @@ struct KParams2 {
     uint8_t* h_sf_ref;
     int h_feats;
     int act;
+    int c_tma;                           // token-major bf16 output in this GPU's memory: the epilogue stores its tiles with TMA (tmC)
 };
 
 enum { SITE_SF = 5, SITE_SIDE = 6, SITE_MMA_SF = 7, SITE_SF_SLOT = 8 };
@@ -610,7 +611,8 @@ template <bool SPARSE, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(640, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                       const __grid_constant__ CUtensorMap tmMETA, const __grid_constant__ KParams2 p) {
+                       const __grid_constant__ CUtensorMap tmMETA, const __grid_constant__ CUtensorMap tmC,
+                       const __grid_constant__ KParams2 p) {
     using C = Cfg2<SPARSE, BN>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ volatile int abort_flag;
@@ -659,6 +661,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         fence_barrier_init();
         tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
         if (SPARSE) tma_prefetch_desc(&tmMETA);
+        if (p.c_tma) tma_prefetch_desc(&tmC);
     }
     if (warp == W_MMA) {
         tmem_alloc_pair(smem_u32(&tmem_base_slot), C::TM_COLS);
@@ -984,6 +987,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
                 for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(bh[e]); bias8[2 * e] = f.x; bias8[2 * e + 1] = f.y; }
             }
+            // the stmatrix epilogue's per-thread constants: its four features fr + 8m (TMEM lanes lane / 4 + 8m of the quadrant)
+            const int fr = o0 + q * 32 + (lane >> 2);
+            float ga4[4], bi4[4];
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                ga4[m] = p.gA ? __ldg(p.gA + a_base + fr + 8 * m) : 1.f;
+                bi4[m] = (p.out_mode == 3 && p.bias && fr + 8 * m < p.bias_ld)
+                             ? __bfloat162float(p.bias[(size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + fr + 8 * m]) : 0.f;
+            }
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
             tc_fence_after();
             const uint32_t t_acc = tmem_base + (uint32_t)(acc * BN + half * HCOLS) + ((uint32_t)(q * 32) << 16);
@@ -1130,24 +1142,26 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acce_leader);
-                const int fr = o0 + q * 32 + (lane >> 2);              // this thread's features: fr + 8m
-                float ga4[4], bi4[4];
-#pragma unroll
-                for (int m = 0; m < 4; m++) {
-                    ga4[m] = p.gA ? __ldg(p.gA + a_base + fr + 8 * m) : 1.f;
-                    bi4[m] = (p.out_mode == 3 && p.bias && fr + 8 * m < p.bias_ld)
-                                 ? __bfloat162float(p.bias[(size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + fr + 8 * m]) : 0.f;
-                }
-                const uint32_t sbuf = epi0 + ew * 2048;               // four 512-byte tiles per warp
+                const uint32_t sbuf = epi0 + ew * 2048;               // two sets of two 512-byte tiles per warp
                 const int st_i = lane & 7, rd_i = lane >> 2;
                 const uint32_t st_off = (uint32_t)(st_i * 64 + (((lane >> 3) ^ ((st_i >> 1) & 3)) * 16));
                 const uint32_t rd_off = (uint32_t)(rd_i * 64 + (((lane & 3) ^ ((rd_i >> 1) & 3)) * 16));
                 const int fcol = o0 + q * 32 + (lane & 3) * 8;          // first of the 8 features this lane stores
+                // Eight rounds of two groups (16 tokens), alternating between the two sets of staging tiles. With the TMA
+                // store one lane hands the 16 x 32 tile (1 KB, 64-byte rows in the 64-byte swizzle the stmatrix addresses
+                // follow) to the copy engine and the warp goes on with the next round; the set is written again two rounds
+                // later, after the store that read it has finished reading. Without it (peer destinations) every lane reads
+                // 16 bytes back and stores them itself.
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
+                for (int r = 0; r < 8; r++) {
+                    const uint32_t sset = sbuf + (uint32_t)(r & 1) * 1024;
+                    if (p.c_tma) {
+                        if (lane == 0) bulk_wait_read<1>();
+                        __syncwarp();
+                    }
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int j = jj * 4 + u, k = j & 7;
+                    for (int u = 0; u < 2; u++) {
+                        const int j = r * 2 + u, k = j & 7;
                         const uint32_t* lo = hf[j >> 3];
                         const uint32_t* hi = hf[2 + (j >> 3)];
                         const int sl = 8 * (j & 1) + 2 * (lane & 3);  // gbv[c] holds the global of column 16c + (lane & 15)
@@ -1171,25 +1185,34 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             }
                             pk[m] = pack_bf16x2(a, b);
                         }
-                        stmatrix_x4_trans(sbuf + u * 512 + st_off, pk[0], pk[1], pk[2], pk[3]);
+                        stmatrix_x4_trans(sset + u * 512 + st_off, pk[0], pk[1], pk[2], pk[3]);
                     }
-                    __syncwarp();
+                    if (p.c_tma) {
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmC, sset, (o0 + q * 32) * 2, n0 + 16 * r);
+                            bulk_commit();
+                        }
+                    } else {
+                        __syncwarp();
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int col = n0 + 8 * (jj * 4 + u) + rd_i;
-                        const uint4 val = lds_v4(sbuf + u * 512 + rd_off);
-                        if (col < p.tok) {
-                            if (p.peer_n) {
-                                // the partial row goes straight into the memory of the rank that owns the token (a plain
-                                // 16-byte store over NVLink, or a local one for this rank's own range)
-                                const int owner = col / p.tok_per_rank;
-                                stg_v4(p.peer_out[owner] + (size_t)(col - owner * p.tok_per_rank) * p.out_f + fcol, val);
-                            } else {
-                                stg_v4(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)col * p.out_f + fcol, val);
+                        for (int u = 0; u < 2; u++) {
+                            const int col = n0 + 8 * (r * 2 + u) + rd_i;
+                            const uint4 val = lds_v4(sset + u * 512 + rd_off);
+                            if (col < p.tok) {
+                                if (p.peer_n) {
+                                    // the partial row goes straight into the memory of the rank that owns the token (a plain
+                                    // 16-byte store over NVLink, or a local one for this rank's own range)
+                                    const int owner = col / p.tok_per_rank;
+                                    stg_v4(p.peer_out[owner] + (size_t)(col - owner * p.tok_per_rank) * p.out_f + fcol, val);
+                                } else {
+                                    stg_v4(reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)col * p.out_f + fcol, val);
+                                }
                             }
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 }
                 acc_phase ^= 1;
               } else {
@@ -1227,7 +1250,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
     }
 
-    // teardown: no CTA may leave while its partner can still signal its barriers
+    // teardown: no CTA may leave while its partner can still signal its barriers, nor while one of its TMA stores is in flight
+    if (p.c_tma && warp >= 8 && warp < 16 && lane == 0) bulk_wait<0>();
     tc_fence_before();
     cluster_sync_all();
     if (warp == W_MMA) {
@@ -1384,7 +1408,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     if (attr_rc) return attr_rc;
     const int kblocks = (a.K + 255) / 256;
     const int atoms_per_rb = kblocks * C::MMAS;
-    CUtensorMap tmA, tmB, tmSFA, tmSFB, tmMETA;
+    CUtensorMap tmA, tmB, tmSFA, tmSFB, tmMETA, tmC;
     int rc = a.a_tiled
                  ? make_map_u8(&tmA, a.A, (uint64_t)C::A_ROW, (uint64_t)a.a_rows * kblocks, C::A_ROW, 128,
                                SPARSE ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B)
@@ -1409,6 +1433,13 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     kp.peer_bpo = (a.peer_n && a.tok_per_rank % BN == 0 && kp.num_n == (a.tok_per_rank / BN) * a.peer_n) ? a.tok_per_rank / BN : 0;
     for (int r = 0; r < 8; r++) { kp.peer_out[r] = (__nv_bfloat16*)a.peer_out[r]; kp.peer_flags[r] = a.peer_flags[r]; }
     kp.h_bytes = (uint8_t*)a.h_bytes; kp.h_sf_atoms = (uint8_t*)a.h_sf_atoms; kp.h_sf_ref = (uint8_t*)a.h_sf_ref; kp.h_feats = a.h_feats; kp.act = a.act;
+    // token-major bf16 output of the one-accumulator tile into this GPU's own memory: 16-token x 32-feature boxes stored by TMA
+    kp.c_tma = 0;
+    tmC = tmA;
+    if (BN == 256 && (a.out_mode == 1 || a.out_mode == 3) && !a.peer_n && a.C && ((uintptr_t)a.C & 15) == 0 && a.out_f % 8 == 0) {
+        if ((rc = make_map_u8(&tmC, a.C, (uint64_t)a.out_f * 2, (uint64_t)a.tok, 64, 16, CU_TENSOR_MAP_SWIZZLE_64B))) return rc;
+        kp.c_tma = 1;
+    }
     int total = kp.num_m2 * kp.num_n;
     int nclusters = sm_count() / 2;
     if (total < nclusters) nclusters = total;
@@ -1422,7 +1453,7 @@ static int launch_pair(const GemmArgs& a, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<SPARSE, BN>, tmA, tmB, tmSFA, tmSFB, tmMETA, kp);
+    return (int)cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair_kernel<SPARSE, BN>, tmA, tmB, tmSFA, tmSFB, tmMETA, tmC, kp);
 }
 
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
