@@ -967,8 +967,10 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const int o0 = m2 * 256 + (int)rank * 128;     // first output feature of this CTA's half
             const int o = o0 + r_in_tile;
             const int a_base = p.eblk ? tile_expert(n) * p.out_f : 0;      // first row of this tile's expert in A / gA / bias
-            // per-tile constants first, so their latency hides behind the accumulator wait
-            const float ga = p.gA ? __ldg(p.gA + a_base + o) : 1.f;
+            // per-tile constants first, so their latency hides behind the accumulator wait; the two forms of the epilogue
+            // need different ones (stm: 16x256b loads + stmatrix; otherwise one feature per lane)
+            const bool stm = C::ACC_STAGES == 1 && (p.out_mode == 1 || p.out_mode == 3);
+            const float ga = (p.gA && !stm) ? __ldg(p.gA + a_base + o) : 1.f;
             float gbv[NCH], rwv[NCH];
 #pragma unroll
             for (int c = 0; c < NCH; c++) {
@@ -981,7 +983,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
             for (int e = 0; e < 8; e++) bias8[e] = 0.f;
             const int f8 = o0 + q * 32 + (lane & 3) * 8;       // bias rows hold bias_ld (a multiple of 8) valid features
-            if ((p.out_mode == 3 || p.out_mode == 4) && p.bias && f8 + 8 <= p.bias_ld) {
+            if (!stm && (p.out_mode == 3 || p.out_mode == 4) && p.bias && f8 + 8 <= p.bias_ld) {
                 const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + (size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + f8));
                 const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&bv);
 #pragma unroll
@@ -992,8 +994,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             float ga4[4], bi4[4];
 #pragma unroll
             for (int m = 0; m < 4; m++) {
-                ga4[m] = p.gA ? __ldg(p.gA + a_base + fr + 8 * m) : 1.f;
-                bi4[m] = (p.out_mode == 3 && p.bias && fr + 8 * m < p.bias_ld)
+                ga4[m] = (p.gA && stm) ? __ldg(p.gA + a_base + fr + 8 * m) : 1.f;
+                bi4[m] = (stm && p.out_mode == 3 && p.bias && fr + 8 * m < p.bias_ld)
                              ? __bfloat162float(p.bias[(size_t)(p.eblk ? tile_expert(n) : 0) * p.bias_ld + fr + 8 * m]) : 0.f;
             }
             if (!mbar_wait(accf_bar(acc), acc_phase, &abort_flag, &g_status, SITE_EPI, QB_BACKOFF)) break;
@@ -1125,7 +1127,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 }
             };
             if constexpr (C::ACC_STAGES == 1) {
-              if (p.out_mode == 1 || p.out_mode == 3) {
+              if (stm) {
                 // Token-major bf16 output of the one-accumulator tile. The slice is read in the 16x256b shape: a thread then
                 // holds, for every group of 8 tokens, two adjacent tokens of four features (lanes t/4 + 8m), which is the
                 // fragment layout stmatrix stores transposed. Scale, round to bf16, store the four 8x8 matrices of a group
