@@ -409,3 +409,86 @@ def test_route_fixed_kernel_matches_torch_routing_up_to_row_order():
         assert torch.equal(pos[src[valid]], torch.nonzero(valid).squeeze(1))
         assert torch.equal(assign[src[valid]].int(), eblk[torch.nonzero(valid).squeeze(1) // 128])
         assert int(valid.sum()) == n and lib.qb_status(0) == 0
+
+
+def test_route_fixed_range_with_segments_padded_to_256():
+    """qb_moe_route_fixed_range(align = 256): every expert's segment is a multiple of 256 rows, the two 128-row blocks of
+    a 256-row tile carry the same expert, the slot -> row table and the count of rows in use agree with the segments,
+    slots of experts outside [e_base, e_base + e) get no row."""
+    import quadbit_b200 as qb
+    import quadbit_b200.moe as qmoe
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(31)
+    dev = "cuda"
+    for n, e_total, e_base, e in ((7, 4, 0, 4), (4096, 16, 4, 8), (32768, 128, 0, 128), (9000, 64, 48, 16)):
+        assign = torch.randint(0, e_total, (n,), device=dev)
+        w_in = torch.rand(n, device=dev)
+        r_cap = qmoe.fixed_capacity(n, e, 256)
+        src = torch.empty(r_cap, dtype=torch.long, device=dev)
+        pos = torch.empty(n, dtype=torch.long, device=dev)
+        eblk = torch.empty(r_cap // 128, dtype=torch.int32, device=dev)
+        rw = torch.empty(r_cap, dtype=torch.float32, device=dev)
+        inverse = torch.empty(n, dtype=torch.int32, device=dev)
+        n_used = torch.zeros(1, dtype=torch.int32, device=dev)
+        assert lib.qb_moe_route_fixed_range(assign.data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, e_base, e, r_cap, 1, 256,
+                                            w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(), n_used.data_ptr(), S()) == 0
+        torch.cuda.synchronize()
+        local = (assign >= e_base) & (assign < e_base + e)
+        counts = torch.bincount((assign[local] - e_base), minlength=e)
+        padded = (counts + 255) // 256 * 256
+        assert int(n_used.item()) == int(padded.sum())
+        want_eblk = torch.repeat_interleave(torch.arange(e, device=dev, dtype=torch.int32), (padded // 128))
+        used_blocks = int(padded.sum()) // 128
+        assert torch.equal(eblk[:used_blocks], want_eblk) and bool((eblk[used_blocks:] == -1).all())
+        assert torch.equal(eblk[0::2], eblk[1::2])
+        assert bool((pos[~local] == -1).all()) and torch.equal(pos.int(), inverse)
+        rows = pos[local]
+        assert rows.unique().numel() == rows.numel()                          # every local slot has a row of its own
+        assert torch.equal(src[rows], torch.nonzero(local).squeeze(1))       # ... which points back at the slot
+        assert torch.equal(eblk[rows // 128].long(), assign[local] - e_base)   # ... inside its expert's segment
+        assert torch.equal(rw[rows], w_in[local])
+        mask = torch.ones(r_cap, dtype=torch.bool, device=dev)
+        mask[rows] = False
+        assert bool((src[mask] == -1).all()) and bool((rw[mask] == 0).all())    # padding and unused capacity
+        assert lib.qb_status(0) == 0
+
+
+def test_dispatch_of_quantised_rows_equals_gather_then_quantise():
+    """qb_quantize_rows + qb_gather_quantized (every token quantised once, routed slots copy the packed row) must give the
+    routed batch of qb_gather_quantize_act_peer (gather of bf16 rows fused into their quantiser) bit for bit, with the
+    rows split over two source buffers as in an expert-parallel layer."""
+    import quadbit_b200 as qb
+    from quadbit_b200.tp import ptr_array
+    lib = qb.load("sparse_fp4")
+    torch.manual_seed(33)
+    dev = "cuda"
+    for T, H, K, R in ((64, 256, 256, 300), (1000, 2880, 2944, 4096)):
+        x = (torch.randn(T, H, device=dev) * 2).to(torch.bfloat16)
+        x[3] = 0                                                              # an all-zero token
+        src = torch.randint(0, T, (R,), device=dev)
+        src[torch.rand(R, device=dev) < 0.2] = -1                            # padding rows
+        half = T // 2
+        xs = [x[:half].contiguous(), x[half:].contiguous()]
+        # reference: gather + quantise of every routed row
+        Bb0 = torch.zeros(R, K // 2, dtype=torch.uint8, device=dev)
+        sf0 = torch.zeros(lib.qb_sf_atoms_bytes(R, K, 32), dtype=torch.uint8, device=dev)
+        g0 = torch.zeros(R, dtype=torch.float32, device=dev)
+        assert lib.qb_gather_quantize_act_peer(ptr_array([t.data_ptr() for t in xs]), 2, half, src.data_ptr(), Bb0.data_ptr(), sf0.data_ptr(),
+                                               g0.data_ptr(), R, K, H, 32, 0, S()) == 0
+        # tokens quantised once per buffer, then the packed rows are copied
+        q = []
+        for t in xs:
+            Bq = torch.empty(half, K // 2, dtype=torch.uint8, device=dev)
+            sq = torch.empty(K // 128, half, 4, dtype=torch.uint8, device=dev)
+            gq = torch.empty(half, dtype=torch.float32, device=dev)
+            assert lib.qb_quantize_rows(t.data_ptr(), Bq.data_ptr(), sq.data_ptr(), gq.data_ptr(), half, K, H, 32, S()) == 0
+            q.append((Bq, sq, gq))
+        Bb1 = torch.zeros_like(Bb0)
+        sf1 = torch.zeros_like(sf0)
+        g1 = torch.zeros_like(g0)
+        assert lib.qb_gather_quantized(ptr_array([a[0].data_ptr() for a in q]), ptr_array([a[1].data_ptr() for a in q]),
+                                       ptr_array([a[2].data_ptr() for a in q]), 2, half, src.data_ptr(), Bb1.data_ptr(), sf1.data_ptr(),
+                                       g1.data_ptr(), R, K, 0, S()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(Bb0, Bb1) and torch.equal(sf0, sf1) and torch.equal(g0, g1)
+        assert lib.qb_status(0) == 0
