@@ -231,6 +231,12 @@ class SparseMoE:
         # tile instead of two (and 257..384 two instead of three); the padding rows cost the quantisers next to nothing.
         self.row_align = 256
 
+    def _side_stream(self, dev):
+        st = getattr(self, "_side", None)
+        if st is None or st.device != torch.device(dev):
+            st = self._side = torch.cuda.Stream(device=dev)
+        return st
+
     def quantize_tokens(self, x: torch.Tensor, out=None):
         """x [T, H] bf16 -> (codes [T, Hp/2] u8, scales [Hp/128, T, 4] u8, globals [T] f32): the layer's input quantiser
         (two-level, per-32), hidden size zero-padded to Hp. `out`: optional (codes ptr, scales ptr, globals ptr) to write to."""
@@ -251,7 +257,7 @@ class SparseMoE:
         return Bq, sq, gq
 
     def _run_padded(self, x, src: torch.Tensor, eblk: torch.Tensor, r_pad: int, rw: torch.Tensor, peer_x=None, d_out=None,
-                    n_used=None, tile: int = 128) -> torch.Tensor:
+                    n_used=None, tile: int = 128, xq=None) -> torch.Tensor:
         """The four kernels of the layer on a routed, padded batch: src [r_pad] = row of x for every padded row (-1 =
         padding), eblk = expert of every 128-row block, rw [r_pad] = routing weight of every row. Returns
         d [r_pad, mpe_dn] bf16 = expert(row) * weight."""
@@ -270,7 +276,7 @@ class SparseMoE:
         else:
             from .tp import ptr_array
             rows_per_rank, nr = max(x.shape[0], 1), 1
-            Bq, sq, gq = self.quantize_tokens(x)
+            Bq, sq, gq = xq if xq is not None else self.quantize_tokens(x)       # xq: quantised by the caller (beside the routing)
             qc, qs, qg = ptr_array([Bq.data_ptr()]), ptr_array([sq.data_ptr()]), ptr_array([gq.data_ptr()])
         check(lib.qb_gather_quantized(qc, qs, qg, nr, rows_per_rank, src.data_ptr(), Bb.data_ptr(), sfb.data_ptr(), gB.data_ptr(), r_pad,
                                       self.Hp, nu, _stream()), "qb_gather_quantized")
@@ -328,6 +334,15 @@ class SparseMoE:
             # routing, token row of every padded row, routing weight of every row and the combine table in one launch
             n, e = assign_g.numel(), self.E
             al = self.row_align
+            # the token quantiser does not depend on the routing: it runs on a second stream beside the routing kernel
+            # (fork / join with events, which a CUDA-graph capture records as parallel branches)
+            main = torch.cuda.current_stream()
+            side = self._side_stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                xq = self.quantize_tokens(x)
+            for t in xq:
+                t.record_stream(main)
             r_cap = fixed_capacity(n, e, al)
             src = torch.empty((r_cap,), dtype=torch.long, device=dev)
             pos = torch.empty((n,), dtype=torch.long, device=dev)
@@ -339,7 +354,8 @@ class SparseMoE:
             check(self.lib.qb_moe_route_fixed_range(assign_g.contiguous().data_ptr(), src.data_ptr(), pos.data_ptr(), eblk.data_ptr(), n, 0, e,
                                                     r_cap, self.topk, al, w_in.data_ptr(), rw.data_ptr(), inverse.data_ptr(),
                                                     n_used.data_ptr(), _stream()), "qb_moe_route_fixed_range")
-            d = self._run_padded(x, src, eblk, r_cap, rw, n_used=n_used, tile=al)
+            main.wait_stream(side)
+            d = self._run_padded(x, src, eblk, r_cap, rw, n_used=n_used, tile=al, xq=xq)
             return combine(self.lib, d, inverse, T, self.H, self.topk)
         if self.e0 == 0 and self.e1 == self.E_total:
             slots = torch.arange(assign_g.numel(), device=dev)
