@@ -419,3 +419,26 @@ def test_prefill_set_at_full_size(lib, name, out_f, K):
     assert bool(same_rows.all()), (name, int((~same_rows).sum()), ties)
     assert torch.equal(lin.meta[:, :256].cpu(), emeta) and torch.equal(lin.scaleA[:, :256].cpu(), escale)
     assert torch.equal(lin.gA[:256].cpu(), egA)
+
+
+@pytest.mark.parametrize("sparse", [1, 0])
+def test_pair_kernel_output_inside_a_larger_buffer(lib, sparse):
+    """The 256-token tile stores its token-major output with TMA (16-token x 32-feature boxes, clipped at the ragged end):
+    an output that starts 16 or 48 bytes into a larger buffer must get the same bytes as a fresh output, and nothing may be
+    written outside it."""
+    out_f, tok, K = 512, 600, 1024
+    torch.manual_seed(5)
+    W = torch.randn(out_f, K) * 0.02
+    x = torch.randn(tok, K)
+    ops = native_operands(W, x, sparse)
+    ref = gemm(lib, ops, out_f, tok, K, sparse, 1, bn=512)
+    p = lambda t: 0 if t is None else t.data_ptr()
+    buf = torch.full((tok * out_f + 64,), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for off in (8, 24):                                  # elements: 16 and 48 bytes into the buffer
+        buf.fill_(float("nan"))
+        C = buf[off: off + tok * out_f].view(tok, out_f)
+        rc = lib.qb_gemm(p(ops["A"]), p(ops["B"]), p(ops["sfa"]), p(ops["sfb"]), p(ops["meta"]), p(ops["gA"]), p(ops["gB"]), C.data_ptr(),
+                         0, 0, 0, 0, out_f, out_f, tok, K, int(sparse), 1, 1, 512, S())
+        assert rc == 0 and lib.qb_status(S()) == 0
+        assert torch.equal(C, ref)
+        assert bool(torch.isnan(buf[:off]).all()) and bool(torch.isnan(buf[off + tok * out_f:]).all())    # nothing written outside
