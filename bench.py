@@ -541,6 +541,40 @@ def run_gpu(args):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / iters * 1e-3
 
+    # ---- optional comparator, not a reference number and not this library's code: FlashInfer's dense NVFP4 mm_fp4 (per-tensor
+    #      global scale, library kernels) on the prefill shapes, with the protocol of the reference's dense leaderboard
+    #      (harness/leaderboard_fp4.py:136-170). The first call of a backend may compile for a minute.
+    if args.only == "flashinfer":
+        try:
+            from flashinfer import SfLayout, mm_fp4, nvfp4_quantize
+        except Exception as e:
+            print(json.dumps({"comparator": "flashinfer mm_fp4", "unavailable": f"{type(e).__name__}: {e}"[:200]}), flush=True)
+            return
+        res = {}
+        for tag, M, N, K in (("qkv", 4096, 6144, 4096), ("o_proj", 4096, 4096, 4096), ("gate", 4096, 14336, 4096), ("down", 4096, 4096, 14336),
+                             ("sq8192", 8192, 8192, 8192)):
+            torch.manual_seed(0)
+            A = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            B = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+            gsa, gsb = (448 * 6) / A.float().abs().max(), (448 * 6) / B.float().abs().max()
+            a_fp4, a_s = nvfp4_quantize(A, gsa, sfLayout=SfLayout.layout_128x4, do_shuffle=False)
+            b_fp4, b_s = nvfp4_quantize(B, gsb, sfLayout=SfLayout.layout_128x4, do_shuffle=False)
+            alpha = 1.0 / (gsa * gsb)
+            for bk in ("cutlass", "cudnn", "trtllm"):
+                out = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+                f = lambda: mm_fp4(a_fp4, b_fp4.T, a_s, b_s.T, alpha, torch.bfloat16, out, block_size=16, use_8x4_sf_layout=False,
+                                   backend=bk, use_nvfp4=True)
+                try:
+                    f()
+                    torch.cuda.synchronize()
+                    t = ev_time(f, 20, 5)
+                    res[f"{tag}_{bk}"] = {"us": t * 1e6, "tflops": 2.0 * M * N * K / t / 1e12}
+                except Exception as e:  # a backend that does not run here is a result too
+                    res[f"{tag}_{bk}"] = {"unavailable": f"{type(e).__name__}: {e}"[:120]}
+        print(json.dumps({"comparator": "flashinfer mm_fp4, dense NVFP4, bf16 out (library kernels; back-to-back calls from Python, so "
+                                        "short kernels include its host overhead)", "results": res}), flush=True)
+        return
+
     # ---- profiling aids: one small workload of a side kernel, timed with CUDA events, nothing else
     if args.only in ("quant", "decode", "swiglu", "gatherq"):
         if args.only == "swiglu":
@@ -1054,7 +1088,8 @@ def main():
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
                     "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'swiglu' / 'gatherq' time one small workload of "
-                    "the activation quantiser / the thin-token GEMM / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead")
+                    "the activation quantiser / the thin-token GEMM / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead; "
+                    "'flashinfer' runs the optional library comparator (FlashInfer mm_fp4, dense NVFP4) on the prefill shapes")
     ap.add_argument("--dp", action="store_true", help="with --gpus N > 1: replicas (tokens sharded, weights replicated, no exchange, weak "
                     "scaling) instead of the default tensor-parallel sharding")
     ap.add_argument("--tp-comm", default="both", choices=["peer", "nccl", "both"], help="tensor-parallel exchange: peer stores from the "
