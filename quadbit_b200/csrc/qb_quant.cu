@@ -212,20 +212,20 @@ __device__ __forceinline__ void swiglu_quant_row(const int row, const uint4* __r
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             const uint4 gv = gq[k], uv = uq[k];
-            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
-            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uv);
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float a, c;
                 if (INTERLEAVED) {
-                    const float2 p0 = __bfloat1622float2(gh[i]), p1 = __bfloat1622float2(uh[i]);
-                    a = swiglu_h<ACT>(p0.x, p0.y);
-                    c = swiglu_h<ACT>(p1.x, p1.y);
-                    h[j][8 * k + i] = a; h[j][8 * k + 4 + i] = c;
+                    if ((i & 1) == 0) {     // words 2i', 2i'+1 of the first half: pairs (g, u) of two neighbouring features
+                        swiglu_h2_pairs<ACT>(gw[i], gw[i + 1], a, c);
+                        h[j][8 * k + i] = a; h[j][8 * k + i + 1] = c;
+                    } else {
+                        swiglu_h2_pairs<ACT>(uw[i - 1], uw[i], a, c);
+                        h[j][8 * k + 4 + i - 1] = a; h[j][8 * k + 4 + i] = c;
+                    }
                 } else {
-                    const float2 g2 = __bfloat1622float2(gh[i]), u2 = __bfloat1622float2(uh[i]);
-                    a = swiglu_h<ACT>(g2.x, u2.x);
-                    c = swiglu_h<ACT>(g2.y, u2.y);
+                    swiglu_h2_split<ACT>(gw[i], uw[i], a, c);
                     h[j][8 * k + 2 * i] = a; h[j][8 * k + 2 * i + 1] = c;
                 }
                 m = fmaxf(m, fmaxf(fabsf(a), fabsf(c)));
