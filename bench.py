@@ -937,9 +937,47 @@ def run_gpu(args):
         fl_moe = 2.0 * 8192 * topk * (2 * Hh * Hh + Hh * Hh)           # useful flops: unpadded dims, routed rows only
         line["moe_grouped"] = {"routed_rows": 8192 * topk, "padded_rows": r_pad, "gate_up_us": t_gu * 1e6, "down_us": t_dn * 1e6,
                                "eff_tflops": fl_moe / (t_gu + t_dn) / 1e12,
-                               "what": "quantise + grouped GEMM (CTA-pair kernel, one expert per 128-token tile) for gate/up and for down with the "
-                                       "routing weight in the epilogue; SwiGLU, gather and combine not included"}
-        del w_gu, w_dn, rows, hrows
+                               "what": "module-level pieces: quantise every padded row + grouped GEMM (one expert per 128-token tile) for gate/up "
+                                       "and for down with the routing weight in the epilogue; SwiGLU, gather and combine not included. The layer "
+                                       "as SparseMoE runs it (256-token tiles, tokens quantised once) is `moe_layer`"}
+        del w_gu, w_dn, rows, hrows, g0, d0
+
+        # ---- the whole MoE layer of configs[4] on one GPU: routing, token quantiser, dispatch of packed rows, grouped gate/up
+        #      GEMM, SwiGLU + quantiser, grouped down GEMM, combine; fixed-capacity routing (no host read), one CUDA graph replay
+        Tm = 8192
+        genm = torch.Generator(device=dev).manual_seed(3)
+        wgu_l = [(torch.randn(2 * Hh, Hh, device=dev, generator=genm) * 0.02).to(torch.bfloat16) for _ in range(E)]
+        wdn_l = [(torch.randn(Hh, Hh, device=dev, generator=genm) * 0.02).to(torch.bfloat16) for _ in range(E)]
+        moe_l = qb.SparseMoE(wgu_l, wdn_l, topk, act="gptoss", fixed_capacity=True)
+        del wgu_l, wdn_l
+        gm = torch.Generator(device="cpu").manual_seed(3)
+        x_m = torch.randn(Tm, Hh, generator=gm).to(torch.bfloat16).to(dev)
+        tw_m, ti_m = torch.softmax(torch.randn(Tm, E, generator=gm), -1).topk(topk, dim=-1)
+        tw_m = (tw_m / tw_m.sum(-1, keepdim=True)).to(dev)
+        ti_m = ti_m.to(dev)
+        side_m = torch.cuda.Stream()
+        side_m.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side_m):
+            for _ in range(3):
+                moe_l.forward(x_m, ti_m, tw_m)
+        torch.cuda.current_stream().wait_stream(side_m)
+        cg_m = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg_m):
+            y_m = moe_l.forward(x_m, ti_m, tw_m)
+        for _ in range(3):
+            cg_m.replay()
+        t_moe = ev_time(cg_m.replay, 20, 3)
+        w_bytes = E * (2 * Hp * Hp + Hq * Hp) * (1 / 4 + 1 / 16 + 1 / 32)      # packed codes + metadata + block scales of every expert
+        line["moe_layer"] = {"ms_per_step": t_moe * 1e3, "tokens_per_s": Tm / t_moe, "useful_tflops": fl_moe / t_moe / 1e12,
+                             "frac_weight_streaming": w_bytes / t_moe / 1e9 / hbm_gbs,
+                             "frac_tensor": fl_moe / t_moe / 1e12 / (bf16_burst * 8),
+                             "weight_bytes": w_bytes, "tokens": Tm,
+                             "what": "SparseMoE.forward (gpt-oss-120b-shaped: hidden 2880, 128 experts, top-4, 8192 tokens, seed 3) with "
+                                     "fixed-capacity routing, replayed from one CUDA graph; fractions: packed expert weights read once / time "
+                                     "against measured HBM, useful flops (unpadded dims, routed rows) / time against 8 x measured bf16"}
+        if lib.qb_status(0):
+            raise RuntimeError("device status after the MoE layer")
+        del moe_l, cg_m, y_m
 
         # ---- what one rank of the tensor-parallel step computes, kernel by kernel on this GPU (no exchange: slots are local):
         #      the compute-side floor of `bench.py --gpus W`, to set beside its measured step time and its NVLink floor
