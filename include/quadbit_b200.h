@@ -219,6 +219,13 @@ long long qb_tiled_weight_bytes(int rows, int K, int sparse);
 int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sfb, const void* meta_native, const void* gA,
                    const void* gB, void* C, void* ws, int out, int tok, int K, int sparse, int out_mode, void* stream);
 long long qb_gemm_decode_ws_bytes(int out, int tok, int K);
+/* One- or two-token linear layer on the dense two-level NVFP4 weight in ONE launch: the activation quantiser
+ * (quantize_act_nvfp4_2lvl, per 16, bit-identical codes and scales) and the matrix-vector product, on the CUDA cores: f16
+ * products and block sums of E2M1 code values are exact, block sums are scaled and accumulated in fp32 in a fixed order.
+ * Counterpart of the reference's dense decode GEMV (cuda/dense_decode_lib.cu:19-141), which also runs beside its
+ * tensor-core kernels for single tokens. x [tok][K] bf16 (tok <= 2), A_tiled / sfa / gA: the weight as qb_pack_dense +
+ * qb_tile_weights leave it, C [tok][out] bf16. out % 128 == 0, K % 128 == 0, K <= 16384; no workspace. */
+int qb_linear_gemv(const void* x, const void* A_tiled, const void* sfa, const void* gA, void* C, int out, int tok, int K, void* stream);
 /* Split-K GEMM without a caller workspace (no counterpart in the reference library, whose
  * split-K entry sparse_down_sk_2lvl always takes the workspace Cf from the caller). Same
  * operands and meaning as qb_gemm with splits > 1, out_mode 0 or 1, plain (not grouped) mode

@@ -64,6 +64,7 @@ _SIGS = {
     "qb_tile_weights": ([P] * 2 + [I] * 3 + [P], I),
     "qb_tiled_weight_bytes": ([I] * 3, c_longlong),
     "qb_gemm_decode_ws_bytes": ([I] * 3, c_longlong),
+    "qb_linear_gemv": ([P] * 5 + [I] * 3 + [P], I),
     "qb_gemm_splitk_static": ([P] * 8 + [I] * 6 + [P], I),
     "qb_gemm_splitk_static_max_elems": ([], c_longlong),
     "qb_peer_alloc": ([P, c_longlong], I),

@@ -25,7 +25,7 @@ from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
-SOURCES = ["qb_abi.cu", "qb_quant.cu", "qb_compress.cu", "qb_gemm.cu", "qb_moe.cu", "qb_noalloc.cu", "qb_peak.cu", "qb_peer.cu", "qb_glue.cu", "qb_ep.cu"]
+SOURCES = ["qb_abi.cu", "qb_quant.cu", "qb_compress.cu", "qb_gemm.cu", "qb_moe.cu", "qb_noalloc.cu", "qb_peak.cu", "qb_peer.cu", "qb_glue.cu", "qb_ep.cu", "qb_gemv.cu"]
 HEADERS = ["qb_common.cuh", "qb_internal.h"]
 FLAVOURS = {"sparse_fp4": [], "dense_nvfp4": ["-DQB_FLAVOUR_DENSE"]}
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC"]

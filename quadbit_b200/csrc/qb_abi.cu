@@ -287,6 +287,9 @@ int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sf
     g.out_mode = out_mode; g.splits = splits; g.bn = bn;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
+int qb_linear_gemv(const void* x, const void* A_tiled, const void* sfa, const void* gA, void* C, int out, int tok, int K, void* stream) {
+    return qb::linear_gemv_dense(x, A_tiled, sfa, gA, C, out, tok, K, (cudaStream_t)stream);
+}
 int qb_tile_weights(const void* A, void* A_tiled, int rows, int K, int sparse, void* stream) {
     return qb::tile_weights(A, A_tiled, rows, K, sparse, (cudaStream_t)stream);
 }

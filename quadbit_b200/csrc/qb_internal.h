@@ -55,6 +55,8 @@ struct ReduceNormArgs {
 };
 int reduce_norm_quant(const ReduceNormArgs& a, cudaStream_t st);
 int quant_status_read_clear();
+// ---- qb_gemv.cu: quantiser + matrix-vector product for one or two tokens on the dense weight (tiled layout)
+int linear_gemv_dense(const void* x, const void* At, const void* sfa, const void* gA, void* C, int out_f, int tok, int K, cudaStream_t st);
 // SwiGLU quantiser over feature-major g, u [hidden][batch]; gH null = single level
 int swiglu_quant_feature_major(const void* g, const void* u, void* Hb, void* scaleH, void* gH, int batch, int hidden, cudaStream_t st);
 int relayout_sf(const void* ref, void* atoms, int rows, int K, int block, cudaStream_t st);

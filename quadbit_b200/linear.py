@@ -45,6 +45,7 @@ def quantize_act(lib, x: torch.Tensor, block: int, two_level: bool = True, want_
 
 
 DECODE_MAX_TOK = 256
+GEMV_MAX_TOK = 2            # tokens up to which the dense layer runs quantiser + matrix-vector product as one CUDA-core launch
 
 
 def tile_weights(lib, A: torch.Tensor, rows: int, K: int, sparse: int) -> torch.Tensor:
@@ -194,8 +195,15 @@ class DenseNVLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor, splits: int = 1, bn: int = 0) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.inn)
-        Bb, sfb, gB = quantize_act(self.lib, x2, 16, True)
         tok = x2.shape[0]
+        if 0 < tok <= GEMV_MAX_TOK and splits == 1 and bn == 0 and self.inn <= 16384:
+            # one or two tokens: quantiser and matrix-vector product in one launch
+            xb = x2.to(torch.bfloat16).contiguous()
+            C = torch.empty((tok, self.out), dtype=torch.bfloat16, device=x.device)
+            check(self.lib.qb_linear_gemv(xb.data_ptr(), self.At.data_ptr(), self.sfa.data_ptr(), self.gA.data_ptr(), C.data_ptr(),
+                                          self.out, tok, self.inn, _stream()), "qb_linear_gemv")
+            return C.reshape(*lead, self.out).to(x.dtype)
+        Bb, sfb, gB = quantize_act(self.lib, x2, 16, True)
         if tok <= DECODE_MAX_TOK and splits == 1 and bn == 0:
             return self.run_decode(Bb, sfb, tok, gB).reshape(*lead, self.out).to(x.dtype)
         return self.run(Bb, sfb, tok, gB, out_t=True, splits=splits, bn=bn).reshape(*lead, self.out).to(x.dtype)
