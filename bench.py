@@ -891,12 +891,15 @@ def run_gpu(args):
                             mode = f"eager ({type(e).__name__})"
                     algo = wbytes + 2 * m_tok * k + 2 * m_tok * n
                     out[f"N{n}_K{k}_M{m_tok}"] = {"us": tl * 1e6, "gbs": algo / tl / 1e9, "frac_of_measured_hbm": algo / tl / 1e9 / hbm_gbs,
-                                                 "timing": mode, "what": "quantise + GEMM per linear (two launches)"}
+                                                 "timing": mode,
+                                                 "what": ("quantiser + matrix-vector product in one CUDA-core launch (qb_linear_gemv)"
+                                                          if getattr(mods[0], "block", 32) == 16 and (m_tok == 1 or (m_tok == 2 and n * k <= 32 * 1024 * 1024))
+                                                          else "quantise + GEMM per linear (two launches)")}
                 del mods
             return out
 
         line["decode_dense"] = decode_sweep(lambda W: qb.DenseNVLinear(W, keep_ref_layout=False),
-                                            lambda n, k: n * k / 2 + n * k / 16 + 4 * n, (1, 16, 64, 128, 256))
+                                            lambda n, k: n * k / 2 + n * k / 16 + 4 * n, (1, 2, 16, 64, 128, 256))
         line["decode_sparse"] = decode_sweep(lambda W: qb.QuadbitLinear(W, keep_ref_layout=False),
                                              lambda n, k: n * k / 4 + n * k / 16 + n * k / 32 + 4 * n, (64, 128, 256))
 

@@ -79,12 +79,15 @@ nvfp4_gemv_kernel(const uint4* __restrict__ At, const uint8_t* __restrict__ sfa,
     const int t_begin = warp * per, t_end = min(T, t_begin + per);
     const int apr = kblocks * 4;                                                   // scale atoms per 128-row block (per-16 scales)
 
+    // item t = (K group g, i-th chunk of the CTA), walked without divisions: (lg, li) belong to the item that is loaded next
+    int lg = nch > 0 ? t_begin / nch : 0, li = nch > 0 ? t_begin - lg * nch : 0;
     auto load_item = [&](int t, GemvItem& it) {
 #pragma unroll
         for (int k = 0; k < 4; k++) it.w[k] = make_uint4(0, 0, 0, 0);
         it.s = make_uint4(0, 0, 0, 0);
         if (t >= t_end) return;
-        const int g = t / nch, c = (int)blockIdx.x + (t - g * nch) * (int)gridDim.x;
+        const int g = lg, c = (int)blockIdx.x + li * (int)gridDim.x;
+        if (++li == nch) { li = 0; lg++; }
         const int kb = g * 4 + kq;
         if (kb >= kblocks) return;
         const int tile = c >> 5, r0 = c & 31;
@@ -94,6 +97,7 @@ nvfp4_gemv_kernel(const uint4* __restrict__ At, const uint8_t* __restrict__ sfa,
         it.s = __ldg(reinterpret_cast<const uint4*>(sfa + ((size_t)tile * apr + kb * 4 + (sub >> 1)) * 512 + (size_t)r0 * 16));
     };
     GemvItem cur;
+    int cg = lg, ci = li;                                // (K group, chunk) of the item in `cur`
     load_item(t_begin, cur);                             // weights are constants: requested before the activations are touched
 
     griddep_wait();
@@ -153,8 +157,9 @@ nvfp4_gemv_kernel(const uint4* __restrict__ At, const uint8_t* __restrict__ sfa,
     int g_have = -1;
     for (int t = t_begin; t < t_end; t++) {
         GemvItem nxt;
-        load_item(t + 1, nxt);
-        const int g = t / nch;
+        load_item(t + 1, nxt);                           // in flight while item t is processed
+        const int g = cg;
+        if (++ci == nch) { ci = 0; cg++; }
         const int kb = g * 4 + kq;
         if (g != g_have) {
             g_have = g;

@@ -45,9 +45,9 @@ def test_gemv_against_oracle_and_tensor_core_path(lib, out_f, K, tok):
     assert lib.qb_status(S()) == 0
     d = (C.float() - Cd.float()).abs() / (Cd.float().abs() + 1.0)
     assert d.max().item() < 6e-3
-    # and forward() takes this path
-    y = lin.forward(xd)
-    assert torch.equal(y, C)
+    # and forward() takes this path for one token (for two only while the weight is small)
+    if tok == 1 or out_f * K <= 32 * 1024 * 1024:
+        assert torch.equal(lin.forward(xd), C)
 
 
 def test_gemv_block_sums_are_exact(lib):
