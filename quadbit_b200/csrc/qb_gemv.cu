@@ -8,17 +8,18 @@
 //   * every CTA quantises the token rows itself (K <= 16384 values each, bit-identical to quant_act_kernel: per-token
 //     global amax / 2688, UE4M3 scale per 16, E2M1 codes from the IEEE quotient) and keeps the CODE VALUES as f16 and the
 //     decoded block scales as f32 in shared memory;
-//   * a warp streams 4 weight rows at a time from the tiled layout (8 lanes per row, one 16-byte load = 32 weights = two
-//     scale blocks per lane; the 4 rows of a unit are 512 contiguous bytes), eight K blocks in flight per lane and the
-//     next eight prefetched, so that every SM keeps ~64 KB of loads in flight;
+//   * a warp works on items of 4 weight rows x 4 K blocks (lane = 32 weights of one K block = two scale blocks; the
+//     rows of an item are 32 apart, so that their scale pairs share one 16-byte piece of a scale atom), the next item's
+//     five 16-byte loads in flight while the current one is processed, and the activation slice of the K group stays in
+//     registers while the rows stream by;
 //   * `cvt.rn.f16x2.e2m1x2` turns a weight byte into two f16 values, `fma.rn.f16x2` multiplies them with the activation
 //     code values and sums 8 products per half: all of these are multiples of 1/4 below 512, so the f16 sums are EXACT;
 //     the two halves are added in fp32 and scaled by (weight scale x activation scale), accumulated in fp32 over the blocks,
 //     and the row result is multiplied by the two globals: the arithmetic of the block-scaled tensor-core instruction with
 //     fp32 accumulation in a fixed order.
-// Work is dealt to warps in units of 4 rows, unit u to CTA u % gridDim.x, so every SM streams the same number of bytes.
-// The weight side of the first eight K blocks is requested before griddepcontrol.wait (weights are constants), the
-// activations after it.
+// Chunks of 4 rows are dealt to CTAs round-robin (every SM streams the same number of bytes), a CTA's (K group, chunk)
+// items to its warps in equal contiguous ranges; the partial sums of the K groups meet in shared memory. The first item
+// is requested before griddepcontrol.wait (weights are constants), the activations after it.
 #include "qb_common.cuh"
 #include "qb_internal.h"
 #include "../../include/quadbit_b200.h"
@@ -75,8 +76,7 @@ nvfp4_gemv_kernel(const uint4* __restrict__ At, const uint8_t* __restrict__ sfa,
     const int nch = (chunks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // chunks of this CTA: blockIdx.x + i * gridDim.x
     const int G = (kblocks + 3) >> 2;
     const int T = G * nch;                                                         // items of this CTA, K group major
-    const int per = (T + GEMV_WARPS - 1) / GEMV_WARPS;
-    const int t_begin = warp * per, t_end = min(T, t_begin + per);
+    const int t_begin = (int)((long long)warp * T / GEMV_WARPS), t_end = (int)((long long)(warp + 1) * T / GEMV_WARPS);   // sizes differ by at most one
     const int apr = kblocks * 4;                                                   // scale atoms per 128-row block (per-16 scales)
 
     // item t = (K group g, i-th chunk of the CTA), walked without divisions: (lg, li) belong to the item that is loaded next
