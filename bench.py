@@ -576,7 +576,7 @@ def run_gpu(args):
         return
 
     # ---- profiling aids: one small workload of a side kernel, timed with CUDA events, nothing else
-    if args.only in ("quant", "decode", "swiglu", "gatherq"):
+    if args.only in ("quant", "decode", "swiglu", "gatherq", "gemv"):
         if args.only == "swiglu":
             # SwiGLU + two-level quantiser of the MoE layer: 16384 routed rows x (gate | up) of 2944 features each
             rows, ih = 16384, 2944
@@ -602,6 +602,14 @@ def run_gpu(args):
                                                                    kp_, hh, 32, torch.cuda.current_stream().cuda_stream), "qb_gather_quantize_act")
             algo = n_valid * hh * 2 + rows * (kp_ * (0.5 + 1 / 32) + 4)
             what = f"quant_act_kernel<32,1,true> gathering {n_valid} of {rows} rows from [{n_tok},{hh}] bf16 (source rows re-read from L2)"
+        elif args.only == "gemv":
+            n, k = 14336, 4096                          # one token: quantiser + matrix-vector product in one launch, six rotating weights > L2
+            mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
+                    for _ in range(6)]
+            xd = torch.randn(1, k, device=dev).to(torch.bfloat16)
+            fn = lambda: [m.forward(xd) for m in mods]
+            algo = 6 * (n * k / 2 + n * k / 16 + 4 * n + 2 * k + 2 * n)
+            what = f"nvfp4_gemv_kernel<1>: six [1]x[{n},{k}] dense linears per step (eager launches)"
         elif args.only == "quant":
             rows, k = 16384, 4096                      # 134 MB of bf16 input: larger than L2
             xq = torch.randn(rows, k, device=dev).to(torch.bfloat16)
@@ -1128,8 +1136,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
-                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'swiglu' / 'gatherq' time one small workload of "
-                    "the activation quantiser / the thin-token GEMM / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead; "
+                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'gemv' / 'swiglu' / 'gatherq' time one small workload of "
+                    "the activation quantiser / the thin-token GEMM / the one-token dense linear / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead; "
                     "'flashinfer' runs the optional library comparator (FlashInfer mm_fp4, dense NVFP4) on the prefill shapes")
     ap.add_argument("--dp", action="store_true", help="with --gpus N > 1: replicas (tokens sharded, weights replicated, no exchange, weak "
                     "scaling) instead of the default tensor-parallel sharding")
