@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 float2 f = acc4[i];
-                if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); f.x = __fadd_rn(f.x, r2.x); f.y = __fadd_rn(f.y, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
+                if (ADD) { float2 r2 = __bfloat1622float2(bh[i]); add_f32x2(f.x, f.y, r2.x, r2.y); oh[i] = __floats2bfloat162_rn(f.x, f.y); }
                 v[j][8 * k + 2 * i] = f.x; v[j][8 * k + 2 * i + 1] = f.y;
                 ss += f.x * f.x + f.y * f.y;
             }
@@ -454,8 +454,8 @@ __global__ void __launch_bounds__(512) norm_quant_kernel(const uint4* __restrict
             for (int i = 0; i < 4; i++) {
                 float2 w2 = __bfloat1622float2(wh[i]);
                 const int e = 8 * k + 2 * i;
-                v[j][e] = __fmul_rn(__fmul_rn(v[j][e], rms), w2.x);
-                v[j][e + 1] = __fmul_rn(__fmul_rn(v[j][e + 1], rms), w2.y);
+                mul_f32x2(v[j][e], v[j][e + 1], rms, rms);            // two IEEE-rounded products per instruction, as the scalar form
+                mul_f32x2(v[j][e], v[j][e + 1], w2.x, w2.y);
                 m = fmaxf(m, fmaxf(fabsf(v[j][e]), fabsf(v[j][e + 1])));
             }
         }
