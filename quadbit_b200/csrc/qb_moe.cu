@@ -29,13 +29,20 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ dbuf, const
     if (vec) {
         for (int f = threadIdx.x * 8; f < H; f += blockDim.x * 8) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int k = 0; k < topk; k++) {
-                int r = rows[k];
-                if (r < 0) continue;
-                uint4 u = __ldg(reinterpret_cast<const uint4*>(dbuf + (size_t)r * Mpe + f));
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+            // four rows at a time, their loads issued together (a skipped row contributes zeros); same summation order
+            for (int k0 = 0; k0 < topk; k0 += 4) {
+                uint4 u[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) { float2 v = __bfloat1622float2(h[i]); acc[2 * i] += v.x; acc[2 * i + 1] += v.y; }
+                for (int j = 0; j < 4; j++) {
+                    const int r = k0 + j < topk ? rows[k0 + j] : -1;
+                    u[j] = r >= 0 ? __ldg(reinterpret_cast<const uint4*>(dbuf + (size_t)r * Mpe + f)) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[j]);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) { float2 v = __bfloat1622float2(h[i]); acc[2 * i] += v.x; acc[2 * i + 1] += v.y; }
+                }
             }
             uint4 o;
             __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -202,7 +209,9 @@ int moe_combine_topk(const void* dbuf, const void* inverse, void* y, int t, int 
     if (t == 0) return QB_OK;
     if (!dbuf || !inverse || !y) return QB_ERR_ARG;
     if ((((uintptr_t)dbuf | (uintptr_t)y) & 15) != 0) return QB_ERR_ARG;
-    moe_combine_kernel<<<t, 256, (size_t)topk * sizeof(int), st>>>((const __nv_bfloat16*)dbuf, (const int*)inverse,
+    int threads = ((H + 7) / 8 + 31) / 32 * 32;          // one 16-byte piece of the row per thread where the row allows it
+    threads = threads < 64 ? 64 : threads > 512 ? 512 : threads;
+    moe_combine_kernel<<<t, threads, (size_t)topk * sizeof(int), st>>>((const __nv_bfloat16*)dbuf, (const int*)inverse,
                                                                   (__nv_bfloat16*)y, H, topk, Mpe);
     return (int)cudaGetLastError();
 }
