@@ -244,12 +244,12 @@ int linear_gemv_dense(const void* x, const void* At, const void* sfa, const void
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const size_t smem = gemv_smem_bytes(tok, kblocks, out_f, sms);
     if (smem > 200 * 1024) return QB_ERR_UNSUPPORTED;
-    static bool attr_set[2] = {false, false};
+    static bool attr_set[64][2] = {};                 // the attribute belongs to the device's context: once per device and kernel
     auto kern = tok == 1 ? nvfp4_gemv_kernel<1> : nvfp4_gemv_kernel<2>;
-    if (!attr_set[tok - 1]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev][tok - 1]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
-        attr_set[tok - 1] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev][tok - 1] = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)sms);
