@@ -223,7 +223,7 @@ long long qb_gemm_decode_ws_bytes(int out, int tok, int K);
  * (quantize_act_nvfp4_2lvl, per 16, bit-identical codes and scales) and the matrix-vector product, on the CUDA cores: f16
  * products and block sums of E2M1 code values are exact, block sums are scaled and accumulated in fp32 in a fixed order.
  * Counterpart of the reference's dense decode GEMV (cuda/dense_decode_lib.cu:19-141), which also runs beside its
- * tensor-core kernels for single tokens. x [tok][K] bf16 (tok <= 2), A_tiled / sfa / gA: the weight as qb_pack_dense +
+ * tensor-core kernels for single tokens. x [tok][K] bf16 (tok <= 2, 16-byte aligned like A_tiled and sfa), A_tiled / sfa / gA: the weight as qb_pack_dense +
  * qb_tile_weights leave it, C [tok][out] bf16. out % 128 == 0, K % 128 == 0, K <= 16384; no workspace. */
 int qb_linear_gemv(const void* x, const void* A_tiled, const void* sfa, const void* gA, void* C, int out, int tok, int K, void* stream);
 /* Split-K GEMM without a caller workspace (no counterpart in the reference library, whose

@@ -237,7 +237,7 @@ static size_t gemv_smem_bytes(int tok, int kblocks, int out_f, int ctas) {
 int linear_gemv_dense(const void* x, const void* At, const void* sfa, const void* gA, void* C, int out_f, int tok, int K, cudaStream_t st) {
     if (out_f <= 0 || K <= 0 || out_f % 128 || K % 128 || tok < 0 || tok > 2) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
-    if (!x || !At || !sfa || !gA || !C || ((uintptr_t)x & 15) || ((uintptr_t)At & 15) || ((uintptr_t)sfa & 3) || ((uintptr_t)C & 1)) return QB_ERR_ARG;
+    if (!x || !At || !sfa || !gA || !C || ((uintptr_t)x & 15) || ((uintptr_t)At & 15) || ((uintptr_t)sfa & 15) || ((uintptr_t)C & 1)) return QB_ERR_ARG;
     const int kblocks = kpad256(K) / 256;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
