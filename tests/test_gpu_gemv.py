@@ -72,6 +72,29 @@ def test_gemv_block_sums_are_exact(lib):
     assert torch.equal(C.float().cpu(), exact.float().to(torch.bfloat16).float())
 
 
+def test_gemv_zero_and_extreme_tokens(lib):
+    """An all-zero token gives exact zeros (global 1e-30, every code 0); a token of very large and one of very small
+    magnitude go through the same global / block scaling as in the stand-alone quantiser and match the oracle."""
+    import quadbit_b200 as qb
+    torch.manual_seed(11)
+    out_f, K = 512, 1024
+    W = torch.randn(out_f, K) * 0.02
+    lin = qb.DenseNVLinear(W.cuda(), keep_ref_layout=False)
+    for scale in (0.0, 1e30, 1e-30):
+        x = (torch.randn(2, K) * scale).to(torch.bfloat16)
+        x[1] = 0
+        C = torch.full((2, out_f), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert lib.qb_linear_gemv(x.cuda().data_ptr(), lin.At.data_ptr(), lin.sfa.data_ptr(), lin.gA.data_ptr(), C.data_ptr(), out_f, 2, K, S()) == 0
+        assert lib.qb_status(S()) == 0
+        y = C.float().cpu()
+        assert torch.isfinite(y).all() and torch.equal(y[1], torch.zeros(out_f))
+        ref = fq.linear_dense(x.float(), W)
+        if scale == 0.0:
+            assert torch.equal(y[0], torch.zeros(out_f))
+        else:
+            assert ((y[0] - ref[0]).abs().max() / ref[0].abs().max()).item() < 1e-2
+
+
 def test_gemv_argument_checks(lib):
     d = torch.zeros(4096, dtype=torch.uint8, device="cuda").data_ptr()
     assert lib.qb_linear_gemv(d, d, d, d, d, 128, 0, 128, S()) == 0              # no tokens: nothing to do
