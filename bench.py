@@ -908,6 +908,31 @@ def run_gpu(args):
 
         line["decode_dense"] = decode_sweep(lambda W: qb.DenseNVLinear(W, keep_ref_layout=False),
                                             lambda n, k: n * k / 2 + n * k / 16 + 4 * n, (1, 2, 16, 64, 128, 256))
+        # ---- the reference's own decode benchmark protocol (harness/bench_decode_bw.py:27-36,84-99): M = 128 tokens, raw E2M1
+        #      operands with unit scales through `dense_fp4_decode_cached_async`, GEMM only, bytes = N K / 2 + 2 M N; here in a
+        #      CUDA graph over rotating weights (> L2) on the legacy stream the entry launches on
+        ref_dec = {}
+        libd = qb.load("dense_nvfp4")
+        for (n, k) in [(4096, 4096), (6144, 4096), (12288, 4096), (14336, 4096), (4096, 14336), (28672, 4096)]:
+            m_tok = 128
+            nrot = max(2, int(300e6 // (n * k // 2)) + 1)
+            wts = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev) for _ in range(nrot)]
+            acts = torch.randint(0, 256, (m_tok, k // 2), dtype=torch.uint8, device=dev)
+            cdec = torch.empty((m_tok, n), dtype=torch.bfloat16, device=dev)
+            ma = libd.qb_encode_map(acts.data_ptr(), m_tok, k, 128)
+            mws = [libd.qb_encode_map(w.data_ptr(), n, k, libd.qb_decode_tn(n)) for w in wts]
+            step_dec = lambda: [libd.dense_fp4_decode_cached_async(ma, mw, cdec.data_ptr(), m_tok, n, k) for mw in mws]
+            step_dec()                                  # sizes the library's persistent buffers outside the timed region
+            torch.cuda.synchronize()
+            t_dec = ev_time(step_dec, 10, 3) / nrot
+            by = n * k / 2 + 2 * m_tok * n
+            ref_dec[f"M128_N{n}_K{k}"] = {"us": t_dec * 1e6, "gbs": by / t_dec / 1e9, "frac_of_measured_hbm": by / t_dec / 1e9 / hbm_gbs}
+            for h in [ma] + mws:
+                libd.qb_free_map(h)
+            del wts, acts, cdec
+        line["decode_reference_protocol"] = {"what": "dense_fp4_decode_cached_async (unit-scale dense FP4 GEMM, one launch per call), M = 128, the six "
+                                                     "shapes and the byte count of harness/bench_decode_bw.py; eager launches on the legacy stream "
+                                                     "over rotating weights larger than L2", **ref_dec}
         line["decode_sparse"] = decode_sweep(lambda W: qb.QuadbitLinear(W, keep_ref_layout=False),
                                              lambda n, k: n * k / 4 + n * k / 16 + n * k / 32 + 4 * n, (64, 128, 256))
 

@@ -54,6 +54,40 @@ int scratch_get(size_t bytes, void** out) {
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// Two more per-device buffers, for the unit-scale entry points only, that keep their CONTENTS between calls so that such a
+// call is one launch: `fill` bytes everywhere (0x38 = scale code of 1.0 for both operands; 0 = a clean split-K workspace,
+// which the decode kernel leaves clean again). Grown like the scratch buffer (first call of a size outside graph capture);
+// the fill runs on the calling stream in front of the first use.
+struct Persistent {
+    void* ptr = nullptr;
+    size_t cap = 0;
+};
+Persistent g_persist[2][64];
+int persistent_get(int which, int fill, size_t bytes, cudaStream_t st, void** out) {
+    int dev = 0;
+    int rc = (int)cudaGetDevice(&dev);
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return QB_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Persistent& s = g_persist[which][dev];
+    if (s.cap < bytes) {
+        if (s.ptr) {
+            rc = (int)cudaDeviceSynchronize();
+            if (rc) return rc;
+            cudaFree(s.ptr);
+            s.ptr = nullptr;
+            s.cap = 0;
+        }
+        size_t cap = bytes + (bytes >> 2) + (1 << 20);
+        rc = (int)cudaMalloc(&s.ptr, cap);
+        if (rc) return rc;
+        s.cap = cap;
+        if ((rc = (int)cudaMemsetAsync(s.ptr, fill, cap, st))) return rc;
+    }
+    *out = s.ptr;
+    return QB_OK;
+}
+
 size_t sf_atoms_bytes(int rows, int K, int block) {
     return (size_t)((rows + 127) / 128) * (size_t)(qb::kpad256(K) / block / 4) * 512;
 }
@@ -334,7 +368,7 @@ int fused_mlp_2lvl_skdown(const void* x, const void* gu_Ac, const void* gu_scale
 // C[M,N] = A[M,K] @ B[N,K]^T on raw E2M1 codes (every block scale 1.0, no globals): the reference's dense_fp4_lib /
 // dense_sk_lib / dense_decode_lib use unit ue8m0 scales for its kernel-only comparisons. Here B plays the weight (the
 // tensor-core A operand, rows = N) and A the tokens, so the token-major output of the native GEMM is C[M][N] as it is;
-// the scale-factor atoms of both operands are filled with the UE4M3 code of 1.0 (0x38) in the scratch buffer.
+// the scale-factor atoms of both operands are one persistent buffer filled once with the UE4M3 code of 1.0 (0x38).
 static int unit_scale_gemm(const void* A, const void* B, void* C, void* Cf, int M, int N, int K, int splits, bool decode, cudaStream_t st) {
     if (M < 0 || N <= 0 || K <= 0 || K % 128 || N % 128) return QB_ERR_ARG;
     if (M == 0) return QB_OK;
@@ -346,19 +380,21 @@ static int unit_scale_gemm(const void* A, const void* B, void* C, void* Cf, int 
         qb::decode_plan(N, M, K, &sp, &bn);
         if (sp > 1) n_ws = align256((size_t)qb_gemm_decode_ws_bytes(N, M, K));
     }
-    void* base = nullptr;
-    int rc = scratch_get(n_w + n_x + n_ws, &base);
+    // every scale code is 1.0: both operands read the same persistent buffer of 0x38 bytes (no per-call fill)
+    void* ones = nullptr;
+    int rc = persistent_get(0, 0x38, n_w > n_x ? n_w : n_x, st, &ones);
     if (rc) return rc;
-    uint8_t* sfw = (uint8_t*)base;
-    uint8_t* sfx = sfw + n_w;
-    if ((rc = (int)cudaMemsetAsync(base, 0x38, n_w + n_x, st))) return rc;
+    uint8_t* sfw = (uint8_t*)ones;
+    uint8_t* sfx = (uint8_t*)ones;
     qb::GemmArgs g{};
     g.A = B; g.B = A; g.sfa = sfw; g.sfb = sfx; g.C = C; g.a_rows = N; g.out_f = N; g.tok = M; g.K = K; g.sparse = 0; g.out_mode = 1;
     g.splits = sp; g.bn = bn;
     if (decode && sp > 1) {
-        // in-kernel split-K finish: counters + sums must be zero on entry (the scratch is shared, so zero it every call)
-        uint8_t* ws = sfx + n_x;
-        if ((rc = (int)cudaMemsetAsync(ws, 0, n_ws, st))) return rc;
+        // in-kernel split-K finish: counters + sums must be zero on entry; the kernel leaves them zero, and this workspace is
+        // used by nothing else, so it is zeroed when it is allocated and never again
+        void* wsp = nullptr;
+        if ((rc = persistent_get(1, 0, n_ws, st, &wsp))) return rc;
+        uint8_t* ws = (uint8_t*)wsp;
         g.sk_counters = ws;
         g.Cf = (float*)(ws + decode_counter_bytes(N, M));
     } else if (sp > 1) {
