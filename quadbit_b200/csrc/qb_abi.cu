@@ -312,13 +312,13 @@ int qb_gemm_decode(const void* A, const void* B, const void* sfa, const void* sf
     if (out <= 0 || tok < 0 || K <= 0 || out % 128 || (out_mode != 0 && out_mode != 1)) return QB_ERR_ARG;
     if (tok == 0) return QB_OK;
     if (!ws || ((uintptr_t)ws & 255)) return QB_ERR_ARG;
-    int splits = 1, bn = 16;
-    qb::decode_plan(out, tok, K, &splits, &bn);
+    int splits = 1, bn = 16, cluster = 0;
+    qb::decode_plan(out, tok, K, &splits, &bn, &cluster);
     qb::GemmArgs g{};
     g.A = A; g.B = B; g.sfa = sfa; g.sfb = sfb; g.meta = meta_native; g.gA = (const float*)gA; g.gB = (const float*)gB;
     g.C = C; g.sk_counters = ws; g.Cf = (float*)((uint8_t*)ws + decode_counter_bytes(out, tok));
     g.a_rows = out; g.out_f = out; g.tok = tok; g.K = K; g.sparse = sparse & 1; g.a_tiled = (sparse >> 1) & 1;
-    g.out_mode = out_mode; g.splits = splits; g.bn = bn;
+    g.out_mode = out_mode; g.splits = splits; g.bn = bn; g.cluster_red = cluster;
     return qb::gemm_nvfp4(g, (cudaStream_t)stream);
 }
 int qb_linear_gemv(const void* x, const void* A_tiled, const void* sfa, const void* gA, void* C, int out, int tok, int K, void* stream) {
@@ -375,10 +375,10 @@ static int unit_scale_gemm(const void* A, const void* B, void* C, void* Cf, int 
     if (!A || !B || !C) return QB_ERR_ARG;
     const size_t n_w = align256(sf_atoms_bytes(N, K, 16)), n_x = align256(sf_atoms_bytes(M, K, 16));
     size_t n_ws = 0;
-    int sp = splits < 1 ? 1 : splits, bn = 0;
+    int sp = splits < 1 ? 1 : splits, bn = 0, cluster = 0;
     if (decode && M <= 256) {
-        qb::decode_plan(N, M, K, &sp, &bn);
-        if (sp > 1) n_ws = align256((size_t)qb_gemm_decode_ws_bytes(N, M, K));
+        qb::decode_plan(N, M, K, &sp, &bn, &cluster);
+        if (sp > 1) n_ws = align256((size_t)qb_gemm_decode_ws_bytes(N, M, K));      // kept ready: the GEMM falls back to it
     }
     // every scale code is 1.0: both operands read the same persistent buffer of 0x38 bytes (no per-call fill)
     void* ones = nullptr;
@@ -388,7 +388,7 @@ static int unit_scale_gemm(const void* A, const void* B, void* C, void* Cf, int 
     uint8_t* sfx = (uint8_t*)ones;
     qb::GemmArgs g{};
     g.A = B; g.B = A; g.sfa = sfw; g.sfb = sfx; g.C = C; g.a_rows = N; g.out_f = N; g.tok = M; g.K = K; g.sparse = 0; g.out_mode = 1;
-    g.splits = sp; g.bn = bn;
+    g.splits = sp; g.bn = bn; g.cluster_red = cluster;
     if (decode && sp > 1) {
         // in-kernel split-K finish: counters + sums must be zero on entry; the kernel leaves them zero, and this workspace is
         // used by nothing else, so it is zeroed when it is allocated and never again

@@ -62,6 +62,7 @@ struct KParams {
     int out_mode;
     int a_tiled;                         // A in 128-row x 256-K tiles: TMA row coordinate = tile * 128, column 0
     int* sk_counters;                    // split-K finished in the kernel: 4 arrival counters per output tile (zero between calls)
+    int cluster_red;                     // split-K inside a cluster of `splits` CTAs: partial tiles meet in distributed shared memory
 };
 
 template <bool SPARSE, int BN>
@@ -153,6 +154,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const int tiles_mn = p.num_m * p.num_n;
     const int total_tiles = tiles_mn * p.splits;
+    // Work items of this CTA. Normally tile = blockIdx.x + i * gridDim.x over (split, tile) pairs. With the cluster reduction
+    // the grid is one cluster of `splits` CTAs per output tile and nothing else: the CTA of rank r takes K split r of tile
+    // blockIdx.x / splits, once.
+    const int crank = p.cluster_red ? (int)cluster_ctarank() : 0;
+    const int tile0 = p.cluster_red ? crank * tiles_mn + (int)blockIdx.x / p.splits : (int)blockIdx.x;
+    const int tile_step = p.cluster_red ? total_tiles : (int)gridDim.x;
     // grouped mode: a 128-token block with expert id < 0 is unused capacity of a fixed-capacity routing; every
     // role skips its tiles (same test everywhere, so the K-block and accumulator counters stay in step)
     auto tile_skipped = [&](int tile) { return p.eblk != nullptr && p.eblk[(tile % tiles_mn) / p.num_m] < 0; };
@@ -192,7 +199,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t phase = 0;
             uint32_t it = 0;
             bool stop = false;
-            for (int tile = blockIdx.x; tile < total_tiles && !abort_flag && pw < NP && !stop; tile += gridDim.x) {
+            for (int tile = tile0; tile < total_tiles && !abort_flag && pw < NP && !stop; tile += tile_step) {
                 if (pass == 1 && tile_skipped(tile)) continue;
                 const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
                 const int m = mn % p.num_m, n = mn / p.num_m;
@@ -230,7 +237,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+            for (int tile = tile0; tile < total_tiles && !abort_flag; tile += tile_step) {
                 if (tile_skipped(tile)) continue;
                 const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
                 const int n = mn / p.num_m;
@@ -289,7 +296,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t lane_sel = (uint32_t)(q * 32) << 16;
         int stage = 0;
         uint32_t phase = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+        for (int tile = tile0; tile < total_tiles && !abort_flag; tile += tile_step) {
             if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn;
             const int kb0 = z * kb_per_split, kb1 = min(p.kblocks, kb0 + kb_per_split);
@@ -344,7 +351,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t stg_s = smem0 + C::STAGES * C::STAGE_BYTES + (warp - 2) * (32 * 80);
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+        for (int tile = tile0; tile < total_tiles && !abort_flag; tile += tile_step) {
             if (tile_skipped(tile)) continue;
             const int z = tile / tiles_mn, mn = tile - z * tiles_mn;
             const int m = mn % p.num_m, n = mn / p.num_m;
@@ -374,10 +381,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (p.splits > 1) {
                     // split-K: raw partial sums are added into the fp32 workspace Cf[tok][out] (fire-and-forget
                     // reductions at the L2); finished by the last split of the tile (below) or by a finish kernel
+                    if (p.cluster_red) {
+                        // cluster reduction: the partial tile goes to this CTA's shared memory, column-major [BN][128] fp32 over
+                        // the operand ring (free by now: the accumulator is complete, so every stage has been consumed and
+                        // this CTA has no other work item)
+#pragma unroll
+                        for (int j = 0; j < C::CH; j++) sts_u32(smem0 + (uint32_t)(((c0 + j) * 128 + r_in_tile) * 4), r[j]);
+                    } else {
 #pragma unroll
                     for (int j = 0; j < C::CH; j++) {
                         const int col = n0 + c0 + j;
                         if (col < p.tok) atomicAdd(p.Cf + (size_t)col * p.out_f + o, __uint_as_float(r[j]));
+                    }
                     }
                 } else if (p.out_mode == 2) {
                     float* Cp = reinterpret_cast<float*>(p.C) + (size_t)o * p.tok;
@@ -483,6 +498,54 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
     }
 
+    if (p.cluster_red) {
+        // Split-K finish inside the cluster: every CTA has staged its partial tile; after a cluster barrier CTA r sums token
+        // columns [r * cpr, (r + 1) * cpr) of all the CTAs' partial tiles (in rank order: the result does not depend on
+        // timing), applies the globals and stores bf16; a second barrier keeps every CTA's shared memory alive until its
+        // peers have read it. All threads of all CTAs of the cluster get here whatever happened before (every wait above is
+        // bounded), so the hardware barrier cannot be left waiting.
+        __syncthreads();
+        cluster_sync_all();
+        const int w = (int)blockIdx.x / p.splits;
+        const int m = w % p.num_m, n = w / p.num_m;
+        const int n0 = n * BN;
+        const int cpr = (BN + p.splits - 1) / p.splits;
+        const int c_begin = crank * cpr;
+        const int c_end = min(min(BN, c_begin + cpr), p.tok - n0);
+        // four consecutive rows of one column per thread and step: one 16-byte load from every CTA of the cluster, all of
+        // them issued before the sums (rank order), 8 bytes of bf16 out
+        for (int idx = threadIdx.x; idx < (c_end - c_begin) * 32; idx += NTHREADS1) {
+            const int row = (idx & 31) * 4, col = c_begin + (idx >> 5);
+            const uint32_t local = smem0 + (uint32_t)((col * 128 + row) * 4);
+            float4 v[8];
+#pragma unroll
+            for (int z = 0; z < 8; z++) {
+                v[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (z < p.splits)
+                    asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                        : "=f"(v[z].x), "=f"(v[z].y), "=f"(v[z].z), "=f"(v[z].w)
+                        : "r"(mapa_shared(local, (uint32_t)z)));
+            }
+            float4 sum = v[0];
+#pragma unroll
+            for (int z = 1; z < 8; z++) { sum.x += v[z].x; sum.y += v[z].y; sum.z += v[z].z; sum.w += v[z].w; }
+            const int o = m * 128 + row, colg = n0 + col;
+            const float4 ga = p.gA ? make_float4(__ldg(p.gA + o), __ldg(p.gA + o + 1), __ldg(p.gA + o + 2), __ldg(p.gA + o + 3)) : make_float4(1.f, 1.f, 1.f, 1.f);
+            const float gb = p.gB ? __ldg(p.gB + colg) : 1.f;
+            const uint32_t h01 = pack_bf16x2((sum.x * ga.x) * gb, (sum.y * ga.y) * gb), h23 = pack_bf16x2((sum.z * ga.z) * gb, (sum.w * ga.w) * gb);
+            __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(p.C);
+            if (p.out_mode == 0) {
+                uint16_t* c16 = reinterpret_cast<uint16_t*>(Cb);
+                c16[(size_t)o * p.tok + colg] = (uint16_t)(h01 & 0xffff);
+                c16[(size_t)(o + 1) * p.tok + colg] = (uint16_t)(h01 >> 16);
+                c16[(size_t)(o + 2) * p.tok + colg] = (uint16_t)(h23 & 0xffff);
+                c16[(size_t)(o + 3) * p.tok + colg] = (uint16_t)(h23 >> 16);
+            } else {
+                *reinterpret_cast<uint2*>(Cb + (size_t)colg * p.out_f + o) = make_uint2(h01, h23);
+            }
+        }
+        cluster_sync_all();
+    }
     // teardown: every role has left its loop (all waits are bounded)
     tc_fence_before();
     __syncthreads();
@@ -1371,17 +1434,50 @@ static int launch(const GemmArgs& a, KParams kp, cudaStream_t st) {
     if (rc) return rc;
     int total = kp.num_m * kp.num_n * kp.splits;
     int grid = total < sm_count() ? total : sm_count();
+    if (kp.cluster_red) grid = total;            // one cluster of `splits` CTAs per output tile (the caller checked that it fits)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(NTHREADS1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;     // see griddep_wait() in the kernel
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (kp.cluster_red) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)kp.splits;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     return (int)cudaLaunchKernelEx(&cfg, nvfp4_gemm_kernel<SPARSE, BN>, tmA, tmB, kp);
+}
+
+// Clusters of `size` CTAs of the single-CTA kernel (one CTA per SM, all its shared memory) that can be resident at once: the
+// SMs of a GPC do not always divide into clusters, so this is less than SMs / size (asked once per size and kernel).
+template <bool SPARSE, int BN>
+static int max_clusters(int size) {
+    using C = Cfg<SPARSE, BN>;
+    static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (size < 1 || size > 8) return 0;
+    if (cache[size]) return cache[size];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(size * 64));
+    cfg.blockDim = dim3(NTHREADS1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, nvfp4_gemm_kernel<SPARSE, BN>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    cache[size] = n > 0 ? n : -1;
+    return cache[size];
 }
 
 
@@ -1541,9 +1637,22 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     kp.splits = splits;
     kp.sfb_rowblocks = (a.tok + 127) / 128;
     kp.out_mode = a.out_mode;
-    const bool slab = splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
+    // split-K finished inside a cluster (no workspace, no atomics): asked for by the caller's plan; one wave, at most 8 CTAs
+    // per cluster, plain (not grouped) bf16 output, one accumulator-sized staging area in the operand ring
+    kp.cluster_red = (a.cluster_red && splits > 1 && splits <= 8 && !a.eblk && (a.out_mode == 0 || a.out_mode == 1) &&
+                      kp.num_m * kp.num_n * splits <= sm_count() && bn <= 128) ? 1 : 0;
+    if (kp.cluster_red) {
+        int mc = 0;
+#define QB_MC(BN) (a.sparse ? max_clusters<true, BN>(splits) : max_clusters<false, BN>(splits))
+        switch (bn) { case 16: mc = QB_MC(16); break; case 32: mc = QB_MC(32); break; case 64: mc = QB_MC(64); break; default: mc = QB_MC(128); break; }
+#undef QB_MC
+        if (kp.num_m * kp.num_n > mc) kp.cluster_red = 0;       // would take two waves of clusters: the workspace form is faster
+    }
+    if (a.cluster_red && !kp.cluster_red && splits > 1 && !a.sk_counters && !a.Cf) return QB_ERR_ARG;
+    if (kp.cluster_red) { kp.sk_counters = nullptr; kp.Cf = nullptr; }
+    const bool slab = !kp.cluster_red && splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
     if (!slab) kp.sk_counters = nullptr;
-    if (splits > 1 && !slab) {
+    if (splits > 1 && !slab && !kp.cluster_red) {
         rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
         if (rc) return rc;
     }
@@ -1557,7 +1666,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     }
 #undef QB_GO
     if (rc) return rc;
-    if (splits > 1 && !slab) {
+    if (splits > 1 && !slab && !kp.cluster_red) {
         size_t n = (size_t)a.out_f * a.tok;
         int blocks = (int)((n + 255) / 256);
         if (blocks > sm_count() * 8) blocks = sm_count() * 8;
@@ -1567,13 +1676,22 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     return rc;
 }
 
-void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
+static int max_clusters_bn(int bn, int size) {
+    switch (bn) {
+        case 16: return max_clusters<false, 16>(size);
+        case 32: return max_clusters<false, 32>(size);
+        case 64: return max_clusters<false, 64>(size);
+        default: return max_clusters<false, 128>(size);
+    }
+}
+
+void decode_plan(int out_f, int tok, int K, int* splits, int* bn, int* cluster) {
     int b = tok <= 16 ? 16 : tok <= 32 ? 32 : tok <= 64 ? 64 : 128;
     const int num_n = (tok + b - 1) / b;
     const int tiles = (out_f / 128) * num_n;
     const int kb = (K + 255) / 256;
     const int sms = sm_count();
-    int best_s = 1;
+    int best_s = 1, best_c = 0;
     double best = 1e30;
     for (int s = 1; s <= kb && s <= 32; s++) {
         const int per = (kb + s - 1) / s;
@@ -1584,10 +1702,17 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn) {
         // fence, the arrival counter and the read-back by the last split (measured)
         const int ncol = tok < b ? tok : b;
         const double cost = waves * (per + 3.0 + (s > 1 ? 10.4 + 0.36 * ncol : 0.0));
-        if (cost < best - 1e-9) { best = cost; best_s = s; }
+        if (cost < best - 1e-9) { best = cost; best_s = s; best_c = 0; }
+        // the same split finished inside a cluster of s CTAs (one wave, s <= 8): two cluster barriers and a pass over the
+        // partial tiles in distributed shared memory
+        if (cluster && s > 1 && s <= 8 && tiles * s <= sms && tiles <= max_clusters_bn(b, s)) {
+            const double cc = per + 3.0 + 6.0 + 0.03 * ncol;
+            if (cc < best - 1e-9) { best = cc; best_s = s; best_c = 1; }
+        }
     }
     *splits = best_s;
     *bn = b;
+    if (cluster) *cluster = best_c;
 }
 
 

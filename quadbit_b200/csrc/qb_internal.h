@@ -87,6 +87,7 @@ struct GemmArgs {
     void* C;               // output
     float* Cf;             // fp32 split-K workspace [tok][out]; with sk_counters it must be zero on entry and is left zero
     void* sk_counters;     // in-kernel finish: int[4 * tiles], zero before the first call, left zero by the kernel
+    int cluster_red;       // 1 = finish the K splits inside a thread-block cluster (distributed shared memory) where the shape allows it
                            // (null = the host zeroes Cf and launches a finish kernel)
     const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
     const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
@@ -125,7 +126,7 @@ struct GemmArgs {
 int gemm_nvfp4(const GemmArgs& a, cudaStream_t st);
 int gemm_init_attrs();
 // splits / token tile that stream the weight over the SMs with the fewest idle waves (thin token counts)
-void decode_plan(int out_f, int tok, int K, int* splits, int* bn);
+void decode_plan(int out_f, int tok, int K, int* splits, int* bn, int* cluster = nullptr);
 int read_status(cudaStream_t st);   // synchronises st and returns + clears the device status word
 
 // ---- qb_moe.cu
