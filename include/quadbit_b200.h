@@ -210,8 +210,11 @@ long long qb_tiled_weight_bytes(int rows, int K, int sparse);
 /* Thin-token (decode) GEMM: streams the weight once with the K range split over CTAs so that all SMs
  * pull from HBM; each split adds its fp32 partial sums into `ws` (reductions at the L2) and the last
  * split to arrive for a tile reads the sums, writes bf16 and zeroes what it read (one launch: no
- * memset, no finish pass; the summation order, hence the last bits, can differ from run to run). The
- * split count and token tile come from the shapes. `ws`: qb_gemm_decode_ws_bytes(out, tok, K) bytes,
+ * memset, no finish pass; the summation order, hence the last bits, can differ from run to run). Where
+ * every (tile, split) pair fits the GPU at once as clusters of <= 8 CTAs, the splits of a tile run as one
+ * thread-block cluster instead and their partial tiles meet in distributed shared memory: no workspace
+ * traffic, no atomics, sums in split order (bit-reproducible). The split count, the form of the finish and
+ * the token tile come from the shapes. `ws`: qb_gemm_decode_ws_bytes(out, tok, K) bytes,
  * 256-byte aligned, ZERO-FILLED ONCE when allocated (arrival counters and sums, all of which every call
  * leaves at zero again); calls sharing a workspace must not overlap on the GPU. out_mode 0 / 1 as in
  * qb_gemm. Replaces the memset + atomics + convert sequence of the reference's split-K decode path
