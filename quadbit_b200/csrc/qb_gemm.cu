@@ -1637,9 +1637,10 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
     kp.splits = splits;
     kp.sfb_rowblocks = (a.tok + 127) / 128;
     kp.out_mode = a.out_mode;
-    // split-K finished inside a cluster (no workspace, no atomics): asked for by the caller's plan; one wave, at most 8 CTAs
-    // per cluster, plain (not grouped) bf16 output, one accumulator-sized staging area in the operand ring
-    kp.cluster_red = (a.cluster_red && splits > 1 && splits <= 8 && !a.eblk && (a.out_mode == 0 || a.out_mode == 1) &&
+    // split-K finished inside a cluster (no workspace, no atomics) whenever the split fits: one wave, at most 8 CTAs per
+    // cluster, plain (not grouped) bf16 output, one accumulator-sized staging area in the operand ring; otherwise through the
+    // caller's workspace
+    kp.cluster_red = (splits > 1 && splits <= 8 && !a.eblk && (a.out_mode == 0 || a.out_mode == 1) &&
                       kp.num_m * kp.num_n * splits <= sm_count() && bn <= 128) ? 1 : 0;
     if (kp.cluster_red) {
         int mc = 0;
@@ -1648,7 +1649,7 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
 #undef QB_MC
         if (kp.num_m * kp.num_n > mc) kp.cluster_red = 0;       // would take two waves of clusters: the workspace form is faster
     }
-    if (a.cluster_red && !kp.cluster_red && splits > 1 && !a.sk_counters && !a.Cf) return QB_ERR_ARG;
+    if (!kp.cluster_red && splits > 1 && !a.sk_counters && !a.Cf) return QB_ERR_ARG;
     if (kp.cluster_red) { kp.sk_counters = nullptr; kp.Cf = nullptr; }
     const bool slab = !kp.cluster_red && splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
     if (!slab) kp.sk_counters = nullptr;

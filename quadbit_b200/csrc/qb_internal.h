@@ -87,7 +87,7 @@ struct GemmArgs {
     void* C;               // output
     float* Cf;             // fp32 split-K workspace [tok][out]; with sk_counters it must be zero on entry and is left zero
     void* sk_counters;     // in-kernel finish: int[4 * tiles], zero before the first call, left zero by the kernel
-    int cluster_red;       // 1 = finish the K splits inside a thread-block cluster (distributed shared memory) where the shape allows it
+    int cluster_red;       // set by the decode plan when it costed the split as a cluster reduction (the GEMM itself decides from the shape)
                            // (null = the host zeroes Cf and launches a finish kernel)
     const int* eblk;       // grouped mode: expert of every 128-token block (null = plain GEMM)
     const void* bias;      // epilogue 3: bf16 per-expert bias [E][out_per_expert] (may be null)
