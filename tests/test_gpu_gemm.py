@@ -176,6 +176,31 @@ def test_decode_gemm_single_launch_split_k(lib, sparse, out_f, tok, K):
     assert int(ws[: ntile * 4].view(torch.int32).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("sparse", [1, 0])
+@pytest.mark.parametrize("out_f,tok,K", [(4096, 64, 14336), (4096, 128, 4096), (768, 200, 2304)])
+def test_decode_split_k_inside_a_cluster_is_reproducible(lib, sparse, out_f, tok, K):
+    """Shapes whose K splits fit the GPU as one wave of clusters: the partial tiles are summed in distributed shared
+    memory in split order, so two calls give the same bits (the workspace form adds at the L2 in arrival order), the
+    workspace is not touched, and the result meets the oracle like every other path."""
+    torch.manual_seed(out_f + tok + K + 9)
+    W = torch.randn(out_f, K) * 0.02
+    x = torch.randn(tok, K)
+    ops = native_operands(W, x, sparse)
+    ref = (fq.linear_sparse if sparse else fq.linear_dense)(x, W)
+    ws = torch.zeros(lib.qb_gemm_decode_ws_bytes(out_f, tok, K), dtype=torch.uint8, device="cuda")
+    p = lambda t: 0 if t is None else t.data_ptr()
+    outs = []
+    for _ in range(3):
+        C = torch.full((tok, out_f), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rc = lib.qb_gemm_decode(p(ops["A"]), p(ops["B"]), p(ops["sfa"]), p(ops["sfb"]), p(ops["meta"]), p(ops["gA"]), p(ops["gB"]),
+                                p(C), p(ws), out_f, tok, K, sparse, 1, S())
+        assert rc == 0 and lib.qb_status(S()) == 0
+        outs.append(C.clone())
+    assert bf16_err(outs[0], ref) < 6e-3
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert int(ws.view(torch.int32).abs().sum()) == 0
+
+
 def test_all_ones_known_answer(lib):
     """Reference KAT (harness/run_torch.py:60-74): all-ones operands, unit scales, pairs {0,1}
     kept -> every output is exactly K/2."""
