@@ -1463,6 +1463,7 @@ static int max_clusters(int size) {
     static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (size < 1 || size > 8) return 0;
     if (cache[size]) return cache[size];
+    if (gemm_init_attrs()) return 0;               // the query needs the kernel's shared-memory attribute in place
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(size * 64));
     cfg.blockDim = dim3(NTHREADS1);
