@@ -1651,22 +1651,34 @@ int gemm_nvfp4(const GemmArgs& a, cudaStream_t st) {
         if (kp.num_m * kp.num_n > mc) kp.cluster_red = 0;       // would take two waves of clusters: the workspace form is faster
     }
     if (!kp.cluster_red && splits > 1 && !a.sk_counters && !a.Cf) return QB_ERR_ARG;
-    if (kp.cluster_red) { kp.sk_counters = nullptr; kp.Cf = nullptr; }
-    const bool slab = !kp.cluster_red && splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
-    if (!slab) kp.sk_counters = nullptr;
-    if (splits > 1 && !slab && !kp.cluster_red) {
-        rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
-        if (rc) return rc;
-    }
+    bool slab = false;
+    // at most two attempts: a cluster launch that the device refuses (SMs taken by another context, a partitioned GPU) is
+    // repeated in the workspace form when the caller gave a workspace
+    for (int attempt = 0; attempt < 2; attempt++) {
+        kp.sk_counters = (int*)a.sk_counters; kp.Cf = a.Cf;
+        if (kp.cluster_red) { kp.sk_counters = nullptr; kp.Cf = nullptr; }
+        slab = !kp.cluster_red && splits > 1 && a.sk_counters != nullptr;     // finish inside the kernel
+        if (!slab) kp.sk_counters = nullptr;
+        if (splits > 1 && !slab && !kp.cluster_red) {
+            rc = (int)cudaMemsetAsync(a.Cf, 0, (size_t)a.out_f * a.tok * sizeof(float), st);
+            if (rc) return rc;
+        }
 #define QB_GO(BN) (a.sparse ? launch<true, BN>(a, kp, st) : launch<false, BN>(a, kp, st))
-    switch (bn) {
-        case 16: rc = QB_GO(16); break;
-        case 32: rc = QB_GO(32); break;
-        case 64: rc = QB_GO(64); break;
-        case 128: rc = QB_GO(128); break;
-        default: rc = QB_GO(256); break;
-    }
+        switch (bn) {
+            case 16: rc = QB_GO(16); break;
+            case 32: rc = QB_GO(32); break;
+            case 64: rc = QB_GO(64); break;
+            case 128: rc = QB_GO(128); break;
+            default: rc = QB_GO(256); break;
+        }
 #undef QB_GO
+        if (rc && kp.cluster_red && (a.sk_counters || a.Cf)) {
+            cudaGetLastError();
+            kp.cluster_red = 0;
+            continue;
+        }
+        break;
+    }
     if (rc) return rc;
     if (splits > 1 && !slab && !kp.cluster_red) {
         size_t n = (size_t)a.out_f * a.tok;
