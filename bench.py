@@ -576,7 +576,7 @@ def run_gpu(args):
         return
 
     # ---- profiling aids: one small workload of a side kernel, timed with CUDA events, nothing else
-    if args.only in ("quant", "decode", "swiglu", "gatherq", "gemv"):
+    if args.only in ("quant", "decode", "decode-splitk", "swiglu", "gatherq", "gemv"):
         if args.only == "swiglu":
             # SwiGLU + two-level quantiser of the MoE layer: 16384 routed rows x (gate | up) of 2944 features each
             rows, ih = 16384, 2944
@@ -616,6 +616,15 @@ def run_gpu(args):
             fn = lambda: qb.quantize_act(lib, xq, 32, True)
             algo = rows * k * 2 + rows * k * (0.5 + 1 / 32) + 4 * rows
             what = f"quant_act_kernel<32,2,1> on [{rows},{k}] bf16"
+        elif args.only == "decode-splitk":
+            n, k, m_tok = 4096, 14336, 128             # 32 weight-row tiles: K split over clusters of four CTAs; six rotating weights > L2
+            mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
+                    for _ in range(6)]
+            xd = torch.randn(m_tok, k, device=dev).to(torch.bfloat16)
+            packs = [qb.quantize_act(m.lib, xd, 16, True) for m in mods]
+            fn = lambda: [m.run_decode(pk[0], pk[1], m_tok, pk[2]) for m, pk in zip(mods, packs)]
+            algo = 6 * (n * k / 2 + n * k / 16 + 4 * n + 2 * m_tok * k + 2 * m_tok * n)
+            what = f"nvfp4_gemm_kernel<dense,128>, split-K inside clusters: six [{m_tok}]x[{n},{k}] decode GEMMs per step"
         else:
             n, k, m_tok = 14336, 4096, 16              # 33 MB of dense weights per linear, six rotating > L2
             mods = [qb.DenseNVLinear((torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16), keep_ref_layout=False)
@@ -1161,8 +1170,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="quadbit_b200", choices=["quadbit_b200", "reference"])
     ap.add_argument("--only", default="", help="profiling aid: run only this GEMM of the set (qkv|o_proj|gate|up|down) "
-                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'gemv' / 'swiglu' / 'gatherq' time one small workload of "
-                    "the activation quantiser / the thin-token GEMM / the one-token dense linear / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead; "
+                    "and skip the per-shape / decode / e2e / CPU extras; 'quant' / 'decode' / 'decode-splitk' / 'gemv' / 'swiglu' / 'gatherq' time one small workload of "
+                    "the activation quantiser / the thin-token GEMM / the same with K split over clusters / the one-token dense linear / the MoE layer's SwiGLU-quantise / gather-quantise kernels instead; "
                     "'flashinfer' runs the optional library comparator (FlashInfer mm_fp4, dense NVFP4) on the prefill shapes")
     ap.add_argument("--dp", action="store_true", help="with --gpus N > 1: replicas (tokens sharded, weights replicated, no exchange, weak "
                     "scaling) instead of the default tensor-parallel sharding")
