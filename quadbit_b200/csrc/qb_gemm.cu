@@ -1720,7 +1720,7 @@ void decode_plan(int out_f, int tok, int K, int* splits, int* bn, int* cluster) 
         // the same split finished inside a cluster of s CTAs (one wave, s <= 8): two cluster barriers and a pass over the
         // partial tiles in distributed shared memory
         if (cluster && s > 1 && s <= 8 && tiles * s <= sms && tiles <= max_clusters_bn(b, s)) {
-            const double cc = per + 3.0 + 6.0 + 0.03 * ncol;
+            const double cc = per + 3.0 + 4.0 + 0.02 * ncol;
             if (cc < best - 1e-9) { best = cc; best_s = s; best_c = 1; }
         }
     }
